@@ -1,0 +1,104 @@
+/* Kernel-level C ABI of libtei_b200.so: one entry point per native kernel that the reference's
+ * Candle backend reaches through a third-party crate.  All pointers named *_dev / "device" are
+ * device pointers owned by the caller; `stream` is a cudaStream_t passed as void* (NULL = the
+ * default stream).  Every function enqueues work and returns immediately: 0 on success, a
+ * cudaError_t / CUresult value otherwise.  `status_dev` is a device int the caller zeroes; a
+ * kernel whose bounded wait ran out stores a non-zero code there (101 producer, 102 MMA issuer,
+ * 103 epilogue, 104 attention, 105 shared-memory alignment) instead of hanging.
+ *
+ * dtype: 0 = float16, 1 = bfloat16.  Nothing here allocates device memory.
+ */
+#ifndef TEI_B200_OPS_H_
+#define TEI_B200_OPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Activations of tei_b200_op_linear. */
+enum {
+  TEI_B200_ACT_NONE = 0,
+  TEI_B200_ACT_GELU = 1,       /* tanh approximation */
+  TEI_B200_ACT_RELU = 2,
+  TEI_B200_ACT_TANH = 3,
+  TEI_B200_ACT_SWIGLU = 4,     /* weight rows interleaved: 128 gate rows, 128 up rows, ... */
+  TEI_B200_ACT_RELU_LOG1P = 5
+};
+
+/* out[M, N'] = act(a[M,K] @ w[N,K]^T + bias[N]) (+ residual[M,N']), N' = N/2 for SWIGLU else N.
+ * Replaces Linear::forward -> CublasLtWrapper::matmul
+ * (backends/candle/src/layers/linear.rs:51-75, layers/cublaslt.rs:49-87).
+ * K and lda must be multiples of 8; a and w 16-byte aligned.  bias / residual may be NULL. */
+int tei_b200_op_linear(const void* a_dev, const void* w_dev, const void* bias_dev,
+                       const void* residual_dev, void* out_dev, int M, int N, int K, int lda,
+                       int ldo, int ldr, int act, int dtype, int* status_dev, void* stream);
+
+/* Host helper: lists the (sequence, 128-row query tile) work items of a packed batch as
+ * {seq_start, seq_len, q0, 0} int quadruples, most expensive first.  Returns the item count;
+ * writes nothing when the count exceeds capacity_items or work_out is NULL.  cu_seqlens is a
+ * HOST array of n_seqs + 1 entries (Batch::cumulative_seq_lengths,
+ * backends/core/src/lib.rs:9-17). */
+int tei_b200_attention_plan(const int32_t* cu_seqlens_host, int n_seqs, int causal,
+                            int32_t* work_out, int capacity_items);
+
+/* Variable-length attention over a packed batch.  Replaces flash_attn_varlen
+ * (backends/candle/src/flash_attn.rs:23-120).  q/k/v are token-major strided views
+ * (row stride ld_* elements, head h at column h*head_dim); work_dev holds the quadruples from
+ * tei_b200_attention_plan copied to the device.  head_dim 64 or 128.  alibi_slopes_dev: fp32
+ * [n_heads] or NULL. */
+int tei_b200_op_attention(const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
+                          const int32_t* work_dev, int n_work, int total_tokens, int n_heads,
+                          int n_kv_heads, int head_dim, int ld_q, int ld_k, int ld_v, int ld_o,
+                          int causal, float softmax_scale, const float* alibi_slopes_dev,
+                          int dtype, int* status_dev, void* stream);
+
+/* out[t] = LayerNorm(word[ids[t]] + type[type_ids[t]] + pos[pos_ids[t]]).  Replaces
+ * BertEmbeddings::forward (backends/candle/src/models/bert.rs:83-101) and
+ * NomicBertEmbeddings::forward (models/nomic.rs:84-95; pos table NULL).  With gamma NULL it is
+ * the plain embedding gather of flash_qwen3.rs:409. */
+int tei_b200_op_embed_layernorm(const int32_t* ids_dev, const int32_t* type_ids_dev,
+                                const int32_t* pos_ids_dev, const void* word_dev,
+                                const void* type_dev, const void* pos_dev, const void* gamma_dev,
+                                const void* beta_dev, void* out_dev, int n_tokens, int hidden,
+                                float eps, int dtype, void* stream);
+
+/* rms = 0: out = LayerNorm(x + residual) (layers/layer_norm.rs:54-72,108-132); residual has the
+ * model dtype.  rms = 1: sum = x + residual kept in fp32 in sum_out_dev (residual_dev is fp32
+ * too and may alias sum_out_dev), out = RMSNorm(sum) (layers/rms_norm.rs:30-83). */
+int tei_b200_op_add_norm(const void* x_dev, const void* residual_dev, const void* gamma_dev,
+                         const void* beta_dev, void* out_dev, float* sum_out_dev, int n_tokens,
+                         int hidden, float eps, int rms, int dtype, void* stream);
+
+/* In place on q and k: optional per-head RMSNorm (flash_qwen3.rs:150-151) then half-rotation
+ * rotary embedding (candle-rotary apply_rotary_inplace at flash_nomic.rs:81, flash_qwen3.rs:153;
+ * CPU formula layers/rotary.rs:118-130).  cos/sin: fp32 [max_pos, head_dim/2]. */
+int tei_b200_op_qk_norm_rope(void* q_dev, void* k_dev, const int32_t* pos_ids_dev,
+                             const float* cos_dev, const float* sin_dev, const void* q_gamma_dev,
+                             const void* k_gamma_dev, int n_tokens, int n_heads, int n_kv_heads,
+                             int head_dim, int ld_q, int ld_k, float eps, int dtype, void* stream);
+
+/* Segmented pooling driven by cu_seqlens: out[i] = pool(rows of sequence seq_index[i]).
+ * mode 0 CLS, 1 mean, 2 max (SPLADE), 3 last token (flash_bert.rs:396-490).  fp32 output,
+ * optionally L2-normalised (core/src/infer.rs:288-303). */
+int tei_b200_op_pool(const void* x_dev, const int32_t* cu_seqlens_dev, const int32_t* seq_index_dev,
+                     float* out_dev, int n_out, int hidden, int mode, int normalize, int dtype,
+                     void* stream);
+
+/* out[i] = float(x[row_index[i]]): the raw-embedding row gather + fp32 cast
+ * (flash_bert.rs:496-523, backends/candle/src/lib.rs:689-692). */
+int tei_b200_op_gather_rows_f32(const void* x_dev, const int32_t* row_index_dev, float* out_dev,
+                                int n_rows, int hidden, int dtype, void* stream);
+
+/* out[r, n] = act(in[r,:] . w[n,:] + b[n]) on fp32 rows: classification heads
+ * (models/bert.rs:405-465) and Dense modules (backends/candle/src/lib.rs:672-680). */
+int tei_b200_op_head_linear(const float* in_dev, const void* w_dev, const void* b_dev,
+                            float* out_dev, int rows, int N, int K, int act, int dtype,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEI_B200_OPS_H_ */

@@ -1,0 +1,310 @@
+"""TEST INFRASTRUCTURE - seeded synthetic model directories and packed batches.
+
+Only tests/, `__graft_entry__.smoke()` and bench.py may import this package.
+
+No checkpoint, tokenizer or dataset is available offline, so every workload is synthetic:
+random-init weights of the named architecture (N(0, 0.02), LayerNorm/RMSNorm gamma = 1,
+beta = 0) written as `config.json` + `model.safetensors` under the tensor names the reference's
+loaders read (flash_bert.rs:30-60,130-158,264-356; nomic.rs:70-79,109-139; flash_nomic.rs:207-270;
+flash_qwen3.rs:43-89,190-204,322-357), and token batches drawn with numpy's PCG64
+`default_rng(seed)`.  The `config.json` fields are the ones the reference deserialises
+(bert.rs:11-30, nomic.rs:11-45, qwen3.rs:13-37), so the same directories load in the real server.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+
+from .packing import Batch, batch_from_encodings
+
+
+# --------------------------------------------------------------------------- configs
+def bert_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30522, max_pos=512,
+                type_vocab=2, model_type="bert", act="gelu", eps=1e-12, pad_token_id=0,
+                id2label=None) -> dict:
+    arch = {"bert": "BertModel", "roberta": "RobertaModel", "xlm-roberta": "XLMRobertaModel",
+            "camembert": "CamembertModel"}[model_type]
+    if id2label is not None:
+        arch = arch.replace("Model", "ForSequenceClassification")
+    c = {
+        "architectures": [arch], "model_type": model_type, "vocab_size": vocab, "hidden_size": hidden,
+        "num_hidden_layers": layers, "num_attention_heads": heads, "intermediate_size": inter,
+        "hidden_act": act, "hidden_dropout_prob": 0.1, "max_position_embeddings": max_pos,
+        "type_vocab_size": type_vocab, "initializer_range": 0.02, "layer_norm_eps": eps,
+        "pad_token_id": pad_token_id, "position_embedding_type": "absolute",
+    }
+    if id2label is not None:
+        c["id2label"] = id2label
+        c["label2id"] = {v: int(k) for k, v in id2label.items()}
+    return c
+
+
+def nomic_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30528, n_positions=2048,
+                 rotary_base=1000.0, eps=1e-12) -> dict:
+    return {
+        "architectures": ["NomicBertModel"], "model_type": "nomic_bert", "prenorm": False,
+        "rotary_emb_fraction": 1.0, "qkv_proj_bias": False, "rotary_emb_base": rotary_base,
+        "rotary_emb_interleaved": False, "mlp_fc1_bias": False, "mlp_fc2_bias": False,
+        "n_embd": hidden, "n_head": heads, "n_inner": inter, "n_layer": layers,
+        "n_positions": n_positions, "max_trained_positions": n_positions,
+        "activation_function": "swiglu", "vocab_size": vocab, "type_vocab_size": 2,
+        "layer_norm_epsilon": eps,
+    }
+
+
+def qwen3_config(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, inter=3072,
+                 vocab=151669, max_pos=8192, theta=1e6, eps=1e-6) -> dict:
+    return {
+        "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "attention_bias": False,
+        "vocab_size": vocab, "hidden_size": hidden, "intermediate_size": inter,
+        "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+        "head_dim": head_dim, "hidden_act": "silu", "max_position_embeddings": max_pos,
+        "rms_norm_eps": eps, "rope_theta": theta, "use_sliding_window": False, "eos_token_id": 151643,
+    }
+
+
+# --------------------------------------------------------------------------- tensor lists
+def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) -> Dict[str, Tuple[tuple, str]]:
+    """name -> (shape, kind) with kind in {normal, ones, zeros}."""
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    t: Dict[str, Tuple[tuple, str]] = {}
+    e = prefix + "embeddings."
+    t[e + "word_embeddings.weight"] = ((V, H), "normal")
+    t[e + "position_embeddings.weight"] = ((c["max_position_embeddings"], H), "normal")
+    t[e + "token_type_embeddings.weight"] = ((c["type_vocab_size"], H), "normal")
+    t[e + "LayerNorm.weight"] = ((H,), "ones")
+    t[e + "LayerNorm.bias"] = ((H,), "zeros")
+    for i in range(c["num_hidden_layers"]):
+        p = f"{prefix}encoder.layer.{i}."
+        for n in ("query", "key", "value"):
+            t[p + f"attention.self.{n}.weight"] = ((H, H), "normal")
+            t[p + f"attention.self.{n}.bias"] = ((H,), "normal")
+        t[p + "attention.output.dense.weight"] = ((H, H), "normal")
+        t[p + "attention.output.dense.bias"] = ((H,), "normal")
+        t[p + "attention.output.LayerNorm.weight"] = ((H,), "ones")
+        t[p + "attention.output.LayerNorm.bias"] = ((H,), "zeros")
+        t[p + "intermediate.dense.weight"] = ((I, H), "normal")
+        t[p + "intermediate.dense.bias"] = ((I,), "normal")
+        t[p + "output.dense.weight"] = ((H, I), "normal")
+        t[p + "output.dense.bias"] = ((H,), "normal")
+        t[p + "output.LayerNorm.weight"] = ((H,), "ones")
+        t[p + "output.LayerNorm.bias"] = ((H,), "zeros")
+    if classifier == "roberta":
+        n_cls = len(c["id2label"])
+        t["classifier.dense.weight"] = ((H, H), "normal")
+        t["classifier.dense.bias"] = ((H,), "normal")
+        t["classifier.out_proj.weight"] = ((n_cls, H), "normal")
+        t["classifier.out_proj.bias"] = ((n_cls,), "normal")
+    elif classifier == "bert":
+        n_cls = len(c["id2label"])
+        t["bert.pooler.dense.weight"] = ((H, H), "normal")
+        t["bert.pooler.dense.bias"] = ((H,), "normal")
+        t["classifier.weight"] = ((n_cls, H), "normal")
+        t["classifier.bias"] = ((n_cls,), "normal")
+    if splade:
+        t["cls.predictions.transform.dense.weight"] = ((H, H), "normal")
+        t["cls.predictions.transform.dense.bias"] = ((H,), "normal")
+        t["cls.predictions.transform.LayerNorm.weight"] = ((H,), "ones")
+        t["cls.predictions.transform.LayerNorm.bias"] = ((H,), "zeros")
+        t["cls.predictions.decoder.weight"] = ((V, H), "normal")
+        t["cls.predictions.bias"] = ((V,), "normal")
+    return t
+
+
+def _nomic_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    H, I, V = c["n_embd"], c["n_inner"], c["vocab_size"]
+    t: Dict[str, Tuple[tuple, str]] = {
+        "embeddings.word_embeddings.weight": ((V, H), "normal"),
+        "embeddings.token_type_embeddings.weight": ((c["type_vocab_size"], H), "normal"),
+        "emb_ln.weight": ((H,), "ones"), "emb_ln.bias": ((H,), "zeros"),
+    }
+    for i in range(c["n_layer"]):
+        p = f"encoder.layers.{i}."
+        t[p + "attn.Wqkv.weight"] = ((3 * H, H), "normal")
+        t[p + "attn.out_proj.weight"] = ((H, H), "normal")
+        t[p + "mlp.fc11.weight"] = ((I, H), "normal")
+        t[p + "mlp.fc12.weight"] = ((I, H), "normal")
+        t[p + "mlp.fc2.weight"] = ((H, I), "normal")
+        for n in ("norm1", "norm2"):
+            t[p + n + ".weight"] = ((H,), "ones")
+            t[p + n + ".bias"] = ((H,), "zeros")
+    return t
+
+
+def _qwen3_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    nh, nkv, dh = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+    t: Dict[str, Tuple[tuple, str]] = {"model.embed_tokens.weight": ((V, H), "normal"),
+                                       "model.norm.weight": ((H,), "ones")}
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        t[p + "self_attn.q_proj.weight"] = ((nh * dh, H), "normal")
+        t[p + "self_attn.k_proj.weight"] = ((nkv * dh, H), "normal")
+        t[p + "self_attn.v_proj.weight"] = ((nkv * dh, H), "normal")
+        t[p + "self_attn.o_proj.weight"] = ((H, nh * dh), "normal")
+        t[p + "self_attn.q_norm.weight"] = ((dh,), "ones")
+        t[p + "self_attn.k_norm.weight"] = ((dh,), "ones")
+        t[p + "mlp.gate_proj.weight"] = ((I, H), "normal")
+        t[p + "mlp.up_proj.weight"] = ((I, H), "normal")
+        t[p + "mlp.down_proj.weight"] = ((H, I), "normal")
+        t[p + "input_layernorm.weight"] = ((H,), "ones")
+        t[p + "post_attention_layernorm.weight"] = ((H,), "ones")
+    return t
+
+
+def tensor_shapes(config: dict, classifier: Optional[str] = None, splade: bool = False,
+                  prefix: Optional[str] = None):
+    mt = config["model_type"]
+    if mt in ("bert", "roberta", "xlm-roberta", "camembert"):
+        if prefix is None:
+            prefix = "" if mt == "bert" else "roberta."
+        return _bert_shapes(config, prefix, classifier, splade)
+    if mt == "nomic_bert":
+        return _nomic_shapes(config)
+    if mt == "qwen3":
+        return _qwen3_shapes(config)
+    raise ValueError(mt)
+
+
+def write_model_dir(path, config: dict, seed: int, classifier: Optional[str] = None,
+                    splade: bool = False, prefix: Optional[str] = None, std: float = 0.02,
+                    norm_jitter: float = 0.0, store_dtype: str = "float32") -> Path:
+    """Draws every tensor (sorted by name) from default_rng(seed) and writes the model dir.
+
+    norm_jitter > 0 perturbs norm weights / biases away from (1, 0) so that tests exercise gamma
+    and beta; the benchmark configs keep the stated gamma = 1, beta = 0.
+    """
+    from safetensors.numpy import save_file
+
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    rng = np.random.default_rng(seed)
+    shapes = tensor_shapes(config, classifier, splade, prefix)
+    np_dtype = {"float32": np.float32, "float16": np.float16}[store_dtype]
+    tensors = {}
+    for name in sorted(shapes):
+        shape, kind = shapes[name]
+        if kind == "normal":
+            arr = rng.standard_normal(size=shape, dtype=np.float32) * np.float32(std)
+        elif kind == "ones":
+            arr = np.ones(shape, dtype=np.float32)
+            if norm_jitter:
+                arr = arr + rng.standard_normal(size=shape, dtype=np.float32) * np.float32(norm_jitter)
+        else:
+            arr = np.zeros(shape, dtype=np.float32)
+            if norm_jitter:
+                arr = arr + rng.standard_normal(size=shape, dtype=np.float32) * np.float32(norm_jitter)
+        tensors[name] = arr.astype(np_dtype)
+    save_file(tensors, str(path / "model.safetensors"))
+    (path / "config.json").write_text(json.dumps(config, indent=1))
+    return path
+
+
+# --------------------------------------------------------------------------- batches
+def _ids(rng, lens, lo, hi) -> List[np.ndarray]:
+    return [rng.integers(lo, hi, size=int(n)) for n in lens]
+
+
+def batch_cfg1() -> Batch:
+    """32 x 512, ids uniform [1000, 30522), 101 first / 102 last, CLS pooling."""
+    ids = np.random.default_rng(10).integers(1000, 30522, size=(32, 512))
+    ids[:, 0] = 101
+    ids[:, 511] = 102
+    return batch_from_encodings(list(ids), list(range(32)), [])
+
+
+def lengths_cfg2() -> np.ndarray:
+    return np.random.default_rng(1).integers(16, 512, size=256, endpoint=True)
+
+
+def batch_cfg2(n_seqs: Optional[int] = None) -> Batch:
+    """256 ragged sequences, lengths uniform [16, 512] (seed 1), ids uniform [1000, 30522)."""
+    rng = np.random.default_rng(1)
+    lens = rng.integers(16, 512, size=256, endpoint=True)
+    encs = _ids(rng, lens, 1000, 30522)
+    if n_seqs is not None:
+        encs = encs[:n_seqs]
+    return batch_from_encodings(encs, list(range(len(encs))), [])
+
+
+def batch_cfg3(n_seqs: Optional[int] = None) -> Batch:
+    """64 sequences, lengths uniform [512, 2048] (seed 3), NomicBERT vocab."""
+    rng = np.random.default_rng(3)
+    lens = rng.integers(512, 2048, size=64, endpoint=True)
+    encs = _ids(rng, lens, 1000, 30528)
+    if n_seqs is not None:
+        encs = encs[:n_seqs]
+    return batch_from_encodings(encs, list(range(len(encs))), [])
+
+
+def batch_cfg4(n_pairs: Optional[int] = None) -> Batch:
+    """512 query/passage pairs as <s> q </s></s> p </s>, XLM-R ids, positions offset by 2."""
+    rng = np.random.default_rng(4)
+    q = rng.integers(8, 32, size=512, endpoint=True)
+    p = rng.integers(64, 480, size=512, endpoint=True)
+    encs = []
+    for qi, pi in zip(q, p):
+        qi, pi = int(qi), int(pi)
+        if qi + pi + 4 > 512:
+            pi = 512 - 4 - qi
+        body_q = rng.integers(5, 250002, size=qi)
+        body_p = rng.integers(5, 250002, size=pi)
+        encs.append(np.concatenate([[0], body_q, [2, 2], body_p, [2]]))
+    if n_pairs is not None:
+        encs = encs[:n_pairs]
+    return batch_from_encodings(encs, list(range(len(encs))), [], position_offset=2)
+
+
+def lengths_cfg5() -> np.ndarray:
+    u = np.random.default_rng(6).random(128)
+    lens = np.floor(np.exp(np.log(128.0) + u * np.log(64.0))).astype(np.int64)
+    return np.clip(lens, 128, 8192)
+
+
+def batch_cfg5(n_seqs: Optional[int] = None, max_len: Optional[int] = None) -> Batch:
+    """128 sequences, lengths log-uniform [128, 8192] (seed 6), Qwen3 vocab."""
+    lens = lengths_cfg5()
+    if max_len is not None:
+        lens = np.minimum(lens, max_len)
+    rng = np.random.default_rng(60)
+    encs = _ids(rng, lens, 1000, 151669)
+    if n_seqs is not None:
+        encs = encs[:n_seqs]
+    return batch_from_encodings(encs, list(range(len(encs))), [])
+
+
+def random_batch(seed: int, lens, vocab_lo: int, vocab_hi: int, pooled=None, raw=None,
+                 type_vocab: int = 1, position_offset: int = 0) -> Batch:
+    rng = np.random.default_rng(seed)
+    encs = _ids(rng, lens, vocab_lo, vocab_hi)
+    types = [rng.integers(0, type_vocab, size=int(n)) for n in lens] if type_vocab > 1 else None
+    n = len(encs)
+    if pooled is None and raw is None:
+        pooled, raw = list(range(n)), []
+    return batch_from_encodings(encs, pooled or [], raw or [], type_ids=types,
+                                position_offset=position_offset)
+
+
+# FLOP model of the hot path (dense layers + attention only; causal counts the unmasked half).
+def algorithmic_flops(config: dict, lens) -> float:
+    mt = config["model_type"]
+    lens = np.asarray(lens, dtype=np.float64)
+    T = lens.sum()
+    if mt == "qwen3":
+        H, I, L = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+        hq = config["num_attention_heads"] * config["head_dim"]
+        hkv = config["num_key_value_heads"] * config["head_dim"]
+        lin = 2.0 * (H * hq + 2 * H * hkv + hq * H + 3 * H * I)
+        attn = 2.0 * hq * (lens * (lens + 1)).sum()
+    elif mt == "nomic_bert":
+        H, I, L = config["n_embd"], config["n_inner"], config["n_layer"]
+        lin = 2.0 * (4 * H * H + 3 * H * I)
+        attn = 4.0 * H * (lens * lens).sum()
+    else:
+        H, I, L = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
+        lin = 2.0 * (4 * H * H + 2 * H * I)
+        attn = 4.0 * H * (lens * lens).sum()
+    return float(L * (lin * T + attn))

@@ -1,0 +1,492 @@
+"""TEST INFRASTRUCTURE - fp32 CPU restatement of the reference's Candle CPU models.
+
+Only tests/, `__graft_entry__.smoke()` and bench.py's cpu_baseline / reference legs may import
+this package; the product path never does.
+
+PARITY UNPINNED by the reference's own golden vectors: every snapshot under
+backends/candle/tests/snapshots/ needs a hub checkpoint and tokenizer that cannot be fetched
+here, and the reference (Rust, un-vendored crates) cannot be compiled or imported.  The
+restatement is instead cross-checked against Hugging Face `transformers` (an independent
+implementation of the same architectures) in tests/test_oracle_vs_hf.py.
+
+What is restated (file:line in the reference):
+  BERT / RoBERTa / XLM-R  backends/candle/src/models/bert.rs
+      embeddings :83-101, attention (CPU arm) :246-255, layer :317-332, classification heads
+      :405-465, SPLADE head :551-558, pooling :819-879; loader name fallbacks flash_bert.rs:264-356
+  NomicBERT               models/nomic.rs  embeddings :84-95, gated MLP :105-153, attention
+      :474-573, block (post-LN) :605-626; rotary layers/rotary.rs:29-130
+  Qwen3                   models/qwen3.rs  attention :137-271, layer :360-385, pooling :639-714;
+      RMSNorm layers/rms_norm.rs:30-57
+  shared                  LayerNorm layers/layer_norm.rs:108-132; Linear + activations
+      layers/linear.rs:5-29,77-101 (every GELU name means the tanh approximation)
+  host post-processing    core/src/infer.rs:288-303 (L2 normalise in f64), :458-480 (sigmoid)
+
+Shape of the restatement: dense layers run on the packed [T, H] matrix (row-wise maths, so
+identical to the padded form), attention runs per sequence on its own unpadded rows.  For real
+tokens this equals the reference's padded form with a -inf bias on pad keys; `forward_padded`
+keeps a literal padded version for small batches so the tests can check that claim.
+"""
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .packing import Batch
+
+Tensor = torch.Tensor
+
+
+# --------------------------------------------------------------------------- building blocks
+def gelu_tanh(x: Tensor) -> Tensor:
+    return F.gelu(x, approximate="tanh")
+
+
+def activation(name: str):
+    # layers/linear.rs:5-17: gelu | gelu_new | gelu_pytorch_tanh all mean tanh-GELU.
+    if name in ("gelu", "gelu_new", "gelu_pytorch_tanh"):
+        return gelu_tanh
+    if name == "relu":
+        return torch.relu
+    if name == "silu":
+        return F.silu
+    if name == "tanh":
+        return torch.tanh
+    if name == "swiglu":
+        def swiglu(x):
+            a, b = x.chunk(2, dim=-1)
+            return F.silu(a) * b
+        return swiglu
+    raise ValueError(f"unsupported activation {name}")
+
+
+def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None) -> Tensor:
+    y = x @ w.t()
+    return y if b is None else y + b
+
+
+def layer_norm(x: Tensor, residual: Optional[Tensor], gamma: Tensor, beta: Tensor, eps: float) -> Tensor:
+    # layers/layer_norm.rs:108-132: biased variance, eps inside the sqrt.
+    if residual is not None:
+        x = x + residual
+    mean = x.mean(dim=-1, keepdim=True)
+    xc = x - mean
+    var = (xc * xc).mean(dim=-1, keepdim=True)
+    return xc / torch.sqrt(var + eps) * gamma + beta
+
+
+def rms_norm(x: Tensor, residual: Optional[Tensor], gamma: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    # layers/rms_norm.rs:30-57: returns (normed, x + residual).
+    if residual is not None:
+        x = x + residual
+    ms = (x * x).mean(dim=-1, keepdim=True)
+    return x / torch.sqrt(ms + eps) * gamma, x
+
+
+def rope_tables(head_dim: int, base: float, max_pos: int) -> Tuple[Tensor, Tensor]:
+    # layers/rotary.rs:29-116: inv_freq_i = 1 / base^(i/dim) for even i, all in f32.
+    base32 = np.float32(base)
+    inv = np.array([np.float32(1.0) / np.power(base32, np.float32(i) / np.float32(head_dim), dtype=np.float32)
+                    for i in range(0, head_dim, 2)], dtype=np.float32)
+    t = np.arange(max_pos, dtype=np.float32)[:, None]
+    freqs = (t * inv[None, :]).astype(np.float32)
+    return torch.from_numpy(np.cos(freqs).astype(np.float32)), torch.from_numpy(np.sin(freqs).astype(np.float32))
+
+
+def apply_rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    # layers/rotary.rs:118-130 with half-width tables: x*cos + rotate_half(x)*sin.
+    # x [L, heads, D]; cos/sin [L, D/2].
+    d = x.shape[-1] // 2
+    x1, x2 = x[..., :d], x[..., d:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+
+
+def alibi_slopes(n_heads: int) -> Tensor:
+    # backends/candle/src/alibi.rs:18-47 (the usual power-of-two construction).
+    def pow2_slopes(n):
+        start = 2.0 ** (-(2.0 ** -(math.log2(n) - 3)))
+        return [start * (start ** i) for i in range(n)]
+    if math.log2(n_heads).is_integer():
+        s = pow2_slopes(n_heads)
+    else:
+        closest = 2 ** math.floor(math.log2(n_heads))
+        s = pow2_slopes(closest) + pow2_slopes(2 * closest)[0::2][: n_heads - closest]
+    return torch.tensor(s, dtype=torch.float32)
+
+
+def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: float, causal: bool,
+                     slopes: Optional[Tensor] = None) -> Tensor:
+    """q [T, nh, D], k/v [T, nkv, D] -> [T, nh*D]; one softmax(QK^T)V per sequence and head."""
+    T, nh, D = q.shape
+    nkv = k.shape[1]
+    out = torch.empty(T, nh * D, dtype=q.dtype)
+    for s in range(len(cu) - 1):
+        a, b = int(cu[s]), int(cu[s + 1])
+        L = b - a
+        if L == 0:
+            continue
+        qs = q[a:b].transpose(0, 1)
+        ks = k[a:b].transpose(0, 1)
+        vs = v[a:b].transpose(0, 1)
+        if nkv != nh:  # GQA: q-head i reads kv-head i // group (models/qwen3.rs:189-205)
+            ks = ks.repeat_interleave(nh // nkv, dim=0)
+            vs = vs.repeat_interleave(nh // nkv, dim=0)
+        sc = (qs @ ks.transpose(1, 2)) * scale
+        if slopes is not None:
+            idx = torch.arange(L)
+            sc = sc - slopes.view(nh, 1, 1) * (idx.view(1, L, 1) - idx.view(1, 1, L)).abs()
+        if causal:
+            sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf"))
+        out[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1).reshape(L, nh * D)
+    return out
+
+
+# --------------------------------------------------------------------------- weights
+def load_model_dir(model_dir) -> Tuple[dict, Dict[str, Tensor]]:
+    """config.json + model.safetensors, every tensor as fp32 (the reference's CPU dtype)."""
+    from safetensors import safe_open
+
+    model_dir = Path(model_dir)
+    config = json.loads((model_dir / "config.json").read_text())
+    tensors: Dict[str, Tensor] = {}
+    with safe_open(str(model_dir / "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            tensors[name] = f.get_tensor(name).to(torch.float32)
+    return config, tensors
+
+
+class _Weights:
+    def __init__(self, tensors: Dict[str, Tensor], prefixes=("",)):
+        self.t = tensors
+        self.prefixes = prefixes
+
+    def has(self, name: str) -> bool:
+        return any((p + name) in self.t for p in self.prefixes)
+
+    def get(self, name: str) -> Tensor:
+        for p in self.prefixes:
+            if (p + name) in self.t:
+                return self.t[p + name]
+        raise KeyError(f"tensor {name} not found (prefixes {self.prefixes})")
+
+    def get_any(self, *names: str) -> Tensor:
+        for n in names:
+            if self.has(n):
+                return self.get(n)
+        raise KeyError(f"none of {names} found")
+
+    def ln(self, prefix: str) -> Tuple[Tensor, Tensor]:
+        # LayerNorm::load accepts weight|gamma and bias|beta (layers/layer_norm.rs:93-98).
+        return (self.get_any(prefix + ".weight", prefix + ".gamma"),
+                self.get_any(prefix + ".bias", prefix + ".beta"))
+
+
+# --------------------------------------------------------------------------- pooling (shared)
+def pool_outputs(hidden: Tensor, batch: Batch, pool: str) -> Tuple[Optional[Tensor], Optional[Tensor]]:
+    """Pooled rows (one per pooled_indices entry, in that order) and raw rows (token rows of the
+    raw_indices sequences, in that order).  flash_bert.rs:396-523 / bert.rs:819-933."""
+    cu = batch.cumulative_seq_lengths.astype(np.int64)
+    pooled = None
+    if len(batch.pooled_indices) > 0:
+        rows = []
+        for i in batch.pooled_indices.astype(np.int64):
+            seg = hidden[int(cu[i]):int(cu[i + 1])]
+            if pool == "cls":
+                rows.append(seg[0])
+            elif pool == "last_token":
+                rows.append(seg[-1])
+            elif pool == "mean":
+                rows.append(seg.sum(dim=0) / float(seg.shape[0]))
+            elif pool == "splade":
+                rows.append(seg.max(dim=0).values)
+            else:
+                raise ValueError(pool)
+        pooled = torch.stack(rows)
+    raw = None
+    if len(batch.raw_indices) > 0:
+        raw = torch.cat([hidden[int(cu[i]):int(cu[i + 1])] for i in batch.raw_indices.astype(np.int64)])
+    return pooled, raw
+
+
+def l2_normalise(v: np.ndarray) -> np.ndarray:
+    # core/src/infer.rs:288-303: scale by 1/sqrt(sum of squares), accumulated in f64.
+    v64 = v.astype(np.float64)
+    n = np.sqrt((v64 * v64).sum(axis=-1, keepdims=True))
+    return (v64 / n).astype(np.float32)
+
+
+def sigmoid_scores(x: np.ndarray) -> np.ndarray:
+    # core/src/infer.rs:458-480: a single class is squashed with a sigmoid, several with softmax.
+    if x.shape[-1] == 1:
+        return (1.0 / (1.0 + np.exp(-x.astype(np.float64)))).astype(np.float32)
+    z = x.astype(np.float64)
+    z = np.exp(z - z.max(axis=-1, keepdims=True))
+    return (z / z.sum(axis=-1, keepdims=True)).astype(np.float32)
+
+
+# --------------------------------------------------------------------------- BERT family
+class BertOracle:
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
+                 pool: str = "cls"):
+        self.cfg = config
+        self.pool = "cls" if model_type == "classifier" else pool
+        self.model_type = model_type
+        mt = config["model_type"]
+        self.roberta = mt in ("roberta", "xlm-roberta", "camembert")
+        # flash_bert.rs:264-279 (bert) / :331-356 (roberta family): bare names first, then prefixes.
+        if self.roberta:
+            cand = ["", "roberta.", "xlm-roberta.", "camembert."]
+        else:
+            cand = ["", "bert."]
+        prefix = next((p for p in cand if (p + "embeddings.word_embeddings.weight") in tensors), None)
+        if prefix is None:
+            raise KeyError("embeddings.word_embeddings.weight not found under any known prefix")
+        self.w = _Weights(tensors, (prefix,))
+        self.all = _Weights(tensors, ("",))
+        self.nh = config["num_attention_heads"]
+        self.hidden = config["hidden_size"]
+        self.dh = self.hidden // self.nh
+        self.eps = float(config["layer_norm_eps"])
+        self.act = activation(config["hidden_act"])
+        self.n_layers = config["num_hidden_layers"]
+        if config.get("position_embedding_type", "absolute") != "absolute":
+            raise ValueError("only absolute position embeddings are supported (bert.rs:51-54)")
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        tids = torch.from_numpy(batch.token_type_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        g, b = w.ln("embeddings.LayerNorm")
+        x = w.get("embeddings.word_embeddings.weight")[ids] + w.get("embeddings.token_type_embeddings.weight")[tids]
+        x = layer_norm(x, w.get("embeddings.position_embeddings.weight")[pids], g, b, self.eps)
+        cu = batch.cumulative_seq_lengths
+        T = x.shape[0]
+        for i in range(self.n_layers):
+            p = f"encoder.layer.{i}."
+            q = linear(x, w.get(p + "attention.self.query.weight"), w.get(p + "attention.self.query.bias"))
+            k = linear(x, w.get(p + "attention.self.key.weight"), w.get(p + "attention.self.key.bias"))
+            v = linear(x, w.get(p + "attention.self.value.weight"), w.get(p + "attention.self.value.bias"))
+            a = attention_varlen(q.view(T, self.nh, self.dh), k.view(T, self.nh, self.dh),
+                                 v.view(T, self.nh, self.dh), cu, 1.0 / math.sqrt(self.dh), False)
+            g1, b1 = w.ln(p + "attention.output.LayerNorm")
+            x1 = layer_norm(linear(a, w.get(p + "attention.output.dense.weight"),
+                                   w.get(p + "attention.output.dense.bias")), x, g1, b1, self.eps)
+            f = self.act(linear(x1, w.get(p + "intermediate.dense.weight"), w.get(p + "intermediate.dense.bias")))
+            g2, b2 = w.ln(p + "output.LayerNorm")
+            x = layer_norm(linear(f, w.get(p + "output.dense.weight"), w.get(p + "output.dense.bias")),
+                           x1, g2, b2, self.eps)
+        return x
+
+    def splade_head(self, x: Tensor) -> Tensor:
+        a = self.all
+        if self.roberta:  # bert.rs:519-541
+            h = gelu_tanh(linear(x, a.get("lm_head.dense.weight"), a.get("lm_head.dense.bias")))
+            g, b = a.ln("lm_head.layer_norm")
+            dec_w, dec_b = a.get("lm_head.decoder.weight"), a.get("lm_head.bias")
+        else:  # bert.rs:477-509
+            h = self.act(linear(x, a.get("cls.predictions.transform.dense.weight"),
+                                a.get("cls.predictions.transform.dense.bias")))
+            g, b = a.ln("cls.predictions.transform.LayerNorm")
+            dec_w = a.get_any("cls.predictions.decoder.weight", "bert.embeddings.word_embeddings.weight")
+            dec_b = a.get("cls.predictions.bias")
+        h = layer_norm(h, None, g, b, self.eps)
+        return torch.log(1.0 + torch.relu(linear(h, dec_w, dec_b)))  # bert.rs:551-558
+
+    def embed(self, batch: Batch) -> Tuple[Optional[Tensor], Optional[Tensor]]:
+        x = self.hidden_states(batch)
+        if self.pool == "splade":
+            pooled, _ = pool_outputs(self.splade_head(x), batch, "splade")
+            _, raw = pool_outputs(x, batch, "cls")
+            return pooled, raw
+        return pool_outputs(x, batch, self.pool)
+
+    def predict(self, batch: Batch) -> Tensor:
+        """Logits [n_seqs, n_classes] by batch position (flash_bert.rs:538-547)."""
+        x = self.hidden_states(batch)
+        cu = batch.cumulative_seq_lengths.astype(np.int64)
+        cls = x[torch.from_numpy(cu[:-1])]
+        a = self.all
+        if self.roberta:  # RobertaClassificationHead, bert.rs:434-465
+            h = torch.tanh(linear(cls, a.get("classifier.dense.weight"), a.get("classifier.dense.bias")))
+            return linear(h, a.get("classifier.out_proj.weight"), a.get("classifier.out_proj.bias"))
+        h = cls  # BertClassificationHead, bert.rs:374-419
+        if a.has("bert.pooler.dense.weight"):
+            h = torch.tanh(linear(h, a.get("bert.pooler.dense.weight"), a.get("bert.pooler.dense.bias")))
+        return linear(h, a.get("classifier.weight"), a.get("classifier.bias"))
+
+    # Literal padded form (bert.rs:706-879) for small batches: used to show that the unpadded
+    # restatement above computes the same numbers.
+    def hidden_states_padded(self, batch: Batch) -> Tensor:
+        w = self.w
+        B, L = len(batch), int(batch.max_length)
+        cu = batch.cumulative_seq_lengths.astype(np.int64)
+        ids = torch.zeros(B, L, dtype=torch.int64)
+        tids = torch.zeros(B, L, dtype=torch.int64)
+        pids = torch.zeros(B, L, dtype=torch.int64)
+        bias = torch.zeros(B, 1, 1, L)
+        for i in range(B):
+            n = int(cu[i + 1] - cu[i])
+            ids[i, :n] = torch.from_numpy(batch.input_ids[cu[i]:cu[i + 1]].astype(np.int64))
+            tids[i, :n] = torch.from_numpy(batch.token_type_ids[cu[i]:cu[i + 1]].astype(np.int64))
+            pids[i, :n] = torch.from_numpy(batch.position_ids[cu[i]:cu[i + 1]].astype(np.int64))
+            bias[i, :, :, n:] = float("-inf")
+        g, b = w.ln("embeddings.LayerNorm")
+        x = w.get("embeddings.word_embeddings.weight")[ids] + w.get("embeddings.token_type_embeddings.weight")[tids]
+        x = layer_norm(x, w.get("embeddings.position_embeddings.weight")[pids], g, b, self.eps)
+        for i in range(self.n_layers):
+            p = f"encoder.layer.{i}."
+
+            def heads(t):
+                return t.view(B, L, self.nh, self.dh).transpose(1, 2)
+            q = heads(linear(x, w.get(p + "attention.self.query.weight"), w.get(p + "attention.self.query.bias")))
+            k = heads(linear(x, w.get(p + "attention.self.key.weight"), w.get(p + "attention.self.key.bias")))
+            v = heads(linear(x, w.get(p + "attention.self.value.weight"), w.get(p + "attention.self.value.bias")))
+            sc = (q @ k.transpose(-1, -2)) * (1.0 / math.sqrt(self.dh)) + bias
+            a = (torch.softmax(sc, dim=-1) @ v).transpose(1, 2).reshape(B, L, self.hidden)
+            g1, b1 = w.ln(p + "attention.output.LayerNorm")
+            x1 = layer_norm(linear(a, w.get(p + "attention.output.dense.weight"),
+                                   w.get(p + "attention.output.dense.bias")), x, g1, b1, self.eps)
+            f = self.act(linear(x1, w.get(p + "intermediate.dense.weight"), w.get(p + "intermediate.dense.bias")))
+            g2, b2 = w.ln(p + "output.LayerNorm")
+            x = layer_norm(linear(f, w.get(p + "output.dense.weight"), w.get(p + "output.dense.bias")),
+                           x1, g2, b2, self.eps)
+        return x  # [B, L, H]
+
+
+# --------------------------------------------------------------------------- NomicBERT
+class NomicOracle:
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
+                 pool: str = "mean"):
+        if model_type == "classifier" or pool == "splade":
+            raise ValueError("NomicBERT supports neither classifier nor splade (flash_nomic.rs:222-233)")
+        c = config
+        # NomicConfig::valid(), models/nomic.rs:49-54
+        if c["prenorm"] or c["rotary_emb_fraction"] != 1.0 or c["rotary_emb_interleaved"] or c["type_vocab_size"] <= 0:
+            raise ValueError("config is not supported")
+        self.cfg = c
+        self.pool = pool
+        self.w = _Weights(tensors, ("",))
+        self.nh = c["n_head"]
+        self.hidden = c["n_embd"]
+        self.dh = self.hidden // self.nh
+        self.eps = float(c["layer_norm_epsilon"])
+        self.n_layers = c["n_layer"]
+        self.act_name = c["activation_function"]
+        self.cos, self.sin = rope_tables(self.dh, float(c["rotary_emb_base"]), int(c["n_positions"]))
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w, c = self.w, self.cfg
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        tids = torch.from_numpy(batch.token_type_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        g, b = w.ln("emb_ln")
+        x = layer_norm(w.get("embeddings.word_embeddings.weight")[ids],
+                       w.get("embeddings.token_type_embeddings.weight")[tids], g, b, self.eps)
+        cos, sin = self.cos[pids], self.sin[pids]
+        T = x.shape[0]
+        cu = batch.cumulative_seq_lengths
+        for i in range(self.n_layers):
+            p = f"encoder.layers.{i}."
+            qkv = linear(x, w.get(p + "attn.Wqkv.weight"),
+                         w.get(p + "attn.Wqkv.bias") if c["qkv_proj_bias"] else None)
+            q, k, v = qkv.view(T, 3, self.nh, self.dh).unbind(dim=1)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), False)
+            a = linear(a, w.get(p + "attn.out_proj.weight"),
+                       w.get(p + "attn.out_proj.bias") if c["qkv_proj_bias"] else None)
+            g1, b1 = w.ln(p + "norm1")
+            x1 = layer_norm(x, a, g1, b1, self.eps)
+            if self.act_name == "swiglu":
+                # fc1 = cat[fc12; fc11]; swiglu = silu(first half) * second half (nomic.rs:115-121)
+                gate = linear(x1, w.get(p + "mlp.fc12.weight"), w.get(p + "mlp.fc12.bias") if c["mlp_fc1_bias"] else None)
+                up = linear(x1, w.get(p + "mlp.fc11.weight"), w.get(p + "mlp.fc11.bias") if c["mlp_fc1_bias"] else None)
+                m = F.silu(gate) * up
+            else:
+                m = activation(self.act_name)(linear(x1, w.get(p + "mlp.fc1.weight"),
+                                                     w.get(p + "mlp.fc1.bias") if c["mlp_fc1_bias"] else None))
+            m = linear(m, w.get(p + "mlp.fc2.weight"), w.get(p + "mlp.fc2.bias") if c["mlp_fc2_bias"] else None)
+            g2, b2 = w.ln(p + "norm2")
+            x = layer_norm(x1, m, g2, b2, self.eps)
+        return x
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+
+# --------------------------------------------------------------------------- Qwen3
+class Qwen3Oracle:
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
+                 pool: str = "last_token"):
+        if model_type == "classifier" or pool == "splade":
+            raise ValueError("Qwen3 supports neither classifier nor splade here")
+        c = config
+        if c.get("use_sliding_window"):
+            raise ValueError("sliding window is not supported (flash_qwen3.rs:32-34)")
+        self.cfg = c
+        self.pool = pool
+        prefix = "model." if "model.embed_tokens.weight" in tensors else ""
+        self.w = _Weights(tensors, (prefix,))
+        self.all = _Weights(tensors, ("",))
+        self.nh = c["num_attention_heads"]
+        self.nkv = c["num_key_value_heads"]
+        self.hidden = c["hidden_size"]
+        self.dh = c.get("head_dim") or self.hidden // self.nh
+        self.eps = float(c["rms_norm_eps"])
+        self.n_layers = c["num_hidden_layers"]
+        theta = c.get("rope_theta")
+        if theta is None:
+            theta = c["rope_parameters"]["rope_theta"]
+        self.causal = not c.get("use_bidirectional_attention", False)
+        self.cos, self.sin = rope_tables(self.dh, float(theta), int(c["max_position_embeddings"]))
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        h = w.get("embed_tokens.weight")[ids]
+        cos, sin = self.cos[pids], self.sin[pids]
+        T = h.shape[0]
+        cu = batch.cumulative_seq_lengths
+        residual = None
+        for i in range(self.n_layers):
+            p = f"layers.{i}."
+            n, residual = rms_norm(h, residual, w.get(p + "input_layernorm.weight"), self.eps)
+            q = linear(n, w.get(p + "self_attn.q_proj.weight")).view(T, self.nh, self.dh)
+            k = linear(n, w.get(p + "self_attn.k_proj.weight")).view(T, self.nkv, self.dh)
+            v = linear(n, w.get(p + "self_attn.v_proj.weight")).view(T, self.nkv, self.dh)
+            q, _ = rms_norm(q, None, w.get(p + "self_attn.q_norm.weight"), self.eps)
+            k, _ = rms_norm(k, None, w.get(p + "self_attn.k_norm.weight"), self.eps)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), self.causal)
+            o = linear(a, w.get(p + "self_attn.o_proj.weight"))
+            n2, residual = rms_norm(o, residual, w.get(p + "post_attention_layernorm.weight"), self.eps)
+            gate = linear(n2, w.get(p + "mlp.gate_proj.weight"))
+            up = linear(n2, w.get(p + "mlp.up_proj.weight"))
+            h = linear(F.silu(gate) * up, w.get(p + "mlp.down_proj.weight"))
+        out, _ = rms_norm(h, residual, w.get("norm.weight"), self.eps)
+        if self.all.has("linear.weight"):  # optional projection, flash_qwen3.rs:344-357,430-435
+            out = linear(out, self.all.get("linear.weight"))
+        return out
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+
+def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
+    """Dispatch on config.json's model_type like backends/candle/src/lib.rs:124-154,282-577."""
+    config, tensors = load_model_dir(model_dir)
+    mt = config["model_type"]
+    if mt in ("bert", "roberta", "xlm-roberta", "camembert"):
+        return BertOracle(config, tensors, model_type, pool)
+    if mt == "nomic_bert":
+        return NomicOracle(config, tensors, model_type, pool)
+    if mt == "qwen3":
+        return Qwen3Oracle(config, tensors, model_type, pool)
+    raise ValueError(f"model_type {mt} is outside the hot path")

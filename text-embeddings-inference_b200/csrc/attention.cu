@@ -1,0 +1,376 @@
+// Variable-length (unpadded) attention on tcgen05 tensor cores.
+//
+// Replaces the reference's flash_attn_varlen call (backends/candle/src/flash_attn.rs:23-120;
+// call sites models/flash_bert.rs:95-108, flash_nomic.rs:83-96, flash_qwen3.rs:155-169):
+// for every sequence s of the packed batch and head h,
+//     out = softmax(scale * Q_s K_s^T  [- slope_h * |i - j|]  [causal mask]) V_s
+// with q-head h reading kv-head h / (n_heads / n_kv_heads).  Q, K and V are strided views of
+// the projection output (token-major rows), exactly as the reference passes them.
+//
+// One CTA handles one (sequence, 128-row query tile, head) work item:
+//   warp 4 (one elected lane)  TMA loads (Q once, K/V double-buffered, 128-byte swizzle, no
+//                              cluster multicast) and tcgen05.mma issue:
+//                              S = Q K^T into TMEM columns [0,128), P V into columns [128,128+D).
+//   warps 0-3 (one row each)   read S from TMEM, online softmax in fp32 registers, write P as
+//                              fp16/bf16 into shared memory in the K-major swizzled operand
+//                              layout, rescale and accumulate the P V result in registers,
+//                              finally normalise and store the output row.
+// Two CTAs fit on an SM (D = 64), so one CTA's softmax overlaps the other's MMAs.
+// Every mbarrier wait is bounded and reports through *status instead of spinning forever.
+#include "kernels.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace tei {
+namespace {
+
+constexpr int BQ = 128;   // query rows per CTA
+constexpr int BKV = 128;  // keys per inner step
+constexpr int ATTN_THREADS = 160;
+
+template <int D>
+struct AttnSmem {
+  static constexpr int Q_BYTES = BQ * D * 2;
+  static constexpr int KV_BYTES = BKV * D * 2;
+  static constexpr int P_BYTES = BQ * BKV * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  // No alignment slack: two CTAs of the D = 64 variant must fit in one SM's shared memory.  The
+  // kernel checks that the dynamic window is 1024-byte aligned and reports an error otherwise.
+  static constexpr int TOTAL = OFF_BAR + 128;
+};
+
+struct AttnParams {
+  void* out;
+  const int* work;  // [n_work][4] = {seq_start, seq_len, q0, unused}
+  int n_heads, n_kv_heads;
+  int ld_o;
+  int causal;
+  float scale_log2;         // scale * log2(e)
+  const float* alibi_slopes;
+  int* status;
+};
+
+template <class T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <class T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+
+template <class T, int D>
+__global__ void __launch_bounds__(ATTN_THREADS, (D == 64 ? 2 : 1))
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
+                         const __grid_constant__ CUtensorMap tm_k,
+                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  using L = AttnSmem<D>;
+  constexpr int D_ATOMS = D / 64;  // 64-element (128-byte) swizzle atoms per head
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (ptx::smem_u32(smem) & 1023u) {  // swizzled operand tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(p.status, DEV_SMEM_ALIGN);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* bar_q = bars;          // Q tile landed
+  uint64_t* bar_kv = bars + 1;     // [2] K/V stage landed
+  uint64_t* bar_s = bars + 3;      // S = Q K^T finished
+  uint64_t* bar_p = bars + 4;      // P written (128 arrivals)
+  uint64_t* bar_o = bars + 5;      // P V finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  constexpr uint32_t TMEM_COLS = 256;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int item = blockIdx.x / p.n_heads;
+  const int head = blockIdx.x % p.n_heads;
+  const int kv_head = head / (p.n_heads / p.n_kv_heads);
+  const int seq_start = p.work[item * 4 + 0];
+  const int seq_len = p.work[item * 4 + 1];
+  const int q0 = p.work[item * 4 + 2];
+  const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar_q, 1);
+    ptx::mbar_init(&bar_kv[0], 1);
+    ptx::mbar_init(&bar_kv[1], 1);
+    ptx::mbar_init(bar_s, 1);
+    ptx::mbar_init(bar_p, BQ);
+    ptx::mbar_init(bar_o, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 4) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      ptx::prefetch_tmap(&tm_q);
+      ptx::prefetch_tmap(&tm_k);
+      ptx::prefetch_tmap(&tm_v);
+      constexpr uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, BKV, 0, 0);
+      // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
+      constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
+      auto load_kv = [&](int j) {
+        const int st = j & 1;
+        ptx::mbar_expect_tx(&bar_kv[st], 2 * L::KV_BYTES);
+#pragma unroll
+        for (int a = 0; a < D_ATOMS; ++a) {
+          ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k,
+                           &bar_kv[st], kv_head * D + a * 64, seq_start + j * BKV);
+          ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v,
+                           &bar_kv[st], kv_head * D + a * 64, seq_start + j * BKV);
+        }
+      };
+      ptx::mbar_expect_tx(bar_q, L::Q_BYTES);
+#pragma unroll
+      for (int a = 0; a < D_ATOMS; ++a) {
+        ptx::tma_load_2d(smem + L::OFF_Q + a * (BQ * 128), &tm_q, bar_q, head * D + a * 64,
+                         seq_start + q0);
+      }
+      load_kv(0);
+      bool ok = ptx::mbar_wait(bar_q, 0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        ok = ptx::mbar_wait(&bar_kv[st], (j >> 1) & 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        // S = Q K_j^T
+        const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
+        const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
+          ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
+                       ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit(bar_s);
+        // The other K/V stage was last read by step j-1's P V, whose completion (bar_o of step
+        // j-1) this thread has already waited for below, so it can be refilled now.
+        if (j + 1 < n_kv) load_kv(j + 1);
+        ok = ptx::mbar_wait(bar_p, j & 1);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        // O_j = P_j V_j
+        const uint32_t sp = ptx::smem_u32(smem + L::OFF_P);
+        const uint32_t sv = ptx::smem_u32(smem + L::OFF_V + st * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          const uint32_t aoff = (k / 4) * (BQ * 128) + (k % 4) * 32;
+          ptx::umma_ss(tmem_o, ptx::make_smem_desc_sw128(sp + aoff, 16, 1024),
+                       ptx::make_smem_desc_sw128(sv + k * 2048, BKV * 128, 1024), idesc_o,
+                       k != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit(bar_o);
+        ok = ptx::mbar_wait(bar_o, j & 1);
+      }
+      if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    const int r = warp * 32 + lane;           // row inside the query tile = TMEM lane
+    const int qi = q0 + r;                    // position inside the sequence
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+    float m = -INFINITY, l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    uint8_t* sp = smem + L::OFF_P;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!ptx::mbar_wait(bar_s, j & 1)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const int k_base = j * BKV;
+      // Keys this row may attend to within the tile: [0, lim).
+      int lim = seq_len - k_base;
+      if (p.causal) lim = min(lim, qi - k_base + 1);
+      lim = max(0, min(lim, BKV));
+      // pass 1: row maximum
+      float m_new = m;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t s[32];
+        ptx::tmem_ld32(tmem_s + lane_off + c * 32, s);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kk = c * 32 + i;
+          float x = __uint_as_float(s[i]) * p.scale_log2;
+          if (p.alibi_slopes) x -= slope * fabsf(static_cast<float>(qi - (k_base + kk)));
+          if (kk < lim) m_new = fmaxf(m_new, x);
+        }
+      }
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m - m_use);  // m = -inf -> 0
+      // pass 2: probabilities, row sum, P to shared memory
+      float row_sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t s[32];
+        ptx::tmem_ld32(tmem_s + lane_off + c * 32, s);
+        ptx::tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kk = c * 32 + i + u;
+            float x = __uint_as_float(s[i + u]) * p.scale_log2;
+            if (p.alibi_slopes) x -= slope * fabsf(static_cast<float>(qi - (k_base + kk)));
+            e[u] = (kk < lim) ? exp2f(x - m_use) : 0.f;
+          }
+          pk[i / 2] = pack2<T>(e[0], e[1]);
+          // Sum what the tensor core will actually multiply (the rounded values).
+          const float2 rounded = unpack2<T>(pk[i / 2]);
+          row_sum += rounded.x + rounded.y;
+        }
+        // K-major 128-byte-swizzled operand tile: [k atom of 64][row][64], 16-byte chunk index
+        // XORed with (row & 7).
+        uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+          *reinterpret_cast<uint4*>(rowp + chunk * 16) =
+              make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+        }
+      }
+      l = l * alpha + row_sum;
+      m = m_new;
+      // P visible to the tensor core (async proxy), S reads finished: hand over.
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar_p);
+      if (!ptx::mbar_wait(bar_o, j & 1)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t t[32];
+        ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(t[i]);
+      }
+      ptx::tc_fence_before();
+    }
+    if (ok && qi < seq_len) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 v;
+        v.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
+        v.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+        v.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
+        v.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+      }
+    }
+    if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <class T, int D>
+int launch_typed(const AttnArgs& a, cudaStream_t stream) {
+  using L = AttnSmem<D>;
+  const CUtensorMapDataType dt =
+      a.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tm_q, tm_k, tm_v;
+  int rc = make_tmap_2d(&tm_q, a.q, dt, 2, static_cast<uint64_t>(a.n_heads) * D, a.total_tokens,
+                        static_cast<uint64_t>(a.ld_q) * 2, 64, BQ);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tm_k, a.k, dt, 2, static_cast<uint64_t>(a.n_kv_heads) * D, a.total_tokens,
+                    static_cast<uint64_t>(a.ld_k) * 2, 64, BKV);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tm_v, a.v, dt, 2, static_cast<uint64_t>(a.n_kv_heads) * D, a.total_tokens,
+                    static_cast<uint64_t>(a.ld_v) * 2, 64, BKV);
+  if (rc) return rc;
+  static bool attr_set[64] = {};
+  auto kern = attention_tcgen05_kernel<T, D>;
+  const int dev = current_device() & 63;
+  if (!attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  AttnParams p;
+  p.out = a.out;
+  p.work = a.work_items;
+  p.n_heads = a.n_heads;
+  p.n_kv_heads = a.n_kv_heads;
+  p.ld_o = a.ld_o;
+  p.causal = a.causal;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.alibi_slopes = a.alibi_slopes;
+  p.status = a.status;
+  const long long grid = static_cast<long long>(a.n_work) * a.n_heads;
+  kern<<<static_cast<unsigned>(grid), ATTN_THREADS, L::TOTAL, stream>>>(tm_q, tm_k, tm_v, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+int launch_attention(const AttnArgs& a, cudaStream_t stream) {
+  if (a.n_work <= 0 || a.total_tokens <= 0) return 0;
+  if (a.n_kv_heads <= 0 || a.n_heads % a.n_kv_heads != 0) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (a.ld_q % 8 || a.ld_k % 8 || a.ld_v % 8 || a.ld_o % 8) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (a.head_dim == 64) {
+    return a.dtype == DT_F16 ? launch_typed<__half, 64>(a, stream)
+                             : launch_typed<__nv_bfloat16, 64>(a, stream);
+  }
+  if (a.head_dim == 128) {
+    return a.dtype == DT_F16 ? launch_typed<__half, 128>(a, stream)
+                             : launch_typed<__nv_bfloat16, 128>(a, stream);
+  }
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+}  // namespace tei

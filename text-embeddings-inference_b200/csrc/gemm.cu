@@ -1,0 +1,399 @@
+// Dense layer on the 5th-generation tensor cores: out = act(a @ w^T + bias) (+ residual).
+//
+// Replaces the cuBLASLt call behind the reference's Linear::forward
+// (backends/candle/src/layers/linear.rs:51-75, layers/cublaslt.rs:49-87): same operand layout
+// (activations [M,K] row-major, weights [N,K] row-major exactly as stored in safetensors), same
+// fused epilogues (bias, tanh-GELU, ReLU), plus SwiGLU, tanh, log1p(relu) and a residual add that
+// the reference runs as separate kernels.
+//
+// Structure (one CTA per SM, persistent over 128x256 output tiles):
+//   warp 0      TMA producer: 128x64 A tile + 256x64 W tile per stage, 128-byte swizzle,
+//               4-stage mbarrier ring.  Plain per-CTA TMA loads, no cluster multicast.
+//   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues
+//               tcgen05.mma.cta_group::1.kind::f16 (M=128, N=256, K=16), four per stage.
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one row per thread), bias /
+//               activation / residual in registers, 16-byte global stores.  Runs while the MMA
+//               warp fills the other accumulator.
+// Every mbarrier wait is bounded; a wait that runs out writes a code to *status and the CTA
+// drains and exits.
+#include "kernels.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace tei {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 64 x 2 B = one 128-byte swizzle row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  const void* bias;
+  const void* residual;
+  void* out;
+  int M, N, K;
+  int ldo, ldr;
+  int* status;
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanh_fast(u));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <class T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) {
+  return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <class T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+template <class T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int ACT>
+__device__ __forceinline__ float apply_act(float x) {
+  if constexpr (ACT == ACT_GELU) return gelu_tanh(x);
+  if constexpr (ACT == ACT_RELU) return fmaxf(x, 0.0f);
+  if constexpr (ACT == ACT_TANH) return tanhf(x);
+  if constexpr (ACT == ACT_RELU_LOG1P) return log1pf(fmaxf(x, 0.0f));
+  return x;
+}
+
+// Adds bias / applies the activation / adds the residual to 32 consecutive columns of one row
+// and stores them.  `col` is the first output column, n_valid the number of columns in range.
+template <class T, int ACT>
+__device__ __forceinline__ void finish_and_store(float (&v)[32], const GemmParams& p, int row,
+                                                 int col, int n_valid, bool vec_ok) {
+  T* out = reinterpret_cast<T*>(p.out) + static_cast<size_t>(row) * p.ldo + col;
+  const T* res = p.residual
+                     ? reinterpret_cast<const T*>(p.residual) + static_cast<size_t>(row) * p.ldr + col
+                     : nullptr;
+  if (vec_ok && n_valid == 32) {
+    if (res) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 r = *reinterpret_cast<const uint4*>(res + j * 8);
+        const T* rr = reinterpret_cast<const T*>(&r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j * 8 + e] += to_f32<T>(rr[e]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 o;
+      o.x = pack2<T>(v[j * 8 + 0], v[j * 8 + 1]);
+      o.y = pack2<T>(v[j * 8 + 2], v[j * 8 + 3]);
+      o.z = pack2<T>(v[j * 8 + 4], v[j * 8 + 5]);
+      o.w = pack2<T>(v[j * 8 + 6], v[j * 8 + 7]);
+      *reinterpret_cast<uint4*>(out + j * 8) = o;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < n_valid) {
+        float x = v[j];
+        if (res) x += to_f32<T>(res[j]);
+        out[j] = from_f32<T>(x);
+      }
+    }
+  }
+}
+
+template <class T, int ACT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                    const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled operand tiles need 1024-byte alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES] TMA -> MMA
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;        // [2] MMA -> epilogue
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;   // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tmap(&tm_a);
+    ptx::prefetch_tmap(&tm_b);
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&acc_full[i], 1);
+      ptx::mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * BM;
+        const int n0 = (tile % tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicExch(p.status, DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          ptx::mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          ptx::tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BK, m0);
+          ptx::tma_load_2d(sb, &tm_b, &full_bar[stage], kb * BK, n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BM, BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicExch(p.status, DEV_TIMEOUT_MMA);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+            atomicExch(p.status, DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = ptx::make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bd = ptx::make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            ptx::umma_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) ptx::umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const bool vec_ok = (p.ldo % 8 == 0) && (p.residual == nullptr || p.ldr % 8 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int m0 = (tile / tiles_n) * BM;
+      const int n0 = (tile % tiles_n) * BN;
+      if (!ptx::mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicExch(p.status, DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      if constexpr (ACT == ACT_SWIGLU) {
+        // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld32(t_row + c * 32, g);
+          ptx::tmem_ld32(t_row + 128 + c * 32, u);
+          ptx::tmem_ld_wait();
+          float v[32];
+          const int gcol = n0 + c * 32;        // column in the interleaved weight
+          const int ocol = n0 / 2 + c * 32;    // output column
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float gv = __uint_as_float(g[j]);
+            float uv = __uint_as_float(u[j]);
+            if (bias) {
+              if (gcol + j < p.N) gv += to_f32<T>(bias[gcol + j]);
+              if (gcol + 128 + j < p.N) uv += to_f32<T>(bias[gcol + 128 + j]);
+            }
+            v[j] = silu(gv) * uv;
+          }
+          const int n_valid = min(32, p.N / 2 - ocol);
+          if (row < p.M && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = n0 + c * 32;
+          if (col >= p.N) break;  // uniform across the CTA
+          uint32_t r[32];
+          ptx::tmem_ld32(t_row + c * 32, r);
+          ptx::tmem_ld_wait();
+          float v[32];
+          const int n_valid = min(32, p.N - col);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]);
+            if (bias && j < n_valid) x += to_f32<T>(bias[col + j]);
+            v[j] = apply_act<ACT>(x);
+          }
+          if (row < p.M) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
+        }
+      }
+      // Hand the accumulator back to the MMA warp.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <class T, int ACT>
+int launch_typed(const GemmArgs& g, cudaStream_t stream) {
+  CUtensorMap tm_a, tm_b;
+  const CUtensorMapDataType dt =
+      g.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int rc = make_tmap_2d(&tm_a, g.a, dt, 2, g.K, g.M, static_cast<uint64_t>(g.lda) * 2, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tm_b, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, BN);
+  if (rc) return rc;
+
+  // The opt-in shared-memory size is a per-device function attribute; setting it twice is
+  // harmless, so a plain flag per device (and per instantiation) is enough.
+  static bool attr_set[64] = {};
+  auto kern = gemm_tcgen05_kernel<T, ACT>;
+  const int dev = current_device() & 63;
+  if (!attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  GemmParams p;
+  p.bias = g.bias;
+  p.residual = g.residual;
+  p.out = g.out;
+  p.M = g.M;
+  p.N = g.N;
+  p.K = g.K;
+  p.ldo = g.ldo;
+  p.ldr = g.ldr;
+  p.status = g.status;
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <class T>
+int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
+  switch (g.act) {
+    case ACT_NONE: return launch_typed<T, ACT_NONE>(g, stream);
+    case ACT_GELU: return launch_typed<T, ACT_GELU>(g, stream);
+    case ACT_RELU: return launch_typed<T, ACT_RELU>(g, stream);
+    case ACT_TANH: return launch_typed<T, ACT_TANH>(g, stream);
+    case ACT_SWIGLU: return launch_typed<T, ACT_SWIGLU>(g, stream);
+    case ACT_RELU_LOG1P: return launch_typed<T, ACT_RELU_LOG1P>(g, stream);
+    default: return static_cast<int>(cudaErrorInvalidValue);
+  }
+}
+
+}  // namespace
+
+int gemm_smem_bytes() { return SMEM_BYTES; }
+
+int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
+  if (g.M <= 0) return 0;
+  if (g.N <= 0 || g.K <= 0 || g.K % 8 != 0 || g.lda % 8 != 0) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (g.act == ACT_SWIGLU && g.N % 256 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.w) & 15)) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  return g.dtype == DT_F16 ? launch_by_act<__half>(g, stream)
+                           : launch_by_act<__nv_bfloat16>(g, stream);
+}
+
+}  // namespace tei

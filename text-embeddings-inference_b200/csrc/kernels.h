@@ -1,0 +1,140 @@
+// Internal C++ interface between the host-side model code and the sm_100a kernels.
+// Every launcher enqueues on the given stream, allocates nothing and returns a cudaError_t /
+// status code; device-side failures (a bounded wait that ran out) are reported through the
+// `status` word the caller passes and reads back after synchronising.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace tei {
+
+enum DType : int { DT_F16 = 0, DT_BF16 = 1 };
+
+// Activation fused into the GEMM epilogue.  ACT_SWIGLU expects the weight rows interleaved in
+// blocks of 128 (128 gate rows, then the 128 matching up rows) and writes N/2 columns.
+enum Act : int {
+  ACT_NONE = 0,
+  ACT_GELU = 1,        // tanh approximation, the only GELU the reference implements
+  ACT_RELU = 2,
+  ACT_TANH = 3,
+  ACT_SWIGLU = 4,      // silu(gate) * up
+  ACT_RELU_LOG1P = 5,  // log(1 + relu(x)), the SPLADE decoder activation
+};
+
+// Device status codes (0 = ok).
+enum DevStatus : int {
+  DEV_OK = 0,
+  DEV_TIMEOUT_PRODUCER = 101,
+  DEV_TIMEOUT_MMA = 102,
+  DEV_TIMEOUT_EPILOGUE = 103,
+  DEV_TIMEOUT_ATTN = 104,
+  DEV_SMEM_ALIGN = 105,
+};
+
+struct GemmArgs {
+  const void* a;        // [M, K] row-major activations, lda elements between rows
+  const void* w;        // [N, K] row-major weights (as stored in safetensors)
+  const void* bias;     // [N] or nullptr, same dtype as a
+  const void* residual; // [M, N_out] or nullptr; added after the activation
+  void* out;            // [M, N_out], ldo elements between rows
+  int M, N, K;
+  int lda, ldo, ldr;
+  int act;
+  int dtype;
+  int* status;          // device int, stays 0 unless a wait ran out
+};
+
+// out = act(a @ w^T + bias) (+ residual).  tcgen05 + TMEM + TMA, persistent over 128x256 tiles.
+int launch_gemm(const GemmArgs& g, cudaStream_t stream);
+// Bytes of dynamic shared memory the GEMM kernel needs (for reporting).
+int gemm_smem_bytes();
+
+struct AttnArgs {
+  const void* q;  // token-major rows; head h of token t at q + t*ld_q + h*head_dim
+  const void* k;
+  const void* v;
+  void* out;      // [T, n_heads*head_dim]
+  const int* cu_seqlens;      // device, [n_seqs + 1]
+  const int* work_items;      // device, [n_work][4] = {seq_start, seq_len, q0, 0}; see plan_attention
+  int n_work;
+  int total_tokens;
+  int n_heads, n_kv_heads, head_dim;
+  int ld_q, ld_k, ld_v, ld_o;  // row strides in elements
+  int causal;
+  float scale;
+  const float* alibi_slopes;  // [n_heads] or nullptr
+  int dtype;
+  int* status;
+};
+int launch_attention(const AttnArgs& a, cudaStream_t stream);
+// Host side: lists the (sequence, 128-row query tile) work items of a packed batch, most
+// expensive first, as {seq_start, seq_len, q0, 0} quadruples.  Returns the number of items
+// needed; when that exceeds capacity_items (or work_out is null) nothing is written.
+int plan_attention(const int* cu_seqlens, int n_seqs, int causal, int* work_out, int capacity_items);
+
+struct EmbedArgs {
+  const int* ids;
+  const int* type_ids;   // nullptr -> no token-type table
+  const int* pos_ids;    // nullptr -> no position table
+  const void* word;      // [V, H]
+  const void* type_tab;  // [type_vocab, H] or nullptr
+  const void* pos_tab;   // [max_pos, H] or nullptr
+  const void* gamma;     // nullptr -> plain gather, no normalisation
+  const void* beta;
+  void* out;             // [T, H]
+  int T, H;
+  float eps;
+  int dtype;
+};
+int launch_embed_layernorm(const EmbedArgs& e, cudaStream_t stream);
+
+struct NormArgs {
+  const void* x;         // [T, H]
+  const void* residual;  // [T, H] or nullptr; model dtype for LayerNorm, fp32 for RMSNorm
+  const void* gamma;
+  const void* beta;      // LayerNorm only
+  void* out;             // normalised rows
+  float* sum_out;        // RMSNorm: fp32 x + residual written here (may alias residual); else nullptr
+  int T, H;
+  float eps;
+  int rms;               // 0 LayerNorm, 1 RMSNorm
+  int dtype;
+};
+int launch_add_norm(const NormArgs& n, cudaStream_t stream);
+
+struct RopeArgs {
+  void* q;               // rows of n_heads*head_dim at stride ld_q
+  void* k;               // rows of n_kv_heads*head_dim at stride ld_k
+  const int* pos_ids;    // [T]
+  const float* cos_tab;  // [max_pos, head_dim/2] fp32
+  const float* sin_tab;
+  const void* q_gamma;   // per-head RMSNorm weight [head_dim] or nullptr
+  const void* k_gamma;
+  int T, n_heads, n_kv_heads, head_dim, ld_q, ld_k;
+  float eps;
+  int dtype;
+};
+// Optional per-head RMSNorm followed by half-rotation RoPE, in place on q and k.
+int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t stream);
+
+struct PoolArgs {
+  const void* x;           // [T, H]
+  const int* cu_seqlens;   // [n_seqs + 1]
+  const int* seq_index;    // [n_out] batch positions to pool
+  float* out;              // [n_out, H] fp32
+  int n_out, H;
+  int mode;                // 0 cls, 1 mean, 2 max (SPLADE), 3 last token
+  int normalize;           // 1 -> L2-normalise each output row
+  int dtype;
+};
+int launch_pool(const PoolArgs& p, cudaStream_t stream);
+
+// Copies the token rows of the listed sequences, in order, to fp32.
+int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int n_rows, int H,
+                           int dtype, cudaStream_t stream);
+
+// Small dense head on pooled fp32 rows: out[r, n] = act(sum_k in[r,k] * w[n,k] + b[n]).
+int launch_head_linear(const float* in, const void* w, const void* b, float* out, int rows, int N,
+                       int K, int act, int dtype, cudaStream_t stream);
+
+}  // namespace tei

@@ -1,0 +1,511 @@
+// HBM-bound row kernels of the encoder forward: fused embedding gather + LayerNorm, fused
+// residual add + LayerNorm / RMSNorm, per-head RMSNorm + rotary embedding, segmented pooling
+// driven by cu_seqlens, row gather to fp32 and the small dense heads.
+//
+// All of them move each byte once with 16-byte accesses, keep the row in registers between the
+// statistics pass and the normalisation pass, and do their arithmetic in fp32.
+#include "kernels.h"
+#include "tmap.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace tei {
+namespace {
+
+template <class T>
+__device__ __forceinline__ float ldf(const T& v);
+template <>
+__device__ __forceinline__ float ldf<__half>(const __half& v) {
+  return __half2float(v);
+}
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16& v) {
+  return __bfloat162float(v);
+}
+template <class T>
+__device__ __forceinline__ T stf(float v);
+template <>
+__device__ __forceinline__ __half stf<__half>(float v) {
+  return __float2half_rn(v);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 stf<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+template <class T>
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const T* t = reinterpret_cast<const T*>(&u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) f[i] = ldf<T>(t[i]);
+}
+template <class T>
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  T* t = reinterpret_cast<T*>(&u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t[i] = stf<T>(f[i]);
+  return u;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ row normalisation core
+// One warp owns one row of H = 8 * n_chunks elements; lane l holds chunks l, l+32, ...
+// (at most MAXC of them) in registers.  Returns with v[] normalised and scaled.
+template <class T, int MAXC, bool RMS>
+__device__ __forceinline__ void normalise_row(float (&v)[MAXC][8], int n_chunks, int lane, int H,
+                                              float eps, const T* gamma, const T* beta) {
+  float s = 0.f;
+  if (!RMS) {
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      if (lane + c * 32 < n_chunks) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += v[c][i];
+      }
+    }
+    s = warp_sum(s);
+  }
+  const float mean = RMS ? 0.f : s / static_cast<float>(H);
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    if (lane + c * 32 < n_chunks) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = v[c][i] - mean;
+        q += d * d;
+      }
+    }
+  }
+  q = warp_sum(q);
+  const float rstd = rsqrtf(q / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + c * 32;
+    if (ch < n_chunks) {
+      float g[8], b[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(gamma + ch * 8), g);
+      if (!RMS && beta) {
+        unpack8<T>(*reinterpret_cast<const uint4*>(beta + ch * 8), b);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) b[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = (v[c][i] - mean) * rstd * g[i] + b[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ embedding (+ LayerNorm)
+// word[ids] + type[type_ids] + pos[pos_ids] -> LayerNorm, as BertEmbeddings::forward
+// (backends/candle/src/models/bert.rs:83-101) and NomicBertEmbeddings::forward
+// (models/nomic.rs:84-95); with gamma == nullptr it is the plain gather of
+// flash_qwen3.rs:409.
+template <class T, int MAXC>
+__global__ void __launch_bounds__(256)
+embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
+                const int* __restrict__ pos_ids, const T* __restrict__ word,
+                const T* __restrict__ type_tab, const T* __restrict__ pos_tab,
+                const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int T_,
+                int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= T_) return;
+  const int n_chunks = H >> 3;
+  const T* w = word + static_cast<size_t>(ids[row]) * H;
+  const T* t = type_tab ? type_tab + static_cast<size_t>(type_ids[row]) * H : nullptr;
+  const T* p = pos_tab ? pos_tab + static_cast<size_t>(pos_ids[row]) * H : nullptr;
+  float v[MAXC][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + c * 32;
+    if (ch < n_chunks) {
+      unpack8<T>(*reinterpret_cast<const uint4*>(w + ch * 8), v[c]);
+      float a[8];
+      if (t) {
+        unpack8<T>(*reinterpret_cast<const uint4*>(t + ch * 8), a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += a[i];
+      }
+      if (p) {
+        unpack8<T>(*reinterpret_cast<const uint4*>(p + ch * 8), a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += a[i];
+      }
+    }
+  }
+  if (gamma) normalise_row<T, MAXC, false>(v, n_chunks, lane, H, eps, gamma, beta);
+  T* o = out + static_cast<size_t>(row) * H;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + c * 32;
+    if (ch < n_chunks) *reinterpret_cast<uint4*>(o + ch * 8) = pack8<T>(v[c]);
+  }
+}
+
+// ------------------------------------------------------------------ residual add + norm
+// LayerNorm: out = LN(x + residual) (backends/candle/src/layers/layer_norm.rs:108-132).
+// RMSNorm:   sum = x + residual, out = sum * rsqrt(mean(sum^2) + eps) * gamma
+//            (layers/rms_norm.rs:30-57); the running sum is kept in fp32 so that rounding does
+//            not pile up over the decoder's layers.
+template <class T, int MAXC, bool RMS>
+__global__ void __launch_bounds__(256)
+add_norm_kernel(const T* __restrict__ x, const void* __restrict__ residual,
+                const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
+                float* __restrict__ sum_out, int T_, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= T_) return;
+  const int n_chunks = H >> 3;
+  const T* xr = x + static_cast<size_t>(row) * H;
+  float v[MAXC][8];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + c * 32;
+    if (ch < n_chunks) {
+      unpack8<T>(*reinterpret_cast<const uint4*>(xr + ch * 8), v[c]);
+      if (residual) {
+        if (RMS) {
+          const float* rr = reinterpret_cast<const float*>(residual) + static_cast<size_t>(row) * H;
+          const float4 r0 = *reinterpret_cast<const float4*>(rr + ch * 8);
+          const float4 r1 = *reinterpret_cast<const float4*>(rr + ch * 8 + 4);
+          v[c][0] += r0.x; v[c][1] += r0.y; v[c][2] += r0.z; v[c][3] += r0.w;
+          v[c][4] += r1.x; v[c][5] += r1.y; v[c][6] += r1.z; v[c][7] += r1.w;
+        } else {
+          const T* rr = reinterpret_cast<const T*>(residual) + static_cast<size_t>(row) * H;
+          float a[8];
+          unpack8<T>(*reinterpret_cast<const uint4*>(rr + ch * 8), a);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[c][i] += a[i];
+        }
+      }
+      if (RMS && sum_out) {
+        float* so = sum_out + static_cast<size_t>(row) * H + ch * 8;
+        *reinterpret_cast<float4*>(so) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
+        *reinterpret_cast<float4*>(so + 4) = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
+      }
+    }
+  }
+  normalise_row<T, MAXC, RMS>(v, n_chunks, lane, H, eps, gamma, beta);
+  T* o = out + static_cast<size_t>(row) * H;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = lane + c * 32;
+    if (ch < n_chunks) *reinterpret_cast<uint4*>(o + ch * 8) = pack8<T>(v[c]);
+  }
+}
+
+// ------------------------------------------------------------------ per-head RMSNorm + RoPE
+// One warp per (token, head).  Optional RMSNorm over the head (flash_qwen3.rs:150-151), then
+// x*cos + rotate_half(x)*sin with the half-rotation pairing (j, j + head_dim/2)
+// (layers/rotary.rs:118-130); cos / sin come from an fp32 [max_pos, head_dim/2] table.
+template <class T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restrict__ pos_ids,
+                    const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                    const T* __restrict__ q_gamma, const T* __restrict__ k_gamma, int T_, int nh,
+                    int nkv, int dh, int ld_q, int ld_k, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int heads = nh + nkv;
+  if (w >= static_cast<long long>(T_) * heads) return;
+  const int tok = static_cast<int>(w / heads);
+  const int h = static_cast<int>(w % heads);
+  T* base = h < nh ? q + static_cast<size_t>(tok) * ld_q + h * dh
+                   : k + static_cast<size_t>(tok) * ld_k + (h - nh) * dh;
+  const T* gamma = h < nh ? q_gamma : k_gamma;
+  const int half = dh >> 1;
+  const float* cs = cos_tab + static_cast<size_t>(pos_ids[tok]) * half;
+  const float* sn = sin_tab + static_cast<size_t>(pos_ids[tok]) * half;
+  // head_dim <= 256: at most 4 pairs per lane.
+  float a[4], b[4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int j = lane + i * 32;
+    if (j < half) {
+      a[i] = ldf<T>(base[j]);
+      b[i] = ldf<T>(base[j + half]);
+      ss += a[i] * a[i] + b[i] * b[i];
+    }
+  }
+  if (gamma) {
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / static_cast<float>(dh) + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = lane + i * 32;
+      if (j < half) {
+        a[i] = a[i] * r * ldf<T>(gamma[j]);
+        b[i] = b[i] * r * ldf<T>(gamma[j + half]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int j = lane + i * 32;
+    if (j < half) {
+      const float c = cs[j], s = sn[j];
+      base[j] = stf<T>(a[i] * c - b[i] * s);
+      base[j + half] = stf<T>(b[i] * c + a[i] * s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ segmented pooling
+// One block per (output row, slab of 256 columns); 32 column groups of 8 x 8 row lanes.
+// mode 0: first row of the sequence, 3: last row, 1: mean over the rows, 2: max over the rows
+// (flash_bert.rs:396-490).  Writes fp32.
+template <class T>
+__global__ void __launch_bounds__(256)
+pool_kernel(const T* __restrict__ x, const int* __restrict__ cu, const int* __restrict__ seq_index,
+            float* __restrict__ out, int H, int mode) {
+  const int o = blockIdx.x;
+  const int s = seq_index[o];
+  const int start = cu[s], end = cu[s + 1];
+  const int cg = threadIdx.x & 31;
+  const int rl = threadIdx.x >> 5;
+  const int col = blockIdx.y * 256 + cg * 8;
+  __shared__ float red[8][32][8];
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = (mode == 2) ? -INFINITY : 0.f;
+  if (col < H) {
+    if (mode == 0 || mode == 3) {
+      if (rl == 0 && end > start) {
+        const int r = mode == 0 ? start : end - 1;
+        unpack8<T>(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H + col), acc);
+      }
+    } else {
+      for (int r = start + rl; r < end; r += 8) {
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H + col), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = (mode == 2) ? fmaxf(acc[i], f[i]) : acc[i] + f[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[rl][cg][i] = acc[i];
+  __syncthreads();
+  if (rl == 0 && col < H) {
+    if (mode == 1 || mode == 2) {
+#pragma unroll
+      for (int r = 1; r < 8; ++r) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[i] = (mode == 2) ? fmaxf(acc[i], red[r][cg][i]) : acc[i] + red[r][cg][i];
+        }
+      }
+      if (mode == 1) {
+        const float inv = 1.0f / static_cast<float>(end - start);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] *= inv;
+      }
+    }
+    float* dst = out + static_cast<size_t>(o) * H + col;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
+// In-place L2 normalisation of fp32 rows (core/src/infer.rs:288-303 does this on the host).
+__global__ void __launch_bounds__(256) l2_normalise_kernel(float* __restrict__ x, int rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float* r = x + static_cast<size_t>(row) * H;
+  float ss = 0.f;
+  for (int j = lane; j < H; j += 32) ss += r[j] * r[j];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss);
+  for (int j = lane; j < H; j += 32) r[j] *= inv;
+}
+
+template <class T>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_index,
+                   float* __restrict__ out, int n_rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const T* src = x + static_cast<size_t>(row_index[row]) * H;
+  float* dst = out + static_cast<size_t>(row) * H;
+  for (int ch = lane; ch < (H >> 3); ch += 32) {
+    float f[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(src + ch * 8), f);
+    *reinterpret_cast<float4*>(dst + ch * 8) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + ch * 8 + 4) = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+// out[r, n] = act(sum_k in[r, k] * w[n, k] + b[n]); one warp per output element.  Used for the
+// classification heads (models/bert.rs:405-465) and Dense modules, whose inputs are a few
+// hundred pooled rows at most.
+template <class T>
+__global__ void __launch_bounds__(256)
+head_linear_kernel(const float* __restrict__ in, const T* __restrict__ w, const T* __restrict__ b,
+                   float* __restrict__ out, int rows, int N, int K, int act) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(rows) * N) return;
+  const int r = static_cast<int>(wid / N);
+  const int n = static_cast<int>(wid % N);
+  const float* x = in + static_cast<size_t>(r) * K;
+  const T* wr = w + static_cast<size_t>(n) * K;
+  float s = 0.f;
+  for (int k = lane; k < K; k += 32) s += x[k] * ldf<T>(wr[k]);
+  s = warp_sum(s);
+  if (lane == 0) {
+    if (b) s += ldf<T>(b[n]);
+    if (act == ACT_TANH) s = tanhf(s);
+    else if (act == ACT_RELU) s = fmaxf(s, 0.f);
+    else if (act == ACT_GELU) {
+      const float u = 0.7978845608028654f * (s + 0.044715f * s * s * s);
+      s = 0.5f * s * (1.0f + tanhf(u));
+    }
+    out[static_cast<size_t>(r) * N + n] = s;
+  }
+}
+
+inline int last_error() { return static_cast<int>(cudaGetLastError()); }
+
+template <class T>
+int embed_typed(const EmbedArgs& e, cudaStream_t st) {
+  const int warps = 8;
+  const int grid = (e.T + warps - 1) / warps;
+  const int n_chunks = e.H / 8;
+#define TEI_EMBED(MAXC)                                                                          \
+  embed_ln_kernel<T, MAXC><<<grid, warps * 32, 0, st>>>(                                         \
+      e.ids, e.type_ids, e.pos_ids, reinterpret_cast<const T*>(e.word),                          \
+      reinterpret_cast<const T*>(e.type_tab), reinterpret_cast<const T*>(e.pos_tab),             \
+      reinterpret_cast<const T*>(e.gamma), reinterpret_cast<const T*>(e.beta),                   \
+      reinterpret_cast<T*>(e.out), e.T, e.H, e.eps)
+  if (n_chunks <= 32 * 4) TEI_EMBED(4);
+  else if (n_chunks <= 32 * 8) TEI_EMBED(8);
+  else TEI_EMBED(16);
+#undef TEI_EMBED
+  return last_error();
+}
+
+template <class T, bool RMS>
+int norm_typed(const NormArgs& n, cudaStream_t st) {
+  const int warps = 8;
+  const int grid = (n.T + warps - 1) / warps;
+  const int n_chunks = n.H / 8;
+#define TEI_NORM(MAXC)                                                                           \
+  add_norm_kernel<T, MAXC, RMS><<<grid, warps * 32, 0, st>>>(                                    \
+      reinterpret_cast<const T*>(n.x), n.residual, reinterpret_cast<const T*>(n.gamma),          \
+      reinterpret_cast<const T*>(n.beta), reinterpret_cast<T*>(n.out),                           \
+      reinterpret_cast<float*>(n.sum_out), n.T, n.H, n.eps)
+  if (n_chunks <= 32 * 4) TEI_NORM(4);
+  else if (n_chunks <= 32 * 8) TEI_NORM(8);
+  else TEI_NORM(16);
+#undef TEI_NORM
+  return last_error();
+}
+
+}  // namespace
+
+int launch_embed_layernorm(const EmbedArgs& e, cudaStream_t st) {
+  if (e.T <= 0) return 0;
+  if (e.H % 8 != 0 || e.H > 4096) return static_cast<int>(cudaErrorInvalidValue);
+  return e.dtype == DT_F16 ? embed_typed<__half>(e, st) : embed_typed<__nv_bfloat16>(e, st);
+}
+
+int launch_add_norm(const NormArgs& n, cudaStream_t st) {
+  if (n.T <= 0) return 0;
+  if (n.H % 8 != 0 || n.H > 4096) return static_cast<int>(cudaErrorInvalidValue);
+  if (n.dtype == DT_F16) {
+    return n.rms ? norm_typed<__half, true>(n, st) : norm_typed<__half, false>(n, st);
+  }
+  return n.rms ? norm_typed<__nv_bfloat16, true>(n, st) : norm_typed<__nv_bfloat16, false>(n, st);
+}
+
+int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
+  if (r.T <= 0) return 0;
+  if (r.head_dim % 2 != 0 || r.head_dim > 256) return static_cast<int>(cudaErrorInvalidValue);
+  const long long warps_total = static_cast<long long>(r.T) * (r.n_heads + r.n_kv_heads);
+  const int warps = 8;
+  const long long grid = (warps_total + warps - 1) / warps;
+  if (r.dtype == DT_F16) {
+    qk_norm_rope_kernel<__half><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+        reinterpret_cast<__half*>(r.q), reinterpret_cast<__half*>(r.k), r.pos_ids, r.cos_tab,
+        r.sin_tab, reinterpret_cast<const __half*>(r.q_gamma),
+        reinterpret_cast<const __half*>(r.k_gamma), r.T, r.n_heads, r.n_kv_heads, r.head_dim,
+        r.ld_q, r.ld_k, r.eps);
+  } else {
+    qk_norm_rope_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+        reinterpret_cast<__nv_bfloat16*>(r.q), reinterpret_cast<__nv_bfloat16*>(r.k), r.pos_ids,
+        r.cos_tab, r.sin_tab, reinterpret_cast<const __nv_bfloat16*>(r.q_gamma),
+        reinterpret_cast<const __nv_bfloat16*>(r.k_gamma), r.T, r.n_heads, r.n_kv_heads,
+        r.head_dim, r.ld_q, r.ld_k, r.eps);
+  }
+  return last_error();
+}
+
+int launch_pool(const PoolArgs& p, cudaStream_t st) {
+  if (p.n_out <= 0) return 0;
+  if (p.H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(p.n_out, (p.H + 255) / 256);
+  if (p.dtype == DT_F16) {
+    pool_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(p.x), p.cu_seqlens,
+                                              p.seq_index, p.out, p.H, p.mode);
+  } else {
+    pool_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.x),
+                                                     p.cu_seqlens, p.seq_index, p.out, p.H,
+                                                     p.mode);
+  }
+  int rc = last_error();
+  if (rc) return rc;
+  if (p.normalize) {
+    const int warps = 8;
+    l2_normalise_kernel<<<(p.n_out + warps - 1) / warps, warps * 32, 0, st>>>(p.out, p.n_out, p.H);
+    rc = last_error();
+  }
+  return rc;
+}
+
+int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int n_rows, int H,
+                           int dtype, cudaStream_t st) {
+  if (n_rows <= 0) return 0;
+  if (H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int warps = 8;
+  const int grid = (n_rows + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    gather_rows_kernel<__half><<<grid, warps * 32, 0, st>>>(reinterpret_cast<const __half*>(x),
+                                                            row_index, out, n_rows, H);
+  } else {
+    gather_rows_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), row_index, out, n_rows, H);
+  }
+  return last_error();
+}
+
+int launch_head_linear(const float* in, const void* w, const void* b, float* out, int rows, int N,
+                       int K, int act, int dtype, cudaStream_t st) {
+  if (rows <= 0 || N <= 0) return 0;
+  const long long total = static_cast<long long>(rows) * N;
+  const int warps = 8;
+  const long long grid = (total + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    head_linear_kernel<__half><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+        in, reinterpret_cast<const __half*>(w), reinterpret_cast<const __half*>(b), out, rows, N, K,
+        act);
+  } else {
+    head_linear_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+        in, reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<const __nv_bfloat16*>(b),
+        out, rows, N, K, act);
+  }
+  return last_error();
+}
+
+}  // namespace tei

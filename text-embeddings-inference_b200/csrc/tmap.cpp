@@ -1,0 +1,68 @@
+#include "tmap.h"
+
+#include <atomic>
+#include <mutex>
+
+namespace tei {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::once_flag g_once;
+EncodeTiledFn g_encode = nullptr;
+
+void resolve_encode() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) {
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+}
+
+constexpr int kMaxDevices = 64;
+std::atomic<int> g_sms[kMaxDevices];
+
+}  // namespace
+
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                 uint64_t inner, uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,
+                 uint32_t box_outer) {
+  std::call_once(g_once, resolve_encode);
+  if (!g_encode) return static_cast<int>(cudaErrorNotSupported);
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) ||
+      box_inner * elem_bytes != 128 || box_outer == 0 || box_outer > 256) {
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return static_cast<int>(r);
+}
+
+int current_device() {
+  int d = 0;
+  cudaGetDevice(&d);
+  return d;
+}
+
+int num_sms() {
+  const int d = current_device();
+  if (d < 0 || d >= kMaxDevices) return 148;
+  int v = g_sms[d].load(std::memory_order_relaxed);
+  if (v == 0) {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d);
+    if (v <= 0) v = 148;
+    g_sms[d].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+}  // namespace tei

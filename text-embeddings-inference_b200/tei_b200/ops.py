@@ -1,0 +1,193 @@
+"""torch-tensor wrappers of the kernel-level C ABI (include/tei_b200_ops.h).
+
+torch is used only to hold device memory and the current stream; every call goes straight into
+libtei_b200.so.  These wrappers exist for the tests and the benchmark; the serving path calls
+the same kernels from C++.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+
+ACT = {"none": 0, "gelu": 1, "relu": 2, "tanh": 3, "swiglu": 4, "relu_log1p": 5}
+POOL = {"cls": 0, "mean": 1, "splade": 2, "max": 2, "last_token": 3}
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def new_status(device="cuda") -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor, what: str = "kernel"):
+    code = int(status.item())
+    if code != 0:
+        raise RuntimeError(f"{what}: device status {code} (a bounded wait ran out)")
+
+
+def linear(a, w, bias=None, residual=None, act="none", out=None, status=None):
+    """out = act(a @ w.T + bias) (+ residual); for act == 'swiglu' w/bias are pre-interleaved."""
+    lib = _lib.load()
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if act == "swiglu" else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=a.dtype, device=a.device)
+    own = status is None
+    if own:
+        status = new_status(a.device)
+    rc = lib.tei_b200_op_linear(
+        _p(a), _p(w), _p(bias), _p(residual), _p(out), M, N, K, a.stride(0), out.stride(0),
+        residual.stride(0) if residual is not None else 0, ACT[act], _dt(a), _p(status), _stream())
+    _check(rc, "tei_b200_op_linear")
+    if own:
+        check_status(status, "linear")
+    return out
+
+
+def interleave_swiglu(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
+    """Rows [gate block 0 (128), up block 0 (128), gate block 1, ...] as the SwiGLU epilogue expects."""
+    inter = gate_w.shape[0]
+    assert inter % 128 == 0 and up_w.shape == gate_w.shape
+    g = gate_w.reshape(inter // 128, 128, *gate_w.shape[1:])
+    u = up_w.reshape(inter // 128, 128, *up_w.shape[1:])
+    return torch.stack([g, u], dim=1).reshape(2 * inter, *gate_w.shape[1:]).contiguous()
+
+
+def attention_plan(cu_seqlens, causal: bool) -> np.ndarray:
+    lib = _lib.load()
+    cu = np.ascontiguousarray(np.asarray(cu_seqlens, dtype=np.int32))
+    n_seqs = len(cu) - 1
+    cu_p = cu.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
+    n = lib.tei_b200_attention_plan(cu_p, n_seqs, int(causal), None, 0)
+    work = np.zeros((max(n, 1), 4), dtype=np.int32)
+    n2 = lib.tei_b200_attention_plan(cu_p, n_seqs, int(causal),
+                                     work.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), n)
+    assert n2 == n
+    return work[:n]
+
+
+def attention(q, k, v, cu_seqlens, causal=False, scale=None, alibi_slopes=None, work=None,
+              out=None, status=None):
+    """q [T, nh, D], k/v [T, nkv, D] (views with unit stride in the last two dims)."""
+    lib = _lib.load()
+    T, nh, D = q.shape
+    nkv = k.shape[1]
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
+    if scale is None:
+        scale = 1.0 / float(D) ** 0.5
+    if work is None:
+        work = torch.from_numpy(attention_plan(cu_seqlens, causal)).to(q.device)
+    if out is None:
+        out = torch.empty((T, nh * D), dtype=q.dtype, device=q.device)
+    own = status is None
+    if own:
+        status = new_status(q.device)
+    rc = lib.tei_b200_op_attention(
+        _p(q), _p(k), _p(v), _p(out), _p(work), work.shape[0], T, nh, nkv, D, q.stride(0),
+        k.stride(0), v.stride(0), out.stride(0), int(causal), float(scale), _p(alibi_slopes),
+        _dt(q), _p(status), _stream())
+    _check(rc, "tei_b200_op_attention")
+    if own:
+        check_status(status, "attention")
+    return out
+
+
+def embed_layernorm(ids, type_ids, pos_ids, word, type_tab, pos_tab, gamma, beta, eps):
+    lib = _lib.load()
+    T = ids.shape[0]
+    H = word.shape[1]
+    out = torch.empty((T, H), dtype=word.dtype, device=word.device)
+    rc = lib.tei_b200_op_embed_layernorm(
+        _p(ids), _p(type_ids), _p(pos_ids), _p(word), _p(type_tab), _p(pos_tab), _p(gamma),
+        _p(beta), _p(out), T, H, float(eps), _dt(word), _stream())
+    _check(rc, "tei_b200_op_embed_layernorm")
+    return out
+
+
+def add_layernorm(x, residual, gamma, beta, eps):
+    lib = _lib.load()
+    T, H = x.shape
+    out = torch.empty_like(x)
+    rc = lib.tei_b200_op_add_norm(_p(x), _p(residual), _p(gamma), _p(beta), _p(out), None, T, H,
+                                  float(eps), 0, _dt(x), _stream())
+    _check(rc, "tei_b200_op_add_norm")
+    return out
+
+
+def add_rmsnorm(x, residual_f32, gamma, eps):
+    """Returns (normed [T,H] model dtype, sum [T,H] fp32)."""
+    lib = _lib.load()
+    T, H = x.shape
+    out = torch.empty_like(x)
+    sum_out = torch.empty((T, H), dtype=torch.float32, device=x.device)
+    rc = lib.tei_b200_op_add_norm(_p(x), _p(residual_f32), _p(gamma), None, _p(out), _p(sum_out),
+                                  T, H, float(eps), 1, _dt(x), _stream())
+    _check(rc, "tei_b200_op_add_norm")
+    return out, sum_out
+
+
+def qk_norm_rope_(q, k, pos_ids, cos, sin, q_gamma=None, k_gamma=None, eps=1e-6):
+    """In place.  q [T, nh, D], k [T, nkv, D] views; cos/sin fp32 [max_pos, D/2]."""
+    lib = _lib.load()
+    T, nh, D = q.shape
+    nkv = k.shape[1]
+    rc = lib.tei_b200_op_qk_norm_rope(
+        _p(q), _p(k), _p(pos_ids), _p(cos), _p(sin), _p(q_gamma), _p(k_gamma), T, nh, nkv, D,
+        q.stride(0), k.stride(0), float(eps), _dt(q), _stream())
+    _check(rc, "tei_b200_op_qk_norm_rope")
+
+
+def pool(x, cu_seqlens_dev, seq_index_dev, mode: str, normalize: bool):
+    lib = _lib.load()
+    H = x.shape[1]
+    n_out = seq_index_dev.shape[0]
+    out = torch.empty((n_out, H), dtype=torch.float32, device=x.device)
+    rc = lib.tei_b200_op_pool(_p(x), _p(cu_seqlens_dev), _p(seq_index_dev), _p(out), n_out, H,
+                              POOL[mode], int(normalize), _dt(x), _stream())
+    _check(rc, "tei_b200_op_pool")
+    return out
+
+
+def gather_rows_f32(x, row_index_dev):
+    lib = _lib.load()
+    n = row_index_dev.shape[0]
+    H = x.shape[1]
+    out = torch.empty((n, H), dtype=torch.float32, device=x.device)
+    rc = lib.tei_b200_op_gather_rows_f32(_p(x), _p(row_index_dev), _p(out), n, H, _dt(x), _stream())
+    _check(rc, "tei_b200_op_gather_rows_f32")
+    return out
+
+
+def head_linear(x_f32, w, b, act="none"):
+    lib = _lib.load()
+    rows, K = x_f32.shape
+    N = w.shape[0]
+    out = torch.empty((rows, N), dtype=torch.float32, device=x_f32.device)
+    rc = lib.tei_b200_op_head_linear(_p(x_f32), _p(w), _p(b), _p(out), rows, N, K, ACT[act],
+                                     _dt(w), _stream())
+    _check(rc, "tei_b200_op_head_linear")
+    return out
