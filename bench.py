@@ -1,0 +1,440 @@
+"""Benchmark of the hot path: tokens/s of the packed, unpadded BERT-base forward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One step = one forward of one packed batch.  Workload at every N: BASELINE.json configs[1] -
+BERT-base (bge-base-en-v1.5 architecture, random-init seed 0), 256 ragged sequences with lengths
+uniform in [16, 512] (seed 1), 68,576 tokens, mean pooling + L2 normalise, fp16 - one such batch
+per GPU per step (request-level data parallelism: every GPU holds a full replica, so scaling is
+weak and no collective runs on the data path; torch.distributed is used for the barrier and the
+max-over-ranks of the timings only).
+
+Printed by rank 0 as ONE JSON line:
+  value        device-resident throughput: the batch is staged in HBM before the timed region,
+               K forwards run back to back, timed with CUDA events on the launching stream
+  e2e          the same metric through the C-ABI `embed` call with HOST buffers: host->device copy
+               of the batch and device->host copy of the pooled rows inside the timed region
+  roofline     dense-layer GEMM kernel: algorithmic FLOPs per launch / mean launch duration,
+               measured with per-launch CUDA events inside the timed region
+  cpu_baseline the fp32 CPU restatement of the reference's Candle CPU path (oracle/), timed on a
+               bounded sample of the same batch on the host cores (rank 0, N = 1 only)
+`--impl reference` times that CPU path alone (rank 0 only), same metric and config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (str(ROOT), str(ROOT / "text-embeddings-inference_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+WORKLOAD = ("cfg2: BERT-base 12x768 (12 heads x 64, FFN 3072 tanh-GELU, post-LN), random-init seed 0; "
+            "256 sequences, lengths uniform [16,512] seed 1, 68576 tokens packed with cu_seqlens; "
+            "mean pooling + L2 normalise")
+MODEL_DIR = Path(os.environ.get("TEI_B200_BENCH_DIR", "/tmp/tei_b200_bench")) / "bert_base_seed0"
+
+
+def ensure_model_dir(local_rank: int) -> Path:
+    """Local rank 0 writes the seeded BERT-base directory once; the others wait for it."""
+    from oracle import generators as G
+    marker = MODEL_DIR / ".complete"
+    if marker.exists():
+        return MODEL_DIR
+    if local_rank == 0:
+        tmp = MODEL_DIR.with_name(MODEL_DIR.name + f".tmp{os.getpid()}")
+        G.write_model_dir(tmp, G.bert_config(), seed=0)
+        (tmp / ".complete").write_text("ok")
+        MODEL_DIR.parent.mkdir(parents=True, exist_ok=True)
+        try:
+            os.replace(tmp, MODEL_DIR)
+        except OSError:
+            pass  # somebody else finished first
+    t0 = time.time()
+    while not marker.exists():
+        if time.time() - t0 > 600:
+            raise RuntimeError("timed out waiting for the model directory")
+        time.sleep(0.2)
+    return MODEL_DIR
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs.
+    Read-only: nothing is set or reset."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+        0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            # honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in vis.split(",") if v.strip().isdigit()]
+            phys = int(ids[index]) if index < len(ids) else index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+class Ranks:
+    """The only cross-rank plumbing of the benchmark: a barrier and max / sum of a scalar.  The
+    data path itself has no collective (replicas share nothing).  backend "nccl" on GPUs, "gloo"
+    for the CPU tests."""
+
+    def __init__(self, world: int, local_rank: int, backend: str = "nccl"):
+        self.world = world
+        self.backend = backend
+        self.dist = None
+        self.device = "cpu"
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            if backend == "nccl":
+                self.device = torch.device("cuda", local_rank)
+                dist.init_process_group("nccl", device_id=self.device)
+            else:
+                dist.init_process_group(backend)
+            self.dist = dist
+
+    def barrier(self):
+        import torch
+        if self.dist is not None:
+            self.dist.barrier()
+        if self.backend == "nccl" and torch.cuda.is_available():
+            torch.cuda.synchronize()
+
+    def _reduce(self, x: float, op_name: str) -> float:
+        if self.dist is None:
+            return float(x)
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=getattr(self.dist.ReduceOp, op_name))
+        return float(t.item())
+
+    def max(self, x: float) -> float:
+        return self._reduce(x, "MAX")
+
+    def sum(self, x: float) -> float:
+        return self._reduce(x, "SUM")
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def whole_job_throughput(ranks: "Ranks", tokens_this_rank: float, steps: int, ms_this_rank: float) -> float:
+    """Units all ranks processed / the slowest rank's device time."""
+    ms = ranks.max(ms_this_rank)
+    total = ranks.sum(float(tokens_this_rank)) * steps
+    return total / (ms / 1e3)
+
+
+def cpu_baseline(model_dir: Path, n_seqs: int, repeats: int = 1):
+    """Times the fp32 CPU restatement of the reference's Candle CPU path on the first n_seqs
+    sequences of the workload, the way that path runs them: at most 4 sequences per forward
+    (backends/candle/src/lib.rs:640-646), each chunk padded to its longest sequence
+    (models/bert.rs:715-757).  Returns (tokens/s, cores, seconds, tokens)."""
+    import numpy as np
+    import torch
+    from oracle import generators as G
+    from oracle import models as M
+    from oracle.packing import batch_from_encodings
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    oracle = M.build_oracle(model_dir, "embedding", "mean")
+    full = G.batch_cfg2(n_seqs=n_seqs)
+    cu = full.cumulative_seq_lengths.astype(np.int64)
+    chunks = []
+    for c0 in range(0, len(full), 4):
+        encs = [full.input_ids[cu[s]:cu[s + 1]] for s in range(c0, min(c0 + 4, len(full)))]
+        chunks.append(batch_from_encodings(encs, list(range(len(encs))), []))
+    tokens = int(cu[-1])
+    best = None
+    with torch.no_grad():
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            for ch in chunks:
+                hs = oracle.hidden_states_padded(ch)
+                lens = ch.lengths()
+                for i in range(len(ch)):
+                    v = hs[i, : int(lens[i])].mean(dim=0)
+                    M.l2_normalise(v.numpy()[None])
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+    return tokens / best, cores, best, tokens
+
+
+def run_reference(args, rank: int):
+    """`--impl reference`: the reference's own implementation cannot be built here (Rust, crates
+    not vendored), so this arm times its CPU restatement (oracle/, kind "port") on a bounded
+    sample of the workload with all host threads."""
+    if rank != 0:
+        return
+    model_dir = ensure_model_dir(0)
+    n_seqs = 32
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_baseline(model_dir, 8)
+    times, tokens, cores = [], 0, 1
+    for _ in range(max(args.steps, 1)):
+        tps, cores, dt, tokens = cpu_baseline(model_dir, n_seqs)
+        times.append(dt)
+    total = sum(times)
+    value = tokens * len(times) / total
+    sample = f"first {n_seqs} of the 256 sequences ({tokens} tokens) per step, forwards of <=4 sequences padded to the chunk max"
+    line = {
+        "impl": "reference", "metric": "tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_kernel(args):
+    """`--kernel NAME`: one kernel of the forward alone at the workload's shapes (68,576 tokens),
+    timed with CUDA events on torch's current stream, which is the stream it is launched on.
+    Used for the burst roofline figures and as the small, single-kernel command for ncu."""
+    import numpy as np
+    import torch
+    from tei_b200 import ops
+    from oracle import generators as G
+
+    torch.cuda.set_device(0)
+    lens = [int(x) for x in G.lengths_cfg2()]
+    T, H, I, nh, D = int(sum(lens)), 768, 3072, 12, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    dt = torch.float16
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device="cuda", generator=g) * scale).to(dt)
+
+    name = args.kernel
+    flops = bytes_ = 0.0
+    st = ops.new_status()
+    if name.startswith("gemm_"):
+        N, K, act = {"gemm_qkv": (3 * H, H, "none"), "gemm_out": (H, H, "none"),
+                     "gemm_ffn1": (I, H, "gelu"), "gemm_ffn2": (H, I, "none")}[name]
+        a, w, b = rnd(T, K, scale=0.5), rnd(N, K, scale=0.05), rnd(N, scale=0.1)
+        out = torch.empty(T, N, device="cuda", dtype=dt)
+        fn = lambda: ops.linear(a, w, b, act=act, out=out, status=st)  # noqa: E731
+        flops = 2.0 * T * N * K
+        bytes_ = 2.0 * (T * K + N * K + T * N)
+    elif name == "attention":
+        qkv = rnd(T, 3 * H)
+        q, k, v = (qkv[:, i * H:(i + 1) * H].view(T, nh, D) for i in range(3))
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        work = torch.from_numpy(ops.attention_plan(cu, False)).cuda()
+        out = torch.empty(T, H, device="cuda", dtype=dt)
+        fn = lambda: ops.attention(q, k, v, cu, work=work, out=out, status=st)  # noqa: E731
+        flops = 4.0 * H * float(sum(n * n for n in lens))
+        bytes_ = 2.0 * 4 * T * H
+    elif name == "add_layernorm":
+        x, r, gm, bt = rnd(T, H), rnd(T, H), rnd(H), rnd(H)
+        fn = lambda: ops.add_layernorm(x, r, gm, bt, 1e-12)  # noqa: E731
+        bytes_ = 3.0 * T * H * 2
+    elif name == "pool_mean":
+        x = rnd(T, H)
+        cu_d = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), device="cuda", dtype=torch.int32)
+        idx = torch.arange(len(lens), device="cuda", dtype=torch.int32)
+        fn = lambda: ops.pool(x, cu_d, idx, "mean", True)  # noqa: E731
+        bytes_ = T * H * 2.0 + len(lens) * H * 4.0
+    else:
+        raise SystemExit(f"unknown kernel {name}")
+    for _ in range(max(args.warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    ops.check_status(st, name)
+    line = {"kernel": name, "ms_per_launch": ms, "tokens": T,
+            "tflops": flops / ms / 1e9 if flops else None, "algorithmic_gbs": bytes_ / ms / 1e6}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None,
+                    help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
+                         "add_layernorm | pool_mean")
+    args = ap.parse_args()
+    if args.kernel:
+        run_kernel(args)
+        return
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import numpy as np
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    ranks = Ranks(world, local_rank, backend="nccl")
+    barrier, max_over_ranks, sum_over_ranks = ranks.barrier, ranks.max, ranks.sum
+
+    import tei_b200
+    from oracle import generators as G
+
+    model_dir = ensure_model_dir(local_rank)
+    be = tei_b200.B200Backend(model_dir, "float16", "embedding", "mean", devices=[local_rank])
+    batch = G.batch_cfg2()
+    tokens = int(batch.cumulative_seq_lengths[-1])
+    lens = batch.lengths()
+    cfg = G.bert_config()
+
+    # ---------------------------------------------------------------- device-resident value
+    be.stage(batch, normalize=True)
+    for _ in range(args.warmup):
+        be.run_staged()
+    be.sync()
+    be.set_profiling(True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ms = be.run_staged_timed(args.steps)
+    clocks = sampler.stop()
+    barrier()
+    kt = be.kernel_times()
+    be.set_profiling(False)
+    launches_per_step = be.stats()["launches"] / args.steps
+    ms = max_over_ranks(ms)
+    total_tokens = sum_over_ranks(float(tokens)) * args.steps
+    value = total_tokens / (ms / 1e3)
+
+    # ---------------------------------------------------------------- end-to-end through embed
+    for _ in range(args.warmup):
+        be.embed(batch, normalize=True)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        be.embed(batch, normalize=True)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    st = be.stats()
+    e2e_s = max_over_ranks(e2e_s)
+    e2e_value = total_tokens / e2e_s
+
+    # ---------------------------------------------------------------- roofline of the GEMM kernel
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    gemm_flops_per_step = L * 2.0 * tokens * (4 * H * H + 2 * H * I)
+    attn_flops_per_step = L * 4.0 * H * float((lens.astype(np.float64) ** 2).sum())
+    peaks = {}
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peaks = json.loads(peaks_file.read_text())
+    peak_tf = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback 1.4 PFLOP/s sustained"
+    gemm_ms_per_step = kt["gemm"]["ms"] / args.steps
+    gemm_launches = kt["gemm"]["launches"] / args.steps
+    achieved = gemm_flops_per_step / (gemm_ms_per_step / 1e3) / 1e12 if gemm_ms_per_step > 0 else 0.0
+    attn_ms_per_step = kt["attention"]["ms"] / args.steps
+    roofline = {
+        "kernel": "gemm_tcgen05_kernel (dense layers: QKV, attention output, FFN up + GELU, FFN down)",
+        "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+        "frac": achieved / peak_tf if peak_tf else None, "peak_source": peak_src,
+        "traffic": None,
+        "flops_per_launch": gemm_flops_per_step / gemm_launches if gemm_launches else None,
+        "ms_per_launch": gemm_ms_per_step / gemm_launches if gemm_launches else None,
+        "launches_per_step": gemm_launches,
+        "per_class_ms_per_step": {k: v["ms"] / args.steps for k, v in kt.items()},
+        "attention_tflops": attn_flops_per_step / (attn_ms_per_step / 1e3) / 1e12 if attn_ms_per_step > 0 else None,
+        "step_tflops": (gemm_flops_per_step + attn_flops_per_step) / (ms / args.steps / 1e3) / 1e12,
+    }
+
+    line = {
+        "metric": "tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch_tokens": tokens, "parallelism": f"replicas x{world}",
+                   "l2": "no flush: every step streams >1 GB of activations and 218 MB of weights, far above the 126 MB L2"},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": st["h2d_bytes"],
+                "d2h_bytes_per_step": st["d2h_bytes"], "ms_per_step": 1e3 * e2e_s / args.steps},
+        "gpu_launches": int(round(launches_per_step * args.steps)),
+        "roofline": roofline, "clocks": clocks,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, cores, dt, sample_tokens = cpu_baseline(model_dir, 48)
+        line["cpu_baseline"] = {
+            "value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"first 48 of the 256 sequences ({sample_tokens} tokens, {dt:.1f} s), forwards of <=4 sequences "
+                      "padded to the chunk max, fp32 torch CPU restatement of the reference's Candle CPU path",
+        }
+    else:
+        line["cpu_baseline"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    be.close()
+    ranks.close()
+
+
+if __name__ == "__main__":
+    main()

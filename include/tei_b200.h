@@ -1,0 +1,140 @@
+/* C ABI of libtei_b200.so: a B200 (sm_100a) implementation of the `Backend` trait of Text
+ * Embeddings Inference (backends/core/src/lib.rs:37-48) for the BERT / RoBERTa / XLM-R,
+ * NomicBERT and Qwen3 model paths that backends/candle serves with flash_bert / flash_nomic /
+ * flash_qwen3.  A Rust shim (`text-embeddings-inference_b200/rust_shim`) binds these functions
+ * and implements `text_embeddings_backend_core::Backend` on top of them.
+ *
+ * Conventions
+ *   - Every function returns a status code: 0 ok, 1 START (-> BackendError::Start), 2 INFERENCE
+ *     (-> Inference), 3 UNHEALTHY (-> Unhealthy), 4 WEIGHTS_NOT_FOUND (-> WeightsNotFound),
+ *     5 TIMEOUT (a kernel's bounded wait ran out; map to Inference).  When `err` is not NULL a
+ *     NUL-terminated message is copied into it (at most err_cap bytes).
+ *   - All batch pointers are HOST pointers borrowed for the duration of the call
+ *     (`Batch`, backends/core/src/lib.rs:9-17); output buffers are caller-allocated host memory.
+ *   - A handle is used by one thread at a time, as the reference's single backend thread does
+ *     (backends/src/lib.rs:612-647).  Nothing throws or aborts across this boundary.
+ *   - The library owns all device memory: weights, a workspace that grows only when a larger
+ *     batch than ever before arrives, and pinned staging buffers.
+ */
+#ifndef TEI_B200_H_
+#define TEI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tei_b200 tei_b200_t;
+
+enum {
+  TEI_B200_OK = 0,
+  TEI_B200_ERR_START = 1,
+  TEI_B200_ERR_INFERENCE = 2,
+  TEI_B200_ERR_UNHEALTHY = 3,
+  TEI_B200_ERR_WEIGHTS_NOT_FOUND = 4,
+  TEI_B200_ERR_TIMEOUT = 5
+};
+
+/* model_type (ModelType, backends/core/src/lib.rs:50-54) */
+enum { TEI_B200_CLASSIFIER = 0, TEI_B200_EMBEDDING = 1 };
+/* pool (Pool, backends/core/src/lib.rs:56-70) */
+enum { TEI_B200_POOL_CLS = 0, TEI_B200_POOL_MEAN = 1, TEI_B200_POOL_SPLADE = 2, TEI_B200_POOL_LAST_TOKEN = 3 };
+
+/* Replaces CandleBackend::new(model_path, dtype, model_type, dense_paths)
+ * (backends/candle/src/lib.rs:163-168): reads config.json and the safetensors weights under
+ * model_dir, dispatches on `model_type` like lib.rs:282-577 and places one full replica on each
+ * listed CUDA device (devices == NULL or n_devices <= 0: device 0 only).  dtype: "float16" or
+ * "bfloat16".  With more than one device a packed batch is split at sequence boundaries
+ * across the replicas inside each call; no data crosses GPUs. */
+int tei_b200_create(const char* model_dir, const char* dtype, int model_type, int pool,
+                    const int* devices, int n_devices, tei_b200_t** out, char* err,
+                    size_t err_cap);
+
+void tei_b200_destroy(tei_b200_t* h);
+
+/* Backend::health (backends/core/src/lib.rs:38).  Cheap when the last call succeeded; after a
+ * failed call it runs a one-token forward, like the probe of backends/src/lib.rs:393-409. */
+int tei_b200_health(tei_b200_t* h);
+
+/* Backend::is_padded: always 0, the path is unpadded (flash_bert.rs:530-532). */
+int tei_b200_is_padded(const tei_b200_t* h);
+/* Backend::max_batch_size: -1 means None (backends/core/src/lib.rs:39-41). */
+int tei_b200_max_batch_size(const tei_b200_t* h);
+/* Width of a pooled embedding row (hidden size; vocabulary size for SPLADE). */
+int tei_b200_output_dim(const tei_b200_t* h);
+/* Width of a raw (per-token) embedding row. */
+int tei_b200_hidden_size(const tei_b200_t* h);
+/* Number of classes of a classifier (0 for embedding models). */
+int tei_b200_num_classes(const tei_b200_t* h);
+
+/* Backend::embed (backends/candle/src/lib.rs:656-709).
+ *   pooled_out [n_pooled, output_dim]: row i is the embedding of batch position pooled_idx[i]
+ *                                      (lib.rs:696-698);
+ *   raw_out    [sum of len(raw_idx[j]), hidden]: token rows of the raw_idx sequences, in
+ *                                      raw_idx order (lib.rs:700-706).
+ * normalize != 0 L2-normalises the pooled rows on the device (the router does it on the host,
+ * core/src/infer.rs:288-303; doing it twice is harmless). */
+int tei_b200_embed(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* token_type_ids,
+                   const uint32_t* position_ids, size_t n_tokens,
+                   const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                   const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx,
+                   size_t n_raw, int normalize, float* pooled_out, float* raw_out, char* err,
+                   size_t err_cap);
+
+/* Backend::predict (backends/candle/src/lib.rs:711-725): scores_out [n_seqs, num_classes],
+ * row i = raw logits of batch position i (sigmoid / softmax stay with the caller,
+ * core/src/infer.rs:458-480). */
+int tei_b200_predict(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* token_type_ids,
+                     const uint32_t* position_ids, size_t n_tokens,
+                     const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                     float* scores_out, char* err, size_t err_cap);
+
+/* The three phases of embed / predict, exposed separately so that a caller can keep a batch
+ * resident in HBM and time the forward alone.  No counterpart in the reference, whose forward
+ * always uploads its inputs (flash_bert.rs:376-383).
+ *   stage : validate, split across replicas, copy the batch to the device(s);
+ *   run   : enqueue one forward of the staged batch on every replica (asynchronous);
+ *   sync  : wait for all replicas and check their status words;
+ *   fetch : copy the results of the last run back (same layout as embed / predict). */
+int tei_b200_stage(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* token_type_ids,
+                   const uint32_t* position_ids, size_t n_tokens,
+                   const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                   const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx,
+                   size_t n_raw, int normalize, int predict, char* err, size_t err_cap);
+int tei_b200_run_staged(tei_b200_t* h, char* err, size_t err_cap);
+int tei_b200_sync(tei_b200_t* h, char* err, size_t err_cap);
+int tei_b200_fetch(tei_b200_t* h, float* pooled_out, float* raw_out, float* scores_out, char* err,
+                   size_t err_cap);
+
+/* Runs the staged forward `steps` times back to back on every replica and returns the device
+ * time of the whole sequence in milliseconds (CUDA events on the launching stream, max over
+ * replicas).  Synchronises before returning. */
+int tei_b200_run_staged_timed(tei_b200_t* h, int steps, double* device_ms, char* err,
+                              size_t err_cap);
+
+/* Per-kernel-class device timing.  While on, every kernel launch is bracketed by a pair of
+ * CUDA events on its stream; tei_b200_kernel_times returns, per class, the milliseconds and
+ * the launches accumulated since profiling was switched on (classes: 0 embedding, 1 dense
+ * layer GEMM, 2 attention, 3 LayerNorm / RMSNorm, 4 rotary, 5 pooling and heads).  Returns the
+ * number of classes written. */
+int tei_b200_set_profiling(tei_b200_t* h, int on);
+int tei_b200_kernel_times(const tei_b200_t* h, double* ms_out, double* launches_out, int n);
+
+/* Counters of the last call, summed / maxed over replicas.  out[0] device ms of the forward
+ * (max over replicas), [1] host-to-device bytes, [2] device-to-host bytes, [3] kernels
+ * launched, [4] tokens, [5] calls so far, [6] total device ms, [7] total tokens.  Returns the
+ * number of values written (at most n). */
+int tei_b200_stats(const tei_b200_t* h, double* out, int n);
+
+/* Host-only helper, no GPU needed: the replica a sequence of a packed batch is sent to when a
+ * handle has n_shards devices.  Cost of a sequence of length L: linear_cost * L +
+ * quadratic_cost * L * L, balanced longest-first.  shard_of_seq has n_seqs entries. */
+int tei_b200_plan_shards(const uint32_t* cumulative_seq_lengths, size_t n_seqs, int n_shards,
+                         double linear_cost, double quadratic_cost, int* shard_of_seq);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEI_B200_H_ */

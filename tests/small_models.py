@@ -1,0 +1,52 @@
+"""Small seeded model directories and batches shared by the tests and the golden-fixture script."""
+from oracle import generators as G
+
+
+def write_all(base):
+    dirs = {}
+    dirs["bert"] = G.write_model_dir(
+        base / "bert", G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+        seed=1, norm_jitter=0.1, std=0.05)
+    dirs["bert_prefixed"] = G.write_model_dir(
+        base / "bert_prefixed", G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+        seed=1, norm_jitter=0.1, std=0.05, prefix="bert.")
+    dirs["bert_cls3"] = G.write_model_dir(
+        base / "bert_cls3",
+        G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512,
+                      id2label={"0": "a", "1": "b", "2": "c"}),
+        seed=6, classifier="bert", norm_jitter=0.1, std=0.05, prefix="bert.")
+    dirs["xlmr"] = G.write_model_dir(
+        base / "xlmr",
+        G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=514, type_vocab=1,
+                      model_type="xlm-roberta", pad_token_id=1, id2label={"0": "LABEL_0"}),
+        seed=3, classifier="roberta", norm_jitter=0.1, std=0.05)
+    dirs["splade"] = G.write_model_dir(
+        base / "splade", G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1003, max_pos=512),
+        seed=7, splade=True, norm_jitter=0.1, std=0.05)
+    dirs["nomic"] = G.write_model_dir(
+        base / "nomic", G.nomic_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, n_positions=2048),
+        seed=4, norm_jitter=0.1, std=0.05)
+    dirs["qwen3"] = G.write_model_dir(
+        base / "qwen3",
+        G.qwen3_config(hidden=256, layers=3, heads=4, kv_heads=2, head_dim=128, inter=512, vocab=1000, max_pos=2048),
+        seed=5, norm_jitter=0.1, std=0.05)
+    return dirs
+
+
+LENS = [5, 1, 300, 77, 128, 129, 200]
+
+# name -> (model dir key, model_type, pool, batch kwargs)
+GOLDEN_CASES = {
+    "bert_mean": ("bert", "embedding", "mean", dict(seed=101, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "bert_cls": ("bert", "embedding", "cls", dict(seed=102, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "xlmr_scores": ("xlmr", "classifier", "cls", dict(seed=103, lens=LENS, lo=5, hi=1000, type_vocab=1, offset=2)),
+    "bert_cls3_scores": ("bert_cls3", "classifier", "cls", dict(seed=104, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "nomic_mean": ("nomic", "embedding", "mean", dict(seed=105, lens=LENS + [700], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "qwen3_last": ("qwen3", "embedding", "last_token", dict(seed=106, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
+}
+
+
+def golden_batch(kw):
+    return G.random_batch(kw["seed"], kw["lens"], kw["lo"], kw["hi"], type_vocab=kw["type_vocab"],
+                          position_offset=kw["offset"])

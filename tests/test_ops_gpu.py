@@ -1,0 +1,251 @@
+"""Kernel-level parity on the GPU, through the C ABI (include/tei_b200_ops.h).
+
+Reference for each op is plain fp32 torch on the same device.  Tolerances (absolute, on values
+of magnitude <= ~8): fp16 2e-2 for GEMM / norm outputs, 1e-2 for attention; bf16 8e-2 / 4e-2
+(bf16 has 8 bits of mantissa, one rounding of a value near 8 is 3e-2).  Integer bookkeeping
+(plans, gathers, CLS / last-token rows) is exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _gen(seed):
+    return torch.Generator(device="cuda").manual_seed(seed)
+
+
+def _close(got, ref, tol):
+    got, ref = got.float(), ref.float()
+    assert not torch.isnan(got).any()
+    err = (got - ref).abs().max().item()
+    assert err <= tol, f"max abs err {err} > {tol}"
+
+
+@pytest.mark.parametrize("M,N,K,act,bias,res,dtype", [
+    (128, 256, 64, "none", False, False, "f16"),      # one tile, one k-block
+    (128, 256, 768, "none", True, False, "f16"),      # pipeline wraps its 4 stages
+    (1, 768, 768, "none", True, False, "f16"),        # single row (health probe shape)
+    (300, 768, 768, "gelu", True, False, "f16"),      # M tail
+    (200, 1000, 512, "relu", True, False, "f16"),     # N tail
+    (77, 1003, 128, "relu_log1p", True, False, "f16"),  # N not a multiple of 8: scalar stores
+    (520, 1024, 768, "swiglu", False, False, "f16"),
+    (520, 512, 256, "swiglu", True, False, "bf16"),
+    (1000, 768, 3072, "none", True, True, "bf16"),
+    (700, 256, 256, "tanh", True, False, "f16"),
+    (20000, 2304, 768, "none", True, False, "f16"),   # many waves of the persistent loop
+])
+def test_linear(lib, M, N, K, act, bias, res, dtype):
+    from tei_b200 import ops
+    dt = DT[dtype]
+    g = _gen(M * 7 + N * 3 + K)
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dt)
+    b = (torch.randn(N, device="cuda", generator=g) * 0.1).to(dt) if bias else None
+    n_out = N // 2 if act == "swiglu" else N
+    r = (torch.randn(M, n_out, device="cuda", generator=g) * 0.5).to(dt) if res else None
+    ww, bb = w, b
+    if act == "swiglu":
+        ww = ops.interleave_swiglu(w[: N // 2], w[N // 2:])
+        bb = ops.interleave_swiglu(b[: N // 2], b[N // 2:]) if bias else None
+    out = ops.linear(a, ww, bb, r, act=act)
+    y = a.float() @ w.float().t()
+    if bias:
+        y = y + b.float()
+    if act == "gelu":
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    elif act == "relu":
+        y = torch.relu(y)
+    elif act == "tanh":
+        y = torch.tanh(y)
+    elif act == "relu_log1p":
+        y = torch.log1p(torch.relu(y))
+    elif act == "swiglu":
+        y = torch.nn.functional.silu(y[:, : N // 2]) * y[:, N // 2:]
+    if res:
+        y = y + r.float()
+    _close(out, y, 2e-2 if dtype == "f16" else 8e-2)
+
+
+def test_linear_is_deterministic_and_rejects_bad_shapes(lib):
+    from tei_b200 import ops
+    g = _gen(5)
+    a = torch.randn(1000, 768, device="cuda", generator=g).half()
+    w = (torch.randn(768, 768, device="cuda", generator=g) * 0.05).half()
+    o1 = ops.linear(a, w)
+    o2 = ops.linear(a, w)
+    assert torch.equal(o1, o2)
+    with pytest.raises(RuntimeError):
+        ops.linear(a[:, :100], w[:, :100])  # K not a multiple of 8
+    # NaN canary: rows beyond M must stay untouched
+    out = torch.full((1100, 768), float("nan"), device="cuda", dtype=torch.float16)
+    ops.linear(a, w, out=out[:1000])
+    assert torch.isnan(out[1000:]).all() and not torch.isnan(out[:1000]).any()
+
+
+def _ref_attention(q, k, v, cu, causal, scale, slopes=None):
+    T, nh, D = q.shape
+    nkv = k.shape[1]
+    out = torch.zeros(T, nh, D, device=q.device, dtype=torch.float32)
+    for s in range(len(cu) - 1):
+        a, b = cu[s], cu[s + 1]
+        L = b - a
+        qs = q[a:b].float().transpose(0, 1)
+        ks = k[a:b].float().transpose(0, 1).repeat_interleave(nh // nkv, dim=0)
+        vs = v[a:b].float().transpose(0, 1).repeat_interleave(nh // nkv, dim=0)
+        sc = qs @ ks.transpose(1, 2) * scale
+        if slopes is not None:
+            idx = torch.arange(L, device=q.device)
+            sc = sc - slopes.view(nh, 1, 1) * (idx.view(1, L, 1) - idx.view(1, 1, L)).abs()
+        if causal:
+            sc = sc.masked_fill(~torch.ones(L, L, device=q.device, dtype=torch.bool).tril(), float("-inf"))
+        out[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1)
+    return out.reshape(T, nh * D)
+
+
+@pytest.mark.parametrize("lens,nh,nkv,D,causal,alibi,dtype", [
+    ([1], 1, 1, 64, False, False, "f16"),
+    ([2, 15, 16, 17], 2, 2, 64, False, False, "f16"),
+    ([63, 64, 65], 2, 2, 64, False, False, "f16"),
+    ([127, 128, 129], 2, 2, 64, False, False, "f16"),
+    ([127, 128, 129], 2, 2, 64, True, False, "f16"),
+    ([5, 1, 300, 77, 128, 129, 512], 12, 12, 64, False, False, "f16"),
+    ([300, 17, 129], 4, 4, 64, True, False, "bf16"),
+    ([300, 40], 4, 2, 128, True, False, "bf16"),      # GQA, head_dim 128, causal
+    ([200, 130], 2, 2, 128, False, False, "f16"),
+    ([200, 130], 4, 4, 64, False, True, "f16"),        # ALiBi
+    ([1000], 4, 1, 128, True, False, "f16"),           # MQA, 8 query tiles
+])
+def test_attention(lib, lens, nh, nkv, D, causal, alibi, dtype):
+    from tei_b200 import ops
+    dt = DT[dtype]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = _gen(T + nh + D)
+    width = (nh + 2 * nkv) * D
+    # NaN canary rows after the batch: the kernel must never let them leak into real rows.
+    buf = torch.full((T + 64, width), float("nan"), device="cuda", dtype=dt)
+    buf[:T] = torch.randn(T, width, device="cuda", generator=g).to(dt)
+    qkv = buf[:T]
+    q = qkv[:, : nh * D].view(T, nh, D)
+    k = qkv[:, nh * D: (nh + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nh + nkv) * D:].view(T, nkv, D)
+    slopes = None
+    if alibi:
+        slopes = torch.tensor([2.0 ** (-(i + 1) * 8.0 / nh) for i in range(nh)], device="cuda")
+    scale = 1.0 / D ** 0.5
+    out = ops.attention(q, k, v, cu, causal=causal, scale=scale, alibi_slopes=slopes)
+    ref = _ref_attention(q, k, v, cu, causal, scale, slopes)
+    _close(out, ref, 1e-2 if dtype == "f16" else 4e-2)
+    out2 = ops.attention(q, k, v, cu, causal=causal, scale=scale, alibi_slopes=slopes)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_embedding_and_norms(lib, dtype):
+    from tei_b200 import ops
+    dt = DT[dtype]
+    tol = 2e-2 if dtype == "f16" else 8e-2
+    g = _gen(1)
+    T, V = 1000, 5000
+    for H in (128, 768, 1024, 2048, 4096):
+        word = (torch.randn(V, H, device="cuda", generator=g) * 0.05).to(dt)
+        typ = (torch.randn(2, H, device="cuda", generator=g) * 0.05).to(dt)
+        pos = (torch.randn(512, H, device="cuda", generator=g) * 0.05).to(dt)
+        gamma = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).to(dt)
+        beta = (0.1 * torch.randn(H, device="cuda", generator=g)).to(dt)
+        ids = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+        tids = torch.randint(0, 2, (T,), device="cuda", dtype=torch.int32)
+        pids = torch.randint(0, 512, (T,), device="cuda", dtype=torch.int32)
+        out = ops.embed_layernorm(ids, tids, pids, word, typ, pos, gamma, beta, 1e-12)
+        x = word[ids.long()].float() + typ[tids.long()].float() + pos[pids.long()].float()
+        _close(out, torch.nn.functional.layer_norm(x, (H,), gamma.float(), beta.float(), 1e-12), tol)
+        out = ops.embed_layernorm(ids, None, None, word, None, None, None, None, 0.0)
+        assert torch.equal(out, word[ids.long()])  # plain gather is exact
+
+        x = torch.randn(T, H, device="cuda", generator=g).to(dt)
+        r = torch.randn(T, H, device="cuda", generator=g).to(dt)
+        out = ops.add_layernorm(x, r, gamma, beta, 1e-12)
+        _close(out, torch.nn.functional.layer_norm(x.float() + r.float(), (H,), gamma.float(), beta.float(), 1e-12), tol)
+        rf = torch.randn(T, H, device="cuda", generator=g)
+        out, sm = ops.add_rmsnorm(x, rf, gamma, 1e-6)
+        s = x.float() + rf
+        _close(out, s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float(), tol)
+        assert torch.equal(sm, s)  # the fp32 running sum is exact
+        out, sm = ops.add_rmsnorm(x, None, gamma, 1e-6)
+        s = x.float()
+        _close(out, s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float(), tol)
+
+
+@pytest.mark.parametrize("nh,nkv,D,use_norm,dtype", [(12, 12, 64, False, "f16"), (16, 8, 128, True, "bf16"),
+                                                     (16, 8, 128, True, "f16")])
+def test_qk_norm_rope(lib, nh, nkv, D, use_norm, dtype):
+    from tei_b200 import ops
+    dt = DT[dtype]
+    g = _gen(2)
+    T = 333
+    qkv = torch.randn(T, (nh + 2 * nkv) * D, device="cuda", generator=g).to(dt)
+    q = qkv[:, : nh * D].view(T, nh, D)
+    k = qkv[:, nh * D: (nh + nkv) * D].view(T, nkv, D)
+    v0 = qkv[:, (nh + nkv) * D:].clone()
+    q0, k0 = q.float().clone(), k.float().clone()
+    posi = torch.randint(0, 2048, (T,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(2048, device="cuda").float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    qg = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dt) if use_norm else None
+    kg = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dt) if use_norm else None
+    ops.qk_norm_rope_(q, k, posi, cos, sin, qg, kg, 1e-6)
+
+    def ref(x, gamma):
+        if gamma is not None:
+            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+        c, s_ = cos[posi.long()][:, None, :], sin[posi.long()][:, None, :]
+        x1, x2 = x[..., : D // 2], x[..., D // 2:]
+        return torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_], dim=-1)
+    tol = 2e-2 if dtype == "f16" else 8e-2
+    _close(q.reshape(T, -1), ref(q0, qg).reshape(T, -1), tol)
+    _close(k.reshape(T, -1), ref(k0, kg).reshape(T, -1), tol)
+    assert torch.equal(qkv[:, (nh + nkv) * D:], v0)  # V untouched
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_pooling_gather_and_heads(lib, dtype):
+    from tei_b200 import ops
+    dt = DT[dtype]
+    g = _gen(3)
+    lens = [5, 1, 300, 77, 128, 129]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    x = torch.randn(cu[-1], 768, device="cuda", generator=g).to(dt)
+    cu_d = torch.tensor(cu, device="cuda", dtype=torch.int32)
+    idx = torch.tensor([0, 2, 3, 5, 1], device="cuda", dtype=torch.int32)
+    for mode in ("cls", "mean", "max", "last_token"):
+        for nrm in (False, True):
+            out = ops.pool(x, cu_d, idx, mode, nrm)
+            rows = []
+            for s in idx.tolist():
+                seg = x[cu[s]:cu[s + 1]].float()
+                rows.append({"cls": seg[0], "last_token": seg[-1], "mean": seg.mean(0),
+                             "max": seg.max(0).values}[mode])
+            ref = torch.stack(rows)
+            if nrm:
+                ref = ref / ref.norm(dim=-1, keepdim=True)
+                _close(out, ref, 1e-5)
+            elif mode in ("cls", "last_token", "max"):
+                assert torch.equal(out, ref)  # row selection is exact
+            else:
+                _close(out, ref, 1e-5)
+    ridx = torch.tensor([3, 4, 5, 100, 7], device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.gather_rows_f32(x, ridx), x[ridx.long()].float())
+    xin = torch.randn(37, 768, device="cuda", generator=g)
+    w = (torch.randn(5, 768, device="cuda", generator=g) * 0.05).to(dt)
+    b = (torch.randn(5, device="cuda", generator=g) * 0.05).to(dt)
+    _close(ops.head_linear(xin, w, b, "tanh"), torch.tanh(xin @ w.float().t() + b.float()), 1e-4)
+    _close(ops.head_linear(xin, w, None, "none"), xin @ w.float().t(), 1e-4)

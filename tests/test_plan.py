@@ -1,0 +1,51 @@
+"""Host-side planning exported by the library: attention work items and replica sharding.
+Integer work, so the checks are exact."""
+import numpy as np
+
+from oracle import generators as G
+
+
+def test_attention_plan_covers_every_query_tile_once(lib):
+    from tei_b200 import ops
+    lens = [int(x) for x in G.lengths_cfg2()]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    for causal in (False, True):
+        work = ops.attention_plan(cu, causal)
+        assert work.shape[0] == sum((n + 127) // 128 for n in lens)
+        seen = set()
+        for start, length, q0, _ in work.tolist():
+            s = int(np.searchsorted(cu, start, side="right") - 1)
+            assert cu[s] == start and lens[s] == length and q0 % 128 == 0 and q0 < length
+            assert (s, q0) not in seen
+            seen.add((s, q0))
+        # most expensive first
+        def cost(w):
+            kv_end = min(w[1], w[2] + 128) if causal else w[1]
+            return (kv_end + 127) // 128
+        costs = [cost(w) for w in work.tolist()]
+        assert costs == sorted(costs, reverse=True)
+
+
+def test_attention_plan_edge_cases(lib):
+    from tei_b200 import ops
+    assert ops.attention_plan([0, 1], False).tolist() == [[0, 1, 0, 0]]
+    assert ops.attention_plan([0, 128], False).tolist() == [[0, 128, 0, 0]]
+    w = ops.attention_plan([0, 129], True).tolist()
+    assert sorted(w) == [[0, 129, 0, 0], [0, 129, 128, 0]]
+
+
+def test_plan_shards_balances_and_is_deterministic(lib):
+    import tei_b200
+    lens = G.lengths_cfg5()
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    a, b = 880.8e6 / 28, 2.0 * 2048  # per-layer linear and causal-attention cost
+    for n in (1, 2, 4, 8):
+        shard = tei_b200.plan_shards(cu, n, a, b)
+        assert shard.min() >= 0 and shard.max() < n
+        cost = a * lens + b * lens.astype(np.float64) ** 2
+        loads = np.array([cost[shard == d].sum() for d in range(n)])
+        # longest-first greedy: the spread is bounded by the largest single item
+        assert loads.max() - loads.min() <= cost.max() + 1e-6
+        assert (tei_b200.plan_shards(cu, n, a, b) == shard).all()
+    one = tei_b200.plan_shards(cu, 1, a, b)
+    assert (one == 0).all()

@@ -137,4 +137,9 @@ int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int 
 int launch_head_linear(const float* in, const void* w, const void* b, float* out, int rows, int N,
                        int K, int act, int dtype, cudaStream_t stream);
 
+// Element-wise dtype conversion used at weight-load time.  src_kind: 0 fp32, 1 fp16, 2 bf16;
+// dst dtype: DT_F16 / DT_BF16, or 2 for fp32.
+int launch_convert(const void* src, int src_kind, void* dst, int dst_kind, size_t n,
+                   cudaStream_t stream);
+
 }  // namespace tei

@@ -1,0 +1,1040 @@
+#include "model.h"
+
+#include "kernels.h"
+#include "plan.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace tei {
+namespace {
+
+#define TEI_CUDA(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess) {                                                               \
+      throw TeiError(ERR_INFERENCE, std::string(#expr) + ": " + cudaGetErrorString(e__));   \
+    }                                                                                       \
+  } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Brackets one kernel launch with a pair of events when per-class timing is switched on.
+#define LAUNCH(cls, call, what) \
+  do {                          \
+    prof_begin();               \
+    launch((call), what);       \
+    prof_end(cls);              \
+  } while (0)
+
+int parse_act(const std::string& s) {
+  // layers/linear.rs:5-17: every GELU spelling means the tanh approximation.
+  if (s == "gelu" || s == "gelu_new" || s == "gelu_pytorch_tanh") return ACT_GELU;
+  if (s == "relu") return ACT_RELU;
+  if (s == "tanh") return ACT_TANH;
+  if (s == "swiglu") return ACT_SWIGLU;
+  if (s == "silu") return -2;
+  return -1;
+}
+
+int64_t need_int(const Json& c, const char* key) {
+  if (!c[key].is_number()) throw TeiError(ERR_START, std::string("config.json: missing field `") + key + "`");
+  return c[key].as_int();
+}
+double need_double(const Json& c, const char* key) {
+  if (!c[key].is_number()) throw TeiError(ERR_START, std::string("config.json: missing field `") + key + "`");
+  return c[key].as_double();
+}
+std::string need_string(const Json& c, const char* key) {
+  if (!c[key].is_string()) throw TeiError(ERR_START, std::string("config.json: missing field `") + key + "`");
+  return c[key].as_string();
+}
+bool need_bool(const Json& c, const char* key) {
+  if (!c[key].is_bool()) throw TeiError(ERR_START, std::string("config.json: missing field `") + key + "`");
+  return c[key].as_bool();
+}
+
+}  // namespace
+
+ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dtype) {
+  ModelSpec s;
+  s.dtype = dtype;
+  s.model_type = need_string(c, "model_type");
+  s.classifier = (model_type_flag == 0);
+  s.pool = s.classifier ? POOL_CLS : pool;  // classifiers always pool CLS (flash_bert.rs:247-249)
+  const std::string& mt = s.model_type;
+  if (mt == "bert" || mt == "roberta" || mt == "xlm-roberta" || mt == "camembert") {
+    s.arch = ARCH_BERT;
+    s.roberta = mt != "bert";
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "hidden_size"));
+    s.layers = static_cast<int>(need_int(c, "num_hidden_layers"));
+    s.heads = static_cast<int>(need_int(c, "num_attention_heads"));
+    s.inter = static_cast<int>(need_int(c, "intermediate_size"));
+    s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
+    s.type_vocab = static_cast<int>(need_int(c, "type_vocab_size"));
+    s.eps = static_cast<float>(need_double(c, "layer_norm_eps"));
+    if (c.get_string("position_embedding_type", "absolute") != "absolute") {
+      throw TeiError(ERR_START, "FlashBert only supports absolute position embeddings");
+    }
+    s.act = parse_act(need_string(c, "hidden_act"));
+    if (s.act != ACT_GELU && s.act != ACT_RELU && s.act != ACT_TANH) {
+      throw TeiError(ERR_START, "unsupported hidden_act for a BERT feed-forward");
+    }
+    if (s.heads <= 0 || s.hidden % s.heads != 0) throw TeiError(ERR_START, "hidden_size is not a multiple of num_attention_heads");
+    s.kv_heads = s.heads;
+    s.head_dim = s.hidden / s.heads;
+    s.qkv_bias = s.out_bias = s.fc1_bias = s.fc2_bias = true;
+    if (s.classifier) {
+      if (!c["id2label"].is_object()) throw TeiError(ERR_START, "`id2label` must be set for classifier models");
+      s.n_classes = static_cast<int>(c["id2label"].size());
+    }
+  } else if (mt == "nomic_bert") {
+    s.arch = ARCH_NOMIC;
+    if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for Nomic");
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Nomic");
+    const bool prenorm = need_bool(c, "prenorm");
+    const double frac = need_double(c, "rotary_emb_fraction");
+    const bool interleaved = need_bool(c, "rotary_emb_interleaved");
+    s.type_vocab = static_cast<int>(need_int(c, "type_vocab_size"));
+    if (prenorm || frac != 1.0 || interleaved || s.type_vocab <= 0) {
+      throw TeiError(ERR_START, "config is not supported");  // NomicConfig::valid(), nomic.rs:49-54
+    }
+    if (c.get_int("num_experts", 0) > 1 || c.get_int("moe_every_n_layers", 0) > 0) {
+      throw TeiError(ERR_START, "NomicBERT mixture-of-experts checkpoints are outside this backend");
+    }
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "n_embd"));
+    s.layers = static_cast<int>(need_int(c, "n_layer"));
+    s.heads = static_cast<int>(need_int(c, "n_head"));
+    s.inter = static_cast<int>(need_int(c, "n_inner"));
+    s.eps = static_cast<float>(need_double(c, "layer_norm_epsilon"));
+    s.qkv_bias = s.out_bias = need_bool(c, "qkv_proj_bias");
+    s.fc1_bias = need_bool(c, "mlp_fc1_bias");
+    s.fc2_bias = need_bool(c, "mlp_fc2_bias");
+    const int act = parse_act(need_string(c, "activation_function"));
+    if (act == ACT_SWIGLU) {
+      s.gated = true;
+      s.act = ACT_SWIGLU;
+    } else if (act == ACT_GELU || act == ACT_RELU) {
+      s.act = act;
+    } else {
+      throw TeiError(ERR_START, "unsupported activation_function for NomicBERT");
+    }
+    if (s.heads <= 0 || s.hidden % s.heads != 0) throw TeiError(ERR_START, "n_embd is not a multiple of n_head");
+    s.kv_heads = s.heads;
+    s.head_dim = s.hidden / s.heads;
+    s.rope = true;
+    s.rope_theta = static_cast<float>(need_double(c, "rotary_emb_base"));
+    s.rope_table_len = static_cast<int>(need_int(c, "n_positions"));
+    s.max_pos = s.rope_table_len;
+    s.rope_scaling_factor = static_cast<float>(c.get_double("rotary_scaling_factor", 0.0));
+    s.nomic_max_pos = static_cast<int>(
+        c.get_int("max_position_embeddings", c.get_int("max_trained_positions", 2048)));
+  } else if (mt == "qwen3") {
+    s.arch = ARCH_QWEN3;
+    if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for Qwen3");
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Qwen3");
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "hidden_size"));
+    s.inter = static_cast<int>(need_int(c, "intermediate_size"));
+    s.layers = static_cast<int>(need_int(c, "num_hidden_layers"));
+    s.heads = static_cast<int>(need_int(c, "num_attention_heads"));
+    s.kv_heads = static_cast<int>(need_int(c, "num_key_value_heads"));
+    s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
+    s.eps = static_cast<float>(need_double(c, "rms_norm_eps"));
+    if (c.get_bool("use_sliding_window", false)) throw TeiError(ERR_START, "sliding window is not supported");
+    if (need_bool(c, "attention_bias")) throw TeiError(ERR_START, "attention_bias = true is not supported");
+    if (parse_act(need_string(c, "hidden_act")) != -2) throw TeiError(ERR_START, "Qwen3 expects hidden_act = silu");
+    s.head_dim = static_cast<int>(c.get_int("head_dim", s.heads > 0 ? s.hidden / s.heads : 0));
+    if (c["rope_theta"].is_number()) {
+      s.rope_theta = static_cast<float>(c["rope_theta"].as_double());
+    } else if (c["rope_parameters"]["rope_theta"].is_number()) {
+      s.rope_theta = static_cast<float>(c["rope_parameters"]["rope_theta"].as_double());
+    } else {
+      throw TeiError(ERR_START, "Neither `rope_theta` nor `rope_parameters.rope_theta` are defined in the `config.json`");
+    }
+    s.gated = true;
+    s.act = ACT_SWIGLU;
+    s.rope = true;
+    s.rope_table_len = s.max_pos;
+    s.causal = !c.get_bool("use_bidirectional_attention", false);
+    s.type_vocab = 0;
+  } else {
+    throw TeiError(ERR_START, "model_type `" + mt + "` is not served by this backend");
+  }
+  if (s.head_dim != 64 && s.head_dim != 128) {
+    throw TeiError(ERR_START, "head_dim must be 64 or 128 for the sm_100a attention kernel");
+  }
+  if (s.kv_heads <= 0 || s.heads % s.kv_heads != 0) throw TeiError(ERR_START, "heads must be a multiple of kv heads");
+  if (s.hidden % 8 != 0 || s.inter % 8 != 0 || s.hidden > 4096) {
+    throw TeiError(ERR_START, "hidden / intermediate sizes must be multiples of 8 and hidden <= 4096");
+  }
+  if (s.gated && s.inter % 128 != 0) throw TeiError(ERR_START, "gated feed-forward needs intermediate_size % 128 == 0");
+  if (s.pool == POOL_SPLADE && s.arch != ARCH_BERT) throw TeiError(ERR_START, "splade needs a BERT-family masked-LM checkpoint");
+  return s;
+}
+
+// ------------------------------------------------------------------------------ Replica
+Replica::Replica(int device, const ModelSpec& spec, const SafeTensors& st)
+    : device_(device), spec_(spec) {
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) throw TeiError(ERR_START, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_);
+  if (major != 10) throw TeiError(ERR_START, "this backend needs an sm_100 (B200) device");
+  TEI_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  TEI_CUDA(cudaEventCreate(&ev_start_));
+  TEI_CUDA(cudaEventCreate(&ev_stop_));
+  try {
+    load_weights(st);
+    if (spec_.rope) build_rope_tables();
+    TEI_CUDA(cudaStreamSynchronize(stream_));
+    if (load_stage_) {
+      cudaFree(load_stage_);
+      load_stage_ = nullptr;
+      load_stage_bytes_ = 0;
+    }
+  } catch (const TeiError&) {
+    throw;
+  } catch (const std::exception& ex) {
+    const std::string m = ex.what();
+    throw TeiError(m.rfind("weights not found", 0) == 0 ? ERR_WEIGHTS_NOT_FOUND : ERR_START, m);
+  }
+}
+
+Replica::~Replica() {
+  cudaSetDevice(device_);
+  if (stream_) cudaStreamSynchronize(stream_);
+  for (void* p : allocs_) cudaFree(p);
+  if (load_stage_) cudaFree(load_stage_);
+  if (arena_) cudaFree(arena_);
+  if (d_ints_) cudaFree(d_ints_);
+  if (h_ints_) cudaFreeHost(h_ints_);
+  if (d_out_) cudaFree(d_out_);
+  if (h_out_) cudaFreeHost(h_out_);
+  for (auto& e : ev_pool_) cudaEventDestroy(e);
+  if (ev_start_) cudaEventDestroy(ev_start_);
+  if (ev_stop_) cudaEventDestroy(ev_stop_);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+int Replica::output_dim() const {
+  if (spec_.pool == POOL_SPLADE) return spec_.vocab;
+  if (projection_) return projection_dim_;
+  return spec_.hidden;
+}
+
+void* Replica::dev_alloc(size_t bytes) {
+  void* p = nullptr;
+  TEI_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 16)));
+  allocs_.push_back(p);
+  return p;
+}
+
+void Replica::set_profiling(bool on) {
+  TEI_CUDA(cudaSetDevice(device_));
+  if (on && ev_pool_.empty()) {
+    ev_pool_.resize(2 * kMaxPairs);
+    for (auto& e : ev_pool_) TEI_CUDA(cudaEventCreate(&e));
+    pair_cls_.resize(kMaxPairs);
+  }
+  profiling_ = on;
+  n_pairs_ = 0;
+  for (int i = 0; i < KC_COUNT; ++i) {
+    class_ms_[i] = 0.0;
+    class_launches_[i] = 0.0;
+  }
+}
+
+void Replica::prof_begin() {
+  if (profiling_ && n_pairs_ < kMaxPairs) cudaEventRecord(ev_pool_[2 * n_pairs_], stream_);
+}
+
+void Replica::prof_end(int cls) {
+  if (profiling_ && n_pairs_ < kMaxPairs) {
+    cudaEventRecord(ev_pool_[2 * n_pairs_ + 1], stream_);
+    pair_cls_[n_pairs_] = cls;
+    ++n_pairs_;
+  }
+}
+
+// Called after a stream synchronise: folds the recorded event pairs into the per-class totals.
+void Replica::prof_drain() {
+  for (int i = 0; i < n_pairs_; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ev_pool_[2 * i], ev_pool_[2 * i + 1]) == cudaSuccess) {
+      class_ms_[pair_cls_[i]] += ms;
+      class_launches_[pair_cls_[i]] += 1.0;
+    }
+  }
+  n_pairs_ = 0;
+}
+
+int Replica::kernel_times(double* ms, double* launches, int n) const {
+  const int m = n < KC_COUNT ? n : KC_COUNT;
+  for (int i = 0; i < m; ++i) {
+    ms[i] = class_ms_[i];
+    launches[i] = class_launches_[i];
+  }
+  return m;
+}
+
+double Replica::timed_runs(int steps) {
+  TEI_CUDA(cudaSetDevice(device_));
+  cudaEvent_t a, b;
+  TEI_CUDA(cudaEventCreate(&a));
+  TEI_CUDA(cudaEventCreate(&b));
+  TEI_CUDA(cudaStreamSynchronize(stream_));
+  TEI_CUDA(cudaEventRecord(a, stream_));
+  int launches = 0;
+  for (int i = 0; i < steps; ++i) {
+    run();
+    launches += launches_;
+  }
+  TEI_CUDA(cudaEventRecord(b, stream_));
+  sync_and_check();
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, a, b);
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  stats_.last_launches = launches;
+  return ms;
+}
+
+void Replica::launch(int rc, const char* what) {
+  if (rc != 0) {
+    throw TeiError(ERR_INFERENCE, std::string(what) + " launch failed with code " + std::to_string(rc));
+  }
+  ++launches_;
+}
+
+void Replica::upload(void* dst, size_t dst_elem_off, const StTensor& src, int dst_kind) {
+  if (dst_kind < 0) dst_kind = spec_.dtype;
+  int src_kind;
+  switch (src.dtype) {
+    case StDType::F32: src_kind = 0; break;
+    case StDType::F16: src_kind = 1; break;
+    case StDType::BF16: src_kind = 2; break;
+    default: throw TeiError(ERR_START, "unsupported tensor dtype in safetensors (need F32, F16 or BF16)");
+  }
+  if (src.nbytes > load_stage_bytes_) {
+    TEI_CUDA(cudaStreamSynchronize(stream_));
+    if (load_stage_) cudaFree(load_stage_);
+    load_stage_bytes_ = align_up(src.nbytes, 1 << 20);
+    TEI_CUDA(cudaMalloc(&load_stage_, load_stage_bytes_));
+  }
+  TEI_CUDA(cudaMemcpyAsync(load_stage_, src.data, src.nbytes, cudaMemcpyHostToDevice, stream_));
+  const size_t es = dst_kind == 2 ? 4 : 2;
+  int rc = launch_convert(load_stage_, src_kind, static_cast<uint8_t*>(dst) + dst_elem_off * es,
+                          dst_kind, static_cast<size_t>(src.numel()), stream_);
+  if (rc) throw TeiError(ERR_START, "dtype conversion kernel failed");
+}
+
+void* Replica::upload_new(const StTensor& src, int dst_kind) {
+  const size_t es = (dst_kind == 2) ? 4 : 2;
+  void* p = dev_alloc(static_cast<size_t>(src.numel()) * es);
+  upload(p, 0, src, dst_kind);
+  return p;
+}
+
+// dst rows: [gate 0..127 | up 0..127 | gate 128..255 | up 128..255 | ...] (the layout the SwiGLU
+// epilogue of the GEMM expects).  Works for matrices [I, K] and for bias vectors [I].
+void Replica::upload_rows_interleaved(void* dst, const StTensor& gate, const StTensor& up) {
+  if (gate.shape != up.shape || gate.shape.empty() || gate.shape[0] % 128 != 0) {
+    throw TeiError(ERR_START, "gate / up shapes do not allow the 128-row interleave");
+  }
+  const size_t rows = static_cast<size_t>(gate.shape[0]);
+  const size_t cols = static_cast<size_t>(gate.numel()) / rows;
+  void* tg = nullptr;
+  void* tu = nullptr;
+  TEI_CUDA(cudaMalloc(&tg, rows * cols * 2));
+  TEI_CUDA(cudaMalloc(&tu, rows * cols * 2));
+  try {
+    upload(tg, 0, gate);
+    upload(tu, 0, up);
+    const size_t blk = 128 * cols * 2;
+    TEI_CUDA(cudaMemcpy2DAsync(dst, 2 * blk, tg, blk, blk, rows / 128, cudaMemcpyDeviceToDevice, stream_));
+    TEI_CUDA(cudaMemcpy2DAsync(static_cast<uint8_t*>(dst) + blk, 2 * blk, tu, blk, blk, rows / 128,
+                               cudaMemcpyDeviceToDevice, stream_));
+    TEI_CUDA(cudaStreamSynchronize(stream_));
+  } catch (...) {
+    cudaFree(tg);
+    cudaFree(tu);
+    throw;
+  }
+  cudaFree(tg);
+  cudaFree(tu);
+}
+
+namespace {
+
+struct Names {
+  const SafeTensors& st;
+  std::string prefix;
+  bool has(const std::string& n) const { return st.contains(prefix + n); }
+  const StTensor& get(const std::string& n) const {
+    if (!st.contains(prefix + n)) throw TeiError(ERR_START, "cannot find tensor " + prefix + n);
+    return st.get(prefix + n);
+  }
+  // LayerNorm::load accepts weight|gamma and bias|beta (layers/layer_norm.rs:93-98).
+  const StTensor& ln_w(const std::string& p) const { return has(p + ".weight") ? get(p + ".weight") : get(p + ".gamma"); }
+  const StTensor& ln_b(const std::string& p) const { return has(p + ".bias") ? get(p + ".bias") : get(p + ".beta"); }
+};
+
+void expect_shape(const StTensor& t, std::initializer_list<int64_t> shape, const std::string& name) {
+  if (t.shape != std::vector<int64_t>(shape)) {
+    throw TeiError(ERR_START, "unexpected shape for tensor " + name);
+  }
+}
+
+}  // namespace
+
+void Replica::load_weights(const SafeTensors& st) {
+  layers_.resize(spec_.layers);
+  switch (spec_.arch) {
+    case ARCH_BERT: load_bert(st); break;
+    case ARCH_NOMIC: load_nomic(st); break;
+    case ARCH_QWEN3: load_qwen3(st); break;
+  }
+}
+
+void Replica::load_bert(const SafeTensors& st) {
+  const ModelSpec& s = spec_;
+  const int H = s.hidden, I = s.inter;
+  // flash_bert.rs:264-279 (bert) and :331-356 (roberta family): bare names, then known prefixes.
+  std::vector<std::string> cand = s.roberta ? std::vector<std::string>{"", "roberta.", "xlm-roberta.", "camembert."}
+                                            : std::vector<std::string>{"", "bert."};
+  std::string prefix;
+  bool found = false;
+  for (const auto& p : cand) {
+    if (st.contains(p + "embeddings.word_embeddings.weight")) {
+      prefix = p;
+      found = true;
+      break;
+    }
+  }
+  if (!found) throw TeiError(ERR_START, "cannot find tensor embeddings.word_embeddings.weight");
+  Names n{st, prefix};
+  Names root{st, ""};
+  expect_shape(n.get("embeddings.word_embeddings.weight"), {s.vocab, H}, "embeddings.word_embeddings.weight");
+  expect_shape(n.get("embeddings.position_embeddings.weight"), {s.max_pos, H}, "embeddings.position_embeddings.weight");
+  expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
+  word_ = upload_new(n.get("embeddings.word_embeddings.weight"));
+  pos_tab_ = upload_new(n.get("embeddings.position_embeddings.weight"));
+  type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
+  emb_g_ = upload_new(n.ln_w("embeddings.LayerNorm"));
+  emb_b_ = upload_new(n.ln_b("embeddings.LayerNorm"));
+  for (int i = 0; i < s.layers; ++i) {
+    LayerW& L = layers_[i];
+    const std::string p = "encoder.layer." + std::to_string(i) + ".";
+    // q, k, v fused by concatenating rows (flash_bert.rs:43-44).
+    L.wqkv = dev_alloc(static_cast<size_t>(3) * H * H * 2);
+    L.bqkv = dev_alloc(static_cast<size_t>(3) * H * 2);
+    const char* qkv[3] = {"query", "key", "value"};
+    for (int j = 0; j < 3; ++j) {
+      const StTensor& w = n.get(p + "attention.self." + qkv[j] + ".weight");
+      expect_shape(w, {H, H}, p + "attention.self." + qkv[j] + ".weight");
+      upload(L.wqkv, static_cast<size_t>(j) * H * H, w);
+      upload(L.bqkv, static_cast<size_t>(j) * H, n.get(p + "attention.self." + qkv[j] + ".bias"));
+    }
+    expect_shape(n.get(p + "attention.output.dense.weight"), {H, H}, p + "attention.output.dense.weight");
+    L.wo = upload_new(n.get(p + "attention.output.dense.weight"));
+    L.bo = upload_new(n.get(p + "attention.output.dense.bias"));
+    L.ln1_g = upload_new(n.ln_w(p + "attention.output.LayerNorm"));
+    L.ln1_b = upload_new(n.ln_b(p + "attention.output.LayerNorm"));
+    expect_shape(n.get(p + "intermediate.dense.weight"), {I, H}, p + "intermediate.dense.weight");
+    L.w1 = upload_new(n.get(p + "intermediate.dense.weight"));
+    L.b1 = upload_new(n.get(p + "intermediate.dense.bias"));
+    expect_shape(n.get(p + "output.dense.weight"), {H, I}, p + "output.dense.weight");
+    L.w2 = upload_new(n.get(p + "output.dense.weight"));
+    L.b2 = upload_new(n.get(p + "output.dense.bias"));
+    L.ln2_g = upload_new(n.ln_w(p + "output.LayerNorm"));
+    L.ln2_b = upload_new(n.ln_b(p + "output.LayerNorm"));
+  }
+  if (s.classifier) {
+    if (s.roberta) {  // RobertaClassificationHead, bert.rs:434-444
+      expect_shape(root.get("classifier.dense.weight"), {H, H}, "classifier.dense.weight");
+      expect_shape(root.get("classifier.out_proj.weight"), {s.n_classes, H}, "classifier.out_proj.weight");
+      cls_dense_w_ = upload_new(root.get("classifier.dense.weight"));
+      cls_dense_b_ = upload_new(root.get("classifier.dense.bias"));
+      cls_out_w_ = upload_new(root.get("classifier.out_proj.weight"));
+      cls_out_b_ = upload_new(root.get("classifier.out_proj.bias"));
+    } else {  // BertClassificationHead, bert.rs:381-395
+      if (root.has("bert.pooler.dense.weight")) {
+        cls_dense_w_ = upload_new(root.get("bert.pooler.dense.weight"));
+        cls_dense_b_ = upload_new(root.get("bert.pooler.dense.bias"));
+      }
+      expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
+      cls_out_w_ = upload_new(root.get("classifier.weight"));
+      cls_out_b_ = upload_new(root.get("classifier.bias"));
+    }
+  }
+  if (s.pool == POOL_SPLADE) {
+    if (s.roberta) {  // bert.rs:519-541
+      sp_dense_w_ = upload_new(root.get("lm_head.dense.weight"));
+      sp_dense_b_ = upload_new(root.get("lm_head.dense.bias"));
+      sp_ln_g_ = upload_new(root.ln_w("lm_head.layer_norm"));
+      sp_ln_b_ = upload_new(root.ln_b("lm_head.layer_norm"));
+      sp_dec_w_ = upload_new(root.get("lm_head.decoder.weight"));
+      sp_dec_b_ = upload_new(root.get("lm_head.bias"));
+      sp_act_ = ACT_GELU;
+    } else {  // bert.rs:477-509
+      sp_dense_w_ = upload_new(root.get("cls.predictions.transform.dense.weight"));
+      sp_dense_b_ = upload_new(root.get("cls.predictions.transform.dense.bias"));
+      sp_ln_g_ = upload_new(root.ln_w("cls.predictions.transform.LayerNorm"));
+      sp_ln_b_ = upload_new(root.ln_b("cls.predictions.transform.LayerNorm"));
+      sp_dec_w_ = root.has("cls.predictions.decoder.weight")
+                      ? upload_new(root.get("cls.predictions.decoder.weight"))
+                      : upload_new(root.get("bert.embeddings.word_embeddings.weight"));
+      sp_dec_b_ = upload_new(root.get("cls.predictions.bias"));
+      sp_act_ = s.act;
+    }
+  }
+}
+
+void Replica::load_nomic(const SafeTensors& st) {
+  const ModelSpec& s = spec_;
+  const int H = s.hidden, I = s.inter;
+  Names n{st, ""};
+  expect_shape(n.get("embeddings.word_embeddings.weight"), {s.vocab, H}, "embeddings.word_embeddings.weight");
+  word_ = upload_new(n.get("embeddings.word_embeddings.weight"));
+  expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
+  type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
+  emb_g_ = upload_new(n.ln_w("emb_ln"));
+  emb_b_ = upload_new(n.ln_b("emb_ln"));
+  for (int i = 0; i < s.layers; ++i) {
+    LayerW& L = layers_[i];
+    const std::string p = "encoder.layers." + std::to_string(i) + ".";
+    expect_shape(n.get(p + "attn.Wqkv.weight"), {3 * H, H}, p + "attn.Wqkv.weight");
+    L.wqkv = upload_new(n.get(p + "attn.Wqkv.weight"));
+    if (s.qkv_bias) L.bqkv = upload_new(n.get(p + "attn.Wqkv.bias"));
+    expect_shape(n.get(p + "attn.out_proj.weight"), {H, H}, p + "attn.out_proj.weight");
+    L.wo = upload_new(n.get(p + "attn.out_proj.weight"));
+    if (s.out_bias) L.bo = upload_new(n.get(p + "attn.out_proj.bias"));
+    if (s.gated) {
+      // fc1 = cat[fc12; fc11] and swiglu = silu(first half) * second half (nomic.rs:109-121):
+      // fc12 is the gate, fc11 the up projection.
+      expect_shape(n.get(p + "mlp.fc11.weight"), {I, H}, p + "mlp.fc11.weight");
+      expect_shape(n.get(p + "mlp.fc12.weight"), {I, H}, p + "mlp.fc12.weight");
+      L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+      upload_rows_interleaved(L.w1, n.get(p + "mlp.fc12.weight"), n.get(p + "mlp.fc11.weight"));
+      if (s.fc1_bias) {
+        L.b1 = dev_alloc(static_cast<size_t>(2) * I * 2);
+        upload_rows_interleaved(L.b1, n.get(p + "mlp.fc12.bias"), n.get(p + "mlp.fc11.bias"));
+      }
+    } else {
+      expect_shape(n.get(p + "mlp.fc1.weight"), {I, H}, p + "mlp.fc1.weight");
+      L.w1 = upload_new(n.get(p + "mlp.fc1.weight"));
+      if (s.fc1_bias) L.b1 = upload_new(n.get(p + "mlp.fc1.bias"));
+    }
+    expect_shape(n.get(p + "mlp.fc2.weight"), {H, I}, p + "mlp.fc2.weight");
+    L.w2 = upload_new(n.get(p + "mlp.fc2.weight"));
+    if (s.fc2_bias) L.b2 = upload_new(n.get(p + "mlp.fc2.bias"));
+    L.ln1_g = upload_new(n.ln_w(p + "norm1"));
+    L.ln1_b = upload_new(n.ln_b(p + "norm1"));
+    L.ln2_g = upload_new(n.ln_w(p + "norm2"));
+    L.ln2_b = upload_new(n.ln_b(p + "norm2"));
+  }
+}
+
+void Replica::load_qwen3(const SafeTensors& st) {
+  const ModelSpec& s = spec_;
+  const int H = s.hidden, I = s.inter, Q = s.q_width(), KV = s.kv_width();
+  // Optional `model.` prefix (flash_qwen3.rs:322-326).
+  Names n{st, st.contains("model.embed_tokens.weight") ? "model." : ""};
+  expect_shape(n.get("embed_tokens.weight"), {s.vocab, H}, "embed_tokens.weight");
+  word_ = upload_new(n.get("embed_tokens.weight"));
+  for (int i = 0; i < s.layers; ++i) {
+    LayerW& L = layers_[i];
+    const std::string p = "layers." + std::to_string(i) + ".";
+    // The reference runs q, k and v as three GEMMs (flash_qwen3.rs:119-121); their weights are
+    // stacked here so that one GEMM produces the [T, Q + 2 KV] activation.
+    expect_shape(n.get(p + "self_attn.q_proj.weight"), {Q, H}, p + "self_attn.q_proj.weight");
+    expect_shape(n.get(p + "self_attn.k_proj.weight"), {KV, H}, p + "self_attn.k_proj.weight");
+    expect_shape(n.get(p + "self_attn.v_proj.weight"), {KV, H}, p + "self_attn.v_proj.weight");
+    L.wqkv = dev_alloc(static_cast<size_t>(Q + 2 * KV) * H * 2);
+    upload(L.wqkv, 0, n.get(p + "self_attn.q_proj.weight"));
+    upload(L.wqkv, static_cast<size_t>(Q) * H, n.get(p + "self_attn.k_proj.weight"));
+    upload(L.wqkv, static_cast<size_t>(Q + KV) * H, n.get(p + "self_attn.v_proj.weight"));
+    expect_shape(n.get(p + "self_attn.o_proj.weight"), {H, Q}, p + "self_attn.o_proj.weight");
+    L.wo = upload_new(n.get(p + "self_attn.o_proj.weight"));
+    L.q_norm = upload_new(n.get(p + "self_attn.q_norm.weight"));
+    L.k_norm = upload_new(n.get(p + "self_attn.k_norm.weight"));
+    expect_shape(n.get(p + "mlp.gate_proj.weight"), {I, H}, p + "mlp.gate_proj.weight");
+    expect_shape(n.get(p + "mlp.up_proj.weight"), {I, H}, p + "mlp.up_proj.weight");
+    L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+    upload_rows_interleaved(L.w1, n.get(p + "mlp.gate_proj.weight"), n.get(p + "mlp.up_proj.weight"));
+    expect_shape(n.get(p + "mlp.down_proj.weight"), {H, I}, p + "mlp.down_proj.weight");
+    L.w2 = upload_new(n.get(p + "mlp.down_proj.weight"));
+    L.ln1_g = upload_new(n.get(p + "input_layernorm.weight"));
+    L.ln2_g = upload_new(n.get(p + "post_attention_layernorm.weight"));
+  }
+  final_norm_ = upload_new(n.get("norm.weight"));
+  if (st.contains("linear.weight")) {  // flash_qwen3.rs:344-357
+    const StTensor& w = st.get("linear.weight");
+    if (w.shape.size() != 2 || w.shape[1] != H) throw TeiError(ERR_START, "unexpected shape for tensor linear.weight");
+    if (w.shape[0] % 8 != 0 || w.shape[0] > H) throw TeiError(ERR_START, "projection width must be a multiple of 8 and at most hidden_size");
+    projection_ = upload_new(w);
+    projection_dim_ = static_cast<int>(w.shape[0]);
+  }
+}
+
+void Replica::build_rope_tables() {
+  // layers/rotary.rs:29-116: inv_freq_i = 1 / base^(i / dim) for even i, angle = pos * inv_freq,
+  // all in f32.  The tables stay in fp32 on the device.
+  const int dh = spec_.head_dim, half = dh / 2, len = spec_.rope_table_len;
+  auto fill = [&](float base, float** d_cos, float** d_sin) {
+    std::vector<float> inv(half);
+    for (int i = 0; i < half; ++i) inv[i] = 1.0f / std::pow(base, static_cast<float>(2 * i) / static_cast<float>(dh));
+    std::vector<float> c(static_cast<size_t>(len) * half), s(static_cast<size_t>(len) * half);
+    for (int p = 0; p < len; ++p) {
+      for (int i = 0; i < half; ++i) {
+        const float a = static_cast<float>(p) * inv[i];
+        c[static_cast<size_t>(p) * half + i] = std::cos(a);
+        s[static_cast<size_t>(p) * half + i] = std::sin(a);
+      }
+    }
+    *d_cos = static_cast<float*>(dev_alloc(c.size() * 4));
+    *d_sin = static_cast<float*>(dev_alloc(s.size() * 4));
+    TEI_CUDA(cudaMemcpy(*d_cos, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
+    TEI_CUDA(cudaMemcpy(*d_sin, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
+  };
+  fill(spec_.rope_theta, &cos_, &sin_);
+  if (spec_.arch == ARCH_NOMIC && spec_.rope_scaling_factor > 0.f) {
+    // flash_nomic.rs:244-258, including its integer exponent: powi((dim / (dim - 2)) as i32).
+    const float sf = spec_.rope_scaling_factor;
+    const float inner = spec_.rope_theta * ((sf * static_cast<float>(spec_.rope_table_len) /
+                                             static_cast<float>(spec_.nomic_max_pos)) - (sf - 1.0f));
+    const int expo = static_cast<int>(static_cast<float>(dh) / (static_cast<float>(dh) - 2.0f));
+    float nb = 1.0f;
+    for (int i = 0; i < expo; ++i) nb *= inner;
+    fill(nb, &cos_scaled_, &sin_scaled_);
+  }
+}
+
+// ------------------------------------------------------------------------------ workspace
+void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t n_pooled,
+                               size_t raw_rows) {
+  const ModelSpec& s = spec_;
+  // integer inputs
+  const size_t ints_need = 3 * tokens + (seqs + 1) + 2 * seqs + raw_rows + 4 * n_work + 64;
+  if (ints_need > ints_cap_) {
+    TEI_CUDA(cudaStreamSynchronize(stream_));
+    if (d_ints_) cudaFree(d_ints_);
+    if (h_ints_) cudaFreeHost(h_ints_);
+    d_ints_ = nullptr;
+    h_ints_ = nullptr;
+    ints_cap_ = ints_need + ints_need / 4;
+    TEI_CUDA(cudaMalloc(&d_ints_, ints_cap_ * 4));
+    TEI_CUDA(cudaMallocHost(&h_ints_, ints_cap_ * 4));
+  }
+  // outputs (+ head scratch after them)
+  const size_t D = static_cast<size_t>(output_dim());
+  const size_t Dpad = align_up(D, 8);
+  const size_t out_need = 64 + n_pooled * Dpad + raw_rows * Dpad +
+                          seqs * static_cast<size_t>(std::max(s.n_classes, 1)) +
+                          2 * seqs * static_cast<size_t>(s.hidden) + 64;
+  if (out_need > out_cap_floats_) {
+    TEI_CUDA(cudaStreamSynchronize(stream_));
+    if (d_out_) cudaFree(d_out_);
+    if (h_out_) cudaFreeHost(h_out_);
+    d_out_ = nullptr;
+    h_out_ = nullptr;
+    out_cap_floats_ = out_need + out_need / 4;
+    TEI_CUDA(cudaMalloc(&d_out_, out_cap_floats_ * 4));
+    TEI_CUDA(cudaMallocHost(&h_out_, out_cap_floats_ * 4));
+  }
+  if (tokens <= cap_tokens_) return;
+  TEI_CUDA(cudaStreamSynchronize(stream_));
+  if (arena_) cudaFree(arena_);
+  arena_ = nullptr;
+  const size_t cap = align_up(tokens, 256);
+  const size_t H = s.hidden;
+  const size_t sz_h = align_up(cap * H * 2, 1024);
+  const size_t sz_qkv = align_up(cap * static_cast<size_t>(s.qkv_width()) * 2, 1024);
+  const size_t sz_attn = align_up(cap * static_cast<size_t>(s.q_width()) * 2, 1024);
+  const size_t sz_ffn = align_up(cap * static_cast<size_t>(s.inter) * 2, 1024);
+  const size_t sz_res = s.arch == ARCH_QWEN3 ? align_up(cap * H * 4, 1024) : 0;
+  const size_t vpad = align_up(static_cast<size_t>(s.vocab), 8);
+  const size_t sz_spl = s.pool == POOL_SPLADE ? align_up(cap * vpad * 2, 1024) : 0;
+  const size_t total = 3 * sz_h + sz_qkv + sz_attn + sz_ffn + sz_res + sz_spl;
+  TEI_CUDA(cudaMalloc(&arena_, total));
+  arena_bytes_ = total;
+  uint8_t* p = static_cast<uint8_t*>(arena_);
+  x_ = p; p += sz_h;
+  x1_ = p; p += sz_h;
+  tmp_ = p; p += sz_h;
+  qkv_ = p; p += sz_qkv;
+  attn_ = p; p += sz_attn;
+  ffn_ = p; p += sz_ffn;
+  resid_ = sz_res ? reinterpret_cast<float*>(p) : nullptr; p += sz_res;
+  splade_ = sz_spl ? p : nullptr; p += sz_spl;
+  if (sz_spl) TEI_CUDA(cudaMemsetAsync(splade_, 0, sz_spl, stream_));
+  cap_tokens_ = cap;
+}
+
+// ------------------------------------------------------------------------------ stage
+void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
+  TEI_CUDA(cudaSetDevice(device_));
+  const ModelSpec& s = spec_;
+  if (b.n_seqs == 0 || b.n_tokens == 0) throw TeiError(ERR_INFERENCE, "empty batch");
+  if (!b.input_ids || !b.cu_seqlens || !b.position_ids) throw TeiError(ERR_INFERENCE, "null batch pointer");
+  if (b.n_tokens > 0x7fffffffu / 8) throw TeiError(ERR_INFERENCE, "batch too large");
+  if (predict && !s.classifier) throw TeiError(ERR_INFERENCE, "`predict` is not implemented for this model");
+  if (b.cu_seqlens[0] != 0 || b.cu_seqlens[b.n_seqs] != b.n_tokens) {
+    throw TeiError(ERR_INFERENCE, "cumulative_seq_lengths must start at 0 and end at the token count");
+  }
+  uint32_t max_len = 0;
+  for (size_t i = 0; i < b.n_seqs; ++i) {
+    if (b.cu_seqlens[i + 1] <= b.cu_seqlens[i]) {
+      throw TeiError(ERR_INFERENCE, "cumulative_seq_lengths must be strictly increasing");
+    }
+    max_len = std::max(max_len, b.cu_seqlens[i + 1] - b.cu_seqlens[i]);
+  }
+  const uint32_t pos_limit = static_cast<uint32_t>(s.arch == ARCH_BERT ? s.max_pos : s.rope_table_len);
+  const bool use_types = s.arch != ARCH_QWEN3;
+  if (use_types && !b.token_type_ids) throw TeiError(ERR_INFERENCE, "null token_type_ids");
+  for (size_t t = 0; t < b.n_tokens; ++t) {
+    if (b.input_ids[t] >= static_cast<uint32_t>(s.vocab)) throw TeiError(ERR_INFERENCE, "input id out of the vocabulary");
+    if (b.position_ids[t] >= pos_limit) throw TeiError(ERR_INFERENCE, "position id beyond the position table");
+    if (use_types && b.token_type_ids[t] >= static_cast<uint32_t>(s.type_vocab)) {
+      throw TeiError(ERR_INFERENCE, "token type id out of range");
+    }
+  }
+  size_t n_pooled = predict ? 0 : b.n_pooled;
+  size_t n_raw = predict ? 0 : b.n_raw;
+  for (size_t i = 0; i < n_pooled; ++i) {
+    if (b.pooled_indices[i] >= b.n_seqs) throw TeiError(ERR_INFERENCE, "pooled index out of range");
+  }
+  size_t raw_rows = 0;
+  for (size_t i = 0; i < n_raw; ++i) {
+    if (b.raw_indices[i] >= b.n_seqs) throw TeiError(ERR_INFERENCE, "raw index out of range");
+    raw_rows += b.cu_seqlens[b.raw_indices[i] + 1] - b.cu_seqlens[b.raw_indices[i]];
+  }
+  if (s.pool == POOL_SPLADE && n_raw > 0) throw TeiError(ERR_INFERENCE, "raw embeddings are not available with splade pooling");
+
+  std::vector<int> cu_i(b.n_seqs + 1);
+  for (size_t i = 0; i <= b.n_seqs; ++i) cu_i[i] = static_cast<int>(b.cu_seqlens[i]);
+  const size_t n_work = static_cast<size_t>(count_attention_items(cu_i.data(), static_cast<int>(b.n_seqs)));
+  ensure_workspace(b.n_tokens, b.n_seqs, n_work, n_pooled, raw_rows);
+
+  T_ = b.n_tokens;
+  B_ = b.n_seqs;
+  n_work_ = n_work;
+  n_pooled_ = n_pooled;
+  n_raw_rows_ = raw_rows;
+  max_length_ = max_len;
+  predict_ = predict;
+  normalize_ = normalize;
+
+  // One pinned block, one copy: ids | types | pos | cu | pooled idx | all idx | raw rows | work.
+  int32_t* h = h_ints_;
+  size_t off = 0;
+  auto put_u32 = [&](const uint32_t* src, size_t n) {
+    size_t o = off;
+    if (src) std::memcpy(h + off, src, n * 4);
+    else std::memset(h + off, 0, n * 4);
+    off += n;
+    return o;
+  };
+  const size_t o_ids = put_u32(b.input_ids, T_);
+  const size_t o_types = put_u32(use_types ? b.token_type_ids : nullptr, T_);
+  const size_t o_pos = put_u32(b.position_ids, T_);
+  const size_t o_cu = put_u32(b.cu_seqlens, B_ + 1);
+  const size_t o_pidx = put_u32(n_pooled ? b.pooled_indices : nullptr, n_pooled);
+  const size_t o_all = off;
+  for (size_t i = 0; i < B_; ++i) h[off++] = static_cast<int32_t>(i);
+  const size_t o_raw = off;
+  for (size_t i = 0; i < n_raw; ++i) {
+    const uint32_t sidx = b.raw_indices[i];
+    for (uint32_t r = b.cu_seqlens[sidx]; r < b.cu_seqlens[sidx + 1]; ++r) h[off++] = static_cast<int32_t>(r);
+  }
+  off = align_up(off, 4);
+  const size_t o_work = off;
+  const int n_planned = plan_attention(cu_i.data(), static_cast<int>(B_), s.causal ? 1 : 0, h + off,
+                                       static_cast<int>(n_work));
+  if (static_cast<size_t>(n_planned) != n_work) throw TeiError(ERR_INFERENCE, "attention planning mismatch");
+  off += 4 * n_work;
+  TEI_CUDA(cudaMemcpyAsync(d_ints_, h_ints_, off * 4, cudaMemcpyHostToDevice, stream_));
+  stats_.last_h2d_bytes = static_cast<double>(off * 4);
+  d_ids_ = d_ints_ + o_ids;
+  d_types_ = d_ints_ + o_types;
+  d_pos_ = d_ints_ + o_pos;
+  d_cu_ = d_ints_ + o_cu;
+  d_pooled_idx_ = d_ints_ + o_pidx;
+  d_all_idx_ = d_ints_ + o_all;
+  d_raw_rows_ = d_ints_ + o_raw;
+  d_work_ = d_ints_ + o_work;
+
+  // Output block: [0,64) status word | pooled | raw | scores || scratch (not copied back).
+  const size_t D = static_cast<size_t>(output_dim());
+  const size_t Dpad = align_up(D, 8);
+  size_t oo = 64;
+  d_pooled_ = d_out_ + oo; oo += n_pooled * Dpad;
+  d_raw_ = d_out_ + oo; oo += raw_rows * D;
+  d_scores_ = d_out_ + oo; oo += predict ? B_ * static_cast<size_t>(s.n_classes) : 0;
+  out_floats_ = oo;
+  oo = align_up(oo, 8);
+  d_cls_ = d_out_ + oo; oo += B_ * s.hidden;
+  d_head_tmp_ = d_out_ + oo;
+  TEI_CUDA(cudaMemsetAsync(d_out_, 0, 256, stream_));
+}
+
+// ------------------------------------------------------------------------------ forward
+void Replica::run() {
+  TEI_CUDA(cudaSetDevice(device_));
+  launches_ = 0;
+  TEI_CUDA(cudaEventRecord(ev_start_, stream_));
+  switch (spec_.arch) {
+    case ARCH_BERT: forward_bert(); break;
+    case ARCH_NOMIC: forward_nomic(); break;
+    case ARCH_QWEN3: forward_qwen3(); break;
+  }
+  pool_and_heads();
+  TEI_CUDA(cudaEventRecord(ev_stop_, stream_));
+  stats_.last_launches = launches_;
+  stats_.last_tokens = static_cast<double>(T_);
+}
+
+namespace {
+GemmArgs gemm_args(const void* a, const void* w, const void* bias, void* out, int M, int N, int K,
+                   int lda, int ldo, int act, int dtype, int* status) {
+  GemmArgs g;
+  g.a = a; g.w = w; g.bias = bias; g.residual = nullptr; g.out = out;
+  g.M = M; g.N = N; g.K = K; g.lda = lda; g.ldo = ldo; g.ldr = 0;
+  g.act = act; g.dtype = dtype; g.status = status;
+  return g;
+}
+}  // namespace
+
+void Replica::forward_bert() {
+  const ModelSpec& s = spec_;
+  const int T = static_cast<int>(T_), H = s.hidden, I = s.inter;
+  int* status = reinterpret_cast<int*>(d_out_);
+  EmbedArgs e;
+  e.ids = d_ids_; e.type_ids = d_types_; e.pos_ids = d_pos_;
+  e.word = word_; e.type_tab = type_tab_; e.pos_tab = pos_tab_;
+  e.gamma = emb_g_; e.beta = emb_b_; e.out = x_; e.T = T; e.H = H; e.eps = s.eps; e.dtype = s.dtype;
+  LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
+  uint8_t* qkv = static_cast<uint8_t*>(qkv_);
+  for (int i = 0; i < s.layers; ++i) {
+    const LayerW& L = layers_[i];
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, 3 * H, H, H, 3 * H, ACT_NONE, s.dtype, status), stream_), "qkv projection");
+    AttnArgs a;
+    a.q = qkv; a.k = qkv + static_cast<size_t>(H) * 2; a.v = qkv + static_cast<size_t>(2 * H) * 2;
+    a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
+    a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
+    a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
+    a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
+    a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
+    NormArgs n1;
+    n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
+    n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
+    LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "attention LayerNorm");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
+    NormArgs n2 = n1;
+    n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
+    LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "output LayerNorm");
+  }
+}
+
+void Replica::forward_nomic() {
+  const ModelSpec& s = spec_;
+  const int T = static_cast<int>(T_), H = s.hidden, I = s.inter;
+  int* status = reinterpret_cast<int*>(d_out_);
+  EmbedArgs e;
+  e.ids = d_ids_; e.type_ids = d_types_; e.pos_ids = nullptr;
+  e.word = word_; e.type_tab = type_tab_; e.pos_tab = nullptr;
+  e.gamma = emb_g_; e.beta = emb_b_; e.out = x_; e.T = T; e.H = H; e.eps = s.eps; e.dtype = s.dtype;
+  LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
+  // flash_nomic.rs:288-306: the NTK-scaled table is used only when the batch is longer than the
+  // trained context.
+  const bool scaled = cos_scaled_ && max_length_ > static_cast<uint32_t>(s.nomic_max_pos);
+  uint8_t* qkv = static_cast<uint8_t*>(qkv_);
+  for (int i = 0; i < s.layers; ++i) {
+    const LayerW& L = layers_[i];
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, 3 * H, H, H, 3 * H, ACT_NONE, s.dtype, status), stream_), "qkv projection");
+    RopeArgs r;
+    r.q = qkv; r.k = qkv + static_cast<size_t>(H) * 2; r.pos_ids = d_pos_;
+    r.cos_tab = scaled ? cos_scaled_ : cos_; r.sin_tab = scaled ? sin_scaled_ : sin_;
+    r.q_gamma = nullptr; r.k_gamma = nullptr; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
+    r.head_dim = s.head_dim; r.ld_q = 3 * H; r.ld_k = 3 * H; r.eps = 0.f; r.dtype = s.dtype;
+    LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "rotary embedding");
+    AttnArgs a;
+    a.q = qkv; a.k = qkv + static_cast<size_t>(H) * 2; a.v = qkv + static_cast<size_t>(2 * H) * 2;
+    a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
+    a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
+    a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
+    a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
+    a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
+    NormArgs n1;
+    n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
+    n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
+    LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "norm1");
+    if (s.gated) {
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gated fc1");
+    } else {
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
+    }
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
+    NormArgs n2 = n1;
+    n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
+    LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "norm2");
+  }
+}
+
+void Replica::forward_qwen3() {
+  const ModelSpec& s = spec_;
+  const int T = static_cast<int>(T_), H = s.hidden, I = s.inter, Q = s.q_width(), KV = s.kv_width();
+  const int W = Q + 2 * KV;
+  int* status = reinterpret_cast<int*>(d_out_);
+  EmbedArgs e;
+  e.ids = d_ids_; e.type_ids = nullptr; e.pos_ids = nullptr;
+  e.word = word_; e.type_tab = nullptr; e.pos_tab = nullptr;
+  e.gamma = nullptr; e.beta = nullptr; e.out = tmp_; e.T = T; e.H = H; e.eps = 0.f; e.dtype = s.dtype;
+  LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
+  uint8_t* qkv = static_cast<uint8_t*>(qkv_);
+  // h (the branch output waiting to be added) lives in tmp_; the fp32 running sum in resid_.
+  for (int i = 0; i < s.layers; ++i) {
+    const LayerW& L = layers_[i];
+    NormArgs n1;
+    n1.x = tmp_; n1.residual = (i == 0) ? nullptr : resid_; n1.gamma = L.ln1_g; n1.beta = nullptr;
+    n1.out = x_; n1.sum_out = resid_; n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 1; n1.dtype = s.dtype;
+    LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "input RMSNorm");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, nullptr, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status), stream_), "qkv projection");
+    RopeArgs r;
+    r.q = qkv; r.k = qkv + static_cast<size_t>(Q) * 2; r.pos_ids = d_pos_; r.cos_tab = cos_; r.sin_tab = sin_;
+    r.q_gamma = L.q_norm; r.k_gamma = L.k_norm; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
+    r.head_dim = s.head_dim; r.ld_q = W; r.ld_k = W; r.eps = s.eps; r.dtype = s.dtype;
+    LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "q/k RMSNorm + rotary embedding");
+    AttnArgs a;
+    a.q = qkv; a.k = qkv + static_cast<size_t>(Q) * 2; a.v = qkv + static_cast<size_t>(Q + KV) * 2;
+    a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
+    a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
+    a.ld_q = a.ld_k = a.ld_v = W; a.ld_o = Q; a.causal = s.causal ? 1 : 0;
+    a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
+    a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, nullptr, tmp_, T, H, Q, Q, H, ACT_NONE, s.dtype, status), stream_), "o projection");
+    NormArgs n2 = n1;
+    n2.x = tmp_; n2.residual = resid_; n2.gamma = L.ln2_g; n2.out = x1_; n2.sum_out = resid_;
+    LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "post-attention RMSNorm");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, nullptr, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gate/up projection");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, nullptr, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "down projection");
+  }
+  NormArgs nf;
+  nf.x = tmp_; nf.residual = resid_; nf.gamma = final_norm_; nf.beta = nullptr; nf.out = x_; nf.sum_out = resid_;
+  nf.T = T; nf.H = H; nf.eps = s.eps; nf.rms = 1; nf.dtype = s.dtype;
+  LAUNCH(KC_NORM, launch_add_norm(nf, stream_), "final RMSNorm");
+  if (projection_) {
+    // Optional `linear.weight` projection applied to every token row (flash_qwen3.rs:430-435).
+    if (projection_dim_ > H) throw TeiError(ERR_INFERENCE, "projection wider than the hidden size is not supported");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, projection_, nullptr, x1_, T, projection_dim_, H, H, projection_dim_, ACT_NONE, s.dtype, status), stream_), "projection");
+    std::swap(x_, x1_);
+  }
+}
+
+void Replica::pool_and_heads() {
+  const ModelSpec& s = spec_;
+  const int T = static_cast<int>(T_), H = s.hidden;
+  int* status = reinterpret_cast<int*>(d_out_);
+  const int D = output_dim();
+  if (predict_) {
+    PoolArgs p;
+    p.x = x_; p.cu_seqlens = d_cu_; p.seq_index = d_all_idx_; p.out = d_cls_;
+    p.n_out = static_cast<int>(B_); p.H = H; p.mode = POOL_CLS; p.normalize = 0; p.dtype = s.dtype;
+    LAUNCH(KC_POOL, launch_pool(p, stream_), "CLS pooling");
+    const float* head_in = d_cls_;
+    if (cls_dense_w_) {  // dense + tanh (RobertaClassificationHead / BERT pooler, bert.rs:405-465)
+      LAUNCH(KC_POOL, launch_head_linear(d_cls_, cls_dense_w_, cls_dense_b_, d_head_tmp_, static_cast<int>(B_), H, H, ACT_TANH, s.dtype, stream_), "classifier dense");
+      head_in = d_head_tmp_;
+    }
+    LAUNCH(KC_POOL, launch_head_linear(head_in, cls_out_w_, cls_out_b_, d_scores_, static_cast<int>(B_), s.n_classes, H, ACT_NONE, s.dtype, stream_), "classifier output");
+    return;
+  }
+  if (n_pooled_ > 0) {
+    PoolArgs p;
+    p.cu_seqlens = d_cu_; p.seq_index = d_pooled_idx_; p.out = d_pooled_;
+    p.n_out = static_cast<int>(n_pooled_); p.dtype = s.dtype;
+    if (s.pool == POOL_SPLADE) {
+      // BertSpladeHead (bert.rs:551-558): dense + act -> LayerNorm -> decoder + ReLU -> log(1 + x),
+      // then the per-sequence maximum (flash_bert.rs:464-490).
+      const int V = s.vocab, Vpad = static_cast<int>(align_up(V, 8));
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, sp_dense_w_, sp_dense_b_, tmp_, T, H, H, H, H, sp_act_, s.dtype, status), stream_), "splade transform");
+      NormArgs n;
+      n.x = tmp_; n.residual = nullptr; n.gamma = sp_ln_g_; n.beta = sp_ln_b_; n.out = x1_; n.sum_out = nullptr;
+      n.T = T; n.H = H; n.eps = s.eps; n.rms = 0; n.dtype = s.dtype;
+      LAUNCH(KC_NORM, launch_add_norm(n, stream_), "splade LayerNorm");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, sp_dec_w_, sp_dec_b_, splade_, T, V, H, H, Vpad, ACT_RELU_LOG1P, s.dtype, status), stream_), "splade decoder");
+      p.x = splade_; p.H = Vpad; p.mode = POOL_SPLADE; p.normalize = 0;
+    } else {
+      p.x = x_; p.H = D; p.mode = s.pool; p.normalize = normalize_ ? 1 : 0;
+    }
+    LAUNCH(KC_POOL, launch_pool(p, stream_), "pooling");
+  }
+  if (n_raw_rows_ > 0) {
+    LAUNCH(KC_POOL, launch_gather_rows_f32(x_, d_raw_rows_, d_raw_, static_cast<int>(n_raw_rows_), D, s.dtype, stream_), "raw rows");
+  }
+}
+
+// ------------------------------------------------------------------------------ fetch
+void Replica::sync_and_check() {
+  TEI_CUDA(cudaSetDevice(device_));
+  int status = 0;
+  TEI_CUDA(cudaMemcpyAsync(h_out_, d_out_, 4, cudaMemcpyDeviceToHost, stream_));
+  TEI_CUDA(cudaStreamSynchronize(stream_));
+  prof_drain();
+  std::memcpy(&status, h_out_, 4);
+  if (status != 0) {
+    throw TeiError(ERR_TIMEOUT, "a kernel's bounded wait ran out (device status " + std::to_string(status) + ")");
+  }
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, ev_start_, ev_stop_) == cudaSuccess) {
+    stats_.last_gpu_ms = ms;
+  }
+}
+
+void Replica::fetch(float* pooled_out, float* raw_out, float* scores_out) {
+  TEI_CUDA(cudaSetDevice(device_));
+  TEI_CUDA(cudaMemcpyAsync(h_out_, d_out_, out_floats_ * 4, cudaMemcpyDeviceToHost, stream_));
+  TEI_CUDA(cudaStreamSynchronize(stream_));
+  prof_drain();
+  stats_.last_d2h_bytes = static_cast<double>(out_floats_ * 4);
+  int status = 0;
+  std::memcpy(&status, h_out_, 4);
+  if (status != 0) {
+    throw TeiError(ERR_TIMEOUT, "a kernel's bounded wait ran out (device status " + std::to_string(status) + ")");
+  }
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, ev_start_, ev_stop_) == cudaSuccess) {
+    stats_.last_gpu_ms = ms;
+    stats_.total_gpu_ms += ms;
+  }
+  stats_.total_tokens += static_cast<double>(T_);
+  stats_.calls += 1.0;
+  const size_t D = static_cast<size_t>(output_dim());
+  const size_t Dpad = align_up(D, 8);
+  const float* hp = h_out_ + (d_pooled_ - d_out_);
+  if (n_pooled_ && pooled_out) {
+    if (D == Dpad) {
+      std::memcpy(pooled_out, hp, n_pooled_ * D * 4);
+    } else {
+      for (size_t i = 0; i < n_pooled_; ++i) std::memcpy(pooled_out + i * D, hp + i * Dpad, D * 4);
+    }
+  }
+  if (n_raw_rows_ && raw_out) {
+    std::memcpy(raw_out, h_out_ + (d_raw_ - d_out_), n_raw_rows_ * D * 4);
+  }
+  if (predict_ && scores_out) {
+    std::memcpy(scores_out, h_out_ + (d_scores_ - d_out_), B_ * static_cast<size_t>(spec_.n_classes) * 4);
+  }
+}
+
+}  // namespace tei

@@ -158,9 +158,9 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
 //            not pile up over the decoder's layers.
 template <class T, int MAXC, bool RMS>
 __global__ void __launch_bounds__(256)
-add_norm_kernel(const T* __restrict__ x, const void* __restrict__ residual,
-                const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out,
-                float* __restrict__ sum_out, int T_, int H, float eps) {
+add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restrict__ gamma,
+                const T* __restrict__ beta, T* __restrict__ out, float* sum_out, int T_, int H,
+                float eps) {  // residual and sum_out may be the same buffer: no __restrict__
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T_) return;
@@ -376,7 +376,31 @@ head_linear_kernel(const float* __restrict__ in, const T* __restrict__ w, const 
   }
 }
 
+template <class S, class D>
+__global__ void __launch_bounds__(256) convert_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v;
+    if constexpr (sizeof(S) == 4) v = src[i];
+    else v = ldf<S>(src[i]);
+    if constexpr (sizeof(D) == 4) dst[i] = v;
+    else dst[i] = stf<D>(v);
+  }
+}
+
 inline int last_error() { return static_cast<int>(cudaGetLastError()); }
+
+template <class S>
+int convert_from(const void* src, void* dst, int dst_kind, size_t n, cudaStream_t st) {
+  const size_t want = (n + 255) / 256;
+  const unsigned grid = static_cast<unsigned>(want < 4096 ? (want ? want : 1) : 4096);
+  const S* s = reinterpret_cast<const S*>(src);
+  if (dst_kind == DT_F16) convert_kernel<S, __half><<<grid, 256, 0, st>>>(s, reinterpret_cast<__half*>(dst), n);
+  else if (dst_kind == DT_BF16) convert_kernel<S, __nv_bfloat16><<<grid, 256, 0, st>>>(s, reinterpret_cast<__nv_bfloat16*>(dst), n);
+  else if (dst_kind == 2) convert_kernel<S, float><<<grid, 256, 0, st>>>(s, reinterpret_cast<float*>(dst), n);
+  else return static_cast<int>(cudaErrorInvalidValue);
+  return last_error();
+}
 
 template <class T>
 int embed_typed(const EmbedArgs& e, cudaStream_t st) {
@@ -488,6 +512,15 @@ int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int 
         reinterpret_cast<const __nv_bfloat16*>(x), row_index, out, n_rows, H);
   }
   return last_error();
+}
+
+int launch_convert(const void* src, int src_kind, void* dst, int dst_kind, size_t n,
+                   cudaStream_t st) {
+  if (n == 0) return 0;
+  if (src_kind == 0) return convert_from<float>(src, dst, dst_kind, n, st);
+  if (src_kind == 1) return convert_from<__half>(src, dst, dst_kind, n, st);
+  if (src_kind == 2) return convert_from<__nv_bfloat16>(src, dst, dst_kind, n, st);
+  return static_cast<int>(cudaErrorInvalidValue);
 }
 
 int launch_head_linear(const float* in, const void* w, const void* b, float* out, int rows, int N,

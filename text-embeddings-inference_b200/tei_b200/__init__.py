@@ -1,0 +1,3 @@
+"""Host-side binding of libtei_b200.so: the `Backend` mirror (`backend`), the kernel-level
+wrappers used by tests and the benchmark (`ops`) and the ctypes loader (`_lib`)."""
+from .backend import B200Backend, BackendError, Batch, Embedding, plan_shards  # noqa: F401

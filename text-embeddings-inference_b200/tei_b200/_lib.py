@@ -30,6 +30,9 @@ _OPS_PROTOTYPES = {
     "tei_b200_op_head_linear": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
 }
 
+_BATCH = [POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t,
+          c_uint32]
+
 _BACKEND_PROTOTYPES = {
     "tei_b200_create": (
         c_int,
@@ -40,28 +43,32 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_is_padded": (c_int, [c_void_p]),
     "tei_b200_max_batch_size": (c_int, [c_void_p]),
     "tei_b200_output_dim": (c_int, [c_void_p]),
-    "tei_b200_num_classes": (c_int, [c_void_p]),
     "tei_b200_hidden_size": (c_int, [c_void_p]),
+    "tei_b200_num_classes": (c_int, [c_void_p]),
     "tei_b200_embed": (
         c_int,
-        [c_void_p, POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t,
-         POINTER(c_uint32), c_size_t, c_uint32, POINTER(c_uint32), c_size_t, POINTER(c_uint32),
-         c_size_t, c_int, POINTER(c_float), POINTER(c_float), c_char_p, c_size_t],
+        [c_void_p] + _BATCH + [POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int,
+                               POINTER(c_float), POINTER(c_float), c_char_p, c_size_t],
     ),
-    "tei_b200_predict": (
+    "tei_b200_predict": (c_int, [c_void_p] + _BATCH + [POINTER(c_float), c_char_p, c_size_t]),
+    "tei_b200_stage": (
         c_int,
-        [c_void_p, POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t,
-         POINTER(c_uint32), c_size_t, c_uint32, POINTER(c_float), c_char_p, c_size_t],
+        [c_void_p] + _BATCH + [POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int, c_int,
+                               c_char_p, c_size_t],
     ),
+    "tei_b200_run_staged": (c_int, [c_void_p, c_char_p, c_size_t]),
+    "tei_b200_sync": (c_int, [c_void_p, c_char_p, c_size_t]),
+    "tei_b200_fetch": (
+        c_int,
+        [c_void_p, POINTER(c_float), POINTER(c_float), POINTER(c_float), c_char_p, c_size_t],
+    ),
+    "tei_b200_run_staged_timed": (c_int, [c_void_p, c_int, POINTER(c_double), c_char_p, c_size_t]),
+    "tei_b200_set_profiling": (c_int, [c_void_p, c_int]),
+    "tei_b200_kernel_times": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), c_int]),
     "tei_b200_stats": (c_int, [c_void_p, POINTER(c_double), c_int]),
     "tei_b200_plan_shards": (
         c_int,
         [POINTER(c_uint32), c_size_t, c_int, c_double, c_double, POINTER(c_int)],
-    ),
-    "tei_b200_forward_device": (
-        c_int,
-        [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, POINTER(c_uint32), c_size_t, c_uint32,
-         c_int, c_void_p, c_char_p, c_size_t],
     ),
 }
 
@@ -84,9 +91,8 @@ def load() -> ctypes.CDLL:
         )
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in prototypes().items():
-        if hasattr(lib, name):
-            fn = getattr(lib, name)
-            fn.restype = restype
-            fn.argtypes = argtypes
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = restype
+        fn.argtypes = argtypes
     _lib = lib
     return lib
