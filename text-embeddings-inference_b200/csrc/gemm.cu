@@ -12,8 +12,11 @@
 //   warp 1      allocates 512 TMEM columns (two 128x256 fp32 accumulators) and issues
 //               tcgen05.mma.cta_group::1.kind::f16 (M=128, N=256, K=16), four per stage.
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator (one row per thread), bias /
-//               activation / residual in registers, 16-byte global stores.  Runs while the MMA
-//               warp fills the other accumulator.
+//               activation in registers, rows packed into a 128-byte-swizzled staging tile in
+//               shared memory and written out with TMA stores (full 128-byte lines; the tensor
+//               map clips the M and N tails).  Runs while the MMA warp fills the other
+//               accumulator.  Outputs whose row pitch is not a multiple of 16 bytes, and the
+//               residual variant, use plain per-thread stores instead.
 // Every mbarrier wait is bounded; a wait that runs out writes a code to *status and the CTA
 // drains and exits.
 #include "kernels.h"
@@ -32,7 +35,10 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// Epilogue staging: per epilogue warp two buffers of 32 rows x 64 columns (128 B per row).
+constexpr int EPI_BUF_BYTES = 32 * 128;
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
   const void* bias;
@@ -40,6 +46,7 @@ struct GemmParams {
   void* out;
   int M, N, K;
   int ldo, ldr;
+  int tma_store;  // 1: outputs leave through the TMA store path
   int* status;
 };
 
@@ -141,12 +148,13 @@ __device__ __forceinline__ void finish_and_store(float (&v)[32], const GemmParam
 template <class T, int ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled operand tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + EPI_BYTES);
   uint64_t* full_bar = bars;                     // [STAGES] TMA -> MMA
   uint64_t* empty_bar = bars + STAGES;           // [STAGES] MMA -> TMA
   uint64_t* acc_full = bars + 2 * STAGES;        // [2] MMA -> epilogue
@@ -164,6 +172,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (threadIdx.x == 0) {
     ptx::prefetch_tmap(&tm_a);
     ptx::prefetch_tmap(&tm_b);
+    if (p.tma_store) ptx::prefetch_tmap(&tm_c);
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(&full_bar[s], 1);
       ptx::mbar_init(&empty_bar[s], 1);
