@@ -78,6 +78,97 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
 }
 
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Online-softmax step of one thread = one query row over a 128-key tile whose scores sit in
+// TMEM at `tmem_row`.  Two passes over TMEM (row maximum, then probabilities) keep the register
+// footprint at one 32-column chunk.  Writes the probabilities as T into the K-major swizzled
+// operand tile `sp` and updates the running maximum m (in the scaled log2 domain), the running
+// sum l and the rescale factor alpha for the accumulator.
+//   MASKED: only keys [0, lim) of the tile count.  ALIBI: subtract slope * |rel - key|, where
+//   rel = query position - first key position of the tile.
+template <class T, bool MASKED, bool ALIBI>
+__device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int r, int lim, float sl2,
+                                             float slope, int rel, float& m, float& l, float& alpha) {
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
+  for (int c = 0; c < BKV / 32; ++c) {
+    uint32_t s[32];
+    ptx::tmem_ld32(tmem_row + c * 32, s);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
+      float x2 = __uint_as_float(s[i + 2]), x3 = __uint_as_float(s[i + 3]);
+      if (ALIBI) {
+        const int kk = c * 32 + i;
+        x0 = x0 * sl2 - slope * fabsf(static_cast<float>(rel - kk));
+        x1 = x1 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1));
+        x2 = x2 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 2));
+        x3 = x3 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 3));
+      }
+      if (MASKED) {
+        const int kk = c * 32 + i;
+        x0 = kk < lim ? x0 : -INFINITY;
+        x1 = kk + 1 < lim ? x1 : -INFINITY;
+        x2 = kk + 2 < lim ? x2 : -INFINITY;
+        x3 = kk + 3 < lim ? x3 : -INFINITY;
+      }
+      mx0 = fmaxf(mx0, x0);
+      mx1 = fmaxf(mx1, x1);
+      mx2 = fmaxf(mx2, x2);
+      mx3 = fmaxf(mx3, x3);
+    }
+  }
+  float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  if (!ALIBI) mx *= sl2;  // the scale is positive, so the maximum commutes with it
+  const float m_new = fmaxf(m, mx);
+  const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+  alpha = ex2_fast(m - m_use);  // m = -inf -> 0
+  float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BKV / 32; ++c) {
+    uint32_t s[32];
+    ptx::tmem_ld32(tmem_row + c * 32, s);
+    ptx::tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const int kk = c * 32 + i;
+      float e0, e1;
+      if (ALIBI) {
+        e0 = ex2_fast(__uint_as_float(s[i]) * sl2 - slope * fabsf(static_cast<float>(rel - kk)) - m_use);
+        e1 = ex2_fast(__uint_as_float(s[i + 1]) * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1)) - m_use);
+      } else {
+        e0 = ex2_fast(fmaf(__uint_as_float(s[i]), sl2, -m_use));
+        e1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), sl2, -m_use));
+      }
+      if (MASKED) {
+        e0 = kk < lim ? e0 : 0.f;
+        e1 = kk + 1 < lim ? e1 : 0.f;
+      }
+      sum0 += e0;
+      sum1 += e1;
+      pk[i / 2] = pack2<T>(e0, e1);
+    }
+    // K-major 128-byte-swizzled operand tile: [k atom of 64][row][64], 16-byte chunk index
+    // XORed with (row & 7).
+    uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
+      *reinterpret_cast<uint4*>(rowp + chunk * 16) =
+          make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+    }
+  }
+  l = l * alpha + (sum0 + sum1);
+  m = m_new;
+}
+
 template <class T, int D>
 __global__ void __launch_bounds__(ATTN_THREADS, (D == 64 ? 2 : 1))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -218,58 +309,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       int lim = seq_len - k_base;
       if (p.causal) lim = min(lim, qi - k_base + 1);
       lim = max(0, min(lim, BKV));
-      // pass 1: row maximum
-      float m_new = m;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t s[32];
-        ptx::tmem_ld32(tmem_s + lane_off + c * 32, s);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kk = c * 32 + i;
-          float x = __uint_as_float(s[i]) * p.scale_log2;
-          if (p.alibi_slopes) x -= slope * fabsf(static_cast<float>(qi - (k_base + kk)));
-          if (kk < lim) m_new = fmaxf(m_new, x);
-        }
+      // Uniform per (CTA, step): interior tiles need no per-element mask.
+      const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
+      float alpha;
+      if (p.alibi_slopes) {
+        softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, p.scale_log2, slope, qi - k_base, m, l, alpha);
+      } else if (tile_full) {
+        softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
+      } else {
+        softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
       }
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m - m_use);  // m = -inf -> 0
-      // pass 2: probabilities, row sum, P to shared memory
-      float row_sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t s[32];
-        ptx::tmem_ld32(tmem_s + lane_off + c * 32, s);
-        ptx::tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kk = c * 32 + i + u;
-            float x = __uint_as_float(s[i + u]) * p.scale_log2;
-            if (p.alibi_slopes) x -= slope * fabsf(static_cast<float>(qi - (k_base + kk)));
-            e[u] = (kk < lim) ? exp2f(x - m_use) : 0.f;
-          }
-          pk[i / 2] = pack2<T>(e[0], e[1]);
-          // Sum what the tensor core will actually multiply (the rounded values).
-          const float2 rounded = unpack2<T>(pk[i / 2]);
-          row_sum += rounded.x + rounded.y;
-        }
-        // K-major 128-byte-swizzled operand tile: [k atom of 64][row][64], 16-byte chunk index
-        // XORed with (row & 7).
-        uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(rowp + chunk * 16) =
-              make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-        }
-      }
-      l = l * alpha + row_sum;
-      m = m_new;
       // P visible to the tensor core (async proxy), S reads finished: hand over.
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before();

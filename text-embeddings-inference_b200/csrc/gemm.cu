@@ -267,6 +267,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const bool vec_ok = (p.ldo % 8 == 0) && (p.residual == nullptr || p.ldr % 8 == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                         ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+    uint8_t* stage_buf = epi_smem + (warp - 2) * (2 * EPI_BUF_BYTES);
+    uint32_t store_count = 0;  // TMA stores issued by this warp (selects the staging buffer)
+    const int n_out = (ACT == ACT_SWIGLU) ? p.N / 2 : p.N;
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
@@ -280,7 +284,86 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       ptx::tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      if constexpr (ACT == ACT_SWIGLU) {
+      if (p.tma_store) {
+        // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
+        constexpr int STEPS = (ACT == ACT_SWIGLU) ? 2 : 4;
+        const int o0 = (ACT == ACT_SWIGLU) ? n0 / 2 : n0;
+#pragma unroll 1
+        for (int c = 0; c < STEPS; ++c) {
+          const int ocol = o0 + c * 64;
+          if (ocol >= n_out) break;  // uniform across the CTA
+          uint32_t packed[32];
+          if constexpr (ACT == ACT_SWIGLU) {
+            // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t g[32], u[32];
+              ptx::tmem_ld32(t_row + c * 64 + hlf * 32, g);
+              ptx::tmem_ld32(t_row + 128 + c * 64 + hlf * 32, u);
+              ptx::tmem_ld_wait();
+              const int gcol = n0 + c * 64 + hlf * 32;
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float gv0 = __uint_as_float(g[j]), gv1 = __uint_as_float(g[j + 1]);
+                float uv0 = __uint_as_float(u[j]), uv1 = __uint_as_float(u[j + 1]);
+                if (bias) {
+                  gv0 += to_f32<T>(bias[gcol + j]);
+                  gv1 += to_f32<T>(bias[gcol + j + 1]);
+                  uv0 += to_f32<T>(bias[gcol + 128 + j]);
+                  uv1 += to_f32<T>(bias[gcol + 128 + j + 1]);
+                }
+                packed[hlf * 16 + j / 2] = pack2<T>(silu(gv0) * uv0, silu(gv1) * uv1);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              uint32_t r[32];
+              ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
+              ptx::tmem_ld_wait();
+              const int col = n0 + c * 64 + hlf * 32;
+              float bv[32];
+              if (bias_vec && col + 32 <= p.N) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint4 b4 = *reinterpret_cast<const uint4*>(bias + col + j * 8);
+                  const T* bt = reinterpret_cast<const T*>(&b4);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) bv[j * 8 + e] = to_f32<T>(bt[e]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) bv[j] = (bias && col + j < p.N) ? to_f32<T>(bias[col + j]) : 0.f;
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float x0 = apply_act<ACT>(__uint_as_float(r[j]) + bv[j]);
+                const float x1 = apply_act<ACT>(__uint_as_float(r[j + 1]) + bv[j + 1]);
+                packed[hlf * 16 + j / 2] = pack2<T>(x0, x1);
+              }
+            }
+          }
+          // The staging buffer used two stores ago must have been read out by its TMA store.
+          uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
+          if (lane == 0) ptx::tma_store_wait_read<1>();
+          __syncwarp();
+          // Row `lane` of the 32 x 64 tile: eight 16-byte chunks, chunk index XORed with
+          // (row & 7) as the 128-byte swizzle of the tensor map expects.
+          uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) * 16)) =
+                make_uint4(packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d(&tm_c, buf, ocol, m0 + quad * 32);
+            ptx::tma_store_commit();
+          }
+          ++store_count;
+        }
+      } else if constexpr (ACT == ACT_SWIGLU) {
         // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -328,6 +411,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
     }
+    // Global writes of the TMA stores must have completed before the CTA exits.
+    if (p.tma_store && lane == 0) ptx::tma_store_wait<0>();
   }
 
   ptx::tc_fence_before();
@@ -347,6 +432,16 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   if (rc) return rc;
   rc = make_tmap_2d(&tm_b, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, BN);
   if (rc) return rc;
+  // Outputs leave through TMA stores when the output rows are 16-byte aligned and no residual
+  // is fused; otherwise the epilogue falls back to per-thread stores.
+  const int n_out = (ACT == ACT_SWIGLU) ? g.N / 2 : g.N;
+  const bool tma_store = g.residual == nullptr && g.ldo % 8 == 0 &&
+                         (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
+  CUtensorMap tm_c = tm_a;  // placeholder when unused (never dereferenced by the kernel)
+  if (tma_store) {
+    rc = make_tmap_2d(&tm_c, g.out, dt, 2, n_out, g.M, static_cast<uint64_t>(g.ldo) * 2, 64, 32);
+    if (rc) return rc;
+  }
 
   // The opt-in shared-memory size is a per-device function attribute; setting it twice is
   // harmless, so a plain flag per device (and per instantiation) is enough.
@@ -368,10 +463,11 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   p.K = g.K;
   p.ldo = g.ldo;
   p.ldr = g.ldr;
+  p.tma_store = tma_store ? 1 : 0;
   p.status = g.status;
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, p);
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, p);
   return static_cast<int>(cudaGetLastError());
 }
 
