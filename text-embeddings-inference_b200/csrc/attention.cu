@@ -7,7 +7,9 @@
 // with q-head h reading kv-head h / (n_heads / n_kv_heads).  Q, K and V are strided views of
 // the projection output (token-major rows), exactly as the reference passes them.
 //
-// One CTA handles one (sequence, 128-row query tile, head) work item:
+// Persistent CTAs (two per SM for D = 64) walk the (sequence, 128-row query tile, head) work
+// units, most expensive first; the next unit's Q and first K/V tile are fetched while the
+// current one finishes.  Within a CTA:
 //   warp 4 (one elected lane)  TMA loads (Q once, K/V double-buffered, 128-byte swizzle, no
 //                              cluster multicast) and tcgen05.mma issue:
 //                              S = Q K^T into TMEM columns [0,128), P V into columns [128,128+D).
@@ -46,6 +48,7 @@ struct AttnSmem {
 struct AttnParams {
   void* out;
   const int* work;  // [n_work][4] = {seq_start, seq_len, q0, unused}
+  int n_work;
   int n_heads, n_kv_heads;
   int ld_o;
   int causal;
@@ -193,15 +196,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  const int item = blockIdx.x / p.n_heads;
-  const int head = blockIdx.x % p.n_heads;
-  const int kv_head = head / (p.n_heads / p.n_kv_heads);
-  const int seq_start = p.work[item * 4 + 0];
-  const int seq_len = p.work[item * 4 + 1];
-  const int q0 = p.work[item * 4 + 2];
-  const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int total = p.n_work * p.n_heads;  // work units: (sequence, query tile) x head
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(bar_q, 1);
@@ -222,7 +217,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + 128;
+  const int group = p.n_heads / p.n_kv_heads;
 
+  // The CTA is persistent: it walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...
+  // `g` counts key/value steps over the CTA's whole life and drives every barrier parity.
   if (warp == 4) {
     if (lane == 0) {
       ptx::prefetch_tmap(&tm_q);
@@ -231,124 +229,157 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       constexpr uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, BKV, 0, 0);
       // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
       constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
-      auto load_kv = [&](int j) {
-        const int st = j & 1;
+      auto load_q = [&](int w) {
+        const int* it = p.work + (w / p.n_heads) * 4;
+        const int head = w % p.n_heads;
+        ptx::mbar_expect_tx(bar_q, L::Q_BYTES);
+#pragma unroll
+        for (int a = 0; a < D_ATOMS; ++a) {
+          ptx::tma_load_2d(smem + L::OFF_Q + a * (BQ * 128), &tm_q, bar_q, head * D + a * 64, it[0] + it[2]);
+        }
+      };
+      auto load_kv = [&](int w, int j, uint32_t step) {
+        const int* it = p.work + (w / p.n_heads) * 4;
+        const int kv_head = (w % p.n_heads) / group;
+        const int st = step & 1;
         ptx::mbar_expect_tx(&bar_kv[st], 2 * L::KV_BYTES);
 #pragma unroll
         for (int a = 0; a < D_ATOMS; ++a) {
-          ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k,
-                           &bar_kv[st], kv_head * D + a * 64, seq_start + j * BKV);
-          ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v,
-                           &bar_kv[st], kv_head * D + a * 64, seq_start + j * BKV);
+          ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_kv[st],
+                           kv_head * D + a * 64, it[0] + j * BKV);
+          ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, &bar_kv[st],
+                           kv_head * D + a * 64, it[0] + j * BKV);
         }
       };
-      ptx::mbar_expect_tx(bar_q, L::Q_BYTES);
-#pragma unroll
-      for (int a = 0; a < D_ATOMS; ++a) {
-        ptx::tma_load_2d(smem + L::OFF_Q + a * (BQ * 128), &tm_q, bar_q, head * D + a * 64,
-                         seq_start + q0);
+      uint32_t g = 0, n_item = 0;
+      bool ok = true;
+      if (static_cast<int>(blockIdx.x) < total) {
+        load_q(blockIdx.x);
+        load_kv(blockIdx.x, 0, 0);
       }
-      load_kv(0);
-      bool ok = ptx::mbar_wait(bar_q, 0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        ok = ptx::mbar_wait(&bar_kv[st], (j >> 1) & 1);
-        if (!ok) break;
-        ptx::tc_fence_after();
-        // S = Q K_j^T
-        const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
-        const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n_item) {
+        const int* it = p.work + (w / p.n_heads) * 4;
+        const int seq_len = it[1], q0 = it[2];
+        const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
+        const int n_kv = (kv_end + BKV - 1) / BKV;
+        ok = ptx::mbar_wait(bar_q, n_item & 1);
+        for (int j = 0; j < n_kv && ok; ++j, ++g) {
+          const int st = g & 1;
+          ok = ptx::mbar_wait(&bar_kv[st], (g >> 1) & 1);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          // S = Q K_j^T
+          const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
+          const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
-          ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
-                       ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
-        }
-        ptx::umma_commit(bar_s);
-        // The other K/V stage was last read by step j-1's P V, whose completion (bar_o of step
-        // j-1) this thread has already waited for below, so it can be refilled now.
-        if (j + 1 < n_kv) load_kv(j + 1);
-        ok = ptx::mbar_wait(bar_p, j & 1);
-        if (!ok) break;
-        ptx::tc_fence_after();
-        // O_j = P_j V_j
-        const uint32_t sp = ptx::smem_u32(smem + L::OFF_P);
-        const uint32_t sv = ptx::smem_u32(smem + L::OFF_V + st * L::KV_BYTES);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
+            ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
+                         ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(bar_s);
+          // The other K/V stage was last read by the previous step's P V, whose completion
+          // (bar_o) this thread has already waited for, so it can be refilled now.
+          if (j + 1 < n_kv) {
+            load_kv(w, j + 1, g + 1);
+          } else if (w + static_cast<int>(gridDim.x) < total) {
+            // Last step of this unit: once S is done nothing reads the Q tile any more, so the
+            // next unit's Q and first K/V tile are fetched while this unit finishes.
+            ok = ptx::mbar_wait(bar_s, g & 1);
+            if (!ok) break;
+            load_q(w + gridDim.x);
+            load_kv(w + gridDim.x, 0, g + 1);
+          }
+          ok = ptx::mbar_wait(bar_p, g & 1);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          // O_j = P_j V_j
+          const uint32_t sp = ptx::smem_u32(smem + L::OFF_P);
+          const uint32_t sv = ptx::smem_u32(smem + L::OFF_V + st * L::KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          const uint32_t aoff = (k / 4) * (BQ * 128) + (k % 4) * 32;
-          ptx::umma_ss(tmem_o, ptx::make_smem_desc_sw128(sp + aoff, 16, 1024),
-                       ptx::make_smem_desc_sw128(sv + k * 2048, BKV * 128, 1024), idesc_o,
-                       k != 0 ? 1u : 0u);
+          for (int k = 0; k < BKV / 16; ++k) {
+            const uint32_t aoff = (k / 4) * (BQ * 128) + (k % 4) * 32;
+            ptx::umma_ss(tmem_o, ptx::make_smem_desc_sw128(sp + aoff, 16, 1024),
+                         ptx::make_smem_desc_sw128(sv + k * 2048, BKV * 128, 1024), idesc_o,
+                         k != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(bar_o);
+          ok = ptx::mbar_wait(bar_o, g & 1);
         }
-        ptx::umma_commit(bar_o);
-        ok = ptx::mbar_wait(bar_o, j & 1);
       }
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {
     // ------------------------------------------------------------ softmax warps
     const int r = warp * 32 + lane;           // row inside the query tile = TMEM lane
-    const int qi = q0 + r;                    // position inside the sequence
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
-    float m = -INFINITY, l = 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
     uint8_t* sp = smem + L::OFF_P;
+    uint32_t g = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!ptx::mbar_wait(bar_s, j & 1)) {
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after();
-      const int k_base = j * BKV;
-      // Keys this row may attend to within the tile: [0, lim).
-      int lim = seq_len - k_base;
-      if (p.causal) lim = min(lim, qi - k_base + 1);
-      lim = max(0, min(lim, BKV));
-      // Uniform per (CTA, step): interior tiles need no per-element mask.
-      const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
-      float alpha;
-      if (p.alibi_slopes) {
-        softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, p.scale_log2, slope, qi - k_base, m, l, alpha);
-      } else if (tile_full) {
-        softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
-      } else {
-        softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
-      }
-      // P visible to the tensor core (async proxy), S reads finished: hand over.
-      ptx::fence_proxy_async_smem();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar_p);
-      if (!ptx::mbar_wait(bar_o, j & 1)) {
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after();
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+      const int* it = p.work + (w / p.n_heads) * 4;
+      const int head = w % p.n_heads;
+      const int seq_start = it[0], seq_len = it[1], q0 = it[2];
+      const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
+      const int n_kv = (kv_end + BKV - 1) / BKV;
+      const int qi = q0 + r;                  // position inside the sequence
+      const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+      float m = -INFINITY, l = 0.f;
+      float o[D];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t t[32];
-        ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
-        ptx::tmem_ld_wait();
+      for (int i = 0; i < D; ++i) o[i] = 0.f;
+      for (int j = 0; j < n_kv; ++j, ++g) {
+        if (!ptx::mbar_wait(bar_s, g & 1)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const int k_base = j * BKV;
+        // Keys this row may attend to within the tile: [0, lim).
+        int lim = seq_len - k_base;
+        if (p.causal) lim = min(lim, qi - k_base + 1);
+        lim = max(0, min(lim, BKV));
+        // Uniform per (CTA, step): interior tiles need no per-element mask.
+        const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
+        float alpha;
+        if (p.alibi_slopes) {
+          softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, p.scale_log2, slope, qi - k_base, m, l, alpha);
+        } else if (tile_full) {
+          softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
+        } else {
+          softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
+        }
+        // P visible to the tensor core (async proxy), S reads finished: hand over.
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_p);
+        if (!ptx::mbar_wait(bar_o, g & 1)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(t[i]);
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t t[32];
+          ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(t[i]);
+        }
+        ptx::tc_fence_before();
       }
-      ptx::tc_fence_before();
-    }
-    if (ok && qi < seq_len) {
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
+      if (ok && qi < seq_len) {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        uint4 v;
-        v.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
-        v.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        v.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-        v.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        for (int c = 0; c < D / 8; ++c) {
+          uint4 v;
+          v.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
+          v.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
+          v.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
+          v.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        }
       }
     }
     if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
@@ -389,6 +420,7 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
   AttnParams p;
   p.out = a.out;
   p.work = a.work_items;
+  p.n_work = a.n_work;
   p.n_heads = a.n_heads;
   p.n_kv_heads = a.n_kv_heads;
   p.ld_o = a.ld_o;
@@ -396,7 +428,10 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.alibi_slopes = a.alibi_slopes;
   p.status = a.status;
-  const long long grid = static_cast<long long>(a.n_work) * a.n_heads;
+  const long long total = static_cast<long long>(a.n_work) * a.n_heads;
+  if (total > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
+  const long long resident = static_cast<long long>(num_sms()) * (D == 64 ? 2 : 1);
+  const long long grid = total < resident ? total : resident;
   kern<<<static_cast<unsigned>(grid), ATTN_THREADS, L::TOTAL, stream>>>(tm_q, tm_k, tm_v, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -34,12 +34,32 @@ __device__ __forceinline__ __nv_bfloat16 stf<__nv_bfloat16>(float v) {
   return __float2bfloat16_rn(v);
 }
 
+// Takes the 16 bytes BY VALUE: a reference to a dereferenced global pointer would let the
+// compiler read the eight elements with eight narrow loads instead of one 128-bit load.
 template <class T>
-__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-  const T* t = reinterpret_cast<const T*>(&u);
+__device__ __forceinline__ void unpack8(uint4 u, float* f);
+template <>
+__device__ __forceinline__ void unpack8<__half>(uint4 u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = ldf<T>(t[i]);
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
 }
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(uint4 u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // bf16 -> fp32 is a 16-bit shift
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+// 128-bit read-only load.
+__device__ __forceinline__ uint4 ld16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 template <class T>
 __device__ __forceinline__ uint4 pack8(const float* f) {
   uint4 u;
@@ -91,9 +111,9 @@ __device__ __forceinline__ void normalise_row(float (&v)[MAXC][8], int n_chunks,
     const int ch = lane + c * 32;
     if (ch < n_chunks) {
       float g[8], b[8];
-      unpack8<T>(*reinterpret_cast<const uint4*>(gamma + ch * 8), g);
+      unpack8<T>(ld16(gamma + ch * 8), g);
       if (!RMS && beta) {
-        unpack8<T>(*reinterpret_cast<const uint4*>(beta + ch * 8), b);
+        unpack8<T>(ld16(beta + ch * 8), b);
       } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) b[i] = 0.f;
@@ -128,15 +148,15 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
   for (int c = 0; c < MAXC; ++c) {
     const int ch = lane + c * 32;
     if (ch < n_chunks) {
-      unpack8<T>(*reinterpret_cast<const uint4*>(w + ch * 8), v[c]);
+      unpack8<T>(ld16(w + ch * 8), v[c]);
       float a[8];
       if (t) {
-        unpack8<T>(*reinterpret_cast<const uint4*>(t + ch * 8), a);
+        unpack8<T>(ld16(t + ch * 8), a);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[c][i] += a[i];
       }
       if (p) {
-        unpack8<T>(*reinterpret_cast<const uint4*>(p + ch * 8), a);
+        unpack8<T>(ld16(p + ch * 8), a);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[c][i] += a[i];
       }
@@ -171,7 +191,7 @@ add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restri
   for (int c = 0; c < MAXC; ++c) {
     const int ch = lane + c * 32;
     if (ch < n_chunks) {
-      unpack8<T>(*reinterpret_cast<const uint4*>(xr + ch * 8), v[c]);
+      unpack8<T>(ld16(xr + ch * 8), v[c]);
       if (residual) {
         if (RMS) {
           const float* rr = reinterpret_cast<const float*>(residual) + static_cast<size_t>(row) * H;
@@ -182,7 +202,7 @@ add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restri
         } else {
           const T* rr = reinterpret_cast<const T*>(residual) + static_cast<size_t>(row) * H;
           float a[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(rr + ch * 8), a);
+          unpack8<T>(ld16(rr + ch * 8), a);
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[c][i] += a[i];
         }
@@ -282,12 +302,12 @@ pool_kernel(const T* __restrict__ x, const int* __restrict__ cu, const int* __re
     if (mode == 0 || mode == 3) {
       if (rl == 0 && end > start) {
         const int r = mode == 0 ? start : end - 1;
-        unpack8<T>(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H + col), acc);
+        unpack8<T>(ld16(x + static_cast<size_t>(r) * H + col), acc);
       }
     } else {
       for (int r = start + rl; r < end; r += 8) {
         float f[8];
-        unpack8<T>(*reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H + col), f);
+        unpack8<T>(ld16(x + static_cast<size_t>(r) * H + col), f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = (mode == 2) ? fmaxf(acc[i], f[i]) : acc[i] + f[i];
       }
@@ -341,7 +361,7 @@ gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_index,
   float* dst = out + static_cast<size_t>(row) * H;
   for (int ch = lane; ch < (H >> 3); ch += 32) {
     float f[8];
-    unpack8<T>(*reinterpret_cast<const uint4*>(src + ch * 8), f);
+    unpack8<T>(ld16(src + ch * 8), f);
     *reinterpret_cast<float4*>(dst + ch * 8) = make_float4(f[0], f[1], f[2], f[3]);
     *reinterpret_cast<float4*>(dst + ch * 8 + 4) = make_float4(f[4], f[5], f[6], f[7]);
   }
