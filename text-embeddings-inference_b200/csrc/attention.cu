@@ -92,14 +92,15 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // footprint at one 32-column chunk.  Writes the probabilities as T into the K-major swizzled
 // operand tile `sp` and updates the running maximum m (in the scaled log2 domain), the running
 // sum l and the rescale factor alpha for the accumulator.
-//   MASKED: only keys [0, lim) of the tile count.  ALIBI: subtract slope * |rel - key|, where
+//   Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.  ALIBI: subtract slope * |rel - key|, where
 //   rel = query position - first key position of the tile.
 template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int r, int lim, float sl2,
-                                             float slope, int rel, float& m, float& l, float& alpha) {
+__device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int r, int lim, int n_chunks,
+                                             float sl2, float slope, int rel, float& m, float& l,
+                                             float& alpha) {
   float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
-  for (int c = 0; c < BKV / 32; ++c) {
+  for (int c = 0; c < n_chunks; ++c) {
     uint32_t s[32];
     ptx::tmem_ld32(tmem_row + c * 32, s);
     ptx::tmem_ld_wait();
@@ -134,7 +135,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int
   alpha = ex2_fast(m - m_use);  // m = -inf -> 0
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll 1
-  for (int c = 0; c < BKV / 32; ++c) {
+  for (int c = 0; c < n_chunks; ++c) {
     uint32_t s[32];
     ptx::tmem_ld32(tmem_row + c * 32, s);
     ptx::tmem_ld_wait();
@@ -226,7 +227,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       ptx::prefetch_tmap(&tm_q);
       ptx::prefetch_tmap(&tm_k);
       ptx::prefetch_tmap(&tm_v);
-      constexpr uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, BKV, 0, 0);
       // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
       constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
       auto load_q = [&](int w) {
@@ -251,59 +251,89 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                            kv_head * D + a * 64, it[0] + j * BKV);
         }
       };
+      // Number of keys of step j of a unit that any row can see (CTA-uniform).
+      auto keys_in_tile = [&](const int* it, int j) {
+        const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
+        return min(BKV, kv_end - j * BKV);
+      };
+      // S = Q K^T for the K tile in stage `st`; only the first ceil(keys/32)*32 columns are
+      // computed (the softmax reads no more than that).
+      auto issue_s = [&](int st, int keys) {
+        const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 31) / 32) * 32, 0, 0);
+        const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
+        const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
+          ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
+                       ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        }
+        ptx::umma_commit(bar_s);
+      };
       uint32_t g = 0, n_item = 0;
       bool ok = true;
       if (static_cast<int>(blockIdx.x) < total) {
         load_q(blockIdx.x);
         load_kv(blockIdx.x, 0, 0);
+        ok = ptx::mbar_wait(bar_q, 0) && ptx::mbar_wait(&bar_kv[0], 0);
+        if (ok) {
+          ptx::tc_fence_after();
+          issue_s(0, keys_in_tile(p.work + (blockIdx.x / p.n_heads) * 4, 0));
+        }
       }
+      // Invariant at the top of every step g: S of step g has been issued and its K/V stage has
+      // landed.  Each step then (1) starts the loads of the next step, (2) waits for P, issues
+      // P V, (3) issues the NEXT step's S right behind it, so that the tensor core computes it
+      // while the softmax warps fold P V into their accumulators.
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n_item) {
         const int* it = p.work + (w / p.n_heads) * 4;
         const int seq_len = it[1], q0 = it[2];
         const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
         const int n_kv = (kv_end + BKV - 1) / BKV;
-        ok = ptx::mbar_wait(bar_q, n_item & 1);
+        const int w_next = w + static_cast<int>(gridDim.x);
         for (int j = 0; j < n_kv && ok; ++j, ++g) {
           const int st = g & 1;
-          ok = ptx::mbar_wait(&bar_kv[st], (g >> 1) & 1);
-          if (!ok) break;
-          ptx::tc_fence_after();
-          // S = Q K_j^T
-          const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
-          const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
-#pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
-            ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
-                         ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
-          }
-          ptx::umma_commit(bar_s);
+          const bool last = (j + 1 == n_kv);
           // The other K/V stage was last read by the previous step's P V, whose completion
           // (bar_o) this thread has already waited for, so it can be refilled now.
-          if (j + 1 < n_kv) {
+          if (!last) {
             load_kv(w, j + 1, g + 1);
-          } else if (w + static_cast<int>(gridDim.x) < total) {
-            // Last step of this unit: once S is done nothing reads the Q tile any more, so the
-            // next unit's Q and first K/V tile are fetched while this unit finishes.
+          } else if (w_next < total) {
+            // Last step of this unit: once its S is done nothing reads the Q tile any more.
             ok = ptx::mbar_wait(bar_s, g & 1);
             if (!ok) break;
-            load_q(w + gridDim.x);
-            load_kv(w + gridDim.x, 0, g + 1);
+            load_q(w_next);
+            load_kv(w_next, 0, g + 1);
           }
           ok = ptx::mbar_wait(bar_p, g & 1);
           if (!ok) break;
           ptx::tc_fence_after();
-          // O_j = P_j V_j
+          // O_j = P_j V_j over the keys of this tile (rounded up to the MMA's K step of 16).
+          const int keys = keys_in_tile(it, j);
+          const int k_steps = (keys + 15) / 16;
           const uint32_t sp = ptx::smem_u32(smem + L::OFF_P);
           const uint32_t sv = ptx::smem_u32(smem + L::OFF_V + st * L::KV_BYTES);
-#pragma unroll
-          for (int k = 0; k < BKV / 16; ++k) {
+#pragma unroll 1
+          for (int k = 0; k < k_steps; ++k) {
             const uint32_t aoff = (k / 4) * (BQ * 128) + (k % 4) * 32;
             ptx::umma_ss(tmem_o, ptx::make_smem_desc_sw128(sp + aoff, 16, 1024),
                          ptx::make_smem_desc_sw128(sv + k * 2048, BKV * 128, 1024), idesc_o,
                          k != 0 ? 1u : 0u);
           }
           ptx::umma_commit(bar_o);
+          // Next step's S, issued right behind P V.
+          if (!last) {
+            ok = ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            issue_s((g + 1) & 1, keys_in_tile(it, j + 1));
+          } else if (w_next < total) {
+            ok = ptx::mbar_wait(bar_q, (n_item + 1) & 1) &&
+                 ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            issue_s((g + 1) & 1, keys_in_tile(p.work + (w_next / p.n_heads) * 4, 0));
+          }
           ok = ptx::mbar_wait(bar_o, g & 1);
         }
       }
@@ -341,13 +371,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         lim = max(0, min(lim, BKV));
         // Uniform per (CTA, step): interior tiles need no per-element mask.
         const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
+        // Columns beyond the tile's last key are neither computed by the S MMA nor read by
+        // the P V MMA: only ceil(keys / 32) chunks of 32 columns are processed.
+        const int n_chunks = (min(BKV, kv_end - k_base) + 31) / 32;
         float alpha;
         if (p.alibi_slopes) {
-          softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, p.scale_log2, slope, qi - k_base, m, l, alpha);
+          softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, slope, qi - k_base, m, l, alpha);
         } else if (tile_full) {
-          softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
+          softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m, l, alpha);
         } else {
-          softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, p.scale_log2, 0.f, 0, m, l, alpha);
+          softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m, l, alpha);
         }
         // P visible to the tensor core (async proxy), S reads finished: hand over.
         ptx::fence_proxy_async_smem();
