@@ -15,13 +15,16 @@
 //                              S = Q K^T into TMEM columns [0,128), P V into columns [128,128+D).
 //   warps 0-3 (one row each)   read S from TMEM, online softmax in fp32 registers, write P as
 //                              fp16/bf16 into shared memory in the K-major swizzled operand
-//                              layout, rescale and accumulate the P V result in registers,
-//                              finally normalise and store the output row.
+//                              layout.  P V accumulates in TMEM across the key tiles; the
+//                              running maximum is raised lazily (only when it grows by more
+//                              than 2^8), in which case the rows rescale their partial output
+//                              in TMEM.  At the end the row is read, normalised and stored.
 // Two CTAs fit on an SM (D = 64), so one CTA's softmax overlaps the other's MMAs.
 // Every mbarrier wait is bounded and reports through *status instead of spinning forever.
 #include "kernels.h"
 #include "ptx.cuh"
 #include "tmap.h"
+
 
 namespace tei {
 namespace {
@@ -87,17 +90,16 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
-// Online-softmax step of one thread = one query row over a 128-key tile whose scores sit in
-// TMEM at `tmem_row`.  Two passes over TMEM (row maximum, then probabilities) keep the register
-// footprint at one 32-column chunk.  Writes the probabilities as T into the K-major swizzled
-// operand tile `sp` and updates the running maximum m (in the scaled log2 domain), the running
-// sum l and the rescale factor alpha for the accumulator.
-//   Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.  ALIBI: subtract slope * |rel - key|, where
-//   rel = query position - first key position of the tile.
-template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int r, int lim, int n_chunks,
-                                             float sl2, float slope, int rel, float& m, float& l,
-                                             float& alpha) {
+// One thread owns one query row of the 128-key score tile that sits in TMEM at `tmem_row`.
+// Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.
+// ALIBI: subtract slope * |rel - key| (rel = query position - first key position of the tile).
+// Two passes over TMEM keep the register footprint at one 32-column chunk (keeping the whole
+// row in registers was measured slower: it costs occupancy-critical registers).
+//
+// Pass 1: row maximum in the scaled log2 domain (-inf when the row sees no key).
+template <bool MASKED, bool ALIBI>
+__device__ __forceinline__ float row_max(uint32_t tmem_row, int lim, int n_chunks, float sl2, float slope,
+                                         int rel) {
   float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
   for (int c = 0; c < n_chunks; ++c) {
@@ -108,15 +110,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int
     for (int i = 0; i < 32; i += 4) {
       float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
       float x2 = __uint_as_float(s[i + 2]), x3 = __uint_as_float(s[i + 3]);
+      const int kk = c * 32 + i;
       if (ALIBI) {
-        const int kk = c * 32 + i;
         x0 = x0 * sl2 - slope * fabsf(static_cast<float>(rel - kk));
         x1 = x1 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1));
         x2 = x2 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 2));
         x3 = x3 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 3));
       }
       if (MASKED) {
-        const int kk = c * 32 + i;
         x0 = kk < lim ? x0 : -INFINITY;
         x1 = kk + 1 < lim ? x1 : -INFINITY;
         x2 = kk + 2 < lim ? x2 : -INFINITY;
@@ -128,11 +129,15 @@ __device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int
       mx3 = fmaxf(mx3, x3);
     }
   }
-  float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-  if (!ALIBI) mx *= sl2;  // the scale is positive, so the maximum commutes with it
-  const float m_new = fmaxf(m, mx);
-  const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-  alpha = ex2_fast(m - m_use);  // m = -inf -> 0
+  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  return ALIBI ? mx : mx * sl2;  // the scale is positive, so the maximum commutes with it
+}
+
+// Pass 2: p = 2^(score - m_use), written as T into the K-major 128-byte-swizzled operand tile
+// `sp` ([k atom of 64][row][64], 16-byte chunk index XORed with (row & 7)); returns the row sum.
+template <class T, bool MASKED, bool ALIBI>
+__device__ __forceinline__ float write_probs(uint32_t tmem_row, uint8_t* sp, int r, int lim, int n_chunks,
+                                             float sl2, float slope, int rel, float m_use) {
   float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll 1
   for (int c = 0; c < n_chunks; ++c) {
@@ -159,8 +164,6 @@ __device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int
       sum1 += e1;
       pk[i / 2] = pack2<T>(e0, e1);
     }
-    // K-major 128-byte-swizzled operand tile: [k atom of 64][row][64], 16-byte chunk index
-    // XORed with (row & 7).
     uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
@@ -169,9 +172,13 @@ __device__ __forceinline__ void softmax_tile(uint32_t tmem_row, uint8_t* sp, int
           make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
     }
   }
-  l = l * alpha + (sum0 + sum1);
-  m = m_new;
+  return sum0 + sum1;
 }
+
+// The running maximum is only raised when it grows by more than this many powers of two; until
+// then probabilities are taken relative to the stale maximum (they stay below 2^8, far inside
+// fp16 / bf16 range) and the accumulator in TMEM needs no rescaling.
+constexpr float kRescaleThreshold = 8.0f;
 
 template <class T, int D>
 __global__ void __launch_bounds__(ATTN_THREADS, (D == 64 ? 2 : 1))
@@ -190,7 +197,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* bar_q = bars;          // Q tile landed
   uint64_t* bar_kv = bars + 1;     // [2] K/V stage landed
   uint64_t* bar_s = bars + 3;      // S = Q K^T finished
-  uint64_t* bar_p = bars + 4;      // P written (128 arrivals)
+  uint64_t* bar_p = bars + 4;      // P written (one arrival per softmax warp)
   uint64_t* bar_o = bars + 5;      // P V finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   constexpr uint32_t TMEM_COLS = 256;
@@ -204,7 +211,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     ptx::mbar_init(&bar_kv[0], 1);
     ptx::mbar_init(&bar_kv[1], 1);
     ptx::mbar_init(bar_s, 1);
-    ptx::mbar_init(bar_p, BQ);
+    ptx::mbar_init(bar_p, 4);  // one arrival per softmax warp
     ptx::mbar_init(bar_o, 1);
     ptx::fence_mbar_init();
   }
@@ -256,19 +263,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
         return min(BKV, kv_end - j * BKV);
       };
+      // Operand descriptors are built once; each MMA adds a constant to the address field
+      // (units of 16 bytes; every operand sits below 256 KB, so the 14-bit field cannot carry).
+      const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
+      const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
+      const uint64_t dp = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_P), 16, 1024);
+      const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
       // S = Q K^T for the K tile in stage `st`; only the first ceil(keys/32)*32 columns are
       // computed (the softmax reads no more than that).
       auto issue_s = [&](int st, int keys) {
         const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 31) / 32) * 32, 0, 0);
-        const uint32_t sq = ptx::smem_u32(smem + L::OFF_Q);
-        const uint32_t sk = ptx::smem_u32(smem + L::OFF_K + st * L::KV_BYTES);
+        const uint64_t dks = dk + static_cast<uint64_t>((st * L::KV_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
-          ptx::umma_ss(tmem_s, ptx::make_smem_desc_sw128(sq + off, 16, 1024),
-                       ptx::make_smem_desc_sw128(sk + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+          constexpr int kAtom = BQ * 128;
+          const uint64_t off = static_cast<uint64_t>(((k / 4) * kAtom + (k % 4) * 32) >> 4);
+          ptx::umma_ss(tmem_s, dq + off, dks + off, idesc_s, k != 0 ? 1u : 0u);
         }
         ptx::umma_commit(bar_s);
+      };
+      // O (+)= P V over the first k_steps * 16 keys of the tile in stage `st`.
+      auto issue_pv = [&](int st, int k_steps, bool accumulate) {
+        const uint64_t dvs = dv + static_cast<uint64_t>((st * L::KV_BYTES) >> 4);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k) {
+          if (k < k_steps) {
+            constexpr int kAtom = BQ * 128;
+            const uint64_t aoff = static_cast<uint64_t>(((k / 4) * kAtom + (k % 4) * 32) >> 4);
+            ptx::umma_ss(tmem_o, dp + aoff, dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o,
+                         (accumulate || k != 0) ? 1u : 0u);
+          }
+        }
+        ptx::umma_commit(bar_o);
       };
       uint32_t g = 0, n_item = 0;
       bool ok = true;
@@ -281,10 +307,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           issue_s(0, keys_in_tile(p.work + (blockIdx.x / p.n_heads) * 4, 0));
         }
       }
-      // Invariant at the top of every step g: S of step g has been issued and its K/V stage has
-      // landed.  Each step then (1) starts the loads of the next step, (2) waits for P, issues
-      // P V, (3) issues the NEXT step's S right behind it, so that the tensor core computes it
-      // while the softmax warps fold P V into their accumulators.
+      // Invariant at the top of every step g: S of step g has been issued.  Each step then
+      // (1) waits for the previous step's P V (its K/V stage becomes free) and starts the loads
+      // of the next step, (2) waits for P, (3) issues the NEXT step's S and, behind it, this
+      // step's P V, which accumulates into the output tile in TMEM.
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n_item) {
         const int* it = p.work + (w / p.n_heads) * 4;
         const int seq_len = it[1], q0 = it[2];
@@ -294,8 +320,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int j = 0; j < n_kv && ok; ++j, ++g) {
           const int st = g & 1;
           const bool last = (j + 1 == n_kv);
-          // The other K/V stage was last read by the previous step's P V, whose completion
-          // (bar_o) this thread has already waited for, so it can be refilled now.
+          if (g > 0) {
+            ok = ptx::mbar_wait(bar_o, (g - 1) & 1);
+            if (!ok) break;
+          }
           if (!last) {
             load_kv(w, j + 1, g + 1);
           } else if (w_next < total) {
@@ -308,35 +336,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           ok = ptx::mbar_wait(bar_p, g & 1);
           if (!ok) break;
           ptx::tc_fence_after();
-          // O_j = P_j V_j over the keys of this tile (rounded up to the MMA's K step of 16).
-          const int keys = keys_in_tile(it, j);
-          const int k_steps = (keys + 15) / 16;
-          const uint32_t sp = ptx::smem_u32(smem + L::OFF_P);
-          const uint32_t sv = ptx::smem_u32(smem + L::OFF_V + st * L::KV_BYTES);
-#pragma unroll 1
-          for (int k = 0; k < k_steps; ++k) {
-            const uint32_t aoff = (k / 4) * (BQ * 128) + (k % 4) * 32;
-            ptx::umma_ss(tmem_o, ptx::make_smem_desc_sw128(sp + aoff, 16, 1024),
-                         ptx::make_smem_desc_sw128(sv + k * 2048, BKV * 128, 1024), idesc_o,
-                         k != 0 ? 1u : 0u);
-          }
-          ptx::umma_commit(bar_o);
-          // Next step's S, issued right behind P V.
+          // Next step's S first: the softmax warps can start on it while P V runs.
           if (!last) {
             ok = ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
             if (!ok) break;
             ptx::tc_fence_after();
             issue_s((g + 1) & 1, keys_in_tile(it, j + 1));
           } else if (w_next < total) {
-            ok = ptx::mbar_wait(bar_q, (n_item + 1) & 1) &&
-                 ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
+            ok = ptx::mbar_wait(bar_q, (n_item + 1) & 1);
+            ok = ok && ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
             if (!ok) break;
             ptx::tc_fence_after();
             issue_s((g + 1) & 1, keys_in_tile(p.work + (w_next / p.n_heads) * 4, 0));
           }
-          ok = ptx::mbar_wait(bar_o, g & 1);
+          // O (+)= P_j V_j over the keys of this tile (rounded up to the MMA's K step of 16).
+          issue_pv(st, (keys_in_tile(it, j) + 15) / 16, j != 0);
         }
       }
+      if (ok && g > 0) ok = ptx::mbar_wait(bar_o, (g - 1) & 1);
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {
@@ -354,10 +371,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int n_kv = (kv_end + BKV - 1) / BKV;
       const int qi = q0 + r;                  // position inside the sequence
       const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
-      float m = -INFINITY, l = 0.f;
-      float o[D];
-#pragma unroll
-      for (int i = 0; i < D; ++i) o[i] = 0.f;
+      float m = -INFINITY, l = 0.f;           // running maximum (scaled log2 domain) and sum
       for (int j = 0; j < n_kv; ++j, ++g) {
         if (!ptx::mbar_wait(bar_s, g & 1)) {
           ok = false;
@@ -369,51 +383,88 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         int lim = seq_len - k_base;
         if (p.causal) lim = min(lim, qi - k_base + 1);
         lim = max(0, min(lim, BKV));
-        // Uniform per (CTA, step): interior tiles need no per-element mask.
-        const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
         // Columns beyond the tile's last key are neither computed by the S MMA nor read by
         // the P V MMA: only ceil(keys / 32) chunks of 32 columns are processed.
         const int n_chunks = (min(BKV, kv_end - k_base) + 31) / 32;
-        float alpha;
-        if (p.alibi_slopes) {
-          softmax_tile<T, true, true>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, slope, qi - k_base, m, l, alpha);
-        } else if (tile_full) {
-          softmax_tile<T, false, false>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m, l, alpha);
-        } else {
-          softmax_tile<T, true, false>(tmem_s + lane_off, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m, l, alpha);
+        // Uniform per (CTA, step): interior tiles need no per-element mask.
+        const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
+        const uint32_t t_s = tmem_s + lane_off;
+        const int rel = qi - k_base;
+        float mx;
+        if (p.alibi_slopes) mx = row_max<true, true>(t_s, lim, n_chunks, p.scale_log2, slope, rel);
+        else if (tile_full) mx = row_max<false, false>(t_s, lim, n_chunks, p.scale_log2, 0.f, 0);
+        else mx = row_max<true, false>(t_s, lim, n_chunks, p.scale_log2, 0.f, 0);
+        // The previous step's P V must be complete before P is overwritten or O is touched.
+        if (g > 0) {
+          if (!ptx::mbar_wait(bar_o, (g - 1) & 1)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
         }
-        // P visible to the tensor core (async proxy), S reads finished: hand over.
+        if (j == 0) {
+          m = mx;  // P V of the first step overwrites the output tile: nothing to rescale
+        } else {
+          const bool grow = mx > m + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            // Raise the maximum of the rows that need it and rescale their partial outputs in
+            // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).
+            const float alpha = grow ? ex2_fast(m - mx) : 1.0f;
+            if (grow) {
+              l *= alpha;
+              m = mx;
+            }
+#pragma unroll 1
+            for (int c = 0; c < D / 16; ++c) {  // small pieces: the score row is live in registers
+              uint32_t t[16];
+              ptx::tmem_ld16(tmem_o + lane_off + c * 16, t);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+              ptx::tmem_st16(tmem_o + lane_off + c * 16, t);
+            }
+            ptx::tmem_st_wait();
+          }
+        }
+        const float m_use = (m == -INFINITY) ? 0.f : m;
+        float sum;
+        if (p.alibi_slopes) sum = write_probs<T, true, true>(t_s, sp, r, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+        else if (tile_full) sum = write_probs<T, false, false>(t_s, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        else sum = write_probs<T, true, false>(t_s, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        l += sum;
+        // P visible to the tensor core (async proxy), S reads and O writes finished: hand over.
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_p);
-        if (!ptx::mbar_wait(bar_o, g & 1)) {
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t t[32];
-          ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(t[i]);
-        }
-        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_p);
       }
-      if (ok && qi < seq_len) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
+      if (!ok) break;
+      // Unit finished: wait for its last P V, read the output row, normalise, store.
+      if (!ptx::mbar_wait(bar_o, (g - 1) & 1)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-          uint4 v;
-          v.x = pack2<T>(o[c * 8 + 0] * inv, o[c * 8 + 1] * inv);
-          v.y = pack2<T>(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-          v.z = pack2<T>(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-          v.w = pack2<T>(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + c * 8) = v;
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t t[32];
+        ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
+        ptx::tmem_ld_wait();
+        if (qi < seq_len) {
+#pragma unroll
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
+            v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
+            v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
+            v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = v;
+          }
         }
       }
+      ptx::tc_fence_before();
     }
     if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
   }
