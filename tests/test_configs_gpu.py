@@ -1,0 +1,93 @@
+"""Full-width architectures of the benchmark configurations (BERT-base, NomicBERT-768,
+XLM-RoBERTa-large reranker, Qwen3-0.6B-style), random-init, against the fp32 CPU oracle on
+subsets of their seeded batches that the oracle finishes in seconds.
+
+Vocabularies of the two large models are cut to 32k rows for the test (the embedding table is a
+plain gather; every other dimension is the real one).  Tolerances: pooled embeddings after L2
+normalisation cosine >= 0.9999 and max-abs <= 2e-2 (fp16); reranker logits abs <= 1e-2; bf16
+cosine >= 0.999 (8 mantissa bits per stored activation; the reference's own bar).
+"""
+import numpy as np
+import pytest
+
+from oracle import generators as G
+from oracle import models as M
+
+pytestmark = pytest.mark.gpu
+
+
+def _cos(a, b):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return (a * b).sum(-1) / np.sqrt((a * a).sum(-1) * (b * b).sum(-1))
+
+
+def _pooled(got, n):
+    return np.stack([got[i].values for i in range(n)])
+
+
+def test_cfg1_bert_base_cls_512(lib, tmp_path):
+    import tei_b200
+    d = G.write_model_dir(tmp_path / "m", G.bert_config(), seed=0)
+    full = G.batch_cfg1()
+    assert len(full) == 32 and int(full.cumulative_seq_lengths[-1]) == 16384
+    assert full.input_ids[0] == 101 and full.input_ids[511] == 102
+    cu = full.cumulative_seq_lengths
+    sub = G.batch_from_encodings([full.input_ids[cu[i]:cu[i + 1]] for i in range(2)], [0, 1], [])
+    be = tei_b200.B200Backend(d, "float16", "embedding", "cls")
+    ref = M.build_oracle(d, "embedding", "cls").embed(sub)[0].numpy()
+    got_full = _pooled(be.embed(full), 32)
+    assert _cos(got_full[:2], ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got_full[:2]) - M.l2_normalise(ref)).max() <= 2e-2
+    # the same two sequences alone give the same rows as inside the batch of 32
+    got_sub = _pooled(be.embed(sub), 2)
+    assert _cos(got_sub, got_full[:2]).min() >= 0.99999
+    be.close()
+
+
+def test_cfg3_nomic_long_context_mean(lib, tmp_path):
+    import tei_b200
+    d = G.write_model_dir(tmp_path / "m", G.nomic_config(), seed=2)
+    sub = G.batch_cfg3(n_seqs=3)  # 1364 + 1210 + 1884 tokens
+    assert int(sub.max_length) > 512
+    be = tei_b200.B200Backend(d, "float16", "embedding", "mean")
+    ref = M.build_oracle(d, "embedding", "mean").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert _cos(got, ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()
+
+
+def test_cfg4_xlm_roberta_large_reranker(lib, tmp_path):
+    import tei_b200
+    cfg = G.bert_config(hidden=1024, layers=24, heads=16, inter=4096, vocab=32000, max_pos=514, type_vocab=1,
+                        model_type="xlm-roberta", pad_token_id=1, id2label={"0": "LABEL_0"})
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=4, classifier="roberta")
+    full = G.batch_cfg4(n_pairs=8)
+    full.input_ids = (full.input_ids % 32000).astype(np.uint32)  # vocabulary cut for the test
+    assert full.position_ids[0] == 2  # RoBERTa-family offset
+    be = tei_b200.B200Backend(d, "float16", "classifier")
+    ref = M.build_oracle(d, "classifier").predict(full).numpy()
+    got = be.predict(full)
+    g = np.array([got[i] for i in range(len(full))], dtype=np.float32)
+    assert g.shape == ref.shape == (8, 1)
+    assert np.abs(g - ref).max() <= 1e-2
+    assert np.abs(M.sigmoid_scores(g) - M.sigmoid_scores(ref)).max() <= 1e-2
+    be.close()
+
+
+@pytest.mark.parametrize("dtype,cos_min", [("float16", 0.9999), ("bfloat16", 0.999)])
+def test_cfg5_qwen3_last_token(lib, tmp_path, dtype, cos_min):
+    import tei_b200
+    cfg = G.qwen3_config(vocab=32000)
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=5)
+    rng = np.random.default_rng(60)
+    lens = [137, 1030, 2300]
+    encs = [rng.integers(1000, 32000, size=n) for n in lens]
+    sub = G.batch_from_encodings(encs, list(range(len(encs))), [])
+    be = tei_b200.B200Backend(d, dtype, "embedding", "last_token")
+    ref = M.build_oracle(d, "embedding", "last_token").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert np.isfinite(got).all()
+    assert _cos(got, ref).min() >= cos_min
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()

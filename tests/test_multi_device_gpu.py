@@ -1,0 +1,66 @@
+"""One handle, several replicas: the packed batch is split at sequence boundaries across the
+GPUs inside a single embed / predict call and the rows come back in their original places.
+Needs at least two GPUs (skipped otherwise).  No collective runs: each replica computes its
+sequences independently."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from oracle import generators as G  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _n_gpus():
+    import torch
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+needs_two = pytest.mark.skipif(_n_gpus() < 2, reason="needs two GPUs")
+
+
+@needs_two
+def test_sharded_embed_matches_single_replica(lib, model_dirs):
+    import tei_b200
+    n = min(_n_gpus(), 4)
+    one = tei_b200.B200Backend(model_dirs["bert"], "float16", "embedding", "mean", devices=[0])
+    many = tei_b200.B200Backend(model_dirs["bert"], "float16", "embedding", "mean", devices=list(range(n)))
+    lens = [7, 300, 33, 150, 2, 64, 129, 511, 90]
+    b = G.random_batch(5, lens, 0, 1000, pooled=[0, 2, 3, 6, 8], raw=[1, 4, 5, 7], type_vocab=2)
+    a, m = one.embed(b), many.embed(b)
+    assert sorted(a) == sorted(m) == list(range(len(lens)))
+    for i in range(len(lens)):
+        assert a[i].kind == m[i].kind and a[i].values.shape == m[i].values.shape
+        # same kernels, same per-sequence inputs: the rows agree to rounding of the GEMM tiling
+        assert np.abs(a[i].values - m[i].values).max() <= 4e-3
+    # a single-sequence batch stays on the first replica
+    solo = G.random_batch(6, [40], 0, 1000, type_vocab=2)
+    assert np.array_equal(one.embed(solo)[0].values, many.embed(solo)[0].values)
+    st = many.stats()
+    assert st["tokens"] > 0
+    one.close()
+    many.close()
+
+
+@needs_two
+def test_sharded_predict_and_errors(lib, model_dirs):
+    import tei_b200
+    one = tei_b200.B200Backend(model_dirs["xlmr"], "float16", "classifier", devices=[0])
+    two = tei_b200.B200Backend(model_dirs["xlmr"], "float16", "classifier", devices=[0, 1])
+    b = G.random_batch(7, [12, 200, 31, 77, 5], 5, 1000, position_offset=2)
+    a, m = one.predict(b), two.predict(b)
+    for i in range(5):
+        assert abs(a[i][0] - m[i][0]) <= 2e-3
+    bad = G.random_batch(7, [12, 200], 5, 1000, position_offset=2)
+    bad.input_ids = np.full(212, 5000, dtype=np.uint32)
+    with pytest.raises(tei_b200.BackendError):
+        two.predict(bad)
+    two.health()
+    again = two.predict(b)
+    for i in range(5):
+        assert again[i] == m[i]
+    one.close()
+    two.close()
