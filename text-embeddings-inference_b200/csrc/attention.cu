@@ -321,7 +321,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           const int st = g & 1;
           const bool last = (j + 1 == n_kv);
           if (g > 0) {
-            ok = ptx::mbar_wait(bar_o, (g - 1) & 1);
+            ok = ptx::mbar_wait_spin(bar_o, (g - 1) & 1);
             if (!ok) break;
           }
           if (!last) {
@@ -333,7 +333,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             load_q(w_next);
             load_kv(w_next, 0, g + 1);
           }
-          ok = ptx::mbar_wait(bar_p, g & 1);
+          ok = ptx::mbar_wait_spin(bar_p, g & 1);
           if (!ok) break;
           ptx::tc_fence_after();
           // Next step's S first: the softmax warps can start on it while P V runs.
@@ -353,7 +353,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           issue_pv(st, (keys_in_tile(it, j) + 15) / 16, j != 0);
         }
       }
-      if (ok && g > 0) ok = ptx::mbar_wait(bar_o, (g - 1) & 1);
+      if (ok && g > 0) ok = ptx::mbar_wait_spin(bar_o, (g - 1) & 1);
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {

@@ -65,6 +65,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded busy-poll (no suspension): lowest wake-up latency, for a thread whose only job is to
+// react to the barrier.  Falls back to the suspending wait after a short burst.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity);
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < 4096; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+  }
+  return mbar_wait(bar, parity);
+}
 // Bounded wait.  Returns false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
