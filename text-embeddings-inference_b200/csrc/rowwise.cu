@@ -177,7 +177,7 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
 //            (layers/rms_norm.rs:30-57); the running sum is kept in fp32 so that rounding does
 //            not pile up over the decoder's layers.
 template <class T, int MAXC, bool RMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (MAXC <= 3 ? 6 : 1))
 add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restrict__ gamma,
                 const T* __restrict__ beta, T* __restrict__ out, float* sum_out, int T_, int H,
                 float eps) {  // residual and sum_out may be the same buffer: no __restrict__
@@ -433,7 +433,8 @@ int embed_typed(const EmbedArgs& e, cudaStream_t st) {
       reinterpret_cast<const T*>(e.type_tab), reinterpret_cast<const T*>(e.pos_tab),             \
       reinterpret_cast<const T*>(e.gamma), reinterpret_cast<const T*>(e.beta),                   \
       reinterpret_cast<T*>(e.out), e.T, e.H, e.eps)
-  if (n_chunks <= 32 * 4) TEI_EMBED(4);
+  if (n_chunks <= 32 * 3) TEI_EMBED(3);
+  else if (n_chunks <= 32 * 4) TEI_EMBED(4);
   else if (n_chunks <= 32 * 8) TEI_EMBED(8);
   else TEI_EMBED(16);
 #undef TEI_EMBED
@@ -450,7 +451,8 @@ int norm_typed(const NormArgs& n, cudaStream_t st) {
       reinterpret_cast<const T*>(n.x), n.residual, reinterpret_cast<const T*>(n.gamma),          \
       reinterpret_cast<const T*>(n.beta), reinterpret_cast<T*>(n.out),                           \
       reinterpret_cast<float*>(n.sum_out), n.T, n.H, n.eps)
-  if (n_chunks <= 32 * 4) TEI_NORM(4);
+  if (n_chunks <= 32 * 3) TEI_NORM(3);
+  else if (n_chunks <= 32 * 4) TEI_NORM(4);
   else if (n_chunks <= 32 * 8) TEI_NORM(8);
   else TEI_NORM(16);
 #undef TEI_NORM
