@@ -23,6 +23,8 @@
 #include "ptx.cuh"
 #include "tmap.h"
 
+#include <cstdlib>
+
 namespace tei {
 namespace {
 
@@ -141,6 +143,143 @@ __device__ __forceinline__ void finish_and_store(float (&v)[32], const GemmParam
         if (res) x += to_f32<T>(res[j]);
         out[j] = from_f32<T>(x);
       }
+    }
+  }
+}
+
+// Epilogue of one 128 x 256 accumulator for one warp (32 rows): bias / activation / optional
+// residual, then either swizzled staging + TMA store (64 columns per step) or plain per-thread
+// stores.  t_row: TMEM address of the warp's lane quadrant in the accumulator; m0 / n0: first
+// row / column of the tile in the output.
+template <class T, int ACT>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
+                                              int m0, int n0, int quad, int lane, const T* bias,
+                                              bool bias_vec, bool vec_ok, uint8_t* stage_buf,
+                                              uint32_t& store_count, int n_out, int part = 0,
+                                              int n_parts = 1) {  // part: this warp's share of the columns
+  const int row = m0 + quad * 32 + lane;
+  if (p.tma_store) {
+    // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
+    constexpr int STEPS = (ACT == ACT_SWIGLU) ? 2 : 4;
+    const int o0 = (ACT == ACT_SWIGLU) ? n0 / 2 : n0;
+#pragma unroll 1
+    for (int c = part * (STEPS / n_parts); c < (part + 1) * (STEPS / n_parts); ++c) {
+      const int ocol = o0 + c * 64;
+      if (ocol >= n_out) break;  // uniform across the CTA
+      uint32_t packed[32];
+      if constexpr (ACT == ACT_SWIGLU) {
+        // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld32(t_row + c * 64 + hlf * 32, g);
+          ptx::tmem_ld32(t_row + 128 + c * 64 + hlf * 32, u);
+          ptx::tmem_ld_wait();
+          const int gcol = n0 + c * 64 + hlf * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float gv0 = __uint_as_float(g[j]), gv1 = __uint_as_float(g[j + 1]);
+            float uv0 = __uint_as_float(u[j]), uv1 = __uint_as_float(u[j + 1]);
+            if (bias) {
+              gv0 += to_f32<T>(bias[gcol + j]);
+              gv1 += to_f32<T>(bias[gcol + j + 1]);
+              uv0 += to_f32<T>(bias[gcol + 128 + j]);
+              uv1 += to_f32<T>(bias[gcol + 128 + j + 1]);
+            }
+            packed[hlf * 16 + j / 2] = pack2<T>(silu(gv0) * uv0, silu(gv1) * uv1);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t r[32];
+          ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
+          ptx::tmem_ld_wait();
+          const int col = n0 + c * 64 + hlf * 32;
+          float bv[32];
+          if (bias_vec && col + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 b4 = *reinterpret_cast<const uint4*>(bias + col + j * 8);
+              const T* bt = reinterpret_cast<const T*>(&b4);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) bv[j * 8 + e] = to_f32<T>(bt[e]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bv[j] = (bias && col + j < p.N) ? to_f32<T>(bias[col + j]) : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float x0 = apply_act<ACT>(__uint_as_float(r[j]) + bv[j]);
+            const float x1 = apply_act<ACT>(__uint_as_float(r[j + 1]) + bv[j + 1]);
+            packed[hlf * 16 + j / 2] = pack2<T>(x0, x1);
+          }
+        }
+      }
+      // The staging buffer used two stores ago must have been read out by its TMA store.
+      uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
+      if (lane == 0) ptx::tma_store_wait_read<1>();
+      __syncwarp();
+      // Row `lane` of the 32 x 64 tile: eight 16-byte chunks, chunk index XORed with
+      // (row & 7) as the 128-byte swizzle of the tensor map expects.
+      uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) * 16)) =
+            make_uint4(packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        // A box that starts beyond the last row has nothing to write (the tensor map would clip
+        // it anyway); the empty group keeps the wait_group accounting uniform.
+        if (m0 + quad * 32 < p.M) ptx::tma_store_2d(tm_c, buf, ocol, m0 + quad * 32);
+        ptx::tma_store_commit();
+      }
+      ++store_count;
+    }
+  } else if constexpr (ACT == ACT_SWIGLU) {
+    // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
+#pragma unroll 1
+    for (int c = part * (4 / n_parts); c < (part + 1) * (4 / n_parts); ++c) {
+      uint32_t g[32], u[32];
+      ptx::tmem_ld32(t_row + c * 32, g);
+      ptx::tmem_ld32(t_row + 128 + c * 32, u);
+      ptx::tmem_ld_wait();
+      float v[32];
+      const int gcol = n0 + c * 32;        // column in the interleaved weight
+      const int ocol = n0 / 2 + c * 32;    // output column
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float gv = __uint_as_float(g[j]);
+        float uv = __uint_as_float(u[j]);
+        if (bias) {
+          if (gcol + j < p.N) gv += to_f32<T>(bias[gcol + j]);
+          if (gcol + 128 + j < p.N) uv += to_f32<T>(bias[gcol + 128 + j]);
+        }
+        v[j] = silu(gv) * uv;
+      }
+      const int n_valid = min(32, p.N / 2 - ocol);
+      if (row < p.M && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
+    }
+  } else {
+#pragma unroll 1
+    for (int c = part * (BN / 32 / n_parts); c < (part + 1) * (BN / 32 / n_parts); ++c) {
+      const int col = n0 + c * 32;
+      if (col >= p.N) break;  // uniform across the CTA
+      uint32_t r[32];
+      ptx::tmem_ld32(t_row + c * 32, r);
+      ptx::tmem_ld_wait();
+      float v[32];
+      const int n_valid = min(32, p.N - col);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float x = __uint_as_float(r[j]);
+        if (bias && j < n_valid) x += to_f32<T>(bias[col + j]);
+        v[j] = apply_act<ACT>(x);
+      }
+      if (row < p.M) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
     }
   }
 }
@@ -282,130 +421,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         break;
       }
       ptx::tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      if (p.tma_store) {
-        // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
-        constexpr int STEPS = (ACT == ACT_SWIGLU) ? 2 : 4;
-        const int o0 = (ACT == ACT_SWIGLU) ? n0 / 2 : n0;
-#pragma unroll 1
-        for (int c = 0; c < STEPS; ++c) {
-          const int ocol = o0 + c * 64;
-          if (ocol >= n_out) break;  // uniform across the CTA
-          uint32_t packed[32];
-          if constexpr (ACT == ACT_SWIGLU) {
-            // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-              uint32_t g[32], u[32];
-              ptx::tmem_ld32(t_row + c * 64 + hlf * 32, g);
-              ptx::tmem_ld32(t_row + 128 + c * 64 + hlf * 32, u);
-              ptx::tmem_ld_wait();
-              const int gcol = n0 + c * 64 + hlf * 32;
-#pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                float gv0 = __uint_as_float(g[j]), gv1 = __uint_as_float(g[j + 1]);
-                float uv0 = __uint_as_float(u[j]), uv1 = __uint_as_float(u[j + 1]);
-                if (bias) {
-                  gv0 += to_f32<T>(bias[gcol + j]);
-                  gv1 += to_f32<T>(bias[gcol + j + 1]);
-                  uv0 += to_f32<T>(bias[gcol + 128 + j]);
-                  uv1 += to_f32<T>(bias[gcol + 128 + j + 1]);
-                }
-                packed[hlf * 16 + j / 2] = pack2<T>(silu(gv0) * uv0, silu(gv1) * uv1);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
-              uint32_t r[32];
-              ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
-              ptx::tmem_ld_wait();
-              const int col = n0 + c * 64 + hlf * 32;
-              float bv[32];
-              if (bias_vec && col + 32 <= p.N) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint4 b4 = *reinterpret_cast<const uint4*>(bias + col + j * 8);
-                  const T* bt = reinterpret_cast<const T*>(&b4);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) bv[j * 8 + e] = to_f32<T>(bt[e]);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) bv[j] = (bias && col + j < p.N) ? to_f32<T>(bias[col + j]) : 0.f;
-              }
-#pragma unroll
-              for (int j = 0; j < 32; j += 2) {
-                const float x0 = apply_act<ACT>(__uint_as_float(r[j]) + bv[j]);
-                const float x1 = apply_act<ACT>(__uint_as_float(r[j + 1]) + bv[j + 1]);
-                packed[hlf * 16 + j / 2] = pack2<T>(x0, x1);
-              }
-            }
-          }
-          // The staging buffer used two stores ago must have been read out by its TMA store.
-          uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
-          if (lane == 0) ptx::tma_store_wait_read<1>();
-          __syncwarp();
-          // Row `lane` of the 32 x 64 tile: eight 16-byte chunks, chunk index XORed with
-          // (row & 7) as the 128-byte swizzle of the tensor map expects.
-          uint8_t* rowp = buf + lane * 128;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) * 16)) =
-                make_uint4(packed[q * 4 + 0], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_2d(&tm_c, buf, ocol, m0 + quad * 32);
-            ptx::tma_store_commit();
-          }
-          ++store_count;
-        }
-      } else if constexpr (ACT == ACT_SWIGLU) {
-        // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t g[32], u[32];
-          ptx::tmem_ld32(t_row + c * 32, g);
-          ptx::tmem_ld32(t_row + 128 + c * 32, u);
-          ptx::tmem_ld_wait();
-          float v[32];
-          const int gcol = n0 + c * 32;        // column in the interleaved weight
-          const int ocol = n0 / 2 + c * 32;    // output column
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float gv = __uint_as_float(g[j]);
-            float uv = __uint_as_float(u[j]);
-            if (bias) {
-              if (gcol + j < p.N) gv += to_f32<T>(bias[gcol + j]);
-              if (gcol + 128 + j < p.N) uv += to_f32<T>(bias[gcol + 128 + j]);
-            }
-            v[j] = silu(gv) * uv;
-          }
-          const int n_valid = min(32, p.N / 2 - ocol);
-          if (row < p.M && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= p.N) break;  // uniform across the CTA
-          uint32_t r[32];
-          ptx::tmem_ld32(t_row + c * 32, r);
-          ptx::tmem_ld_wait();
-          float v[32];
-          const int n_valid = min(32, p.N - col);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(r[j]);
-            if (bias && j < n_valid) x += to_f32<T>(bias[col + j]);
-            v[j] = apply_act<ACT>(x);
-          }
-          if (row < p.M) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
-        }
-      }
+      epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
+                            n_out);
       // Hand the accumulator back to the MMA warp.
       ptx::tc_fence_before();
       __syncwarp();
@@ -421,6 +439,199 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): a cluster of two CTAs computes one 256 x 256 output tile.
+// Each CTA loads its own 128 rows of A and HALF of the W tile (128 of the 256 rows) per stage -
+// 32 KB instead of 48 KB for the same 128 x 256 x 64 of work - so the L2 -> shared-memory
+// traffic, which bounds the single-CTA kernel on these shapes, drops by a third.  The freed
+// shared memory pays for eight epilogue warps (two per TMEM lane quadrant, half of the columns
+// each), which halves the time an accumulator stays busy.  The even CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads both
+// CTAs' shared memory and writes each CTA's 128 x 256 accumulator in its own TMEM; commits are
+// multicast to the mbarriers of both CTAs.  TMA loads are plain per-CTA loads whose bytes are
+// counted on the even CTA's "full" barrier.
+constexpr int P_STAGES = 5;
+constexpr int P_EPI_WARPS = 8;  // two warps per TMEM lane quadrant, each takes half of the columns
+constexpr int P_THREADS = (2 + P_EPI_WARPS) * 32;
+constexpr int P_EPI_BYTES = P_EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr int P_B_BYTES = 128 * BK * 2;
+constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 + 256;
+
+template <class T, int ACT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                         const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // The same offset in both CTAs: shared-memory windows of a cluster's CTAs are congruent.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_smem = smem + P_STAGES * P_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + P_EPI_BYTES);
+  uint64_t* full_bar = bars;                       // [P_STAGES] used in the even CTA only
+  uint64_t* empty_bar = bars + P_STAGES;           // [P_STAGES] one per CTA, signalled by commit
+  uint64_t* acc_full = bars + 2 * P_STAGES;        // [2] one per CTA, signalled by commit
+  uint64_t* acc_empty = bars + 2 * P_STAGES + 2;   // [2] used in the even CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tmap(&tm_a);
+    ptx::prefetch_tmap(&tm_b);
+    if (p.tma_store) ptx::prefetch_tmap(&tm_c);
+    for (int s = 0; s < P_STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&acc_full[i], 1);
+      ptx::mbar_init(&acc_empty[i], 2 * P_EPI_WARPS);  // one arrival per epilogue warp of both CTAs
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+        const int n0 = (tile % tiles_n) * BN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            atomicExch(p.status, DEV_TIMEOUT_PRODUCER);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * P_STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          // The even CTA arms its barrier for the bytes of both CTAs.
+          if (rank == 0) ptx::mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+          const uint32_t bar = ptx::smem_u32(&full_bar[stage]) & ptx::kPeerBitMask;
+          ptx::tma_load_2d_pair(sa, &tm_a, bar, kb * BK, m0);
+          ptx::tma_load_2d_pair(sb, &tm_b, bar, kb * BK, n0);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, 2 * BM, BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1)) {
+          atomicExch(p.status, DEV_TIMEOUT_MMA);
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(&full_bar[stage], phase)) {
+            atomicExch(p.status, DEV_TIMEOUT_MMA);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa = ptx::smem_u32(smem + stage * P_STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = ptx::make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bd = ptx::make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            ptx::umma_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit_pair(&empty_bar[stage], 3);  // the stage is free in both CTAs
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) ptx::umma_commit_pair(&acc_full[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const int quad = warp & 3;           // TMEM lane quadrant this warp may read
+    const int part = (warp - 2) >> 2;    // which half of the 256 columns it handles
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const bool vec_ok = (p.ldo % 8 == 0) && (p.residual == nullptr || p.ldr % 8 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
+    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+    uint8_t* stage_buf = epi_smem + (warp - 2) * (2 * EPI_BUF_BYTES);
+    uint32_t store_count = 0;
+    const int n_out = (ACT == ACT_SWIGLU) ? p.N / 2 : p.N;
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+      const int n0 = (tile % tiles_n) * BN;
+      if (!ptx::mbar_wait(&acc_full[acc], acc_phase)) {
+        if (lane == 0) atomicExch(p.status, DEV_TIMEOUT_EPILOGUE);
+        break;
+      }
+      ptx::tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
+                            n_out, part, 2);
+      // Hand the accumulator back to the MMA thread of the even CTA.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::smem_u32(&acc_empty[acc]) & ptx::kPeerBitMask);
+    }
+    if (p.tma_store && lane == 0) ptx::tma_store_wait<0>();
+  }
+
+  // Neither CTA may leave while the other can still read its shared memory or signal its
+  // barriers.
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// TEI_B200_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel (for A/B timing).
+inline bool pair_mode_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("TEI_B200_GEMM_PAIR");
+    return !(v && v[0] == '0');
+  }();
+  return on;
 }
 
 template <class T, int ACT>
@@ -446,14 +657,8 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   // The opt-in shared-memory size is a per-device function attribute; setting it twice is
   // harmless, so a plain flag per device (and per instantiation) is enough.
   static bool attr_set[64] = {};
-  auto kern = gemm_tcgen05_kernel<T, ACT>;
+  static bool attr_set_pair[64] = {};
   const int dev = current_device() & 63;
-  if (!attr_set[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set[dev] = true;
-  }
   GemmParams p;
   p.bias = g.bias;
   p.residual = g.residual;
@@ -465,6 +670,30 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   p.ldr = g.ldr;
   p.tma_store = tma_store ? 1 : 0;
   p.status = g.status;
+  if (g.M > BM && pair_mode_enabled()) {
+    // CTA pairs: 256 x 256 tiles, W loaded in halves of 128 rows.
+    CUtensorMap tm_b2;
+    rc = make_tmap_2d(&tm_b2, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, 128);
+    if (rc) return rc;
+    auto kern2 = gemm_tcgen05_pair_kernel<T, ACT>;
+    if (!attr_set_pair[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      attr_set_pair[dev] = true;
+    }
+    const int tiles2 = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
+    const int max_pairs = num_sms() / 2;
+    const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
+    kern2<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b2, tm_c, p);
+    return static_cast<int>(cudaGetLastError());
+  }
+  auto kern = gemm_tcgen05_kernel<T, ACT>;
+  if (!attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, p);
