@@ -8,44 +8,46 @@
 // the projection output (token-major rows), exactly as the reference passes them.
 //
 // Persistent CTAs (two per SM for D = 64) walk the (sequence, 128-row query tile, head) work
-// units, most expensive first; the next unit's Q and first K/V tile are fetched while the
-// current one finishes.  Within a CTA:
-//   warp 4 (one elected lane)  TMA loads (Q once, K/V double-buffered, 128-byte swizzle, no
-//                              cluster multicast) and tcgen05.mma issue:
-//                              S = Q K^T into TMEM columns [0,128), P V into columns [128,128+D).
-//   warps 0-3 (one row each)   read S from TMEM, online softmax in fp32 registers, write P as
-//                              fp16/bf16 into shared memory in the K-major swizzled operand
-//                              layout.  P V accumulates in TMEM across the key tiles; the
-//                              running maximum is raised lazily (only when it grows by more
-//                              than 2^8), in which case the rows rescale their partial output
-//                              in TMEM.  At the end the row is read, normalised and stored.
-// Two CTAs fit on an SM (D = 64), so one CTA's softmax overlaps the other's MMAs.
+// units, most expensive first, in steps of 64 keys.  Everything a step needs is double- or
+// triple-buffered, so the three roles of a CTA run decoupled:
+//   warp 5 (one lane)  TMA producer: Q tile per unit (2 buffers), K/V tiles per step (3 stages),
+//                      128-byte swizzle, plain per-CTA loads (no cluster multicast); runs up to
+//                      three steps and one unit ahead.
+//   warp 4 (one lane)  MMA issuer: S = Q K^T of step g+1 into the other of two 64-column score
+//                      buffers in TMEM while the softmax warps still work on step g, then
+//                      O += P V of step g (V as MN-major operand) into TMEM columns [128,128+D).
+//   warps 0-3          one query row per thread: row maximum and exp2 straight from TMEM, P
+//                      written as fp16/bf16 into one of two swizzled K-major operand tiles in
+//                      shared memory.  O stays in TMEM across the key steps; the running maximum
+//                      is raised lazily (only when it grows by more than 2^8), in which case the
+//                      rows rescale their partial output in TMEM.  At the end of a unit the row
+//                      is read, normalised and stored.
 // Every mbarrier wait is bounded and reports through *status instead of spinning forever.
 #include "kernels.h"
 #include "ptx.cuh"
 #include "tmap.h"
 
-
 namespace tei {
 namespace {
 
-constexpr int BQ = 128;   // query rows per CTA
-constexpr int BKV = 128;  // keys per inner step
-constexpr int ATTN_THREADS = 160;
+constexpr int BQ = 128;  // query rows per CTA
+constexpr int BKV = 64;  // keys per step
+constexpr int KV_STAGES = 3;
+constexpr int ATTN_THREADS = 192;
 
 template <int D>
 struct AttnSmem {
   static constexpr int Q_BYTES = BQ * D * 2;
-  static constexpr int KV_BYTES = BKV * D * 2;
+  static constexpr int KV_BYTES = BKV * D * 2;   // one K or one V tile
   static constexpr int P_BYTES = BQ * BKV * 2;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // 2 stages
-  static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_Q = 0;                               // 2 buffers
+  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;             // KV_STAGES stages
+  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;    // KV_STAGES stages
+  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;    // 2 buffers
+  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
   // No alignment slack: two CTAs of the D = 64 variant must fit in one SM's shared memory.  The
   // kernel checks that the dynamic window is 1024-byte aligned and reports an error otherwise.
-  static constexpr int TOTAL = OFF_BAR + 128;
+  static constexpr int TOTAL = OFF_BAR + 160;  // 16 mbarriers + the TMEM address slot
 };
 
 struct AttnParams {
@@ -90,22 +92,20 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
-// One thread owns one query row of the 128-key score tile that sits in TMEM at `tmem_row`.
+// One thread owns one query row of the 64-key score tile; the row is read from TMEM into
+// registers once per step (one wait) and both passes work from there.
 // Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.
 // ALIBI: subtract slope * |rel - key| (rel = query position - first key position of the tile).
-// Two passes over TMEM keep the register footprint at one 32-column chunk (keeping the whole
-// row in registers was measured slower: it costs occupancy-critical registers).
 //
 // Pass 1: row maximum in the scaled log2 domain (-inf when the row sees no key).
 template <bool MASKED, bool ALIBI>
-__device__ __forceinline__ float row_max(uint32_t tmem_row, int lim, int n_chunks, float sl2, float slope,
-                                         int rel) {
+__device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int lim, int n_chunks, float sl2,
+                                         float slope, int rel) {
   float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-  for (int c = 0; c < n_chunks; ++c) {
-    uint32_t s[32];
-    ptx::tmem_ld32(tmem_row + c * 32, s);
-    ptx::tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < BKV / 32; ++c) {
+    if (c >= n_chunks) break;
+    const uint32_t (&s)[32] = sc[c];
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
       float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
@@ -136,14 +136,13 @@ __device__ __forceinline__ float row_max(uint32_t tmem_row, int lim, int n_chunk
 // Pass 2: p = 2^(score - m_use), written as T into the K-major 128-byte-swizzled operand tile
 // `sp` ([k atom of 64][row][64], 16-byte chunk index XORed with (row & 7)); returns the row sum.
 template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ float write_probs(uint32_t tmem_row, uint8_t* sp, int r, int lim, int n_chunks,
-                                             float sl2, float slope, int rel, float m_use) {
+__device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint8_t* sp, int r, int lim,
+                                             int n_chunks, float sl2, float slope, int rel, float m_use) {
   float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll 1
-  for (int c = 0; c < n_chunks; ++c) {
-    uint32_t s[32];
-    ptx::tmem_ld32(tmem_row + c * 32, s);
-    ptx::tmem_ld_wait();
+#pragma unroll
+  for (int c = 0; c < BKV / 32; ++c) {
+    if (c >= n_chunks) break;
+    const uint32_t (&s)[32] = sc[c];
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -180,6 +179,7 @@ __device__ __forceinline__ float write_probs(uint32_t tmem_row, uint8_t* sp, int
 // fp16 / bf16 range) and the accumulator in TMEM needs no rescaling.
 constexpr float kRescaleThreshold = 8.0f;
 
+
 template <class T, int D>
 __global__ void __launch_bounds__(ATTN_THREADS, (D == 64 ? 2 : 1))
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -194,12 +194,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     return;
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* bar_q = bars;          // Q tile landed
-  uint64_t* bar_kv = bars + 1;     // [2] K/V stage landed
-  uint64_t* bar_s = bars + 3;      // S = Q K^T finished
-  uint64_t* bar_p = bars + 4;      // P written (one arrival per softmax warp)
-  uint64_t* bar_o = bars + 5;      // P V finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* bar_q = bars;            // [2] Q buffer landed
+  uint64_t* bar_qfree = bars + 2;    // [2] last S of the unit that used the Q buffer is done
+  uint64_t* bar_kv = bars + 4;       // [3] K/V stage landed
+  uint64_t* bar_kvfree = bars + 7;   // [3] the P V that read the stage is done
+  uint64_t* bar_s = bars + 10;       // [2] S buffer holds the scores of its step
+  uint64_t* bar_p = bars + 12;       // [2] P buffer written, S buffer read (one arrival per warp)
+  uint64_t* bar_pv = bars + 14;      // [2] the P V that read the P buffer is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   constexpr uint32_t TMEM_COLS = 256;
 
   const int warp = threadIdx.x >> 5;
@@ -207,12 +209,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int total = p.n_work * p.n_heads;  // work units: (sequence, query tile) x head
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar_q, 1);
-    ptx::mbar_init(&bar_kv[0], 1);
-    ptx::mbar_init(&bar_kv[1], 1);
-    ptx::mbar_init(bar_s, 1);
-    ptx::mbar_init(bar_p, 4);  // one arrival per softmax warp
-    ptx::mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&bar_q[i], 1);
+      ptx::mbar_init(&bar_qfree[i], 1);
+      ptx::mbar_init(&bar_s[i], 1);
+      ptx::mbar_init(&bar_p[i], 4);
+      ptx::mbar_init(&bar_pv[i], 1);
+    }
+    for (int i = 0; i < KV_STAGES; ++i) {
+      ptx::mbar_init(&bar_kv[i], 1);
+      ptx::mbar_init(&bar_kvfree[i], 1);
+    }
     ptx::fence_mbar_init();
   }
   if (warp == 4) {
@@ -223,149 +230,191 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + 128;
+  // Scores: columns [0,64) and [64,128).  Output tiles from column 128 on: two of them for
+  // D = 64 (units alternate), so that a finished unit's rows can be read out while the next
+  // unit is already running; one for D = 128.
+  constexpr int O_BUFS = (D == 64) ? 2 : 1;
+  const uint32_t tmem_o0 = tmem_base + 128;
   const int group = p.n_heads / p.n_kv_heads;
 
+  // Steps of one unit: 64-key tiles up to the last key any row of the query tile can see.
+  auto unit_steps = [&](const int* it) {
+    const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
+    return (kv_end + BKV - 1) / BKV;
+  };
+  // Number of keys of step j of a unit that any row can see (CTA-uniform).
+  auto keys_in_tile = [&](const int* it, int j) {
+    const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
+    return min(BKV, kv_end - j * BKV);
+  };
+
   // The CTA is persistent: it walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...
-  // `g` counts key/value steps over the CTA's whole life and drives every barrier parity.
-  if (warp == 4) {
+  // `g` counts key steps over the CTA's whole life, `n` counts units; they drive every buffer
+  // index and barrier parity in all three roles.
+  if (warp == 5) {
+    // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       ptx::prefetch_tmap(&tm_q);
       ptx::prefetch_tmap(&tm_k);
       ptx::prefetch_tmap(&tm_v);
-      // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
-      constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
-      auto load_q = [&](int w) {
+      uint32_t g = 0, n = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
         const int* it = p.work + (w / p.n_heads) * 4;
         const int head = w % p.n_heads;
-        ptx::mbar_expect_tx(bar_q, L::Q_BYTES);
+        const int kv_head = head / group;
+        const int n_kv = unit_steps(it);
+        // Q of this unit into buffer n & 1, once the unit that used it two units ago is past
+        // its last S.
+        const int qb = n & 1;
+        if (n >= 2) {
+          ok = ptx::mbar_wait(&bar_qfree[qb], ((n >> 1) - 1) & 1);
+          if (!ok) break;
+        }
+        ptx::mbar_expect_tx(&bar_q[qb], L::Q_BYTES);
 #pragma unroll
         for (int a = 0; a < D_ATOMS; ++a) {
-          ptx::tma_load_2d(smem + L::OFF_Q + a * (BQ * 128), &tm_q, bar_q, head * D + a * 64, it[0] + it[2]);
+          ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * 128), &tm_q, &bar_q[qb],
+                           head * D + a * 64, it[0] + it[2]);
         }
-      };
-      auto load_kv = [&](int w, int j, uint32_t step) {
-        const int* it = p.work + (w / p.n_heads) * 4;
-        const int kv_head = (w % p.n_heads) / group;
-        const int st = step & 1;
-        ptx::mbar_expect_tx(&bar_kv[st], 2 * L::KV_BYTES);
+        for (int j = 0; j < n_kv && ok; ++j, ++g) {
+          const int st = g % KV_STAGES;
+          if (g >= KV_STAGES) {
+            ok = ptx::mbar_wait(&bar_kvfree[st], ((g / KV_STAGES) - 1) & 1);
+            if (!ok) break;
+          }
+          ptx::mbar_expect_tx(&bar_kv[st], 2 * L::KV_BYTES);
 #pragma unroll
-        for (int a = 0; a < D_ATOMS; ++a) {
-          ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_kv[st],
-                           kv_head * D + a * 64, it[0] + j * BKV);
-          ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, &bar_kv[st],
-                           kv_head * D + a * 64, it[0] + j * BKV);
+          for (int a = 0; a < D_ATOMS; ++a) {
+            ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_kv[st],
+                             kv_head * D + a * 64, it[0] + j * BKV);
+            ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, &bar_kv[st],
+                             kv_head * D + a * 64, it[0] + j * BKV);
+          }
         }
-      };
-      // Number of keys of step j of a unit that any row can see (CTA-uniform).
-      auto keys_in_tile = [&](const int* it, int j) {
-        const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
-        return min(BKV, kv_end - j * BKV);
-      };
+      }
+      if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
+      constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
       // Operand descriptors are built once; each MMA adds a constant to the address field
       // (units of 16 bytes; every operand sits below 256 KB, so the 14-bit field cannot carry).
       const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
       const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
       const uint64_t dp = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_P), 16, 1024);
       const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
-      // S = Q K^T for the K tile in stage `st`; only the first ceil(keys/32)*32 columns are
-      // computed (the softmax reads no more than that).
-      auto issue_s = [&](int st, int keys) {
-        const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 31) / 32) * 32, 0, 0);
-        const uint64_t dks = dk + static_cast<uint64_t>((st * L::KV_BYTES) >> 4);
+      // S = Q K^T for step `step` (Q buffer qb): only ceil(keys/16)*16 columns are computed.
+      auto issue_s = [&](uint32_t step, int qb, int keys, bool last_of_unit) {
+        const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 15) / 16) * 16, 0, 0);
+        const uint64_t dqs = dq + static_cast<uint64_t>((qb * L::Q_BYTES) >> 4);
+        const uint64_t dks = dk + static_cast<uint64_t>(((step % KV_STAGES) * L::KV_BYTES) >> 4);
+        const uint32_t d_s = tmem_base + (step & 1) * BKV;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          constexpr int kAtom = BQ * 128;
-          const uint64_t off = static_cast<uint64_t>(((k / 4) * kAtom + (k % 4) * 32) >> 4);
-          ptx::umma_ss(tmem_s, dq + off, dks + off, idesc_s, k != 0 ? 1u : 0u);
+          const uint64_t qoff = static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
+          const uint64_t koff = static_cast<uint64_t>(((k / 4) * (BKV * 128) + (k % 4) * 32) >> 4);
+          ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
         }
-        ptx::umma_commit(bar_s);
+        ptx::umma_commit(&bar_s[step & 1]);
+        if (last_of_unit) ptx::umma_commit(&bar_qfree[qb]);
       };
-      // O (+)= P V over the first k_steps * 16 keys of the tile in stage `st`.
-      auto issue_pv = [&](int st, int k_steps, bool accumulate) {
-        const uint64_t dvs = dv + static_cast<uint64_t>((st * L::KV_BYTES) >> 4);
-#pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          if (k < k_steps) {
-            constexpr int kAtom = BQ * 128;
-            const uint64_t aoff = static_cast<uint64_t>(((k / 4) * kAtom + (k % 4) * 32) >> 4);
-            ptx::umma_ss(tmem_o, dp + aoff, dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o,
-                         (accumulate || k != 0) ? 1u : 0u);
-          }
-        }
-        ptx::umma_commit(bar_o);
-      };
-      uint32_t g = 0, n_item = 0;
+      uint32_t g = 0, n = 0;
       bool ok = true;
+      // Prologue: S of the very first step.
       if (static_cast<int>(blockIdx.x) < total) {
-        load_q(blockIdx.x);
-        load_kv(blockIdx.x, 0, 0);
-        ok = ptx::mbar_wait(bar_q, 0) && ptx::mbar_wait(&bar_kv[0], 0);
+        const int* it0 = p.work + (blockIdx.x / p.n_heads) * 4;
+        ok = ptx::mbar_wait(&bar_q[0], 0) && ptx::mbar_wait(&bar_kv[0], 0);
         if (ok) {
           ptx::tc_fence_after();
-          issue_s(0, keys_in_tile(p.work + (blockIdx.x / p.n_heads) * 4, 0));
+          issue_s(0, 0, keys_in_tile(it0, 0), unit_steps(it0) == 1);
         }
       }
-      // Invariant at the top of every step g: S of step g has been issued.  Each step then
-      // (1) waits for the previous step's P V (its K/V stage becomes free) and starts the loads
-      // of the next step, (2) waits for P, (3) issues the NEXT step's S and, behind it, this
-      // step's P V, which accumulates into the output tile in TMEM.
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n_item) {
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
         const int* it = p.work + (w / p.n_heads) * 4;
-        const int seq_len = it[1], q0 = it[2];
-        const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
-        const int n_kv = (kv_end + BKV - 1) / BKV;
+        const int n_kv = unit_steps(it);
         const int w_next = w + static_cast<int>(gridDim.x);
+        const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
         for (int j = 0; j < n_kv && ok; ++j, ++g) {
-          const int st = g & 1;
-          const bool last = (j + 1 == n_kv);
-          if (g > 0) {
-            ok = ptx::mbar_wait_spin(bar_o, (g - 1) & 1);
+          // (1) S of step g+1 into the other score buffer.  That buffer was last read by the
+          // softmax of step g-1, whose bar_p this thread waited for before issuing P V of g-1.
+          if (j + 1 < n_kv) {
+            ok = ptx::mbar_wait(&bar_kv[(g + 1) % KV_STAGES], ((g + 1) / KV_STAGES) & 1);
             if (!ok) break;
-          }
-          if (!last) {
-            load_kv(w, j + 1, g + 1);
+            ptx::tc_fence_after();
+            issue_s(g + 1, n & 1, keys_in_tile(it, j + 1), j + 2 == n_kv);
           } else if (w_next < total) {
-            // Last step of this unit: once its S is done nothing reads the Q tile any more.
-            ok = ptx::mbar_wait(bar_s, g & 1);
+            const int* itn = p.work + (w_next / p.n_heads) * 4;
+            ok = ptx::mbar_wait(&bar_q[(n + 1) & 1], ((n + 1) >> 1) & 1) &&
+                 ptx::mbar_wait(&bar_kv[(g + 1) % KV_STAGES], ((g + 1) / KV_STAGES) & 1);
             if (!ok) break;
-            load_q(w_next);
-            load_kv(w_next, 0, g + 1);
+            ptx::tc_fence_after();
+            issue_s(g + 1, (n + 1) & 1, keys_in_tile(itn, 0), unit_steps(itn) == 1);
           }
-          ok = ptx::mbar_wait_spin(bar_p, g & 1);
+          // (2) O (+)= P V of step g, once its P is written.
+          ok = ptx::mbar_wait_spin(&bar_p[g & 1], (g >> 1) & 1);
           if (!ok) break;
           ptx::tc_fence_after();
-          // Next step's S first: the softmax warps can start on it while P V runs.
-          if (!last) {
-            ok = ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            issue_s((g + 1) & 1, keys_in_tile(it, j + 1));
-          } else if (w_next < total) {
-            ok = ptx::mbar_wait(bar_q, (n_item + 1) & 1);
-            ok = ok && ptx::mbar_wait(&bar_kv[(g + 1) & 1], ((g + 1) >> 1) & 1);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            issue_s((g + 1) & 1, keys_in_tile(p.work + (w_next / p.n_heads) * 4, 0));
+          const int k_steps = (keys_in_tile(it, j) + 15) / 16;
+          const uint64_t dps = dp + static_cast<uint64_t>(((g & 1) * L::P_BYTES) >> 4);
+          const uint64_t dvs = dv + static_cast<uint64_t>(((g % KV_STAGES) * L::KV_BYTES) >> 4);
+#pragma unroll
+          for (int k = 0; k < BKV / 16; ++k) {
+            if (k < k_steps) {
+              ptx::umma_ss(tmem_o, dps + static_cast<uint64_t>((k * 32) >> 4),
+                           dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o, (j | k) != 0 ? 1u : 0u);
+            }
           }
-          // O (+)= P_j V_j over the keys of this tile (rounded up to the MMA's K step of 16).
-          issue_pv(st, (keys_in_tile(it, j) + 15) / 16, j != 0);
+          ptx::umma_commit(&bar_pv[g & 1]);
+          ptx::umma_commit(&bar_kvfree[g % KV_STAGES]);
         }
       }
-      if (ok && g > 0) ok = ptx::mbar_wait_spin(bar_o, (g - 1) & 1);
+      // Nothing may be in flight when the CTA frees its TMEM.
+      if (ok && g > 0) ok = ptx::mbar_wait(&bar_pv[(g - 1) & 1], ((g - 1) >> 1) & 1);
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {
     // ------------------------------------------------------------ softmax warps
     const int r = warp * 32 + lane;           // row inside the query tile = TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    uint8_t* sp = smem + L::OFF_P;
-    uint32_t g = 0;
+    uint32_t g = 0, n = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+    // A finished unit whose output rows still sit in TMEM (deferred read-out, D = 64).
+    bool pend = false, pend_store = false;
+    uint32_t pend_g = 0, pend_o = 0;
+    float pend_inv = 0.f;
+    T* pend_dst = nullptr;
+    // Reads a finished unit's output row from TMEM, normalises and stores it.  g_last: the
+    // unit's last step (its P V must be complete).
+    auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* dst, bool store) -> bool {
+      if (!ptx::mbar_wait(&bar_pv[g_last & 1], (g_last >> 1) & 1)) return false;
+      ptx::tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t t[32];
+        ptx::tmem_ld32(t_o + c * 32, t);
+        ptx::tmem_ld_wait();
+        if (store) {
+#pragma unroll
+          for (int q8 = 0; q8 < 4; ++q8) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
+            v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
+            v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
+            v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = v;
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      return true;
+    };
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
       const int* it = p.work + (w / p.n_heads) * 4;
       const int head = w % p.n_heads;
+      const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
       const int seq_start = it[0], seq_len = it[1], q0 = it[2];
       const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
       const int n_kv = (kv_end + BKV - 1) / BKV;
@@ -373,7 +422,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
       float m = -INFINITY, l = 0.f;           // running maximum (scaled log2 domain) and sum
       for (int j = 0; j < n_kv; ++j, ++g) {
-        if (!ptx::mbar_wait(bar_s, g & 1)) {
+        const int b = g & 1;
+        if (!ptx::mbar_wait(&bar_s[b], (g >> 1) & 1)) {
           ok = false;
           break;
         }
@@ -388,27 +438,34 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int n_chunks = (min(BKV, kv_end - k_base) + 31) / 32;
         // Uniform per (CTA, step): interior tiles need no per-element mask.
         const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
-        const uint32_t t_s = tmem_s + lane_off;
+        const uint32_t t_s = tmem_base + b * BKV + lane_off;
+        uint8_t* sp = smem + L::OFF_P + b * L::P_BYTES;
         const int rel = qi - k_base;
-        float mx;
-        if (p.alibi_slopes) mx = row_max<true, true>(t_s, lim, n_chunks, p.scale_log2, slope, rel);
-        else if (tile_full) mx = row_max<false, false>(t_s, lim, n_chunks, p.scale_log2, 0.f, 0);
-        else mx = row_max<true, false>(t_s, lim, n_chunks, p.scale_log2, 0.f, 0);
-        // The previous step's P V must be complete before P is overwritten or O is touched.
-        if (g > 0) {
-          if (!ptx::mbar_wait(bar_o, (g - 1) & 1)) {
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after();
+        // The score row of this step: one TMEM read, one wait.
+        uint32_t sc[BKV / 32][32];
+#pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          if (c < n_chunks) ptx::tmem_ld32(t_s + c * 32, sc[c]);
         }
+        ptx::tmem_ld_wait();
+        float mx;
+        if (p.alibi_slopes) mx = row_max<true, true>(sc, lim, n_chunks, p.scale_log2, slope, rel);
+        else if (tile_full) mx = row_max<false, false>(sc, lim, n_chunks, p.scale_log2, 0.f, 0);
+        else mx = row_max<true, false>(sc, lim, n_chunks, p.scale_log2, 0.f, 0);
         if (j == 0) {
           m = mx;  // P V of the first step overwrites the output tile: nothing to rescale
         } else {
           const bool grow = mx > m + kRescaleThreshold;
           if (__any_sync(0xffffffffu, grow)) {
             // Raise the maximum of the rows that need it and rescale their partial outputs in
-            // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).
+            // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
+            // P V issued so far must be complete; the next one is only issued after this
+            // warp's arrival on bar_p below.
+            if (!ptx::mbar_wait(&bar_pv[(g - 1) & 1], ((g - 1) >> 1) & 1)) {
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
             const float alpha = grow ? ex2_fast(m - mx) : 1.0f;
             if (grow) {
               l *= alpha;
@@ -426,46 +483,54 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             ptx::tmem_st_wait();
           }
         }
+        // The P buffer was last read by the P V of step g-2.
+        if (g >= 2) {
+          if (!ptx::mbar_wait(&bar_pv[b], ((g - 2) >> 1) & 1)) {
+            ok = false;
+            break;
+          }
+        }
         const float m_use = (m == -INFINITY) ? 0.f : m;
         float sum;
-        if (p.alibi_slopes) sum = write_probs<T, true, true>(t_s, sp, r, lim, n_chunks, p.scale_log2, slope, rel, m_use);
-        else if (tile_full) sum = write_probs<T, false, false>(t_s, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
-        else sum = write_probs<T, true, false>(t_s, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, sp, r, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+        else if (tile_full) sum = write_probs<T, false, false>(sc, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        else sum = write_probs<T, true, false>(sc, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
         l += sum;
         // P visible to the tensor core (async proxy), S reads and O writes finished: hand over.
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_p);
-      }
-      if (!ok) break;
-      // Unit finished: wait for its last P V, read the output row, normalise, store.
-      if (!ptx::mbar_wait(bar_o, (g - 1) & 1)) {
-        ok = false;
-        break;
-      }
-      ptx::tc_fence_after();
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t t[32];
-        ptx::tmem_ld32(tmem_o + lane_off + c * 32, t);
-        ptx::tmem_ld_wait();
-        if (qi < seq_len) {
-#pragma unroll
-          for (int q8 = 0; q8 < 4; ++q8) {
-            uint4 v;
-            v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
-            v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
-            v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
-            v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = v;
+        if (lane == 0) ptx::mbar_arrive(&bar_p[b]);
+        if (pend) {
+          // The previous unit's rows leave TMEM now, behind this unit's first step: its last
+          // P V has long finished, so nothing waits.
+          pend = false;
+          if (!flush(pend_g, pend_o, pend_inv, pend_dst, pend_store)) {
+            ok = false;
+            break;
           }
         }
       }
-      ptx::tc_fence_before();
+      if (!ok) break;
+      // Unit finished.  With two output tiles the read-out is deferred behind the next unit's
+      // first step; with one it happens now (after the unit's last P V).
+      {
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
+        if (O_BUFS == 2) {
+          pend = true;
+          pend_g = g - 1;
+          pend_o = tmem_o + lane_off;
+          pend_inv = inv;
+          pend_dst = dst;
+          pend_store = qi < seq_len;
+        } else if (!flush(g - 1, tmem_o + lane_off, inv, dst, qi < seq_len)) {
+          ok = false;
+          break;
+        }
+      }
     }
+    if (ok && pend) ok = flush(pend_g, pend_o, pend_inv, pend_dst, pend_store);
     if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
   }
 
