@@ -92,6 +92,32 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
+// Blackwell-only arithmetic: three-input maximum and packed pairs of fp32 (one instruction
+// works on two adjacent registers).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // One thread owns one query row of the 64-key score tile; the row is read from TMEM into
 // registers once per step (one wait) and both passes work from there.
 // Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.
@@ -101,36 +127,28 @@ __device__ __forceinline__ float ex2_fast(float x) {
 template <bool MASKED, bool ALIBI>
 __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int lim, int n_chunks, float sl2,
                                          float slope, int rel) {
-  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
 #pragma unroll
   for (int c = 0; c < BKV / 32; ++c) {
     if (c >= n_chunks) break;
     const uint32_t (&s)[32] = sc[c];
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
+    for (int i = 0; i < 32; i += 2) {
       float x0 = __uint_as_float(s[i]), x1 = __uint_as_float(s[i + 1]);
-      float x2 = __uint_as_float(s[i + 2]), x3 = __uint_as_float(s[i + 3]);
       const int kk = c * 32 + i;
       if (ALIBI) {
         x0 = x0 * sl2 - slope * fabsf(static_cast<float>(rel - kk));
         x1 = x1 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1));
-        x2 = x2 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 2));
-        x3 = x3 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 3));
       }
       if (MASKED) {
         x0 = kk < lim ? x0 : -INFINITY;
         x1 = kk + 1 < lim ? x1 : -INFINITY;
-        x2 = kk + 2 < lim ? x2 : -INFINITY;
-        x3 = kk + 3 < lim ? x3 : -INFINITY;
       }
-      mx0 = fmaxf(mx0, x0);
-      mx1 = fmaxf(mx1, x1);
-      mx2 = fmaxf(mx2, x2);
-      mx3 = fmaxf(mx3, x3);
+      mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], x0, x1);
     }
   }
-  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-  return ALIBI ? mx : mx * sl2;  // the scale is positive, so the maximum commutes with it
+  const float mx_all = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
+  return ALIBI ? mx_all : mx_all * sl2;  // the scale is positive, so the maximum commutes with it
 }
 
 // Pass 2: p = 2^(score - m_use), written as T into the K-major 128-byte-swizzled operand tile
@@ -138,7 +156,9 @@ __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int
 template <class T, bool MASKED, bool ALIBI>
 __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint8_t* sp, int r, int lim,
                                              int n_chunks, float sl2, float slope, int rel, float m_use) {
-  float sum0 = 0.f, sum1 = 0.f;
+  // Packed pairs: one FMA scales and shifts two scores, one add accumulates two probabilities.
+  const uint64_t sl2_2 = pack_f32x2(sl2, sl2), neg_m2 = pack_f32x2(-m_use, -m_use);
+  uint64_t acc[2] = {0ull, 0ull};  // two independent accumulator pairs
 #pragma unroll
   for (int c = 0; c < BKV / 32; ++c) {
     if (c >= n_chunks) break;
@@ -152,15 +172,16 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
         e0 = ex2_fast(__uint_as_float(s[i]) * sl2 - slope * fabsf(static_cast<float>(rel - kk)) - m_use);
         e1 = ex2_fast(__uint_as_float(s[i + 1]) * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1)) - m_use);
       } else {
-        e0 = ex2_fast(fmaf(__uint_as_float(s[i]), sl2, -m_use));
-        e1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), sl2, -m_use));
+        float a0, a1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sl2_2, neg_m2), a0, a1);
+        e0 = ex2_fast(a0);
+        e1 = ex2_fast(a1);
       }
       if (MASKED) {
         e0 = kk < lim ? e0 : 0.f;
         e1 = kk + 1 < lim ? e1 : 0.f;
       }
-      sum0 += e0;
-      sum1 += e1;
+      acc[(i >> 1) & 1] = add_f32x2(acc[(i >> 1) & 1], pack_f32x2(e0, e1));
       pk[i / 2] = pack2<T>(e0, e1);
     }
     uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
@@ -171,7 +192,10 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
           make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
     }
   }
-  return sum0 + sum1;
+  float s0, s1, s2, s3;
+  unpack_f32x2(acc[0], s0, s1);
+  unpack_f32x2(acc[1], s2, s3);
+  return (s0 + s1) + (s2 + s3);
 }
 
 // The running maximum is only raised when it grows by more than this many powers of two; until
@@ -382,21 +406,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     uint32_t g = 0, n = 0;
     bool ok = true;
     // A finished unit whose output rows still sit in TMEM (deferred read-out, D = 64).
-    bool pend = false, pend_store = false;
+    bool pend = false;
     uint32_t pend_g = 0, pend_o = 0;
+    int pend_rows = 0;
     float pend_inv = 0.f;
     T* pend_dst = nullptr;
-    // Reads a finished unit's output row from TMEM, normalises and stores it.  g_last: the
-    // unit's last step (its P V must be complete).
-    auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* dst, bool store) -> bool {
+    // Reads a finished unit's 32 output rows of this warp from TMEM, normalises them and stores
+    // them.  g_last: the unit's last step (its P V must be complete).  Each thread holds one
+    // row, but a store instruction should cover whole 128-byte lines: the rows are transposed
+    // through this warp's own 4 KB slice of the P buffer that the P V of g_last read (free
+    // once that P V is done; the warp itself is the next writer), 64 columns at a time, and
+    // written back with 8 lanes per row.  warp_dst: row 0 of the warp; rows_valid: how many of
+    // the 32 rows belong to the sequence.
+    auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* warp_dst, int rows_valid) -> bool {
       if (!ptx::mbar_wait(&bar_pv[g_last & 1], (g_last >> 1) & 1)) return false;
       ptx::tc_fence_after();
+      uint8_t* stage = smem + L::OFF_P + (g_last & 1) * L::P_BYTES + warp * (32 * 128);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t t[32];
-        ptx::tmem_ld32(t_o + c * 32, t);
-        ptx::tmem_ld_wait();
-        if (store) {
+      for (int c2 = 0; c2 < D / 64; ++c2) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t t[32];
+          ptx::tmem_ld32(t_o + c2 * 64 + h * 32, t);
+          ptx::tmem_ld_wait();
 #pragma unroll
           for (int q8 = 0; q8 < 4; ++q8) {
             uint4 v;
@@ -404,9 +436,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
             v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
             v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + q8 * 8) = v;
+            // 16-byte chunk index XORed with (row & 7): conflict-free both ways
+            *reinterpret_cast<uint4*>(stage + lane * 128 + (((h * 4 + q8) ^ (lane & 7)) * 16)) = v;
           }
         }
+        __syncwarp();
+        const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+        for (int i4 = 0; i4 < 8; ++i4) {
+          const int row = i4 * 4 + sub;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((ch ^ (row & 7)) * 16));
+          if (row < rows_valid) {
+            *reinterpret_cast<uint4*>(warp_dst + static_cast<size_t>(row) * p.ld_o + c2 * 64 + ch * 8) = v;
+          }
+        }
+        __syncwarp();
       }
       ptx::tc_fence_before();
       return true;
@@ -505,7 +549,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           // The previous unit's rows leave TMEM now, behind this unit's first step: its last
           // P V has long finished, so nothing waits.
           pend = false;
-          if (!flush(pend_g, pend_o, pend_inv, pend_dst, pend_store)) {
+          if (!flush(pend_g, pend_o, pend_inv, pend_dst, pend_rows)) {
             ok = false;
             break;
           }
@@ -516,21 +560,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       // first step; with one it happens now (after the unit's last P V).
       {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* dst = reinterpret_cast<T*>(p.out) + static_cast<size_t>(seq_start + qi) * p.ld_o + head * D;
+        T* warp_dst = reinterpret_cast<T*>(p.out) +
+                      static_cast<size_t>(seq_start + q0 + warp * 32) * p.ld_o + head * D;
+        const int rows_valid = max(0, min(32, seq_len - q0 - warp * 32));
         if (O_BUFS == 2) {
           pend = true;
           pend_g = g - 1;
           pend_o = tmem_o + lane_off;
           pend_inv = inv;
-          pend_dst = dst;
-          pend_store = qi < seq_len;
-        } else if (!flush(g - 1, tmem_o + lane_off, inv, dst, qi < seq_len)) {
+          pend_dst = warp_dst;
+          pend_rows = rows_valid;
+        } else if (!flush(g - 1, tmem_o + lane_off, inv, warp_dst, rows_valid)) {
           ok = false;
           break;
         }
       }
     }
-    if (ok && pend) ok = flush(pend_g, pend_o, pend_inv, pend_dst, pend_store);
+    if (ok && pend) ok = flush(pend_g, pend_o, pend_inv, pend_dst, pend_rows);
     if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
   }
 
