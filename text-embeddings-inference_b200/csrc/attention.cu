@@ -15,13 +15,17 @@
 //                      three steps and one unit ahead.
 //   warp 4 (one lane)  MMA issuer: S = Q K^T of step g+1 into the other of two 64-column score
 //                      buffers in TMEM while the softmax warps still work on step g, then
-//                      O += P V of step g (V as MN-major operand) into TMEM columns [128,128+D).
-//   warps 0-3          one query row per thread: row maximum and exp2 straight from TMEM, P
-//                      written as fp16/bf16 into one of two swizzled K-major operand tiles in
-//                      shared memory.  O stays in TMEM across the key steps; the running maximum
-//                      is raised lazily (only when it grows by more than 2^8), in which case the
-//                      rows rescale their partial output in TMEM.  At the end of a unit the row
-//                      is read, normalised and stored.
+//                      O += P V of step g into an output tile in TMEM from column 128 on, with P
+//                      read from TMEM (A operand) and V from shared memory (MN-major operand).
+//   warps 0-3          one query row per thread: the 64 scores of the step are read from TMEM
+//                      into registers once; row maximum, exp2, and P written back as fp16/bf16
+//                      over the row's own scores in TMEM, so P never touches shared memory (the
+//                      kernel is bound by shared-memory bandwidth otherwise: every MMA operand
+//                      read and every TMA write goes through it).  O stays in TMEM across the
+//                      key steps; the running maximum is raised lazily (only when it grows by
+//                      more than 2^8), in which case the rows rescale their partial output in
+//                      TMEM.  A finished unit's rows are read, normalised, transposed through
+//                      a staging tile in shared memory and stored as whole 128-byte lines.
 // Every mbarrier wait is bounded and reports through *status instead of spinning forever.
 #include "kernels.h"
 #include "ptx.cuh"
@@ -39,12 +43,12 @@ template <int D>
 struct AttnSmem {
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int KV_BYTES = BKV * D * 2;   // one K or one V tile
-  static constexpr int P_BYTES = BQ * BKV * 2;
+  static constexpr int STAGE_BYTES = BQ * 128;                   // output rows, 64 columns at a time
   static constexpr int OFF_Q = 0;                               // 2 buffers
   static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;             // KV_STAGES stages
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;    // KV_STAGES stages
-  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;    // 2 buffers
-  static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
+  static constexpr int OFF_STAGE = OFF_V + KV_STAGES * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_STAGE + STAGE_BYTES;
   // No alignment slack: two CTAs of the D = 64 variant must fit in one SM's shared memory.  The
   // kernel checks that the dynamic window is 1024-byte aligned and reports an error otherwise.
   static constexpr int TOTAL = OFF_BAR + 160;  // 16 mbarriers + the TMEM address slot
@@ -151,10 +155,11 @@ __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int
   return ALIBI ? mx_all : mx_all * sl2;  // the scale is positive, so the maximum commutes with it
 }
 
-// Pass 2: p = 2^(score - m_use), written as T into the K-major 128-byte-swizzled operand tile
-// `sp` ([k atom of 64][row][64], 16-byte chunk index XORed with (row & 7)); returns the row sum.
+// Pass 2: p = 2^(score - m_use), written as T back into TMEM over the row's own scores (two
+// values per 32-bit column from column `t_p` on: the A operand of the P V MMA); returns the row
+// sum.
 template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint8_t* sp, int r, int lim,
+__device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lim,
                                              int n_chunks, float sl2, float slope, int rel, float m_use) {
   // Packed pairs: one FMA scales and shifts two scores, one add accumulates two probabilities.
   const uint64_t sl2_2 = pack_f32x2(sl2, sl2), neg_m2 = pack_f32x2(-m_use, -m_use);
@@ -184,13 +189,7 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
       acc[(i >> 1) & 1] = add_f32x2(acc[(i >> 1) & 1], pack_f32x2(e0, e1));
       pk[i / 2] = pack2<T>(e0, e1);
     }
-    uint8_t* rowp = sp + (c >> 1) * (BQ * 128) + r * 128;
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-      const int chunk = ((c & 1) * 4 + q4) ^ (r & 7);
-      *reinterpret_cast<uint4*>(rowp + chunk * 16) =
-          make_uint4(pk[q4 * 4 + 0], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-    }
+    ptx::tmem_st16(t_p + c * 16, pk);  // 32 keys = 16 columns of packed pairs
   }
   float s0, s1, s2, s3;
   unpack_f32x2(acc[0], s0, s1);
@@ -223,8 +222,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* bar_kv = bars + 4;       // [3] K/V stage landed
   uint64_t* bar_kvfree = bars + 7;   // [3] the P V that read the stage is done
   uint64_t* bar_s = bars + 10;       // [2] S buffer holds the scores of its step
-  uint64_t* bar_p = bars + 12;       // [2] P buffer written, S buffer read (one arrival per warp)
-  uint64_t* bar_pv = bars + 14;      // [2] the P V that read the P buffer is done
+  uint64_t* bar_p = bars + 12;       // [2] P written over the scores of the step (one arrival per warp)
+  uint64_t* bar_pv = bars + 14;      // [2] the P V of the step is done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   constexpr uint32_t TMEM_COLS = 256;
 
@@ -322,13 +321,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   } else if (warp == 4) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // P V: A = P (K-major), B = V tile [keys][D] = MN-major (D contiguous).
+      // P V: A = P from TMEM (row = lane, two keys per 32-bit column), B = V tile [keys][D] =
+      // MN-major (D contiguous).
       constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
       // Operand descriptors are built once; each MMA adds a constant to the address field
       // (units of 16 bytes; every operand sits below 256 KB, so the 14-bit field cannot carry).
       const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
       const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
-      const uint64_t dp = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_P), 16, 1024);
       const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
       // S = Q K^T for step `step` (Q buffer qb): only ceil(keys/16)*16 columns are computed.
       auto issue_s = [&](uint32_t step, int qb, int keys, bool last_of_unit) {
@@ -362,8 +361,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int w_next = w + static_cast<int>(gridDim.x);
         const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
         for (int j = 0; j < n_kv && ok; ++j, ++g) {
-          // (1) S of step g+1 into the other score buffer.  That buffer was last read by the
-          // softmax of step g-1, whose bar_p this thread waited for before issuing P V of g-1.
+          // (1) S of step g+1 into the other score buffer.  That buffer holds P of step g-1,
+          // read by the P V of g-1 issued one iteration ago: MMAs run in issue order.
           if (j + 1 < n_kv) {
             ok = ptx::mbar_wait(&bar_kv[(g + 1) % KV_STAGES], ((g + 1) / KV_STAGES) & 1);
             if (!ok) break;
@@ -382,13 +381,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           ptx::tc_fence_after();
           const int k_steps = (keys_in_tile(it, j) + 15) / 16;
-          const uint64_t dps = dp + static_cast<uint64_t>(((g & 1) * L::P_BYTES) >> 4);
+          const uint32_t t_p = tmem_base + (g & 1) * BKV;  // P lies over the scores of the step
           const uint64_t dvs = dv + static_cast<uint64_t>(((g % KV_STAGES) * L::KV_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
             if (k < k_steps) {
-              ptx::umma_ss(tmem_o, dps + static_cast<uint64_t>((k * 32) >> 4),
-                           dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o, (j | k) != 0 ? 1u : 0u);
+              ptx::umma_ts(tmem_o, t_p + k * 8, dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o,
+                           (j | k) != 0 ? 1u : 0u);
             }
           }
           ptx::umma_commit(&bar_pv[g & 1]);
@@ -414,14 +413,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     // Reads a finished unit's 32 output rows of this warp from TMEM, normalises them and stores
     // them.  g_last: the unit's last step (its P V must be complete).  Each thread holds one
     // row, but a store instruction should cover whole 128-byte lines: the rows are transposed
-    // through this warp's own 4 KB slice of the P buffer that the P V of g_last read (free
-    // once that P V is done; the warp itself is the next writer), 64 columns at a time, and
+    // through this warp's own 4 KB slice of the staging tile, 64 columns at a time, and
     // written back with 8 lanes per row.  warp_dst: row 0 of the warp; rows_valid: how many of
     // the 32 rows belong to the sequence.
     auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* warp_dst, int rows_valid) -> bool {
       if (!ptx::mbar_wait(&bar_pv[g_last & 1], (g_last >> 1) & 1)) return false;
       ptx::tc_fence_after();
-      uint8_t* stage = smem + L::OFF_P + (g_last & 1) * L::P_BYTES + warp * (32 * 128);
+      uint8_t* stage = smem + L::OFF_STAGE + warp * (32 * 128);
 #pragma unroll
       for (int c2 = 0; c2 < D / 64; ++c2) {
 #pragma unroll
@@ -483,7 +481,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         // Uniform per (CTA, step): interior tiles need no per-element mask.
         const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
         const uint32_t t_s = tmem_base + b * BKV + lane_off;
-        uint8_t* sp = smem + L::OFF_P + b * L::P_BYTES;
         const int rel = qi - k_base;
         // The score row of this step: one TMEM read, one wait.
         uint32_t sc[BKV / 32][32];
@@ -527,21 +524,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             ptx::tmem_st_wait();
           }
         }
-        // The P buffer was last read by the P V of step g-2.
-        if (g >= 2) {
-          if (!ptx::mbar_wait(&bar_pv[b], ((g - 2) >> 1) & 1)) {
-            ok = false;
-            break;
-          }
-        }
+        // P goes over this step's scores.  Their columns were last read by the P V of step
+        // g-2, which ran before the S MMA of this step wrote them (MMAs run in issue order).
         const float m_use = (m == -INFINITY) ? 0.f : m;
         float sum;
-        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, sp, r, lim, n_chunks, p.scale_log2, slope, rel, m_use);
-        else if (tile_full) sum = write_probs<T, false, false>(sc, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
-        else sum = write_probs<T, true, false>(sc, sp, r, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, t_s, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+        else if (tile_full) sum = write_probs<T, false, false>(sc, t_s, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        else sum = write_probs<T, true, false>(sc, t_s, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
         l += sum;
-        // P visible to the tensor core (async proxy), S reads and O writes finished: hand over.
-        ptx::fence_proxy_async_smem();
+        // P and the rescaled O written, S read: hand over to the MMA thread.
+        ptx::tmem_st_wait();
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&bar_p[b]);
