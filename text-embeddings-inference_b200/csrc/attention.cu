@@ -96,32 +96,6 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
-// Blackwell-only arithmetic: three-input maximum and packed pairs of fp32 (one instruction
-// works on two adjacent registers).
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-
 // One thread owns one query row of the 64-key score tile; the row is read from TMEM into
 // registers once per step (one wait) and both passes work from there.
 // Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.
@@ -148,10 +122,10 @@ __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int
         x0 = kk < lim ? x0 : -INFINITY;
         x1 = kk + 1 < lim ? x1 : -INFINITY;
       }
-      mx[(i >> 1) & 3] = max3(mx[(i >> 1) & 3], x0, x1);
+      mx[(i >> 1) & 3] = ptx::max3(mx[(i >> 1) & 3], x0, x1);
     }
   }
-  const float mx_all = fmaxf(max3(mx[0], mx[1], mx[2]), mx[3]);
+  const float mx_all = fmaxf(ptx::max3(mx[0], mx[1], mx[2]), mx[3]);
   return ALIBI ? mx_all : mx_all * sl2;  // the scale is positive, so the maximum commutes with it
 }
 
@@ -162,7 +136,7 @@ template <class T, bool MASKED, bool ALIBI>
 __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lim,
                                              int n_chunks, float sl2, float slope, int rel, float m_use) {
   // Packed pairs: one FMA scales and shifts two scores, one add accumulates two probabilities.
-  const uint64_t sl2_2 = pack_f32x2(sl2, sl2), neg_m2 = pack_f32x2(-m_use, -m_use);
+  const uint64_t sl2_2 = ptx::pack_f32x2(sl2, sl2), neg_m2 = ptx::pack_f32x2(-m_use, -m_use);
   uint64_t acc[2] = {0ull, 0ull};  // two independent accumulator pairs
 #pragma unroll
   for (int c = 0; c < BKV / 32; ++c) {
@@ -178,7 +152,7 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
         e1 = ex2_fast(__uint_as_float(s[i + 1]) * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1)) - m_use);
       } else {
         float a0, a1;
-        unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sl2_2, neg_m2), a0, a1);
+        ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sl2_2, neg_m2), a0, a1);
         e0 = ex2_fast(a0);
         e1 = ex2_fast(a1);
       }
@@ -186,14 +160,14 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
         e0 = kk < lim ? e0 : 0.f;
         e1 = kk + 1 < lim ? e1 : 0.f;
       }
-      acc[(i >> 1) & 1] = add_f32x2(acc[(i >> 1) & 1], pack_f32x2(e0, e1));
+      acc[(i >> 1) & 1] = ptx::add_f32x2(acc[(i >> 1) & 1], ptx::pack_f32x2(e0, e1));
       pk[i / 2] = pack2<T>(e0, e1);
     }
     ptx::tmem_st16(t_p + c * 16, pk);  // 32 keys = 16 columns of packed pairs
   }
   float s0, s1, s2, s3;
-  unpack_f32x2(acc[0], s0, s1);
-  unpack_f32x2(acc[1], s2, s3);
+  ptx::unpack_f32x2(acc[0], s0, s1);
+  ptx::unpack_f32x2(acc[1], s2, s3);
   return (s0 + s1) + (s2 + s3);
 }
 

@@ -107,6 +107,29 @@ __device__ __forceinline__ float apply_act(float x) {
   return x;
 }
 
+// Activation of a packed pair of fp32 values (one instruction per two values where the
+// hardware has one), rounded to two T.
+template <class T, int ACT>
+__device__ __forceinline__ uint32_t act_pack2(uint64_t x) {
+  if constexpr (ACT == ACT_GELU) {
+    // 0.5 x (1 + tanh(k0 (x + k1 x^3))) = hx + hx tanh(x (k0 + k0 k1 x^2)), hx = x / 2
+    const uint64_t kk = ptx::pack_f32x2(0.7978845608028654f * 0.044715f, 0.7978845608028654f * 0.044715f);
+    const uint64_t k0 = ptx::pack_f32x2(0.7978845608028654f, 0.7978845608028654f);
+    const uint64_t half = ptx::pack_f32x2(0.5f, 0.5f);
+    const uint64_t u = ptx::mul_f32x2(x, ptx::fma_f32x2(ptx::mul_f32x2(x, x), kk, k0));
+    float u0, u1;
+    ptx::unpack_f32x2(u, u0, u1);
+    const uint64_t hx = ptx::mul_f32x2(x, half);
+    float r0, r1;
+    ptx::unpack_f32x2(ptx::fma_f32x2(hx, ptx::pack_f32x2(tanh_fast(u0), tanh_fast(u1)), hx), r0, r1);
+    return pack2<T>(r0, r1);
+  } else {
+    float x0, x1;
+    ptx::unpack_f32x2(x, x0, x1);
+    return pack2<T>(apply_act<ACT>(x0), apply_act<ACT>(x1));
+  }
+}
+
 // Adds bias / applies the activation / adds the residual to 32 consecutive columns of one row
 // and stores them.  `col` is the first output column, n_valid the number of columns in range.
 template <class T, int ACT>
@@ -196,24 +219,31 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
           ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
           ptx::tmem_ld_wait();
           const int col = n0 + c * 64 + hlf * 32;
-          float bv[32];
-          if (bias_vec && col + 32 <= p.N) {
+          if (bias == nullptr) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 b4 = *reinterpret_cast<const uint4*>(bias + col + j * 8);
-              const T* bt = reinterpret_cast<const T*>(&b4);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) bv[j * 8 + e] = to_f32<T>(bt[e]);
+            for (int j = 0; j < 32; j += 2) {
+              packed[hlf * 16 + j / 2] = act_pack2<T, ACT>(ptx::pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])));
             }
           } else {
+            float bv[32];
+            if (bias_vec && col + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) bv[j] = (bias && col + j < p.N) ? to_f32<T>(bias[col + j]) : 0.f;
-          }
+              for (int j = 0; j < 4; ++j) {
+                const uint4 b4 = *reinterpret_cast<const uint4*>(bias + col + j * 8);
+                const T* bt = reinterpret_cast<const T*>(&b4);
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float x0 = apply_act<ACT>(__uint_as_float(r[j]) + bv[j]);
-            const float x1 = apply_act<ACT>(__uint_as_float(r[j + 1]) + bv[j + 1]);
-            packed[hlf * 16 + j / 2] = pack2<T>(x0, x1);
+                for (int e = 0; e < 8; ++e) bv[j * 8 + e] = to_f32<T>(bt[e]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) bv[j] = (col + j < p.N) ? to_f32<T>(bias[col + j]) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const uint64_t x = ptx::add_f32x2(ptx::pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                                                ptx::pack_f32x2(bv[j], bv[j + 1]));
+              packed[hlf * 16 + j / 2] = act_pack2<T, ACT>(x);
+            }
           }
         }
       }
