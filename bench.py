@@ -397,12 +397,12 @@ def main():
     achieved = gemm_flops_per_step / (gemm_ms_per_step / 1e3) / 1e12 if gemm_ms_per_step > 0 else 0.0
     attn_ms_per_step = kt["attention"]["ms"] / args.steps
     roofline = {
-        "kernel": "gemm_tcgen05_kernel (dense layers: QKV, attention output, FFN up + GELU, FFN down)",
+        "kernel": "gemm_tcgen05_pair_kernel (dense layers: QKV, attention output, FFN up + GELU, FFN down)",
         "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
         "frac": achieved / peak_tf if peak_tf else None, "peak_source": peak_src,
         # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures of the four
         # GEMM shapes (profiles/gemm_tcgen05_bert_base_shapes.md), mean over the shapes.
-        "traffic": 378e6, "traffic_unit": "bytes per launch (mean of the 4 shapes, ncu)",
+        "traffic": 382e6, "traffic_unit": "bytes per launch (mean of the 4 shapes, ncu)",
         # inputs + weights + outputs of QKV, attention-output, FFN-up and FFN-down, mean per launch
         "algorithmic_bytes_per_launch": 2.0 * (tokens * (4 * H + 2 * H + 2 * (H + I)) + 4 * H * H + 2 * H * I) / 4.0,
         "flops_per_launch": gemm_flops_per_step / gemm_launches if gemm_launches else None,
