@@ -52,6 +52,18 @@ int tei_b200_create(const char* model_dir, const char* dtype, int model_type, in
                     const int* devices, int n_devices, tei_b200_t** out, char* err,
                     size_t err_cap);
 
+/* The `dense_paths` argument of CandleBackend::new (backends/candle/src/lib.rs:579-629): appends
+ * the Sentence-Transformers Dense module stored under `<model_dir>/<dense_path>/`
+ * (`config.json` with in_features / out_features / bias / activation_function, and
+ * `model.safetensors` with `linear.weight` [out, in] and `linear.bias`;
+ * backends/candle/src/models/dense.rs:26-75).  Modules are applied to the pooled rows, in the
+ * order of the calls, before the rows leave the device (lib.rs:672-680); raw rows are not
+ * affected and tei_b200_output_dim() reports the last module's out_features.  A path without a
+ * weight file is skipped like the reference does (returns OK, `err` holds the warning);
+ * everything else that is wrong is TEI_B200_ERR_START.  Call between create and the first
+ * batch. */
+int tei_b200_add_dense(tei_b200_t* h, const char* dense_path, char* err, size_t err_cap);
+
 void tei_b200_destroy(tei_b200_t* h);
 
 /* Backend::health (backends/core/src/lib.rs:38).  Cheap when the last call succeeded; after a

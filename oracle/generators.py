@@ -203,6 +203,31 @@ def write_model_dir(path, config: dict, seed: int, classifier: Optional[str] = N
     return path
 
 
+DENSE_ACTIVATIONS = {"tanh": "torch.nn.modules.activation.Tanh", "identity": "torch.nn.modules.linear.Identity"}
+
+
+def write_dense_dir(model_dir, dense_path: str, in_features: int, out_features: int, seed: int,
+                    bias: bool = True, activation: Optional[str] = "tanh", std: float = 0.05) -> Path:
+    """A Sentence-Transformers Dense module under `<model_dir>/<dense_path>/` in the layout the
+    reference loads (backends/candle/src/lib.rs:579-629, models/dense.rs:26-62): config.json with
+    in_features / out_features / bias / activation_function, model.safetensors with
+    `linear.weight` [out, in] and `linear.bias` [out]."""
+    from safetensors.numpy import save_file
+
+    path = Path(model_dir) / dense_path
+    path.mkdir(parents=True, exist_ok=True)
+    rng = np.random.default_rng(seed)
+    tensors = {"linear.weight": rng.standard_normal(size=(out_features, in_features), dtype=np.float32) * np.float32(std)}
+    if bias:
+        tensors["linear.bias"] = rng.standard_normal(size=(out_features,), dtype=np.float32) * np.float32(std)
+    save_file(tensors, str(path / "model.safetensors"))
+    cfg = {"in_features": in_features, "out_features": out_features, "bias": bias}
+    if activation is not None:
+        cfg["activation_function"] = DENSE_ACTIVATIONS[activation]
+    (path / "config.json").write_text(json.dumps(cfg, indent=1))
+    return path
+
+
 # --------------------------------------------------------------------------- batches
 def _ids(rng, lens, lo, hi) -> List[np.ndarray]:
     return [rng.integers(lo, hi, size=int(n)) for n in lens]

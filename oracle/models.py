@@ -161,6 +161,31 @@ def load_model_dir(model_dir) -> Tuple[dict, Dict[str, Tensor]]:
     return config, tensors
 
 
+def apply_dense(pooled: Tensor, model_dir, dense_paths) -> Tensor:
+    """Sentence-Transformers Dense modules on the pooled rows, in order
+    (backends/candle/src/lib.rs:672-680; models/dense.rs:64-75: linear, then Tanh or Identity,
+    Identity when `activation_function` is absent `:54-57`).  Paths without a weight file are
+    skipped as the loader does (lib.rs:586-626)."""
+    from safetensors import safe_open
+
+    for dense_path in dense_paths or []:
+        d = Path(model_dir) / dense_path
+        if not (d / "model.safetensors").exists():
+            continue
+        cfg = json.loads((d / "config.json").read_text())
+        with safe_open(str(d / "model.safetensors"), framework="pt") as f:
+            w = f.get_tensor("linear.weight").to(torch.float32)
+            b = f.get_tensor("linear.bias").to(torch.float32) if cfg["bias"] else None
+        assert tuple(w.shape) == (cfg["out_features"], cfg["in_features"])
+        pooled = linear(pooled, w, b)
+        act = cfg.get("activation_function") or "torch.nn.modules.linear.Identity"
+        if act == "torch.nn.modules.activation.Tanh":
+            pooled = torch.tanh(pooled)
+        elif act != "torch.nn.modules.linear.Identity":
+            raise ValueError(f"unknown activation_function {act}")
+    return pooled
+
+
 class _Weights:
     def __init__(self, tensors: Dict[str, Tensor], prefixes=("",)):
         self.t = tensors

@@ -152,6 +152,48 @@ def test_normalize_flag(lib, model_dirs):
     be.close()
 
 
+def test_dense_modules_follow_the_pooling(lib, model_dirs, tmp_path):
+    # backends/candle/src/lib.rs:579-629,672-680: Dense modules run on the pooled rows, in order;
+    # raw rows keep the model's width; a path without weights is skipped with a warning.
+    import shutil
+    import tei_b200
+    d = tmp_path / "bert_dense"
+    shutil.copytree(model_dirs["bert"], d)
+    G.write_dense_dir(d, "2_Dense", 128, 64, seed=21, bias=True, activation="tanh")
+    G.write_dense_dir(d, "3_Dense", 64, 100, seed=22, bias=False, activation=None)
+    paths = ["2_Dense", "9_Missing", "3_Dense"]
+    be = tei_b200.B200Backend(d, "float16", "embedding", "mean", dense_paths=paths)
+    assert be.output_dim == 100 and be.hidden_size == 128
+    assert len(be.warnings) == 1 and "9_Missing" in be.warnings[0]
+    o = M.build_oracle(d, "embedding", "mean")
+    lens = [7, 33, 150, 2, 64, 129]
+    b = G.random_batch(43, lens, 0, 1000, pooled=[0, 2, 3, 5], raw=[1, 4], type_vocab=2)
+    got = be.embed(b)
+    ref_pooled, ref_raw = o.embed(b)
+    ref_pooled = M.apply_dense(ref_pooled, d, paths)
+    assert tuple(ref_pooled.shape) == (4, 100)
+    _check_embeddings(np.stack([got[i].values for i in (0, 2, 3, 5)]), ref_pooled.numpy())
+    _check_embeddings(np.concatenate([got[i].values for i in (1, 4)]), ref_raw.numpy())
+    assert got[1].values.shape == (33, 128)
+    normed = be.embed(b, normalize=True)
+    for i in (0, 2, 3, 5):
+        assert abs(np.linalg.norm(normed[i].values.astype(np.float64)) - 1.0) < 1e-5
+        assert np.abs(M.l2_normalise(got[i].values) - normed[i].values).max() < 1e-6
+    be.close()
+    # a single module, CLS pooling
+    be = tei_b200.B200Backend(d, "float16", "embedding", "cls", dense_paths=["2_Dense"])
+    o = M.build_oracle(d, "embedding", "cls")
+    b = G.random_batch(44, lens, 0, 1000, type_vocab=2)
+    got = be.embed(b)
+    ref = M.apply_dense(o.embed(b)[0], d, ["2_Dense"])
+    _check_embeddings(np.stack([got[i].values for i in range(len(lens))]), ref.numpy())
+    be.close()
+    # the wrong input width is a Start error, as is a classifier with Dense modules
+    with pytest.raises(tei_b200.BackendError) as e:
+        tei_b200.B200Backend(d, "float16", "embedding", "mean", dense_paths=["3_Dense"])
+    assert e.value.kind == "Start" and "input features" in str(e.value)
+
+
 def test_trait_surface_and_health(lib, model_dirs):
     be = _backend(model_dirs, "bert", "embedding", "cls")
     assert be.is_padded() is False

@@ -47,6 +47,7 @@ std::string read_file(const std::string& path) {
 
 struct tei_b200 {
   ModelSpec spec;
+  std::string model_dir;
   std::vector<std::unique_ptr<Replica>> replicas;
   bool healthy = true;
   // state of the staged batch (stage / run / sync / fetch)
@@ -238,13 +239,14 @@ void do_fetch(tei_b200* h, float* pooled_out, float* raw_out, float* scores_out)
     return;
   }
   const size_t D = static_cast<size_t>(h->replicas[0]->output_dim());
+  const size_t DR = static_cast<size_t>(h->replicas[0]->raw_dim());
   const size_t C = static_cast<size_t>(std::max(h->spec.n_classes, 1));
   const bool predict = h->staged_predict;
   for_each_shard_parallel(h, [&](Replica& r, Shard& sh) {
     size_t raw_rows = 0;
     for (size_t l : sh.raw_len) raw_rows += l;
     sh.pooled.resize(sh.pooled_idx.size() * D);
-    sh.raw.resize(raw_rows * D);
+    sh.raw.resize(raw_rows * DR);
     sh.scores.resize(predict ? sh.seqs.size() * C : 0);
     r.fetch(sh.pooled.data(), sh.raw.data(), sh.scores.data());
   });
@@ -259,7 +261,7 @@ void do_fetch(tei_b200* h, float* pooled_out, float* raw_out, float* scores_out)
     if (raw_out) {
       size_t src_row = 0;
       for (size_t i = 0; i < sh.raw_dst_row.size(); ++i) {
-        std::memcpy(raw_out + sh.raw_dst_row[i] * D, sh.raw.data() + src_row * D, sh.raw_len[i] * D * 4);
+        std::memcpy(raw_out + sh.raw_dst_row[i] * DR, sh.raw.data() + src_row * DR, sh.raw_len[i] * DR * 4);
         src_row += sh.raw_len[i];
       }
     }
@@ -293,6 +295,7 @@ int tei_b200_create(const char* model_dir, const char* dtype, int model_type, in
     }
     if (pool < 0 || pool > 3) throw TeiError(ERR_START, "unknown pool");
     const std::string dir = model_dir;
+    h->model_dir = dir;
     Json config;
     try {
       config = Json::parse(read_file(dir + "/config.json"));
@@ -332,6 +335,29 @@ int tei_b200_create(const char* model_dir, const char* dtype, int model_type, in
   return rc;
 }
 
+int tei_b200_add_dense(tei_b200_t* h, const char* dense_path, char* err, size_t err_cap) {
+  if (!h) return TEI_B200_ERR_START;
+  int rc = guarded(nullptr, err, err_cap, [&]() {
+    if (!dense_path) throw TeiError(ERR_START, "dense_path is required");
+    const std::string dir = h->model_dir + "/" + dense_path;
+    auto exists = [](const std::string& p) {
+      std::ifstream f(p, std::ios::binary);
+      return static_cast<bool>(f);
+    };
+    if (!exists(dir + "/model.safetensors")) {
+      if (exists(dir + "/pytorch_model.bin")) {
+        throw TeiError(ERR_START, "Dense module `" + std::string(dense_path) + "` has only pytorch_model.bin; safetensors is required");
+      }
+      // backends/candle/src/lib.rs:624-626: a path without weight files is skipped with a warning.
+      set_err(err, err_cap, "Dense module files not found for path: " + std::string(dense_path));
+      return;
+    }
+    for (auto& r : h->replicas) r->add_dense(dir);
+    h->staged = false;
+  });
+  return rc;
+}
+
 void tei_b200_destroy(tei_b200_t* h) { delete h; }
 
 int tei_b200_health(tei_b200_t* h) {
@@ -356,7 +382,7 @@ int tei_b200_max_batch_size(const tei_b200_t*) { return -1; }
 int tei_b200_output_dim(const tei_b200_t* h) { return h ? h->replicas[0]->output_dim() : 0; }
 int tei_b200_hidden_size(const tei_b200_t* h) {
   if (!h) return 0;
-  return h->spec.pool == POOL_SPLADE ? h->spec.hidden : h->replicas[0]->output_dim();
+  return h->spec.pool == POOL_SPLADE ? h->spec.hidden : h->replicas[0]->raw_dim();
 }
 int tei_b200_num_classes(const tei_b200_t* h) { return h ? h->spec.n_classes : 0; }
 

@@ -129,6 +129,9 @@ struct PoolArgs {
 };
 int launch_pool(const PoolArgs& p, cudaStream_t stream);
 
+// In-place L2 normalisation of fp32 rows of width H.
+int launch_l2_normalise(float* x, int rows, int H, cudaStream_t stream);
+
 // Copies the token rows of the listed sequences, in order, to fp32.
 int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int n_rows, int H,
                            int dtype, cudaStream_t stream);

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 
 namespace tei {
@@ -220,10 +221,74 @@ Replica::~Replica() {
   if (stream_) cudaStreamDestroy(stream_);
 }
 
-int Replica::output_dim() const {
+int Replica::raw_dim() const {
   if (spec_.pool == POOL_SPLADE) return spec_.vocab;
   if (projection_) return projection_dim_;
   return spec_.hidden;
+}
+
+int Replica::output_dim() const { return dense_.empty() ? raw_dim() : dense_.back().out; }
+
+void Replica::add_dense(const std::string& dir) {
+  TEI_CUDA(cudaSetDevice(device_));
+  if (spec_.classifier) throw TeiError(ERR_START, "Dense modules apply to embedding models only");
+  if (spec_.pool == POOL_SPLADE) throw TeiError(ERR_START, "Dense modules cannot follow SPLADE pooling");
+  std::string text;
+  {
+    std::FILE* f = std::fopen((dir + "/config.json").c_str(), "rb");
+    if (!f) throw TeiError(ERR_START, "Unable to read `" + dir + "/config.json` file");
+    char buf[4096];
+    size_t n;
+    while ((n = std::fread(buf, 1, sizeof(buf), f)) > 0) text.append(buf, n);
+    std::fclose(f);
+  }
+  Json cfg;
+  try {
+    cfg = Json::parse(text);
+  } catch (const std::exception& e) {
+    throw TeiError(ERR_START, "Unable to parse `" + dir + "/config.json`: " + e.what());
+  }
+  // DenseConfig (dense.rs:26-32): in_features, out_features and bias are required.
+  if (!cfg["in_features"].is_number() || !cfg["out_features"].is_number() || !cfg["bias"].is_bool()) {
+    throw TeiError(ERR_START, "Unable to parse `" + dir + "/config.json`: in_features, out_features and bias are required");
+  }
+  DenseW d;
+  d.in = static_cast<int>(cfg["in_features"].as_int());
+  d.out = static_cast<int>(cfg["out_features"].as_int());
+  d.act = ACT_NONE;
+  if (cfg["activation_function"].is_string()) {
+    const std::string a = cfg["activation_function"].as_string();
+    if (a == "torch.nn.modules.activation.Tanh") d.act = ACT_TANH;
+    else if (a == "torch.nn.modules.linear.Identity") d.act = ACT_NONE;
+    else throw TeiError(ERR_START, "Unable to parse `" + dir + "/config.json`: unknown activation_function " + a);
+  }
+  if (d.in <= 0 || d.out <= 0) throw TeiError(ERR_START, "Dense module with an empty dimension");
+  if (d.in != output_dim()) {
+    throw TeiError(ERR_START, "Dense module expects " + std::to_string(d.in) + " input features, the model gives " +
+                                  std::to_string(output_dim()));
+  }
+  SafeTensors st;
+  try {
+    st.open_file(dir + "/model.safetensors");
+  } catch (const std::exception& e) {
+    throw TeiError(ERR_START, std::string("Dense module weights: ") + e.what());
+  }
+  if (!st.contains("linear.weight")) throw TeiError(ERR_START, "Dense module without `linear.weight`");
+  const StTensor& w = st.get("linear.weight");
+  if (w.shape.size() != 2 || w.shape[0] != static_cast<size_t>(d.out) || w.shape[1] != static_cast<size_t>(d.in)) {
+    throw TeiError(ERR_START, "Dense module `linear.weight` does not have the shape [out_features, in_features]");
+  }
+  d.w = upload_new(w);
+  if (cfg["bias"].as_bool()) {
+    if (!st.contains("linear.bias")) throw TeiError(ERR_START, "Dense module without `linear.bias`");
+    const StTensor& b = st.get("linear.bias");
+    if (b.shape.size() != 1 || b.shape[0] != static_cast<size_t>(d.out)) {
+      throw TeiError(ERR_START, "Dense module `linear.bias` does not have the shape [out_features]");
+    }
+    d.b = upload_new(b);
+  }
+  TEI_CUDA(cudaStreamSynchronize(stream_));
+  dense_.push_back(d);
 }
 
 void* Replica::dev_alloc(size_t bytes) {
@@ -633,9 +698,15 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
   // outputs (+ head scratch after them)
   const size_t D = static_cast<size_t>(output_dim());
   const size_t Dpad = align_up(D, 8);
-  const size_t out_need = 64 + n_pooled * Dpad + raw_rows * Dpad +
+  const size_t Draw = align_up(static_cast<size_t>(raw_dim()), 8);
+  size_t dense_w = 0;  // widest row of the Dense chain (two ping-pong buffers of pooled rows)
+  if (!dense_.empty()) {
+    dense_w = Draw;
+    for (const DenseW& d : dense_) dense_w = std::max(dense_w, align_up(static_cast<size_t>(d.out), 8));
+  }
+  const size_t out_need = 64 + n_pooled * Dpad + raw_rows * Draw +
                           seqs * static_cast<size_t>(std::max(s.n_classes, 1)) +
-                          2 * seqs * static_cast<size_t>(s.hidden) + 64;
+                          2 * seqs * static_cast<size_t>(s.hidden) + 2 * n_pooled * dense_w + 64;
   if (out_need > out_cap_floats_) {
     TEI_CUDA(cudaStreamSynchronize(stream_));
     if (d_out_) cudaFree(d_out_);
@@ -770,15 +841,22 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
 
   // Output block: [0,64) status word | pooled | raw | scores || scratch (not copied back).
   const size_t D = static_cast<size_t>(output_dim());
-  const size_t Dpad = align_up(D, 8);
+  // The Dense chain writes rows of exactly D floats; the pooling kernel rows of Dpad.
+  pooled_ld_ = dense_.empty() ? align_up(D, 8) : D;
   size_t oo = 64;
-  d_pooled_ = d_out_ + oo; oo += n_pooled * Dpad;
-  d_raw_ = d_out_ + oo; oo += raw_rows * D;
+  d_pooled_ = d_out_ + oo; oo += align_up(n_pooled * pooled_ld_, 8);
+  d_raw_ = d_out_ + oo; oo += raw_rows * static_cast<size_t>(raw_dim());
   d_scores_ = d_out_ + oo; oo += predict ? B_ * static_cast<size_t>(s.n_classes) : 0;
   out_floats_ = oo;
   oo = align_up(oo, 8);
   d_cls_ = d_out_ + oo; oo += B_ * s.hidden;
-  d_head_tmp_ = d_out_ + oo;
+  d_head_tmp_ = d_out_ + oo; oo += B_ * s.hidden;
+  if (!dense_.empty()) {
+    size_t dense_w = align_up(static_cast<size_t>(raw_dim()), 8);
+    for (const DenseW& d : dense_) dense_w = std::max(dense_w, align_up(static_cast<size_t>(d.out), 8));
+    d_dense_a_ = d_out_ + oo; oo += n_pooled * dense_w;
+    d_dense_b_ = d_out_ + oo;
+  }
   TEI_CUDA(cudaMemsetAsync(d_out_, 0, 256, stream_));
 }
 
@@ -945,7 +1023,7 @@ void Replica::pool_and_heads() {
   const ModelSpec& s = spec_;
   const int T = static_cast<int>(T_), H = s.hidden;
   int* status = reinterpret_cast<int*>(d_out_);
-  const int D = output_dim();
+  const int D = raw_dim();
   if (predict_) {
     PoolArgs p;
     p.x = x_; p.cu_seqlens = d_cu_; p.seq_index = d_all_idx_; p.out = d_cls_;
@@ -975,9 +1053,24 @@ void Replica::pool_and_heads() {
       LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, sp_dec_w_, sp_dec_b_, splade_, T, V, H, H, Vpad, ACT_RELU_LOG1P, s.dtype, status), stream_), "splade decoder");
       p.x = splade_; p.H = Vpad; p.mode = POOL_SPLADE; p.normalize = 0;
     } else {
-      p.x = x_; p.H = D; p.mode = s.pool; p.normalize = normalize_ ? 1 : 0;
+      p.x = x_; p.H = D; p.mode = s.pool; p.normalize = (normalize_ && dense_.empty()) ? 1 : 0;
+      if (!dense_.empty()) p.out = d_dense_a_;
     }
     LAUNCH(KC_POOL, launch_pool(p, stream_), "pooling");
+    if (!dense_.empty() && s.pool != POOL_SPLADE) {
+      // Dense modules on the pooled rows, in order (backends/candle/src/lib.rs:672-680); the
+      // last one writes into the output block.
+      const float* in = d_dense_a_;
+      for (size_t i = 0; i < dense_.size(); ++i) {
+        const DenseW& d = dense_[i];
+        float* out = i + 1 == dense_.size() ? d_pooled_ : (in == d_dense_a_ ? d_dense_b_ : d_dense_a_);
+        LAUNCH(KC_POOL, launch_head_linear(in, d.w, d.b, out, static_cast<int>(n_pooled_), d.out, d.in, d.act, s.dtype, stream_), "dense module");
+        in = out;
+      }
+      if (normalize_) {
+        LAUNCH(KC_POOL, launch_l2_normalise(d_pooled_, static_cast<int>(n_pooled_), dense_.back().out, stream_), "normalise");
+      }
+    }
   }
   if (n_raw_rows_ > 0) {
     LAUNCH(KC_POOL, launch_gather_rows_f32(x_, d_raw_rows_, d_raw_, static_cast<int>(n_raw_rows_), D, s.dtype, stream_), "raw rows");
@@ -1020,7 +1113,7 @@ void Replica::fetch(float* pooled_out, float* raw_out, float* scores_out) {
   stats_.total_tokens += static_cast<double>(T_);
   stats_.calls += 1.0;
   const size_t D = static_cast<size_t>(output_dim());
-  const size_t Dpad = align_up(D, 8);
+  const size_t Dpad = pooled_ld_;
   const float* hp = h_out_ + (d_pooled_ - d_out_);
   if (n_pooled_ && pooled_out) {
     if (D == Dpad) {
@@ -1030,7 +1123,7 @@ void Replica::fetch(float* pooled_out, float* raw_out, float* scores_out) {
     }
   }
   if (n_raw_rows_ && raw_out) {
-    std::memcpy(raw_out, h_out_ + (d_raw_ - d_out_), n_raw_rows_ * D * 4);
+    std::memcpy(raw_out, h_out_ + (d_raw_ - d_out_), n_raw_rows_ * static_cast<size_t>(raw_dim()) * 4);
   }
   if (predict_ && scores_out) {
     std::memcpy(scores_out, h_out_ + (d_scores_ - d_out_), B_ * static_cast<size_t>(spec_.n_classes) * 4);

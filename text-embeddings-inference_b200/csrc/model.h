@@ -105,7 +105,15 @@ class Replica {
 
   const ModelSpec& spec() const { return spec_; }
   int device() const { return device_; }
-  int output_dim() const;  // width of a pooled row
+  int output_dim() const;  // width of a pooled row (after the Dense modules, if any)
+  int raw_dim() const;     // width of a raw (per-token) row
+
+  // Appends a Sentence-Transformers Dense module (backends/candle/src/models/dense.rs:26-75,
+  // loaded as in backends/candle/src/lib.rs:579-629): `<dir>/config.json` + `<dir>/model.safetensors`
+  // with `linear.weight` [out, in] and optional `linear.bias`.  Modules run on the pooled rows in
+  // the order they were added.  Throws TeiError(ERR_START).
+  void add_dense(const std::string& dir);
+  size_t dense_count() const { return dense_.size(); }
 
   // Validates the batch (throws TeiError(ERR_INFERENCE)), copies it to pinned memory and
   // enqueues the single host-to-device copy.  `predict` selects the classifier path (CLS rows of
@@ -139,6 +147,13 @@ class Replica {
     void *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
     void *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr;
     void *q_norm = nullptr, *k_norm = nullptr;
+  };
+
+  struct DenseW {
+    void* w = nullptr;
+    void* b = nullptr;
+    int in = 0, out = 0;
+    int act = 0;  // ACT_NONE or ACT_TANH
   };
 
   void load_weights(const SafeTensors& st);
@@ -189,6 +204,7 @@ class Replica {
   // classification heads
   void *cls_dense_w_ = nullptr, *cls_dense_b_ = nullptr, *cls_out_w_ = nullptr,
        *cls_out_b_ = nullptr;
+  std::vector<DenseW> dense_;
   // SPLADE head
   void *sp_dense_w_ = nullptr, *sp_dense_b_ = nullptr, *sp_ln_g_ = nullptr, *sp_ln_b_ = nullptr,
        *sp_dec_w_ = nullptr, *sp_dec_b_ = nullptr;
@@ -212,7 +228,8 @@ class Replica {
   float* h_out_ = nullptr;      // pinned mirror
   size_t out_cap_floats_ = 0;
   float *d_pooled_ = nullptr, *d_raw_ = nullptr, *d_scores_ = nullptr, *d_cls_ = nullptr,
-        *d_head_tmp_ = nullptr;
+        *d_head_tmp_ = nullptr, *d_dense_a_ = nullptr, *d_dense_b_ = nullptr;
+  size_t pooled_ld_ = 0;        // floats between pooled rows in the output block
 
   // staged batch
   size_t T_ = 0, B_ = 0, n_work_ = 0, n_pooled_ = 0, n_raw_rows_ = 0;

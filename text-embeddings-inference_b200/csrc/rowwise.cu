@@ -520,6 +520,13 @@ int launch_pool(const PoolArgs& p, cudaStream_t st) {
   return rc;
 }
 
+int launch_l2_normalise(float* x, int rows, int H, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const int warps = 8;
+  l2_normalise_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, st>>>(x, rows, H);
+  return last_error();
+}
+
 int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int n_rows, int H,
                            int dtype, cudaStream_t st) {
   if (n_rows <= 0) return 0;

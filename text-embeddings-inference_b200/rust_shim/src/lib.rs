@@ -28,6 +28,12 @@ extern "C" {
         err: *mut c_char,
         err_cap: usize,
     ) -> c_int;
+    fn tei_b200_add_dense(
+        h: *mut TeiB200,
+        dense_path: *const c_char,
+        err: *mut c_char,
+        err_cap: usize,
+    ) -> c_int;
     fn tei_b200_destroy(h: *mut TeiB200);
     fn tei_b200_health(h: *mut TeiB200) -> c_int;
     fn tei_b200_is_padded(h: *const TeiB200) -> c_int;
@@ -103,11 +109,6 @@ impl B200Backend {
         model_type: ModelType,
         dense_paths: Option<Vec<String>>,
     ) -> Result<Self, BackendError> {
-        if dense_paths.map(|d| !d.is_empty()).unwrap_or(false) {
-            return Err(BackendError::Start(
-                "Dense modules are not supported by the b200 backend yet".into(),
-            ));
-        }
         let (mt, pool) = match model_type {
             ModelType::Classifier => (0, 0),
             ModelType::Embedding(pool) => (
@@ -144,6 +145,23 @@ impl B200Backend {
         };
         if rc != 0 {
             return Err(to_error(rc, &err));
+        }
+        // Dense modules run on the pooled rows inside the library, in this order.
+        for dense_path in dense_paths.unwrap_or_default() {
+            let path = CString::new(dense_path.as_bytes())
+                .map_err(|e| BackendError::Start(e.to_string()))?;
+            let mut err = vec![0 as c_char; ERR_CAP];
+            let rc =
+                unsafe { tei_b200_add_dense(handle, path.as_ptr(), err.as_mut_ptr(), ERR_CAP) };
+            if rc != 0 {
+                unsafe { tei_b200_destroy(handle) };
+                return Err(to_error(rc, &err));
+            }
+            if err[0] != 0 {
+                tracing::warn!("{}", unsafe { CStr::from_ptr(err.as_ptr()) }.to_string_lossy());
+            } else {
+                tracing::info!("Loaded Dense module from path: {dense_path}");
+            }
         }
         let (output_dim, hidden_size, num_classes) = unsafe {
             (

@@ -38,6 +38,7 @@ _BACKEND_PROTOTYPES = {
         c_int,
         [c_char_p, c_char_p, c_int, c_int, POINTER(c_int), c_int, POINTER(c_void_p), c_char_p, c_size_t],
     ),
+    "tei_b200_add_dense": (c_int, [c_void_p, c_char_p, c_char_p, c_size_t]),
     "tei_b200_destroy": (None, [c_void_p]),
     "tei_b200_health": (c_int, [c_void_p]),
     "tei_b200_is_padded": (c_int, [c_void_p]),

@@ -70,8 +70,6 @@ class B200Backend:
     def __init__(self, model_path, dtype: str = "float16", model_type: Union[str, tuple] = "embedding",
                  pool: str = "cls", dense_paths: Optional[Sequence[str]] = None,
                  devices: Optional[Sequence[int]] = None):
-        if dense_paths:
-            raise BackendError(1, "Dense modules are not supported yet")
         self._lib = _lib.load()
         self._h = ctypes.c_void_p()
         mt = 0 if model_type == "classifier" else 1
@@ -83,6 +81,16 @@ class B200Backend:
         if rc != 0:
             self._h = ctypes.c_void_p()
             raise BackendError(rc, err.value.decode(errors="replace"))
+        self.warnings = []
+        for dense_path in dense_paths or []:
+            err = ctypes.create_string_buffer(1024)
+            rc = self._lib.tei_b200_add_dense(self._h, str(dense_path).encode(), err, len(err))
+            if rc != 0:
+                msg = err.value.decode(errors="replace")
+                self.close()
+                raise BackendError(rc, msg)
+            if err.value:
+                self.warnings.append(err.value.decode(errors="replace"))
         self.output_dim = self._lib.tei_b200_output_dim(self._h)
         self.hidden_size = self._lib.tei_b200_hidden_size(self._h)
         self.num_classes = self._lib.tei_b200_num_classes(self._h)
