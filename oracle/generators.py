@@ -42,6 +42,17 @@ def bert_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30522, max_po
     return c
 
 
+def jina_config(alibi: bool = True, **kw) -> dict:
+    """A JinaBERT config: model_type "bert" plus the markers the reference dispatches on
+    (backends/candle/src/lib.rs:83-121) and `position_embedding_type`."""
+    c = bert_config(**kw)
+    c["_name_or_path"] = "jinaai/jina-bert-implementation"
+    c["auto_map"] = {"AutoConfig": "jinaai/jina-bert-implementation--configuration_bert.JinaBertConfig"}
+    c["position_embedding_type"] = "alibi" if alibi else "absolute"
+    c["feed_forward_type"] = "geglu"
+    return c
+
+
 def nomic_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30528, n_positions=2048,
                  rotary_base=1000.0, eps=1e-12) -> dict:
     return {
@@ -72,8 +83,10 @@ def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) 
     H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
     t: Dict[str, Tuple[tuple, str]] = {}
     e = prefix + "embeddings."
+    jina = c.get("_name_or_path") == "jinaai/jina-bert-implementation"
     t[e + "word_embeddings.weight"] = ((V, H), "normal")
-    t[e + "position_embeddings.weight"] = ((c["max_position_embeddings"], H), "normal")
+    if c.get("position_embedding_type", "absolute") == "absolute":
+        t[e + "position_embeddings.weight"] = ((c["max_position_embeddings"], H), "normal")
     t[e + "token_type_embeddings.weight"] = ((c["type_vocab_size"], H), "normal")
     t[e + "LayerNorm.weight"] = ((H,), "ones")
     t[e + "LayerNorm.bias"] = ((H,), "zeros")
@@ -86,6 +99,13 @@ def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) 
         t[p + "attention.output.dense.bias"] = ((H,), "normal")
         t[p + "attention.output.LayerNorm.weight"] = ((H,), "ones")
         t[p + "attention.output.LayerNorm.bias"] = ((H,), "zeros")
+        if jina:  # flash_jina.rs:133-155
+            t[p + "mlp.gated_layers.weight"] = ((2 * I, H), "normal")
+            t[p + "mlp.wo.weight"] = ((H, I), "normal")
+            t[p + "mlp.wo.bias"] = ((H,), "normal")
+            t[p + "mlp.layernorm.weight"] = ((H,), "ones")
+            t[p + "mlp.layernorm.bias"] = ((H,), "zeros")
+            continue
         t[p + "intermediate.dense.weight"] = ((I, H), "normal")
         t[p + "intermediate.dense.bias"] = ((I,), "normal")
         t[p + "output.dense.weight"] = ((H, I), "normal")

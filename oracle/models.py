@@ -504,10 +504,85 @@ class Qwen3Oracle:
         return pool_outputs(self.hidden_states(batch), batch, self.pool)
 
 
+# --------------------------------------------------------------------------- JinaBERT
+def is_jina_bert(config: dict) -> bool:
+    # BertConfigWrapper, backends/candle/src/lib.rs:83-121
+    name = config.get("_name_or_path", "") or ""
+    auto = (config.get("auto_map") or {}).get("AutoConfig", "") or ""
+    return config.get("model_type") == "bert" and (
+        name == "jinaai/jina-bert-implementation" or "jinaai/jina-bert-implementation" in auto)
+
+
+class JinaBertOracle(BertOracle):
+    """models/jina.rs (CPU arm) / flash_jina.rs: BERT with a gated feed-forward
+    (`mlp.gated_layers` without bias -> act(first half) * second half -> `mlp.wo` -> `mlp.layernorm`
+    with the residual, jina.rs:260-300, flash_jina.rs:166-189), and either ALiBi
+    (bias = -slope_h * |i - j|, alibi.rs:49-80; no position table, jina.rs:54-74) or absolute
+    positions.  Head: optional `bert.pooler.dense` + tanh, then `classifier` (jina.rs:342-393)."""
+
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
+                 pool: str = "cls"):
+        cfg = dict(config)
+        pos = cfg.get("position_embedding_type", "absolute")
+        if pos not in ("absolute", "alibi"):
+            raise ValueError("not supported")  # flash_jina.rs:243
+        cfg["position_embedding_type"] = "absolute"  # the base class only checks the field
+        super().__init__(cfg, tensors, model_type, pool)
+        if self.pool == "splade":
+            raise ValueError("`splade` is not supported for Jina")
+        self.alibi = pos == "alibi"
+        self.inter = config["intermediate_size"]
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        tids = torch.from_numpy(batch.token_type_ids.astype(np.int64))
+        g, b = w.ln("embeddings.LayerNorm")
+        word = w.get("embeddings.word_embeddings.weight")[ids]
+        typ = w.get("embeddings.token_type_embeddings.weight")[tids]
+        if self.alibi:
+            x = layer_norm(word, typ, g, b, self.eps)
+        else:
+            pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+            x = layer_norm(word + typ, w.get("embeddings.position_embeddings.weight")[pids], g, b, self.eps)
+        slopes = alibi_slopes(self.nh) if self.alibi else None
+        cu = batch.cumulative_seq_lengths
+        T = x.shape[0]
+        for i in range(self.n_layers):
+            p = f"encoder.layer.{i}."
+            q = linear(x, w.get(p + "attention.self.query.weight"), w.get(p + "attention.self.query.bias"))
+            k = linear(x, w.get(p + "attention.self.key.weight"), w.get(p + "attention.self.key.bias"))
+            v = linear(x, w.get(p + "attention.self.value.weight"), w.get(p + "attention.self.value.bias"))
+            a = attention_varlen(q.view(T, self.nh, self.dh), k.view(T, self.nh, self.dh),
+                                 v.view(T, self.nh, self.dh), cu, 1.0 / math.sqrt(self.dh), False, slopes)
+            g1, b1 = w.ln(p + "attention.output.LayerNorm")
+            x1 = layer_norm(linear(a, w.get(p + "attention.output.dense.weight"),
+                                   w.get(p + "attention.output.dense.bias")), x, g1, b1, self.eps)
+            h = linear(x1, w.get(p + "mlp.gated_layers.weight"), None)
+            f = self.act(h[:, :self.inter]) * h[:, self.inter:]
+            g2, b2 = w.ln(p + "mlp.layernorm")
+            x = layer_norm(linear(f, w.get(p + "mlp.wo.weight"), w.get(p + "mlp.wo.bias")), x1, g2, b2, self.eps)
+        return x
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+    def predict(self, batch: Batch) -> Tensor:
+        x = self.hidden_states(batch)
+        cu = batch.cumulative_seq_lengths.astype(np.int64)
+        h = x[torch.from_numpy(cu[:-1])]
+        a = self.all
+        if a.has("bert.pooler.dense.weight"):
+            h = torch.tanh(linear(h, a.get("bert.pooler.dense.weight"), a.get("bert.pooler.dense.bias")))
+        return linear(h, a.get("classifier.weight"), a.get("classifier.bias"))
+
+
 def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
     """Dispatch on config.json's model_type like backends/candle/src/lib.rs:124-154,282-577."""
     config, tensors = load_model_dir(model_dir)
     mt = config["model_type"]
+    if is_jina_bert(config):
+        return JinaBertOracle(config, tensors, model_type, pool)
     if mt in ("bert", "roberta", "xlm-roberta", "camembert"):
         return BertOracle(config, tensors, model_type, pool)
     if mt == "nomic_bert":

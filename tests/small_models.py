@@ -23,6 +23,17 @@ def write_all(base):
     dirs["splade"] = G.write_model_dir(
         base / "splade", G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1003, max_pos=512),
         seed=7, splade=True, norm_jitter=0.1, std=0.05)
+    dirs["jina"] = G.write_model_dir(
+        base / "jina", G.jina_config(alibi=True, hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+        seed=8, norm_jitter=0.1, std=0.05)
+    dirs["jina_alibi6"] = G.write_model_dir(
+        base / "jina_alibi6", G.jina_config(alibi=True, hidden=384, layers=2, heads=6, inter=512, vocab=1000, max_pos=512),
+        seed=10, norm_jitter=0.1, std=0.05)
+    dirs["jina_abs_cls"] = G.write_model_dir(
+        base / "jina_abs_cls",
+        G.jina_config(alibi=False, hidden=384, layers=2, heads=6, inter=512, vocab=1000, max_pos=512,
+                      id2label={"0": "a", "1": "b"}),
+        seed=9, classifier="bert", norm_jitter=0.1, std=0.05, prefix="bert.")
     dirs["nomic"] = G.write_model_dir(
         base / "nomic", G.nomic_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, n_positions=2048),
         seed=4, norm_jitter=0.1, std=0.05)
@@ -43,6 +54,9 @@ GOLDEN_CASES = {
     "bert_cls3_scores": ("bert_cls3", "classifier", "cls", dict(seed=104, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "nomic_mean": ("nomic", "embedding", "mean", dict(seed=105, lens=LENS + [700], lo=0, hi=1000, type_vocab=2, offset=0)),
     "qwen3_last": ("qwen3", "embedding", "last_token", dict(seed=106, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "jina_mean": ("jina", "embedding", "mean", dict(seed=108, lens=LENS + [511], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "jina_alibi6_cls": ("jina_alibi6", "embedding", "cls", dict(seed=109, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "jina_abs_scores": ("jina_abs_cls", "classifier", "cls", dict(seed=110, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

@@ -34,6 +34,8 @@ def _close(got, ref, tol):
     (77, 1003, 128, "relu_log1p", True, False, "f16"),  # N not a multiple of 8: scalar stores
     (520, 1024, 768, "swiglu", False, False, "f16"),
     (520, 512, 256, "swiglu", True, False, "bf16"),
+    (520, 1024, 768, "geglu", False, False, "f16"),
+    (130, 512, 256, "geglu", True, False, "bf16"),
     (1000, 768, 3072, "none", True, True, "bf16"),
     (700, 256, 256, "tanh", True, False, "f16"),
     (20000, 2304, 768, "none", True, False, "f16"),   # many waves of the persistent loop
@@ -45,10 +47,10 @@ def test_linear(lib, M, N, K, act, bias, res, dtype):
     a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dt)
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dt)
     b = (torch.randn(N, device="cuda", generator=g) * 0.1).to(dt) if bias else None
-    n_out = N // 2 if act == "swiglu" else N
+    n_out = N // 2 if act in ("swiglu", "geglu") else N
     r = (torch.randn(M, n_out, device="cuda", generator=g) * 0.5).to(dt) if res else None
     ww, bb = w, b
-    if act == "swiglu":
+    if act in ("swiglu", "geglu"):
         ww = ops.interleave_swiglu(w[: N // 2], w[N // 2:])
         bb = ops.interleave_swiglu(b[: N // 2], b[N // 2:]) if bias else None
     out = ops.linear(a, ww, bb, r, act=act)
@@ -65,6 +67,8 @@ def test_linear(lib, M, N, K, act, bias, res, dtype):
         y = torch.log1p(torch.relu(y))
     elif act == "swiglu":
         y = torch.nn.functional.silu(y[:, : N // 2]) * y[:, N // 2:]
+    elif act == "geglu":
+        y = torch.nn.functional.gelu(y[:, : N // 2], approximate="tanh") * y[:, N // 2:]
     if res:
         y = y + r.float()
     _close(out, y, 2e-2 if dtype == "f16" else 8e-2)

@@ -98,6 +98,13 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Gate activation of the gated feed-forwards.
+template <int ACT>
+__device__ __forceinline__ float glu_gate(float x) {
+  if constexpr (ACT == ACT_GEGLU) return gelu_tanh(x);
+  return silu(x);
+}
+
 template <int ACT>
 __device__ __forceinline__ float apply_act(float x) {
   if constexpr (ACT == ACT_GELU) return gelu_tanh(x);
@@ -183,14 +190,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
   const int row = m0 + quad * 32 + lane;
   if (p.tma_store) {
     // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
-    constexpr int STEPS = (ACT == ACT_SWIGLU) ? 2 : 4;
-    const int o0 = (ACT == ACT_SWIGLU) ? n0 / 2 : n0;
+    constexpr int STEPS = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? 2 : 4;
+    const int o0 = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? n0 / 2 : n0;
 #pragma unroll 1
     for (int c = part * (STEPS / n_parts); c < (part + 1) * (STEPS / n_parts); ++c) {
       const int ocol = o0 + c * 64;
       if (ocol >= n_out) break;  // uniform across the CTA
       uint32_t packed[32];
-      if constexpr (ACT == ACT_SWIGLU) {
+      if constexpr (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) {
         // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
@@ -209,7 +216,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
               uv0 += to_f32<T>(bias[gcol + 128 + j]);
               uv1 += to_f32<T>(bias[gcol + 128 + j + 1]);
             }
-            packed[hlf * 16 + j / 2] = pack2<T>(silu(gv0) * uv0, silu(gv1) * uv1);
+            packed[hlf * 16 + j / 2] = pack2<T>(glu_gate<ACT>(gv0) * uv0, glu_gate<ACT>(gv1) * uv1);
           }
         }
       } else {
@@ -269,7 +276,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
       }
       ++store_count;
     }
-  } else if constexpr (ACT == ACT_SWIGLU) {
+  } else if constexpr (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) {
     // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
 #pragma unroll 1
     for (int c = part * (4 / n_parts); c < (part + 1) * (4 / n_parts); ++c) {
@@ -288,7 +295,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
           if (gcol + j < p.N) gv += to_f32<T>(bias[gcol + j]);
           if (gcol + 128 + j < p.N) uv += to_f32<T>(bias[gcol + 128 + j]);
         }
-        v[j] = silu(gv) * uv;
+        v[j] = glu_gate<ACT>(gv) * uv;
       }
       const int n_valid = min(32, p.N / 2 - ocol);
       if (row < p.M && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
@@ -439,7 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
     uint8_t* stage_buf = epi_smem + (warp - 2) * (2 * EPI_BUF_BYTES);
     uint32_t store_count = 0;  // TMA stores issued by this warp (selects the staging buffer)
-    const int n_out = (ACT == ACT_SWIGLU) ? p.N / 2 : p.N;
+    const int n_out = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? p.N / 2 : p.N;
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
@@ -621,7 +628,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
     uint8_t* stage_buf = epi_smem + (warp - 2) * (2 * EPI_BUF_BYTES);
     uint32_t store_count = 0;
-    const int n_out = (ACT == ACT_SWIGLU) ? p.N / 2 : p.N;
+    const int n_out = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? p.N / 2 : p.N;
     int local = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
       const int acc = local & 1;
@@ -675,7 +682,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   if (rc) return rc;
   // Outputs leave through TMA stores when the output rows are 16-byte aligned and no residual
   // is fused; otherwise the epilogue falls back to per-thread stores.
-  const int n_out = (ACT == ACT_SWIGLU) ? g.N / 2 : g.N;
+  const int n_out = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? g.N / 2 : g.N;
   const bool tma_store = g.residual == nullptr && g.ldo % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
   CUtensorMap tm_c = tm_a;  // placeholder when unused (never dereferenced by the kernel)
@@ -739,6 +746,7 @@ int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
     case ACT_TANH: return launch_typed<T, ACT_TANH>(g, stream);
     case ACT_SWIGLU: return launch_typed<T, ACT_SWIGLU>(g, stream);
     case ACT_RELU_LOG1P: return launch_typed<T, ACT_RELU_LOG1P>(g, stream);
+    case ACT_GEGLU: return launch_typed<T, ACT_GEGLU>(g, stream);
     default: return static_cast<int>(cudaErrorInvalidValue);
   }
 }
@@ -752,7 +760,7 @@ int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   if (g.N <= 0 || g.K <= 0 || g.K % 8 != 0 || g.lda % 8 != 0) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
-  if (g.act == ACT_SWIGLU && g.N % 256 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (act_is_glu(g.act) && g.N % 256 != 0) return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.w) & 15)) {
     return static_cast<int>(cudaErrorInvalidValue);
   }

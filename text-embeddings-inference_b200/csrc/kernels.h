@@ -10,8 +10,9 @@ namespace tei {
 
 enum DType : int { DT_F16 = 0, DT_BF16 = 1 };
 
-// Activation fused into the GEMM epilogue.  ACT_SWIGLU expects the weight rows interleaved in
-// blocks of 128 (128 gate rows, then the 128 matching up rows) and writes N/2 columns.
+// Activation fused into the GEMM epilogue.  ACT_SWIGLU and ACT_GEGLU expect the weight rows
+// interleaved in blocks of 128 (128 gate rows, then the 128 matching up rows) and write N/2
+// columns.
 enum Act : int {
   ACT_NONE = 0,
   ACT_GELU = 1,        // tanh approximation, the only GELU the reference implements
@@ -19,7 +20,9 @@ enum Act : int {
   ACT_TANH = 3,
   ACT_SWIGLU = 4,      // silu(gate) * up
   ACT_RELU_LOG1P = 5,  // log(1 + relu(x)), the SPLADE decoder activation
+  ACT_GEGLU = 6,       // gelu_tanh(gate) * up, the JinaBERT feed-forward
 };
+inline bool act_is_glu(int act) { return act == ACT_SWIGLU || act == ACT_GEGLU; }
 
 // Device status codes (0 = ok).
 enum DevStatus : int {

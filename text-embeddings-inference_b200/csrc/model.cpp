@@ -76,17 +76,37 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
     s.type_vocab = static_cast<int>(need_int(c, "type_vocab_size"));
     s.eps = static_cast<float>(need_double(c, "layer_norm_eps"));
-    if (c.get_string("position_embedding_type", "absolute") != "absolute") {
+    // BertConfigWrapper (backends/candle/src/lib.rs:83-121): `_name_or_path` or
+    // `auto_map.AutoConfig` select the JinaBERT implementations for model_type "bert".
+    const std::string name_or_path = c.get_string("_name_or_path", "");
+    const std::string auto_config = c["auto_map"].is_object() ? c["auto_map"].get_string("AutoConfig", "") : "";
+    const std::string pos_type = c.get_string("position_embedding_type", "absolute");
+    if (mt == "bert" && (name_or_path == "jinaai/jina-bert-implementation" ||
+                         auto_config.find("jinaai/jina-bert-implementation") != std::string::npos)) {
+      s.jina = true;
+      if (pos_type == "alibi") s.alibi = true;
+      else if (pos_type != "absolute") throw TeiError(ERR_START, "not supported");  // flash_jina.rs:243
+      if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Jina");
+    } else if (mt == "bert" && (name_or_path == "jinaai/jina-bert-v2-qk-post-norm" ||
+                                auto_config.find("jinaai/jina-bert-v2-qk-post-norm") != std::string::npos)) {
+      throw TeiError(ERR_START, "JinaCodeBert checkpoints are outside this backend");
+    } else if (pos_type != "absolute") {
       throw TeiError(ERR_START, "FlashBert only supports absolute position embeddings");
     }
     s.act = parse_act(need_string(c, "hidden_act"));
-    if (s.act != ACT_GELU && s.act != ACT_RELU && s.act != ACT_TANH) {
+    if (s.jina) {
+      // gated feed-forward: act(first half) * second half (flash_jina.rs:177-182)
+      if (s.act != ACT_GELU) throw TeiError(ERR_START, "unsupported hidden_act for the JinaBERT feed-forward");
+      s.gated = true;
+      s.act = ACT_GEGLU;
+    } else if (s.act != ACT_GELU && s.act != ACT_RELU && s.act != ACT_TANH) {
       throw TeiError(ERR_START, "unsupported hidden_act for a BERT feed-forward");
     }
     if (s.heads <= 0 || s.hidden % s.heads != 0) throw TeiError(ERR_START, "hidden_size is not a multiple of num_attention_heads");
     s.kv_heads = s.heads;
     s.head_dim = s.hidden / s.heads;
     s.qkv_bias = s.out_bias = s.fc1_bias = s.fc2_bias = true;
+    if (s.jina) s.fc1_bias = false;
     if (s.classifier) {
       if (!c["id2label"].is_object()) throw TeiError(ERR_START, "`id2label` must be set for classifier models");
       s.n_classes = static_cast<int>(c["id2label"].size());
@@ -484,10 +504,33 @@ void Replica::load_bert(const SafeTensors& st) {
   Names n{st, prefix};
   Names root{st, ""};
   expect_shape(n.get("embeddings.word_embeddings.weight"), {s.vocab, H}, "embeddings.word_embeddings.weight");
-  expect_shape(n.get("embeddings.position_embeddings.weight"), {s.max_pos, H}, "embeddings.position_embeddings.weight");
   expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
   word_ = upload_new(n.get("embeddings.word_embeddings.weight"));
-  pos_tab_ = upload_new(n.get("embeddings.position_embeddings.weight"));
+  if (!s.alibi) {  // JinaEmbeddings::load, jina.rs:20-31
+    expect_shape(n.get("embeddings.position_embeddings.weight"), {s.max_pos, H}, "embeddings.position_embeddings.weight");
+    pos_tab_ = upload_new(n.get("embeddings.position_embeddings.weight"));
+  } else {
+    // alibi_head_slopes (alibi.rs:18-47), f64 on the host, fp32 on the device as flash_jina.rs:237-241
+    auto pow2_slopes = [](int k) {
+      const double start = std::pow(2.0, -std::pow(2.0, -(std::log2(static_cast<double>(k)) - 3.0)));
+      std::vector<double> v(k);
+      for (int i = 0; i < k; ++i) v[i] = start * std::pow(start, i);
+      return v;
+    };
+    std::vector<double> sl;
+    const double lg = std::log2(static_cast<double>(s.heads));
+    if (lg == std::floor(lg)) {
+      sl = pow2_slopes(s.heads);
+    } else {
+      const int closest = 1 << static_cast<int>(std::floor(lg));
+      sl = pow2_slopes(closest);
+      const std::vector<double> extra = pow2_slopes(2 * closest);
+      for (int i = 0; static_cast<int>(sl.size()) < s.heads; i += 2) sl.push_back(extra[i]);
+    }
+    std::vector<float> slf(sl.begin(), sl.end());
+    alibi_slopes_ = static_cast<float*>(dev_alloc(slf.size() * 4));
+    TEI_CUDA(cudaMemcpy(alibi_slopes_, slf.data(), slf.size() * 4, cudaMemcpyHostToDevice));
+  }
   type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
   emb_g_ = upload_new(n.ln_w("embeddings.LayerNorm"));
   emb_b_ = upload_new(n.ln_b("embeddings.LayerNorm"));
@@ -509,6 +552,25 @@ void Replica::load_bert(const SafeTensors& st) {
     L.bo = upload_new(n.get(p + "attention.output.dense.bias"));
     L.ln1_g = upload_new(n.ln_w(p + "attention.output.LayerNorm"));
     L.ln1_b = upload_new(n.ln_b(p + "attention.output.LayerNorm"));
+    if (s.jina) {
+      // JinaBertLayer::load (flash_jina.rs:133-155): `mlp.gated_layers.weight` [2I, H] without
+      // bias, rows [0, I) gated by the activation, rows [I, 2I) not; `mlp.wo`; `mlp.layernorm`.
+      const StTensor& gw = n.get(p + "mlp.gated_layers.weight");
+      expect_shape(gw, {2 * I, H}, p + "mlp.gated_layers.weight");
+      StTensor gate = gw, up = gw;
+      gate.shape = {I, H};
+      up.shape = {I, H};
+      gate.nbytes = up.nbytes = gw.nbytes / 2;
+      up.data = gw.data + gw.nbytes / 2;
+      L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+      upload_rows_interleaved(L.w1, gate, up);
+      expect_shape(n.get(p + "mlp.wo.weight"), {H, I}, p + "mlp.wo.weight");
+      L.w2 = upload_new(n.get(p + "mlp.wo.weight"));
+      L.b2 = upload_new(n.get(p + "mlp.wo.bias"));
+      L.ln2_g = upload_new(n.ln_w(p + "mlp.layernorm"));
+      L.ln2_b = upload_new(n.ln_b(p + "mlp.layernorm"));
+      continue;
+    }
     expect_shape(n.get(p + "intermediate.dense.weight"), {I, H}, p + "intermediate.dense.weight");
     L.w1 = upload_new(n.get(p + "intermediate.dense.weight"));
     L.b1 = upload_new(n.get(p + "intermediate.dense.bias"));
@@ -764,7 +826,8 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
     }
     max_len = std::max(max_len, b.cu_seqlens[i + 1] - b.cu_seqlens[i]);
   }
-  const uint32_t pos_limit = static_cast<uint32_t>(s.arch == ARCH_BERT ? s.max_pos : s.rope_table_len);
+  // ALiBi models have no position table to index (flash_jina.rs never reads position_ids then).
+  const uint32_t pos_limit = s.alibi ? 0xffffffffu : static_cast<uint32_t>(s.arch == ARCH_BERT ? s.max_pos : s.rope_table_len);
   const bool use_types = s.arch != ARCH_QWEN3;
   if (use_types && !b.token_type_ids) throw TeiError(ERR_INFERENCE, "null token_type_ids");
   for (size_t t = 0; t < b.n_tokens; ++t) {
@@ -892,7 +955,7 @@ void Replica::forward_bert() {
   const int T = static_cast<int>(T_), H = s.hidden, I = s.inter;
   int* status = reinterpret_cast<int*>(d_out_);
   EmbedArgs e;
-  e.ids = d_ids_; e.type_ids = d_types_; e.pos_ids = d_pos_;
+  e.ids = d_ids_; e.type_ids = d_types_; e.pos_ids = pos_tab_ ? d_pos_ : nullptr;
   e.word = word_; e.type_tab = type_tab_; e.pos_tab = pos_tab_;
   e.gamma = emb_g_; e.beta = emb_b_; e.out = x_; e.T = T; e.H = H; e.eps = s.eps; e.dtype = s.dtype;
   LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
@@ -906,14 +969,18 @@ void Replica::forward_bert() {
     a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
     a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
-    a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    a.alibi_slopes = alibi_slopes_; a.dtype = s.dtype; a.status = status;
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
     NormArgs n1;
     n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
     n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "attention LayerNorm");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+    if (s.gated) {  // JinaBERT: act(gate) * up in the epilogue of one [T, 2I] projection
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, nullptr, ffn_, T, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated projection");
+    } else {
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+    }
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
     NormArgs n2 = n1;
     n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;

@@ -43,6 +43,8 @@ struct ModelSpec {
   Arch arch = ARCH_BERT;
   std::string model_type;
   bool roberta = false;
+  bool jina = false;       // JinaBERT: gated feed-forward, optional ALiBi (models/flash_jina.rs)
+  bool alibi = false;      // ALiBi slopes instead of a position table
   int hidden = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, inter = 0;
   int vocab = 0, max_pos = 0, type_vocab = 0;
   float eps = 1e-12f;
@@ -201,6 +203,7 @@ class Replica {
   void* projection_ = nullptr;  // optional Qwen3 `linear.weight`
   int projection_dim_ = 0;
   float *cos_ = nullptr, *sin_ = nullptr, *cos_scaled_ = nullptr, *sin_scaled_ = nullptr;
+  float* alibi_slopes_ = nullptr;  // [heads], fp32 (alibi.rs:18-47)
   // classification heads
   void *cls_dense_w_ = nullptr, *cls_dense_b_ = nullptr, *cls_out_w_ = nullptr,
        *cls_out_b_ = nullptr;

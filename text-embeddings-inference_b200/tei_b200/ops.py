@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-ACT = {"none": 0, "gelu": 1, "relu": 2, "tanh": 3, "swiglu": 4, "relu_log1p": 5}
+ACT = {"none": 0, "gelu": 1, "relu": 2, "tanh": 3, "swiglu": 4, "relu_log1p": 5, "geglu": 6}
 POOL = {"cls": 0, "mean": 1, "splade": 2, "max": 2, "last_token": 3}
 
 
@@ -49,11 +49,11 @@ def check_status(status: torch.Tensor, what: str = "kernel"):
 
 
 def linear(a, w, bias=None, residual=None, act="none", out=None, status=None):
-    """out = act(a @ w.T + bias) (+ residual); for act == 'swiglu' w/bias are pre-interleaved."""
+    """out = act(a @ w.T + bias) (+ residual); for act == 'swiglu' / 'geglu' w/bias are pre-interleaved."""
     lib = _lib.load()
     M, K = a.shape
     N = w.shape[0]
-    n_out = N // 2 if act == "swiglu" else N
+    n_out = N // 2 if act in ("swiglu", "geglu") else N
     if out is None:
         out = torch.empty((M, n_out), dtype=a.dtype, device=a.device)
     own = status is None
