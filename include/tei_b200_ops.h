@@ -43,6 +43,14 @@ int tei_b200_op_linear(const void* a_dev, const void* w_dev, const void* bias_de
  * backends/core/src/lib.rs:9-17). */
 int tei_b200_attention_plan(const int32_t* cu_seqlens_host, int n_seqs, int causal,
                             int32_t* work_out, int capacity_items);
+/* The same for sliding-window attention (window_size_left / window_size_right of
+ * backends/candle/src/flash_attn.rs:23-36,72-95): key j counts for query i when
+ * i - window_left <= j <= i + window_right, -1 = no limit on that side, causal forces
+ * window_right = 0.  The fourth number of each quadruple is the first key the tile can see,
+ * rounded down to a multiple of 64. */
+int tei_b200_attention_plan_windowed(const int32_t* cu_seqlens_host, int n_seqs, int causal,
+                                     int window_left, int window_right, int32_t* work_out,
+                                     int capacity_items);
 
 /* Variable-length attention over a packed batch.  Replaces flash_attn_varlen
  * (backends/candle/src/flash_attn.rs:23-120).  q/k/v are token-major strided views
@@ -54,6 +62,15 @@ int tei_b200_op_attention(const void* q_dev, const void* k_dev, const void* v_de
                           int n_kv_heads, int head_dim, int ld_q, int ld_k, int ld_v, int ld_o,
                           int causal, float softmax_scale, const float* alibi_slopes_dev,
                           int dtype, int* status_dev, void* stream);
+/* The same with a sliding window; work_dev must come from tei_b200_attention_plan_windowed
+ * called with the same causal / window arguments. */
+int tei_b200_op_attention_windowed(const void* q_dev, const void* k_dev, const void* v_dev,
+                                   void* out_dev, const int32_t* work_dev, int n_work,
+                                   int total_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int ld_q, int ld_k, int ld_v, int ld_o, int causal,
+                                   int window_left, int window_right, float softmax_scale,
+                                   const float* alibi_slopes_dev, int dtype, int* status_dev,
+                                   void* stream);
 
 /* out[t] = LayerNorm(word[ids[t]] + type[type_ids[t]] + pos[pos_ids[t]]).  Replaces
  * BertEmbeddings::forward (backends/candle/src/models/bert.rs:83-101) and

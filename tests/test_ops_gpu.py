@@ -150,6 +150,54 @@ def test_attention(lib, lens, nh, nkv, D, causal, alibi, dtype):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("lens,nh,nkv,D,causal,wl,wr,dtype", [
+    ([300, 40, 129], 4, 4, 64, True, 64, -1, "f16"),      # Mistral-style: causal, left window
+    ([1000, 5], 4, 2, 128, True, 100, -1, "bf16"),        # window not a multiple of the tile
+    ([700], 2, 2, 64, True, 0, -1, "f16"),                # every token sees only itself
+    ([513, 64, 200], 4, 4, 64, False, 64, 64, "f16"),     # ModernBERT-style local attention
+    ([400], 2, 2, 128, False, 17, 130, "f16"),            # asymmetric
+    ([300, 130], 4, 4, 64, True, 4096, -1, "f16"),        # window wider than the sequences
+])
+def test_attention_sliding_window(lib, lens, nh, nkv, D, causal, wl, wr, dtype):
+    # flash_attn.rs:23-36,72-95: key j counts for query i when i - wl <= j <= i + wr.
+    from tei_b200 import ops
+    dt = DT[dtype]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = _gen(T + nh + D + wl)
+    width = (nh + 2 * nkv) * D
+    buf = torch.full((T + 64, width), float("nan"), device="cuda", dtype=dt)
+    buf[:T] = torch.randn(T, width, device="cuda", generator=g).to(dt)
+    qkv = buf[:T]
+    q = qkv[:, : nh * D].view(T, nh, D)
+    k = qkv[:, nh * D: (nh + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nh + nkv) * D:].view(T, nkv, D)
+    scale = 1.0 / D ** 0.5
+    out = ops.attention(q, k, v, cu, causal=causal, scale=scale, window_left=wl, window_right=wr)
+    ref = torch.zeros(T, nh, D, device="cuda", dtype=torch.float32)
+    for s in range(len(lens)):
+        a, b = cu[s], cu[s + 1]
+        L = b - a
+        qs = q[a:b].float().transpose(0, 1)
+        ks = k[a:b].float().transpose(0, 1).repeat_interleave(nh // nkv, dim=0)
+        vs = v[a:b].float().transpose(0, 1).repeat_interleave(nh // nkv, dim=0)
+        sc = qs @ ks.transpose(1, 2) * scale
+        i = torch.arange(L, device="cuda").view(L, 1)
+        j = torch.arange(L, device="cuda").view(1, L)
+        right = 0 if causal else wr
+        ok = torch.ones(L, L, device="cuda", dtype=torch.bool)
+        if wl >= 0:
+            ok &= j >= i - wl
+        if right >= 0:
+            ok &= j <= i + right
+        sc = sc.masked_fill(~ok, float("-inf"))
+        ref[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1)
+    _close(out, ref.reshape(T, nh * D), 1e-2 if dtype == "f16" else 4e-2)
+    assert torch.equal(out, ops.attention(q, k, v, cu, causal=causal, scale=scale, window_left=wl, window_right=wr))
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_embedding_and_norms(lib, dtype):
     from tei_b200 import ops

@@ -34,6 +34,30 @@ def test_attention_plan_edge_cases(lib):
     assert sorted(w) == [[0, 129, 0, 0], [0, 129, 128, 0]]
 
 
+def test_attention_plan_with_a_sliding_window(lib):
+    # flash_attn.rs:23-36: key j counts for query i when i - left <= j <= i + right.  The plan
+    # stores the 64-aligned first key of each tile and orders tiles by their 64-key steps.
+    from tei_b200 import ops
+    lens = [1000, 5, 129, 300]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    for causal, left, right in ((True, 100, -1), (False, 64, 64), (True, 0, -1), (False, -1, 10), (True, 5000, -1)):
+        work = ops.attention_plan(cu, causal, left, right).tolist()
+        assert len(work) == sum((n + 127) // 128 for n in lens)
+        r = 0 if causal else right
+        costs = []
+        for start, length, q0, first in work:
+            want_first = (max(0, q0 - left) // 64) * 64 if left >= 0 else 0
+            assert first == want_first
+            # no visible key of any row of the tile lies before `first`
+            if left >= 0:
+                assert first <= max(0, q0 - left)
+            kv_end = min(length, q0 + 128 + r) if r >= 0 else length
+            costs.append((kv_end - first + 63) // 64)
+        assert costs == sorted(costs, reverse=True)
+    # without a window the two entry points agree
+    assert ops.attention_plan(cu, True, -1, -1).tolist() == ops.attention_plan(cu, True).tolist()
+
+
 def test_plan_shards_balances_and_is_deterministic(lib):
     import tei_b200
     lens = G.lengths_cfg5()

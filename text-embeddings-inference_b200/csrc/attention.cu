@@ -56,11 +56,11 @@ struct AttnSmem {
 
 struct AttnParams {
   void* out;
-  const int* work;  // [n_work][4] = {seq_start, seq_len, q0, unused}
+  const int* work;  // [n_work][4] = {seq_start, seq_len, q0, first key of the unit (multiple of 64)}
   int n_work;
   int n_heads, n_kv_heads;
   int ld_o;
-  int causal;
+  int win_left, win_right;  // keys j of query i count when i - win_left <= j <= i + win_right; -1: no limit
   float scale_log2;         // scale * log2(e)
   const float* alibi_slopes;
   int* status;
@@ -98,13 +98,14 @@ __device__ __forceinline__ float ex2_fast(float x) {
 
 // One thread owns one query row of the 64-key score tile; the row is read from TMEM into
 // registers once per step (one wait) and both passes work from there.
-// Only the first n_chunks * 32 columns are touched.  MASKED: only keys [0, lim) count.
+// Only the first n_chunks * 32 columns are touched.  MASKED: only keys [lo, lim) count.
 // ALIBI: subtract slope * |rel - key| (rel = query position - first key position of the tile).
 //
 // Pass 1: row maximum in the scaled log2 domain (-inf when the row sees no key).
 template <bool MASKED, bool ALIBI>
-__device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int lim, int n_chunks, float sl2,
+__device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int lo, int lim, int n_chunks, float sl2,
                                          float slope, int rel) {
+  const unsigned span = static_cast<unsigned>(max(0, lim - lo));  // visible keys: [lo, lim)
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
 #pragma unroll
   for (int c = 0; c < BKV / 32; ++c) {
@@ -119,8 +120,8 @@ __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int
         x1 = x1 * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1));
       }
       if (MASKED) {
-        x0 = kk < lim ? x0 : -INFINITY;
-        x1 = kk + 1 < lim ? x1 : -INFINITY;
+        x0 = static_cast<unsigned>(kk - lo) < span ? x0 : -INFINITY;
+        x1 = static_cast<unsigned>(kk + 1 - lo) < span ? x1 : -INFINITY;
       }
       mx[(i >> 1) & 3] = ptx::max3(mx[(i >> 1) & 3], x0, x1);
     }
@@ -133,8 +134,9 @@ __device__ __forceinline__ float row_max(const uint32_t (&sc)[BKV / 32][32], int
 // values per 32-bit column from column `t_p` on: the A operand of the P V MMA); returns the row
 // sum.
 template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lim,
+__device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lo, int lim,
                                              int n_chunks, float sl2, float slope, int rel, float m_use) {
+  const unsigned span = static_cast<unsigned>(max(0, lim - lo));  // visible keys: [lo, lim)
   // Packed pairs: one FMA scales and shifts two scores, one add accumulates two probabilities.
   const uint64_t sl2_2 = ptx::pack_f32x2(sl2, sl2), neg_m2 = ptx::pack_f32x2(-m_use, -m_use);
   uint64_t acc[2] = {0ull, 0ull};  // two independent accumulator pairs
@@ -157,8 +159,8 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
         e1 = ex2_fast(a1);
       }
       if (MASKED) {
-        e0 = kk < lim ? e0 : 0.f;
-        e1 = kk + 1 < lim ? e1 : 0.f;
+        e0 = static_cast<unsigned>(kk - lo) < span ? e0 : 0.f;
+        e1 = static_cast<unsigned>(kk + 1 - lo) < span ? e1 : 0.f;
       }
       acc[(i >> 1) & 1] = ptx::add_f32x2(acc[(i >> 1) & 1], ptx::pack_f32x2(e0, e1));
       pk[i / 2] = pack2<T>(e0, e1);
@@ -234,16 +236,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t tmem_o0 = tmem_base + 128;
   const int group = p.n_heads / p.n_kv_heads;
 
-  // Steps of one unit: 64-key tiles up to the last key any row of the query tile can see.
-  auto unit_steps = [&](const int* it) {
-    const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
-    return (kv_end + BKV - 1) / BKV;
+  // One past the last key any row of the query tile can see (causal = win_right 0).
+  auto unit_kv_end = [&](const int* it) {
+    return p.win_right >= 0 ? min(it[1], it[2] + BQ + p.win_right) : it[1];
   };
+  // Steps of one unit: 64-key tiles from the unit's first key (it[3]; 0 unless a left window
+  // cuts the early keys off) up to the last key any row can see.
+  auto unit_steps = [&](const int* it) { return (unit_kv_end(it) - it[3] + BKV - 1) / BKV; };
   // Number of keys of step j of a unit that any row can see (CTA-uniform).
-  auto keys_in_tile = [&](const int* it, int j) {
-    const int kv_end = p.causal ? min(it[1], it[2] + BQ) : it[1];
-    return min(BKV, kv_end - j * BKV);
-  };
+  auto keys_in_tile = [&](const int* it, int j) { return min(BKV, unit_kv_end(it) - it[3] - j * BKV); };
 
   // The CTA is persistent: it walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...
   // `g` counts key steps over the CTA's whole life, `n` counts units; they drive every buffer
@@ -284,9 +285,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
             ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_kv[st],
-                             kv_head * D + a * 64, it[0] + j * BKV);
+                             kv_head * D + a * 64, it[0] + it[3] + j * BKV);
             ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, &bar_kv[st],
-                             kv_head * D + a * 64, it[0] + j * BKV);
+                             kv_head * D + a * 64, it[0] + it[3] + j * BKV);
           }
         }
       }
@@ -432,8 +433,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int head = w % p.n_heads;
       const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
       const int seq_start = it[0], seq_len = it[1], q0 = it[2];
-      const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
-      const int n_kv = (kv_end + BKV - 1) / BKV;
+      const int kv_begin = it[3];
+      const int kv_end = unit_kv_end(it);
+      const int n_kv = (kv_end - kv_begin + BKV - 1) / BKV;
       const int qi = q0 + r;                  // position inside the sequence
       const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
       float m = -INFINITY, l = 0.f;           // running maximum (scaled log2 domain) and sum
@@ -444,16 +446,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           break;
         }
         ptx::tc_fence_after();
-        const int k_base = j * BKV;
-        // Keys this row may attend to within the tile: [0, lim).
+        const int k_base = kv_begin + j * BKV;
+        // Keys this row may attend to within the tile: [lo, lim).
         int lim = seq_len - k_base;
-        if (p.causal) lim = min(lim, qi - k_base + 1);
+        if (p.win_right >= 0) lim = min(lim, qi - k_base + p.win_right + 1);
         lim = max(0, min(lim, BKV));
+        const int lo = p.win_left >= 0 ? max(0, qi - p.win_left - k_base) : 0;
         // Columns beyond the tile's last key are neither computed by the S MMA nor read by
         // the P V MMA: only ceil(keys / 32) chunks of 32 columns are processed.
         const int n_chunks = (min(BKV, kv_end - k_base) + 31) / 32;
         // Uniform per (CTA, step): interior tiles need no per-element mask.
-        const bool tile_full = (k_base + BKV <= seq_len) && (!p.causal || k_base + BKV <= q0 + 1);
+        const bool tile_full = (k_base + BKV <= seq_len) &&
+                               (p.win_right < 0 || k_base + BKV <= q0 + p.win_right + 1) &&
+                               (p.win_left < 0 || q0 + BQ - 1 - p.win_left <= k_base);
         const uint32_t t_s = tmem_base + b * BKV + lane_off;
         const int rel = qi - k_base;
         // The score row of this step: one TMEM read, one wait.
@@ -464,9 +469,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         ptx::tmem_ld_wait();
         float mx;
-        if (p.alibi_slopes) mx = row_max<true, true>(sc, lim, n_chunks, p.scale_log2, slope, rel);
-        else if (tile_full) mx = row_max<false, false>(sc, lim, n_chunks, p.scale_log2, 0.f, 0);
-        else mx = row_max<true, false>(sc, lim, n_chunks, p.scale_log2, 0.f, 0);
+        if (p.alibi_slopes) mx = row_max<true, true>(sc, lo, lim, n_chunks, p.scale_log2, slope, rel);
+        else if (tile_full) mx = row_max<false, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+        else mx = row_max<true, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
         if (j == 0) {
           m = mx;  // P V of the first step overwrites the output tile: nothing to rescale
         } else {
@@ -502,9 +507,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         // g-2, which ran before the S MMA of this step wrote them (MMAs run in issue order).
         const float m_use = (m == -INFINITY) ? 0.f : m;
         float sum;
-        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, t_s, lim, n_chunks, p.scale_log2, slope, rel, m_use);
-        else if (tile_full) sum = write_probs<T, false, false>(sc, t_s, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
-        else sum = write_probs<T, true, false>(sc, t_s, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+        else if (tile_full) sum = write_probs<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        else sum = write_probs<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
         l += sum;
         // P and the rescaled O written, S read: hand over to the MMA thread.
         ptx::tmem_st_wait();
@@ -585,7 +590,9 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
   p.n_heads = a.n_heads;
   p.n_kv_heads = a.n_kv_heads;
   p.ld_o = a.ld_o;
-  p.causal = a.causal;
+  // causal is a right window of 0 (backends/candle/src/flash_attn.rs:72-78)
+  p.win_left = a.window_left;
+  p.win_right = a.causal ? 0 : a.window_right;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.alibi_slopes = a.alibi_slopes;
   p.status = a.status;

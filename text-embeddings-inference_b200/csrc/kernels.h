@@ -58,12 +58,16 @@ struct AttnArgs {
   const void* v;
   void* out;      // [T, n_heads*head_dim]
   const int* cu_seqlens;      // device, [n_seqs + 1]
-  const int* work_items;      // device, [n_work][4] = {seq_start, seq_len, q0, 0}; see plan_attention
+  const int* work_items;      // device, [n_work][4] = {seq_start, seq_len, q0, first key}; see plan_attention
   int n_work;
   int total_tokens;
   int n_heads, n_kv_heads, head_dim;
   int ld_q, ld_k, ld_v, ld_o;  // row strides in elements
   int causal;
+  // Sliding window (flash_attn.rs:82-95): key j counts for query i when
+  // i - window_left <= j <= i + window_right; -1 = no limit on that side.  causal forces
+  // window_right = 0.
+  int window_left = -1, window_right = -1;
   float scale;
   const float* alibi_slopes;  // [n_heads] or nullptr
   int dtype;
@@ -71,9 +75,11 @@ struct AttnArgs {
 };
 int launch_attention(const AttnArgs& a, cudaStream_t stream);
 // Host side: lists the (sequence, 128-row query tile) work items of a packed batch, most
-// expensive first, as {seq_start, seq_len, q0, 0} quadruples.  Returns the number of items
+// expensive first, as {seq_start, seq_len, q0, first key} quadruples (first key: the 64-aligned
+// start of the keys the tile can see; 0 without a left window).  Returns the number of items
 // needed; when that exceeds capacity_items (or work_out is null) nothing is written.
-int plan_attention(const int* cu_seqlens, int n_seqs, int causal, int* work_out, int capacity_items);
+int plan_attention(const int* cu_seqlens, int n_seqs, int causal, int* work_out, int capacity_items,
+                   int window_left = -1, int window_right = -1);
 
 struct EmbedArgs {
   const int* ids;

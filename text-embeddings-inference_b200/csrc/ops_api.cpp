@@ -33,12 +33,34 @@ int tei_b200_attention_plan(const int32_t* cu_seqlens_host, int n_seqs, int caus
   return plan_attention(cu_seqlens_host, n_seqs, causal, work_out, capacity_items);
 }
 
+int tei_b200_attention_plan_windowed(const int32_t* cu_seqlens_host, int n_seqs, int causal,
+                                     int window_left, int window_right, int32_t* work_out,
+                                     int capacity_items) {
+  return plan_attention(cu_seqlens_host, n_seqs, causal, work_out, capacity_items, window_left,
+                        window_right);
+}
+
 int tei_b200_op_attention(const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
                           const int32_t* work_dev, int n_work, int total_tokens, int n_heads,
                           int n_kv_heads, int head_dim, int ld_q, int ld_k, int ld_v, int ld_o,
                           int causal, float softmax_scale, const float* alibi_slopes_dev,
                           int dtype, int* status_dev, void* stream) {
+  return tei_b200_op_attention_windowed(q_dev, k_dev, v_dev, out_dev, work_dev, n_work, total_tokens,
+                                        n_heads, n_kv_heads, head_dim, ld_q, ld_k, ld_v, ld_o, causal,
+                                        -1, -1, softmax_scale, alibi_slopes_dev, dtype, status_dev,
+                                        stream);
+}
+
+int tei_b200_op_attention_windowed(const void* q_dev, const void* k_dev, const void* v_dev,
+                                   void* out_dev, const int32_t* work_dev, int n_work,
+                                   int total_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int ld_q, int ld_k, int ld_v, int ld_o, int causal,
+                                   int window_left, int window_right, float softmax_scale,
+                                   const float* alibi_slopes_dev, int dtype, int* status_dev,
+                                   void* stream) {
   AttnArgs a;
+  a.window_left = window_left;
+  a.window_right = window_right;
   a.q = q_dev;
   a.k = k_dev;
   a.v = v_dev;

@@ -11,18 +11,20 @@
 namespace tei {
 
 int plan_attention(const int* cu_seqlens, int n_seqs, int causal, int* work_out,
-                   int capacity_items) {
+                   int capacity_items, int window_left, int window_right) {
   struct Item {
-    int start, len, q0;
+    int start, len, q0, kv_begin;
     long long cost;
   };
+  if (causal) window_right = 0;
   std::vector<Item> items;
   for (int s = 0; s < n_seqs; ++s) {
     const int start = cu_seqlens[s];
     const int len = cu_seqlens[s + 1] - start;
     for (int q0 = 0; q0 < len; q0 += 128) {
-      const int kv_end = causal ? std::min(len, q0 + 128) : len;
-      items.push_back({start, len, q0, static_cast<long long>((kv_end + 127) / 128)});
+      const int kv_end = window_right >= 0 ? std::min(len, q0 + 128 + window_right) : len;
+      const int kv_begin = window_left >= 0 ? std::max(0, q0 - window_left) / 64 * 64 : 0;
+      items.push_back({start, len, q0, kv_begin, static_cast<long long>((kv_end - kv_begin + 63) / 64)});
     }
   }
   // Most expensive first: the hardware hands CTAs to SMs in index order, so this is the
@@ -35,7 +37,7 @@ int plan_attention(const int* cu_seqlens, int n_seqs, int causal, int* work_out,
     work_out[i * 4 + 0] = items[i].start;
     work_out[i * 4 + 1] = items[i].len;
     work_out[i * 4 + 2] = items[i].q0;
-    work_out[i * 4 + 3] = 0;
+    work_out[i * 4 + 3] = items[i].kv_begin;
   }
   return n;
 }

@@ -18,9 +18,15 @@ _lib = None
 _OPS_PROTOTYPES = {
     "tei_b200_op_linear": (c_int, [c_void_p] * 5 + [c_int] * 8 + [c_void_p, c_void_p]),
     "tei_b200_attention_plan": (c_int, [POINTER(c_int32), c_int, c_int, POINTER(c_int32), c_int]),
+    "tei_b200_attention_plan_windowed": (
+        c_int, [POINTER(c_int32), c_int, c_int, c_int, c_int, POINTER(c_int32), c_int]),
     "tei_b200_op_attention": (
         c_int,
         [c_void_p] * 5 + [c_int] * 10 + [c_float, c_void_p, c_int, c_void_p, c_void_p],
+    ),
+    "tei_b200_op_attention_windowed": (
+        c_int,
+        [c_void_p] * 5 + [c_int] * 12 + [c_float, c_void_p, c_int, c_void_p, c_void_p],
     ),
     "tei_b200_op_embed_layernorm": (c_int, [c_void_p] * 9 + [c_int, c_int, c_float, c_int, c_void_p]),
     "tei_b200_op_add_norm": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_int, c_void_p]),

@@ -77,22 +77,23 @@ def interleave_swiglu(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
     return torch.stack([g, u], dim=1).reshape(2 * inter, *gate_w.shape[1:]).contiguous()
 
 
-def attention_plan(cu_seqlens, causal: bool) -> np.ndarray:
+def attention_plan(cu_seqlens, causal: bool, window_left: int = -1, window_right: int = -1) -> np.ndarray:
     lib = _lib.load()
     cu = np.ascontiguousarray(np.asarray(cu_seqlens, dtype=np.int32))
     n_seqs = len(cu) - 1
     cu_p = cu.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))
-    n = lib.tei_b200_attention_plan(cu_p, n_seqs, int(causal), None, 0)
+    n = lib.tei_b200_attention_plan_windowed(cu_p, n_seqs, int(causal), window_left, window_right, None, 0)
     work = np.zeros((max(n, 1), 4), dtype=np.int32)
-    n2 = lib.tei_b200_attention_plan(cu_p, n_seqs, int(causal),
-                                     work.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), n)
+    n2 = lib.tei_b200_attention_plan_windowed(cu_p, n_seqs, int(causal), window_left, window_right,
+                                              work.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)), n)
     assert n2 == n
     return work[:n]
 
 
 def attention(q, k, v, cu_seqlens, causal=False, scale=None, alibi_slopes=None, work=None,
-              out=None, status=None):
-    """q [T, nh, D], k/v [T, nkv, D] (views with unit stride in the last two dims)."""
+              out=None, status=None, window_left: int = -1, window_right: int = -1):
+    """q [T, nh, D], k/v [T, nkv, D] (views with unit stride in the last two dims).  Key j counts
+    for query i when i - window_left <= j <= i + window_right (-1: no limit; causal: right 0)."""
     lib = _lib.load()
     T, nh, D = q.shape
     nkv = k.shape[1]
@@ -100,16 +101,16 @@ def attention(q, k, v, cu_seqlens, causal=False, scale=None, alibi_slopes=None, 
     if scale is None:
         scale = 1.0 / float(D) ** 0.5
     if work is None:
-        work = torch.from_numpy(attention_plan(cu_seqlens, causal)).to(q.device)
+        work = torch.from_numpy(attention_plan(cu_seqlens, causal, window_left, window_right)).to(q.device)
     if out is None:
         out = torch.empty((T, nh * D), dtype=q.dtype, device=q.device)
     own = status is None
     if own:
         status = new_status(q.device)
-    rc = lib.tei_b200_op_attention(
+    rc = lib.tei_b200_op_attention_windowed(
         _p(q), _p(k), _p(v), _p(out), _p(work), work.shape[0], T, nh, nkv, D, q.stride(0),
-        k.stride(0), v.stride(0), out.stride(0), int(causal), float(scale), _p(alibi_slopes),
-        _dt(q), _p(status), _stream())
+        k.stride(0), v.stride(0), out.stride(0), int(causal), int(window_left), int(window_right),
+        float(scale), _p(alibi_slopes), _dt(q), _p(status), _stream())
     _check(rc, "tei_b200_op_attention")
     if own:
         check_status(status, "attention")
