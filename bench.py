@@ -307,6 +307,88 @@ def run_kernel(args):
     print(json.dumps(line), flush=True)
 
 
+def run_config(args):
+    """One of the other benchmark configurations (BASELINE.json configs[0], [2], [3], [4]) through
+    the same harness on one GPU: device-resident and end-to-end tokens/s, per-class kernel time and
+    the algorithmic TFLOP/s of the dense layers + attention.  The headline line stays cfg2."""
+    import numpy as np
+    import torch
+    import tei_b200
+    from oracle import generators as G
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    name = args.config
+    base = Path(os.environ.get("TEI_B200_BENCH_DIR", "/tmp/tei_b200_bench"))
+    if name == "cfg1":
+        cfg, seed, kw = G.bert_config(), 0, {}
+        batch, mtype, pool, dtype = G.batch_cfg1(), "embedding", "cls", "float16"
+        what = "cfg1: BERT-base, 32 sequences x 512 tokens, CLS pooling"
+    elif name == "cfg3":
+        cfg, seed, kw = G.nomic_config(), 2, {}
+        batch, mtype, pool, dtype = G.batch_cfg3(), "embedding", "mean", "float16"
+        what = "cfg3: NomicBERT 12x768 (RoPE theta 1000, SwiGLU), 64 sequences of 512..2048 tokens, mean pooling"
+    elif name == "cfg4":
+        cfg = G.bert_config(hidden=1024, layers=24, heads=16, inter=4096, vocab=250002, max_pos=514, type_vocab=1,
+                            model_type="xlm-roberta", pad_token_id=1, id2label={"0": "LABEL_0"})
+        seed, kw = 4, {"classifier": "roberta"}
+        batch, mtype, pool, dtype = G.batch_cfg4(), "classifier", "cls", "float16"
+        what = "cfg4: XLM-RoBERTa-large reranker (24x1024), 512 query/passage pairs, one logit per pair"
+    elif name == "cfg5":
+        cfg, seed, kw = G.qwen3_config(), 5, {}
+        batch, mtype, pool, dtype = G.batch_cfg5(), "embedding", "last_token", args.dtype or "bfloat16"
+        what = "cfg5: Qwen3-0.6B-style (28x1024, 16/8 heads x 128, causal), 128 sequences of 128..8192 tokens, last-token pooling"
+    else:
+        raise SystemExit(f"unknown config {name}")
+    dtype = args.dtype or dtype
+    model_dir = base / f"{name}_seed{seed}"
+    if not (model_dir / ".complete").exists():
+        G.write_model_dir(model_dir, cfg, seed=seed, store_dtype="float16", **kw)
+        (model_dir / ".complete").write_text("ok")
+    be = tei_b200.B200Backend(model_dir, dtype, mtype, pool, devices=[0])
+    predict = mtype == "classifier"
+    tokens = int(batch.cumulative_seq_lengths[-1])
+    flops = G.algorithmic_flops(cfg, batch.lengths())
+    be.stage(batch, normalize=not predict, predict=predict)
+    for _ in range(max(args.warmup, 3)):
+        be.run_staged()
+    be.sync()
+    be.set_profiling(True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = be.run_staged_timed(args.steps)
+    clocks = sampler.stop()
+    kt = be.kernel_times()
+    be.set_profiling(False)
+    launches = be.stats()["launches"]
+    call = (lambda: be.predict(batch)) if predict else (lambda: be.embed(batch, normalize=True))
+    for _ in range(3):
+        call()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        call()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    st = be.stats()
+    line = {
+        "metric": "tokens_per_sec", "value": tokens * args.steps / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {"float16": "f16", "bfloat16": "bf16"}[dtype], "data": "synthetic",
+        "config": {"workload": what, "per_gpu_batch_tokens": tokens, "sequences": len(batch),
+                   "l2": "no flush: activations and weights of a step are far above the 126 MB L2"},
+        "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": st["h2d_bytes"],
+                "d2h_bytes_per_step": st["d2h_bytes"], "ms_per_step": 1e3 * e2e_s / args.steps},
+        "gpu_launches": int(launches * args.steps),
+        "algorithmic_tflop_per_step": flops / 1e12,
+        "step_tflops": flops / (ms / args.steps / 1e3) / 1e12,
+        "per_class_ms_per_step": {k: v["ms"] / args.steps for k, v in kt.items()},
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    be.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -317,9 +399,16 @@ def main():
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
                          "add_layernorm | pool_mean")
+    ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
+                    help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
+    ap.add_argument("--dtype", default=None, choices=["float16", "bfloat16"],
+                    help="only with --config cfg1/3/4/5 (cfg5 defaults to bfloat16)")
     args = ap.parse_args()
     if args.kernel:
         run_kernel(args)
+        return
+    if args.config != "cfg2" and args.impl == "b200":
+        run_config(args)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 

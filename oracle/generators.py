@@ -77,6 +77,37 @@ def qwen3_config(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, int
     }
 
 
+def qwen2_config(hidden=1536, layers=28, heads=12, kv_heads=2, inter=8960, vocab=151646, max_pos=32768,
+                 theta=1e6, eps=1e-6, is_causal: Optional[bool] = None) -> dict:
+    """Fields of Qwen2Config (models/qwen2.rs:9-28); `is_causal` absent means causal."""
+    c = {
+        "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab,
+        "hidden_size": hidden, "intermediate_size": inter, "num_hidden_layers": layers,
+        "num_attention_heads": heads, "num_key_value_heads": kv_heads, "hidden_act": "silu",
+        "max_position_embeddings": max_pos, "rms_norm_eps": eps, "rope_theta": theta,
+        "sliding_window": None, "use_sliding_window": False,
+    }
+    if is_causal is not None:
+        c["is_causal"] = is_causal
+    return c
+
+
+def mistral_config(hidden=4096, layers=32, heads=32, kv_heads=8, inter=14336, vocab=32000, max_pos=32768,
+                   theta=10000.0, eps=1e-5, sliding_window: Optional[int] = 4096, model_type="mistral") -> dict:
+    """Fields of MistralConfig (models/mistral.rs:5-24); model_type "llama" is run through the
+    same model (backends/candle/src/lib.rs:549-575)."""
+    c = {
+        "architectures": ["MistralModel" if model_type == "mistral" else "LlamaModel"], "model_type": model_type,
+        "vocab_size": vocab, "hidden_size": hidden, "intermediate_size": inter,
+        "num_hidden_layers": layers, "num_attention_heads": heads, "num_key_value_heads": kv_heads,
+        "hidden_act": "silu", "max_position_embeddings": max_pos, "initializer_range": 0.02,
+        "rms_norm_eps": eps, "rope_theta": theta, "rope_scaling": None,
+    }
+    if model_type == "mistral":
+        c["sliding_window"] = sliding_window
+    return c
+
+
 # --------------------------------------------------------------------------- tensor lists
 def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) -> Dict[str, Tuple[tuple, str]]:
     """name -> (shape, kind) with kind in {normal, ones, zeros}."""
@@ -155,18 +186,29 @@ def _nomic_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
 
 
 def _qwen3_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    """Qwen3, and with fewer tensors Qwen2 (q/k/v biases, no q/k norm; `model.` prefix as in
+    flash_qwen2.rs:266-275) and Mistral / Llama (neither; bare names as flash_mistral.rs:257-267
+    reads them)."""
     H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
-    nh, nkv, dh = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
-    t: Dict[str, Tuple[tuple, str]] = {"model.embed_tokens.weight": ((V, H), "normal"),
-                                       "model.norm.weight": ((H,), "ones")}
+    mt = c["model_type"]
+    nh, nkv = c["num_attention_heads"], c["num_key_value_heads"]
+    dh = c["head_dim"] if mt == "qwen3" else H // nh
+    root = "" if mt in ("mistral", "llama") else "model."
+    t: Dict[str, Tuple[tuple, str]] = {root + "embed_tokens.weight": ((V, H), "normal"),
+                                       root + "norm.weight": ((H,), "ones")}
     for i in range(c["num_hidden_layers"]):
-        p = f"model.layers.{i}."
+        p = f"{root}layers.{i}."
         t[p + "self_attn.q_proj.weight"] = ((nh * dh, H), "normal")
         t[p + "self_attn.k_proj.weight"] = ((nkv * dh, H), "normal")
         t[p + "self_attn.v_proj.weight"] = ((nkv * dh, H), "normal")
         t[p + "self_attn.o_proj.weight"] = ((H, nh * dh), "normal")
-        t[p + "self_attn.q_norm.weight"] = ((dh,), "ones")
-        t[p + "self_attn.k_norm.weight"] = ((dh,), "ones")
+        if mt == "qwen3":
+            t[p + "self_attn.q_norm.weight"] = ((dh,), "ones")
+            t[p + "self_attn.k_norm.weight"] = ((dh,), "ones")
+        if mt == "qwen2":
+            t[p + "self_attn.q_proj.bias"] = ((nh * dh,), "normal")
+            t[p + "self_attn.k_proj.bias"] = ((nkv * dh,), "normal")
+            t[p + "self_attn.v_proj.bias"] = ((nkv * dh,), "normal")
         t[p + "mlp.gate_proj.weight"] = ((I, H), "normal")
         t[p + "mlp.up_proj.weight"] = ((I, H), "normal")
         t[p + "mlp.down_proj.weight"] = ((H, I), "normal")
@@ -184,7 +226,7 @@ def tensor_shapes(config: dict, classifier: Optional[str] = None, splade: bool =
         return _bert_shapes(config, prefix, classifier, splade)
     if mt == "nomic_bert":
         return _nomic_shapes(config)
-    if mt == "qwen3":
+    if mt in ("qwen3", "qwen2", "mistral", "llama"):
         return _qwen3_shapes(config)
     raise ValueError(mt)
 

@@ -121,8 +121,10 @@ def alibi_slopes(n_heads: int) -> Tensor:
 
 
 def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: float, causal: bool,
-                     slopes: Optional[Tensor] = None) -> Tensor:
-    """q [T, nh, D], k/v [T, nkv, D] -> [T, nh*D]; one softmax(QK^T)V per sequence and head."""
+                     slopes: Optional[Tensor] = None, window_left: Optional[int] = None) -> Tensor:
+    """q [T, nh, D], k/v [T, nkv, D] -> [T, nh*D]; one softmax(QK^T)V per sequence and head.
+    window_left: key j counts for query i only when j >= i - window_left (flash-attn's
+    window_size_left, as passed by flash_mistral.rs:95-110 through flash_attn.rs:82-95)."""
     T, nh, D = q.shape
     nkv = k.shape[1]
     out = torch.empty(T, nh * D, dtype=q.dtype)
@@ -143,6 +145,9 @@ def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: flo
             sc = sc - slopes.view(nh, 1, 1) * (idx.view(1, L, 1) - idx.view(1, 1, L)).abs()
         if causal:
             sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf"))
+        if window_left is not None:
+            idx = torch.arange(L)
+            sc = sc.masked_fill(idx.view(1, L) < idx.view(L, 1) - window_left, float("-inf"))
         out[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1).reshape(L, nh * D)
     return out
 
@@ -447,13 +452,24 @@ class NomicOracle:
 
 # --------------------------------------------------------------------------- Qwen3
 class Qwen3Oracle:
+    """The decoder families: Qwen3 (models/qwen3.rs, flash_qwen3.rs), Qwen2 (flash_qwen2.rs: q/k/v
+    biases, `is_causal`, no q/k norm) and Mistral / Llama (flash_mistral.rs: no biases, no q/k norm,
+    optional `sliding_window` as the attention's left window; Llama configs run as Mistral,
+    backends/candle/src/lib.rs:549-575)."""
+
     def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
                  pool: str = "last_token"):
         if model_type == "classifier" or pool == "splade":
-            raise ValueError("Qwen3 supports neither classifier nor splade here")
+            raise ValueError("the decoder families support neither classifier nor splade here")
         c = config
-        if c.get("use_sliding_window"):
-            raise ValueError("sliding window is not supported (flash_qwen3.rs:32-34)")
+        mt = c["model_type"]
+        if mt in ("qwen3", "qwen2") and c.get("use_sliding_window"):
+            raise ValueError("sliding window is not supported (flash_qwen3.rs:32-34, flash_qwen2.rs:26-29)")
+        if mt in ("mistral", "llama") and c.get("rope_scaling") is not None:
+            raise ValueError("rope scaling is outside this restatement")
+        self.qk_norm = mt == "qwen3"
+        self.qkv_bias = mt == "qwen2"
+        self.window_left = c.get("sliding_window") if mt == "mistral" else None
         self.cfg = c
         self.pool = pool
         prefix = "model." if "model.embed_tokens.weight" in tensors else ""
@@ -462,13 +478,16 @@ class Qwen3Oracle:
         self.nh = c["num_attention_heads"]
         self.nkv = c["num_key_value_heads"]
         self.hidden = c["hidden_size"]
-        self.dh = c.get("head_dim") or self.hidden // self.nh
+        self.dh = (c.get("head_dim") if mt == "qwen3" else None) or self.hidden // self.nh
         self.eps = float(c["rms_norm_eps"])
         self.n_layers = c["num_hidden_layers"]
         theta = c.get("rope_theta")
         if theta is None:
             theta = c["rope_parameters"]["rope_theta"]
-        self.causal = not c.get("use_bidirectional_attention", False)
+        if mt == "qwen2":
+            self.causal = bool(c.get("is_causal", True))  # qwen2.rs:4-7,26-27
+        else:
+            self.causal = not c.get("use_bidirectional_attention", False)
         self.cos, self.sin = rope_tables(self.dh, float(theta), int(c["max_position_embeddings"]))
 
     def hidden_states(self, batch: Batch) -> Tensor:
@@ -483,13 +502,15 @@ class Qwen3Oracle:
         for i in range(self.n_layers):
             p = f"layers.{i}."
             n, residual = rms_norm(h, residual, w.get(p + "input_layernorm.weight"), self.eps)
-            q = linear(n, w.get(p + "self_attn.q_proj.weight")).view(T, self.nh, self.dh)
-            k = linear(n, w.get(p + "self_attn.k_proj.weight")).view(T, self.nkv, self.dh)
-            v = linear(n, w.get(p + "self_attn.v_proj.weight")).view(T, self.nkv, self.dh)
-            q, _ = rms_norm(q, None, w.get(p + "self_attn.q_norm.weight"), self.eps)
-            k, _ = rms_norm(k, None, w.get(p + "self_attn.k_norm.weight"), self.eps)
+            bias = (lambda name: w.get(p + f"self_attn.{name}.bias")) if self.qkv_bias else (lambda name: None)
+            q = linear(n, w.get(p + "self_attn.q_proj.weight"), bias("q_proj")).view(T, self.nh, self.dh)
+            k = linear(n, w.get(p + "self_attn.k_proj.weight"), bias("k_proj")).view(T, self.nkv, self.dh)
+            v = linear(n, w.get(p + "self_attn.v_proj.weight"), bias("v_proj")).view(T, self.nkv, self.dh)
+            if self.qk_norm:
+                q, _ = rms_norm(q, None, w.get(p + "self_attn.q_norm.weight"), self.eps)
+                k, _ = rms_norm(k, None, w.get(p + "self_attn.k_norm.weight"), self.eps)
             q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), self.causal)
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), self.causal, None, self.window_left)
             o = linear(a, w.get(p + "self_attn.o_proj.weight"))
             n2, residual = rms_norm(o, residual, w.get(p + "post_attention_layernorm.weight"), self.eps)
             gate = linear(n2, w.get(p + "mlp.gate_proj.weight"))
@@ -587,6 +608,6 @@ def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
         return BertOracle(config, tensors, model_type, pool)
     if mt == "nomic_bert":
         return NomicOracle(config, tensors, model_type, pool)
-    if mt == "qwen3":
+    if mt in ("qwen3", "qwen2", "mistral", "llama"):
         return Qwen3Oracle(config, tensors, model_type, pool)
     raise ValueError(f"model_type {mt} is outside the hot path")

@@ -41,6 +41,24 @@ def write_all(base):
         base / "qwen3",
         G.qwen3_config(hidden=256, layers=3, heads=4, kv_heads=2, head_dim=128, inter=512, vocab=1000, max_pos=2048),
         seed=5, norm_jitter=0.1, std=0.05)
+    dirs["qwen2"] = G.write_model_dir(
+        base / "qwen2",
+        G.qwen2_config(hidden=256, layers=2, heads=4, kv_heads=2, inter=512, vocab=1000, max_pos=2048),
+        seed=11, norm_jitter=0.1, std=0.05)
+    dirs["qwen2_bidir"] = G.write_model_dir(
+        base / "qwen2_bidir",
+        G.qwen2_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048, is_causal=False),
+        seed=12, norm_jitter=0.1, std=0.05)
+    dirs["mistral"] = G.write_model_dir(
+        base / "mistral",
+        G.mistral_config(hidden=512, layers=2, heads=4, kv_heads=2, inter=512, vocab=1000, max_pos=2048,
+                         sliding_window=100),
+        seed=13, norm_jitter=0.1, std=0.05)
+    dirs["llama"] = G.write_model_dir(
+        base / "llama",
+        G.mistral_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048,
+                         model_type="llama"),
+        seed=14, norm_jitter=0.1, std=0.05)
     return dirs
 
 
@@ -57,6 +75,11 @@ GOLDEN_CASES = {
     "jina_mean": ("jina", "embedding", "mean", dict(seed=108, lens=LENS + [511], lo=0, hi=1000, type_vocab=2, offset=0)),
     "jina_alibi6_cls": ("jina_alibi6", "embedding", "cls", dict(seed=109, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "jina_abs_scores": ("jina_abs_cls", "classifier", "cls", dict(seed=110, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "qwen2_last": ("qwen2", "embedding", "last_token", dict(seed=111, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "qwen2_bidir_mean": ("qwen2_bidir", "embedding", "mean", dict(seed=112, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
+    "mistral_window_last": ("mistral", "embedding", "last_token", dict(seed=113, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "mistral_window_mean": ("mistral", "embedding", "mean", dict(seed=114, lens=[400, 101, 100, 99], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "llama_cls": ("llama", "embedding", "cls", dict(seed=115, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

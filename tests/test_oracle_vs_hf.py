@@ -86,6 +86,47 @@ def test_qwen3_matches_hf(model_dirs):
         assert (ref - hs[a:e]).abs().max().item() < TOL
 
 
+def test_qwen2_matches_hf(model_dirs):
+    d = model_dirs["qwen2"]
+    cfg = json.load(open(d / "config.json"))
+    hf = transformers.Qwen2Model(transformers.Qwen2Config(**cfg)).eval()
+    _, tensors = M.load_model_dir(d)
+    hf.load_state_dict({k[len("model."):]: v for k, v in tensors.items()}, strict=True)
+    o = M.build_oracle(d, "embedding", "last_token")
+    b = G.random_batch(6, [7, 40, 130], 0, 1000)
+    hs = o.hidden_states(b)
+    for s, a, e in _per_sequence(b):
+        with torch.no_grad():
+            ref = hf(input_ids=_t(b.input_ids[a:e])).last_hidden_state[0]
+        assert (ref - hs[a:e]).abs().max().item() < TOL
+
+
+def test_mistral_sliding_window_matches_hf(model_dirs):
+    d = model_dirs["mistral"]
+    cfg = json.load(open(d / "config.json"))
+    # The reference hands `sliding_window` to flash-attn as window_size_left
+    # (flash_mistral.rs:56,95-110): key j counts when j >= i - sliding_window, i.e. the token
+    # itself plus `sliding_window` earlier ones.  Hugging Face masks `j > i - sliding_window`
+    # (one key fewer), so its config gets the window + 1 to describe the same mask.
+    hcfg = dict(cfg)
+    hcfg["sliding_window"] = cfg["sliding_window"] + 1
+    hcfg["attn_implementation"] = "eager"
+    hf = transformers.MistralModel(transformers.MistralConfig(**hcfg)).eval()
+    _, tensors = M.load_model_dir(d)
+    hf.load_state_dict(tensors, strict=True)
+    o = M.build_oracle(d, "embedding", "last_token")
+    assert o.window_left == 100
+    b = G.random_batch(7, [7, 101, 102, 230], 0, 1000)
+    hs = o.hidden_states(b)
+    for s, a, e in _per_sequence(b):
+        with torch.no_grad():
+            ref = hf(input_ids=_t(b.input_ids[a:e])).last_hidden_state[0]
+        assert (ref - hs[a:e]).abs().max().item() < TOL
+    # the window matters at these lengths: without it the long sequence comes out differently
+    o.window_left = None
+    assert (o.hidden_states(b)[-1] - hs[-1]).abs().max().item() > 1e-3
+
+
 def test_nomic_matches_hf(model_dirs):
     mod = pytest.importorskip("transformers.models.nomic_bert.modeling_nomic_bert")
     d = model_dirs["nomic"]

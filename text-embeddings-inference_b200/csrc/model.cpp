@@ -153,10 +153,14 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     s.rope_scaling_factor = static_cast<float>(c.get_double("rotary_scaling_factor", 0.0));
     s.nomic_max_pos = static_cast<int>(
         c.get_int("max_position_embeddings", c.get_int("max_trained_positions", 2048)));
-  } else if (mt == "qwen3") {
+  } else if (mt == "qwen3" || mt == "qwen2" || mt == "mistral" || mt == "llama") {
+    // One decoder skeleton (pre-RMSNorm, GQA, RoPE, SiLU-gated feed-forward) serves
+    // flash_qwen3.rs, flash_qwen2.rs and flash_mistral.rs (Llama configs are run as Mistral,
+    // backends/candle/src/lib.rs:549-575); the differences are flags.
     s.arch = ARCH_QWEN3;
-    if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for Qwen3");
-    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Qwen3");
+    const std::string family = mt == "qwen3" ? "Qwen3" : mt == "qwen2" ? "Qwen2" : "Mistral";
+    if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for " + family);
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for " + family);
     s.vocab = static_cast<int>(need_int(c, "vocab_size"));
     s.hidden = static_cast<int>(need_int(c, "hidden_size"));
     s.inter = static_cast<int>(need_int(c, "intermediate_size"));
@@ -165,10 +169,28 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     s.kv_heads = static_cast<int>(need_int(c, "num_key_value_heads"));
     s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
     s.eps = static_cast<float>(need_double(c, "rms_norm_eps"));
-    if (c.get_bool("use_sliding_window", false)) throw TeiError(ERR_START, "sliding window is not supported");
-    if (need_bool(c, "attention_bias")) throw TeiError(ERR_START, "attention_bias = true is not supported");
-    if (parse_act(need_string(c, "hidden_act")) != -2) throw TeiError(ERR_START, "Qwen3 expects hidden_act = silu");
-    s.head_dim = static_cast<int>(c.get_int("head_dim", s.heads > 0 ? s.hidden / s.heads : 0));
+    if (parse_act(need_string(c, "hidden_act")) != -2) throw TeiError(ERR_START, family + " expects hidden_act = silu");
+    if (mt == "qwen3") {
+      if (c.get_bool("use_sliding_window", false)) throw TeiError(ERR_START, "sliding window is not supported");
+      if (need_bool(c, "attention_bias")) throw TeiError(ERR_START, "attention_bias = true is not supported");
+      s.head_dim = static_cast<int>(c.get_int("head_dim", s.heads > 0 ? s.hidden / s.heads : 0));
+      s.qk_norm = true;
+      s.causal = !c.get_bool("use_bidirectional_attention", false);
+    } else if (mt == "qwen2") {
+      // flash_qwen2.rs:26-29,36-57: q/k/v carry biases, no sliding window, `is_causal`
+      // defaults to true (qwen2.rs:4-7,26-27).
+      if (need_bool(c, "use_sliding_window")) throw TeiError(ERR_START, "Sliding window is not supported for Qwen2");
+      s.head_dim = s.heads > 0 ? s.hidden / s.heads : 0;
+      s.qkv_bias = true;
+      s.causal = c.get_bool("is_causal", true);
+    } else {
+      // flash_mistral.rs:56,95-110: `sliding_window` is the left window of the attention;
+      // Llama's rope_scaling is refused (lib.rs:549-553), so is Mistral's here.
+      if (!c["rope_scaling"].is_null()) throw TeiError(ERR_START, "Rope scaling is not supported for " + std::string(mt == "llama" ? "FlashLlama yet" : "this Mistral backend"));
+      s.head_dim = s.heads > 0 ? s.hidden / s.heads : 0;
+      if (mt == "mistral" && c["sliding_window"].is_number()) s.window_left = static_cast<int>(c["sliding_window"].as_int());
+      s.causal = !c.get_bool("use_bidirectional_attention", false);
+    }
     if (c["rope_theta"].is_number()) {
       s.rope_theta = static_cast<float>(c["rope_theta"].as_double());
     } else if (c["rope_parameters"]["rope_theta"].is_number()) {
@@ -180,7 +202,6 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     s.act = ACT_SWIGLU;
     s.rope = true;
     s.rope_table_len = s.max_pos;
-    s.causal = !c.get_bool("use_bidirectional_attention", false);
     s.type_vocab = 0;
   } else {
     throw TeiError(ERR_START, "model_type `" + mt + "` is not served by this backend");
@@ -687,8 +708,16 @@ void Replica::load_qwen3(const SafeTensors& st) {
     upload(L.wqkv, static_cast<size_t>(Q + KV) * H, n.get(p + "self_attn.v_proj.weight"));
     expect_shape(n.get(p + "self_attn.o_proj.weight"), {H, Q}, p + "self_attn.o_proj.weight");
     L.wo = upload_new(n.get(p + "self_attn.o_proj.weight"));
-    L.q_norm = upload_new(n.get(p + "self_attn.q_norm.weight"));
-    L.k_norm = upload_new(n.get(p + "self_attn.k_norm.weight"));
+    if (s.qkv_bias) {  // flash_qwen2.rs:37-57
+      L.bqkv = dev_alloc(static_cast<size_t>(Q + 2 * KV) * 2);
+      upload(L.bqkv, 0, n.get(p + "self_attn.q_proj.bias"));
+      upload(L.bqkv, static_cast<size_t>(Q), n.get(p + "self_attn.k_proj.bias"));
+      upload(L.bqkv, static_cast<size_t>(Q + KV), n.get(p + "self_attn.v_proj.bias"));
+    }
+    if (s.qk_norm) {
+      L.q_norm = upload_new(n.get(p + "self_attn.q_norm.weight"));
+      L.k_norm = upload_new(n.get(p + "self_attn.k_norm.weight"));
+    }
     expect_shape(n.get(p + "mlp.gate_proj.weight"), {I, H}, p + "mlp.gate_proj.weight");
     expect_shape(n.get(p + "mlp.up_proj.weight"), {I, H}, p + "mlp.up_proj.weight");
     L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
@@ -888,7 +917,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   off = align_up(off, 4);
   const size_t o_work = off;
   const int n_planned = plan_attention(cu_i.data(), static_cast<int>(B_), s.causal ? 1 : 0, h + off,
-                                       static_cast<int>(n_work));
+                                       static_cast<int>(n_work), s.window_left, -1);
   if (static_cast<size_t>(n_planned) != n_work) throw TeiError(ERR_INFERENCE, "attention planning mismatch");
   off += 4 * n_work;
   TEI_CUDA(cudaMemcpyAsync(d_ints_, h_ints_, off * 4, cudaMemcpyHostToDevice, stream_));
@@ -1053,7 +1082,7 @@ void Replica::forward_qwen3() {
     n1.x = tmp_; n1.residual = (i == 0) ? nullptr : resid_; n1.gamma = L.ln1_g; n1.beta = nullptr;
     n1.out = x_; n1.sum_out = resid_; n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 1; n1.dtype = s.dtype;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "input RMSNorm");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, nullptr, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status), stream_), "qkv projection");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status), stream_), "qkv projection");
     RopeArgs r;
     r.q = qkv; r.k = qkv + static_cast<size_t>(Q) * 2; r.pos_ids = d_pos_; r.cos_tab = cos_; r.sin_tab = sin_;
     r.q_gamma = L.q_norm; r.k_gamma = L.k_norm; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
@@ -1064,6 +1093,7 @@ void Replica::forward_qwen3() {
     a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
     a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
     a.ld_q = a.ld_k = a.ld_v = W; a.ld_o = Q; a.causal = s.causal ? 1 : 0;
+    a.window_left = s.window_left;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
     a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");

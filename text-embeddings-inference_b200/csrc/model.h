@@ -52,6 +52,8 @@ struct ModelSpec {
   bool gated = false;      // SwiGLU feed-forward
   bool qkv_bias = false, out_bias = false, fc1_bias = false, fc2_bias = false;
   bool causal = false;
+  bool qk_norm = false;    // per-head RMSNorm on q and k before RoPE (Qwen3)
+  int window_left = -1;    // sliding window of the decoder families (Mistral), -1: none
   bool rope = false;
   float rope_theta = 10000.f;
   float rope_scaling_factor = 0.f;  // NomicBERT dynamic table switch (flash_nomic.rs:244-258)

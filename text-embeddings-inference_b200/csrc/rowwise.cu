@@ -280,6 +280,68 @@ qk_norm_rope_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restrict_
   }
 }
 
+// The same for head_dim 64 and 128 with 16-byte accesses: DH / 16 lanes share one (token, head);
+// each lane owns 8 consecutive elements of the first half and the 8 they pair with in the
+// second half, so every load and store is a full 16 bytes and a warp covers 8 (or 4) heads of a
+// token at once.  The RMSNorm sum is reduced across the lanes of the group.
+template <class T, int DH>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_vec_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restrict__ pos_ids,
+                        const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
+                        const T* __restrict__ q_gamma, const T* __restrict__ k_gamma, int T_, int nh,
+                        int nkv, int ld_q, int ld_k, float eps) {
+  constexpr int G = DH / 16;     // lanes per (token, head)
+  constexpr int HALF = DH / 2;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int heads = nh + nkv;
+  const long long total = static_cast<long long>(T_) * heads;
+  long long w = tid / G;
+  const int sub = static_cast<int>(tid % G);
+  const bool valid = w < total;   // whole groups are valid or not; no early exit (warp shuffles)
+  if (!valid) w = total - 1;
+  const int tok = static_cast<int>(w / heads);
+  const int h = static_cast<int>(w % heads);
+  T* base = (h < nh ? q + static_cast<size_t>(tok) * ld_q + h * DH
+                    : k + static_cast<size_t>(tok) * ld_k + (h - nh) * DH) + sub * 8;
+  const T* gamma = h < nh ? q_gamma : k_gamma;
+  float a[8], b[8];
+  unpack8<T>(ld16(base), a);
+  unpack8<T>(ld16(base + HALF), b);
+  if (gamma) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float r = rsqrtf(ss / static_cast<float>(DH) + eps);
+    float ga[8], gb[8];
+    unpack8<T>(ld16(gamma + sub * 8), ga);
+    unpack8<T>(ld16(gamma + HALF + sub * 8), gb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = a[i] * r * ga[i];
+      b[i] = b[i] * r * gb[i];
+    }
+  }
+  const size_t trow = static_cast<size_t>(pos_ids[tok]) * HALF + sub * 8;
+  const float4 c0 = *reinterpret_cast<const float4*>(cos_tab + trow);
+  const float4 c1 = *reinterpret_cast<const float4*>(cos_tab + trow + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sin_tab + trow);
+  const float4 s1 = *reinterpret_cast<const float4*>(sin_tab + trow + 4);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  float oa[8], ob[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    oa[i] = a[i] * c[i] - b[i] * sn[i];
+    ob[i] = b[i] * c[i] + a[i] * sn[i];
+  }
+  if (valid) {
+    *reinterpret_cast<uint4*>(base) = pack8<T>(oa);
+    *reinterpret_cast<uint4*>(base + HALF) = pack8<T>(ob);
+  }
+}
+
 // ------------------------------------------------------------------ segmented pooling
 // One block per (output row, slab of 256 columns); 32 column groups of 8 x 8 row lanes.
 // mode 0: first row of the sequence, 3: last row, 1: mean over the rows, 2: max over the rows
@@ -480,6 +542,27 @@ int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
   if (r.T <= 0) return 0;
   if (r.head_dim % 2 != 0 || r.head_dim > 256) return static_cast<int>(cudaErrorInvalidValue);
   const long long warps_total = static_cast<long long>(r.T) * (r.n_heads + r.n_kv_heads);
+  const bool aligned = r.ld_q % 8 == 0 && r.ld_k % 8 == 0 &&
+                       (reinterpret_cast<uintptr_t>(r.q) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.k) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(r.q_gamma) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.k_gamma) & 15) == 0;
+  if (aligned && (r.head_dim == 64 || r.head_dim == 128)) {
+    const long long threads = warps_total * (r.head_dim / 16);
+    const unsigned grid_v = static_cast<unsigned>((threads + 255) / 256);
+#define TEI_ROPE_VEC(TYPE, DH)                                                                     \
+  qk_norm_rope_vec_kernel<TYPE, DH><<<grid_v, 256, 0, st>>>(                                       \
+      reinterpret_cast<TYPE*>(r.q), reinterpret_cast<TYPE*>(r.k), r.pos_ids, r.cos_tab, r.sin_tab, \
+      reinterpret_cast<const TYPE*>(r.q_gamma), reinterpret_cast<const TYPE*>(r.k_gamma), r.T,     \
+      r.n_heads, r.n_kv_heads, r.ld_q, r.ld_k, r.eps)
+    if (r.dtype == DT_F16) {
+      if (r.head_dim == 64) TEI_ROPE_VEC(__half, 64);
+      else TEI_ROPE_VEC(__half, 128);
+    } else {
+      if (r.head_dim == 64) TEI_ROPE_VEC(__nv_bfloat16, 64);
+      else TEI_ROPE_VEC(__nv_bfloat16, 128);
+    }
+#undef TEI_ROPE_VEC
+    return last_error();
+  }
   const int warps = 8;
   const long long grid = (warps_total + warps - 1) / warps;
   if (r.dtype == DT_F16) {
