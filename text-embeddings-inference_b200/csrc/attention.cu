@@ -36,22 +36,39 @@ namespace {
 
 constexpr int BQ = 128;  // query rows per CTA
 constexpr int BKV = 64;  // keys per step
-constexpr int KV_STAGES = 3;
 constexpr int ATTN_THREADS = 192;
+
+// Depth of the pipeline per head size.  What bounds the kernel is the latency of the chain
+// "S MMA -> commit -> softmax -> P -> P V MMA" of one step, so the number of steps in flight
+// (score tiles in TMEM) decides the throughput.  D = 64: two CTAs per SM with 256 TMEM columns
+// each hold two score tiles and two output tiles; D = 128: one CTA per SM (shared memory) has
+// all 512 columns: four score tiles and one output tile.
+template <int D>
+struct AttnCfg {
+  static constexpr int S_BUFS = (D == 64) ? 2 : 4;     // score / P tiles of 64 columns
+  static constexpr int O_BUFS = (D == 64) ? 2 : 1;     // output tiles of D columns
+  static constexpr int Q_BUFS = (D == 64) ? 2 : 1;
+  static constexpr int KV_STAGES = S_BUFS + 1;         // the steps in flight plus one being loaded
+  static constexpr int CTAS_PER_SM = (D == 64) ? 2 : 1;
+  static constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512;
+  static_assert(S_BUFS * BKV + O_BUFS * D <= TMEM_COLS, "TMEM budget");
+};
 
 template <int D>
 struct AttnSmem {
+  using C = AttnCfg<D>;
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int KV_BYTES = BKV * D * 2;   // one K or one V tile
-  static constexpr int STAGE_BYTES = BQ * 128;                   // output rows, 64 columns at a time
-  static constexpr int OFF_Q = 0;                               // 2 buffers
-  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;             // KV_STAGES stages
-  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;    // KV_STAGES stages
-  static constexpr int OFF_STAGE = OFF_V + KV_STAGES * KV_BYTES;
+  static constexpr int STAGE_BYTES = BQ * 128;   // output rows, 64 columns at a time
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + C::Q_BUFS * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + C::KV_STAGES * KV_BYTES;
+  static constexpr int OFF_STAGE = OFF_V + C::KV_STAGES * KV_BYTES;
   static constexpr int OFF_BAR = OFF_STAGE + STAGE_BYTES;
   // No alignment slack: two CTAs of the D = 64 variant must fit in one SM's shared memory.  The
   // kernel checks that the dynamic window is 1024-byte aligned and reports an error otherwise.
-  static constexpr int TOTAL = OFF_BAR + 160;  // 16 mbarriers + the TMEM address slot
+  static constexpr int TOTAL = OFF_BAR + 256;  // up to 26 mbarriers + the TMEM address slot
+  static_assert(C::CTAS_PER_SM * (TOTAL + 1024) <= 228 * 1024, "shared memory budget");
 };
 
 struct AttnParams {
@@ -180,7 +197,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 
 template <class T, int D>
-__global__ void __launch_bounds__(ATTN_THREADS, (D == 64 ? 2 : 1))
+__global__ void __launch_bounds__(ATTN_THREADS, AttnCfg<D>::CTAS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -192,25 +209,29 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (threadIdx.x == 0) atomicExch(p.status, DEV_SMEM_ALIGN);
     return;
   }
+  using C = AttnCfg<D>;
+  constexpr int S_BUFS = C::S_BUFS, O_BUFS = C::O_BUFS, Q_BUFS = C::Q_BUFS, KV_STAGES = C::KV_STAGES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* bar_q = bars;            // [2] Q buffer landed
-  uint64_t* bar_qfree = bars + 2;    // [2] last S of the unit that used the Q buffer is done
-  uint64_t* bar_kv = bars + 4;       // [3] K/V stage landed
-  uint64_t* bar_kvfree = bars + 7;   // [3] the P V that read the stage is done
-  uint64_t* bar_s = bars + 10;       // [2] S buffer holds the scores of its step
-  uint64_t* bar_p = bars + 12;       // [2] P written over the scores of the step (one arrival per warp)
-  uint64_t* bar_pv = bars + 14;      // [2] the P V of the step is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  constexpr uint32_t TMEM_COLS = 256;
+  uint64_t* bar_q = bars;             // [Q_BUFS <= 2] Q buffer landed
+  uint64_t* bar_qfree = bars + 2;     // [Q_BUFS] last S of the unit that used the Q buffer is done
+  uint64_t* bar_kv = bars + 4;        // [KV_STAGES <= 5] K/V stage landed
+  uint64_t* bar_kvfree = bars + 9;    // [KV_STAGES] the P V that read the stage is done
+  uint64_t* bar_s = bars + 14;        // [S_BUFS <= 4] score tile holds the scores of its step
+  uint64_t* bar_p = bars + 18;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
+  uint64_t* bar_pv = bars + 22;       // [S_BUFS] the P V of the step is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
+  constexpr uint32_t TMEM_COLS = C::TMEM_COLS;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total = p.n_work * p.n_heads;  // work units: (sequence, query tile) x head
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < Q_BUFS; ++i) {
       ptx::mbar_init(&bar_q[i], 1);
       ptx::mbar_init(&bar_qfree[i], 1);
+    }
+    for (int i = 0; i < S_BUFS; ++i) {
       ptx::mbar_init(&bar_s[i], 1);
       ptx::mbar_init(&bar_p[i], 4);
       ptx::mbar_init(&bar_pv[i], 1);
@@ -229,11 +250,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  // Scores: columns [0,64) and [64,128).  Output tiles from column 128 on: two of them for
-  // D = 64 (units alternate), so that a finished unit's rows can be read out while the next
-  // unit is already running; one for D = 128.
-  constexpr int O_BUFS = (D == 64) ? 2 : 1;
-  const uint32_t tmem_o0 = tmem_base + 128;
+  // Score tiles: S_BUFS x 64 columns from column 0; output tiles behind them.  With two output
+  // tiles (D = 64) units alternate, so that a finished unit's rows can be read out while the
+  // next unit is already running.
+  const uint32_t tmem_o0 = tmem_base + S_BUFS * BKV;
   const int group = p.n_heads / p.n_kv_heads;
 
   // One past the last key any row of the query tile can see (causal = win_right 0).
@@ -262,11 +282,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         const int head = w % p.n_heads;
         const int kv_head = head / group;
         const int n_kv = unit_steps(it);
-        // Q of this unit into buffer n & 1, once the unit that used it two units ago is past
-        // its last S.
-        const int qb = n & 1;
-        if (n >= 2) {
-          ok = ptx::mbar_wait(&bar_qfree[qb], ((n >> 1) - 1) & 1);
+        // Q of this unit into buffer n % Q_BUFS, once the unit that used it before is past its
+        // last S.
+        const int qb = n % Q_BUFS;
+        if (n >= Q_BUFS) {
+          ok = ptx::mbar_wait(&bar_qfree[qb], ((n / Q_BUFS) - 1) & 1);
           if (!ok) break;
         }
         ptx::mbar_expect_tx(&bar_q[qb], L::Q_BYTES);
@@ -304,73 +324,92 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
       const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
       const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
-      // S = Q K^T for step `step` (Q buffer qb): only ceil(keys/16)*16 columns are computed.
-      auto issue_s = [&](uint32_t step, int qb, int keys, bool last_of_unit) {
-        const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 15) / 16) * 16, 0, 0);
-        const uint64_t dqs = dq + static_cast<uint64_t>((qb * L::Q_BYTES) >> 4);
-        const uint64_t dks = dk + static_cast<uint64_t>(((step % KV_STAGES) * L::KV_BYTES) >> 4);
-        const uint32_t d_s = tmem_base + (step & 1) * BKV;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t qoff = static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
-          const uint64_t koff = static_cast<uint64_t>(((k / 4) * (BKV * 128) + (k % 4) * 32) >> 4);
-          ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
-        }
-        ptx::umma_commit(&bar_s[step & 1]);
-        if (last_of_unit) ptx::umma_commit(&bar_qfree[qb]);
+      // Two cursors walk the CTA's steps: `cs` is the next step whose S = Q K^T is to be issued,
+      // `cp` the next step whose O (+)= P V is.  S runs up to S_BUFS - 1 steps ahead of P V, across
+      // unit boundaries; whichever of the two has its inputs ready is issued next.
+      struct Cursor {
+        int w, j, n_kv;
+        uint32_t n;
+        const int* it;
       };
-      uint32_t g = 0, n = 0;
-      bool ok = true;
-      // Prologue: S of the very first step.
-      if (static_cast<int>(blockIdx.x) < total) {
-        const int* it0 = p.work + (blockIdx.x / p.n_heads) * 4;
-        ok = ptx::mbar_wait(&bar_q[0], 0) && ptx::mbar_wait(&bar_kv[0], 0);
-        if (ok) {
-          ptx::tc_fence_after();
-          issue_s(0, 0, keys_in_tile(it0, 0), unit_steps(it0) == 1);
+      auto load_unit = [&](Cursor& c) {
+        if (c.w < total) {
+          c.it = p.work + (c.w / p.n_heads) * 4;
+          c.n_kv = unit_steps(c.it);
         }
-      }
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
-        const int* it = p.work + (w / p.n_heads) * 4;
-        const int n_kv = unit_steps(it);
-        const int w_next = w + static_cast<int>(gridDim.x);
-        const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
-        for (int j = 0; j < n_kv && ok; ++j, ++g) {
-          // (1) S of step g+1 into the other score buffer.  That buffer holds P of step g-1,
-          // read by the P V of g-1 issued one iteration ago: MMAs run in issue order.
-          if (j + 1 < n_kv) {
-            ok = ptx::mbar_wait(&bar_kv[(g + 1) % KV_STAGES], ((g + 1) / KV_STAGES) & 1);
-            if (!ok) break;
+      };
+      auto advance = [&](Cursor& c) {
+        if (++c.j == c.n_kv) {
+          c.w += static_cast<int>(gridDim.x);
+          ++c.n;
+          c.j = 0;
+          load_unit(c);
+        }
+      };
+      Cursor cs{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cp = cs;
+      load_unit(cs);
+      load_unit(cp);
+      uint32_t gs = 0, g = 0;  // steps whose S / P V has been issued
+      uint32_t idle = 0;
+      bool ok = true;
+      while (cp.w < total) {
+        bool progress = false;
+        // S of step gs into score tile gs % S_BUFS.  The tile holds P of step gs - S_BUFS, whose
+        // P V must have been issued (MMAs run in issue order): gs - S_BUFS < g.
+        if (cs.w < total && gs < g + S_BUFS) {
+          const int qb = cs.n % Q_BUFS;
+          const bool ready = (cs.j != 0 || ptx::mbar_test_wait(&bar_q[qb], (cs.n / Q_BUFS) & 1)) &&
+                             ptx::mbar_test_wait(&bar_kv[gs % KV_STAGES], (gs / KV_STAGES) & 1);
+          if (ready) {
             ptx::tc_fence_after();
-            issue_s(g + 1, n & 1, keys_in_tile(it, j + 1), j + 2 == n_kv);
-          } else if (w_next < total) {
-            const int* itn = p.work + (w_next / p.n_heads) * 4;
-            ok = ptx::mbar_wait(&bar_q[(n + 1) & 1], ((n + 1) >> 1) & 1) &&
-                 ptx::mbar_wait(&bar_kv[(g + 1) % KV_STAGES], ((g + 1) / KV_STAGES) & 1);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            issue_s(g + 1, (n + 1) & 1, keys_in_tile(itn, 0), unit_steps(itn) == 1);
+            const int keys = keys_in_tile(cs.it, cs.j);
+            // only ceil(keys / 16) * 16 columns are computed
+            const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 15) / 16) * 16, 0, 0);
+            const uint64_t dqs = dq + static_cast<uint64_t>((qb * L::Q_BYTES) >> 4);
+            const uint64_t dks = dk + static_cast<uint64_t>(((gs % KV_STAGES) * L::KV_BYTES) >> 4);
+            const uint32_t d_s = tmem_base + (gs % S_BUFS) * BKV;
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+              const uint64_t qoff = static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
+              const uint64_t koff = static_cast<uint64_t>(((k / 4) * (BKV * 128) + (k % 4) * 32) >> 4);
+              ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
+            }
+            ptx::umma_commit(&bar_s[gs % S_BUFS]);
+            if (cs.j + 1 == cs.n_kv) ptx::umma_commit(&bar_qfree[qb]);  // last S of the unit
+            ++gs;
+            advance(cs);
+            progress = true;
           }
-          // (2) O (+)= P V of step g, once its P is written.
-          ok = ptx::mbar_wait_spin(&bar_p[g & 1], (g >> 1) & 1);
-          if (!ok) break;
+        }
+        // O (+)= P V of step g, once its P is written.
+        if (g < gs && ptx::mbar_test_wait(&bar_p[g % S_BUFS], (g / S_BUFS) & 1)) {
           ptx::tc_fence_after();
-          const int k_steps = (keys_in_tile(it, j) + 15) / 16;
-          const uint32_t t_p = tmem_base + (g & 1) * BKV;  // P lies over the scores of the step
+          const int k_steps = (keys_in_tile(cp.it, cp.j) + 15) / 16;
+          const uint32_t tmem_o = tmem_o0 + (cp.n % O_BUFS) * D;
+          const uint32_t t_p = tmem_base + (g % S_BUFS) * BKV;  // P lies over the scores of the step
           const uint64_t dvs = dv + static_cast<uint64_t>(((g % KV_STAGES) * L::KV_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
             if (k < k_steps) {
               ptx::umma_ts(tmem_o, t_p + k * 8, dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o,
-                           (j | k) != 0 ? 1u : 0u);
+                           (cp.j | k) != 0 ? 1u : 0u);
             }
           }
-          ptx::umma_commit(&bar_pv[g & 1]);
+          ptx::umma_commit(&bar_pv[g % S_BUFS]);
           ptx::umma_commit(&bar_kvfree[g % KV_STAGES]);
+          ++g;
+          advance(cp);
+          progress = true;
+        }
+        if (progress) {
+          idle = 0;
+        } else if (++idle > ptx::kSpinLimit) {  // bounded: nothing became ready for too long
+          ok = false;
+          break;
         }
       }
       // Nothing may be in flight when the CTA frees its TMEM.
-      if (ok && g > 0) ok = ptx::mbar_wait(&bar_pv[(g - 1) & 1], ((g - 1) >> 1) & 1);
+      if (ok && g > 0) ok = ptx::mbar_wait(&bar_pv[(g - 1) % S_BUFS], ((g - 1) / S_BUFS) & 1);
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {
@@ -392,7 +431,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     // written back with 8 lanes per row.  warp_dst: row 0 of the warp; rows_valid: how many of
     // the 32 rows belong to the sequence.
     auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* warp_dst, int rows_valid) -> bool {
-      if (!ptx::mbar_wait(&bar_pv[g_last & 1], (g_last >> 1) & 1)) return false;
+      if (!ptx::mbar_wait(&bar_pv[g_last % S_BUFS], (g_last / S_BUFS) & 1)) return false;
       ptx::tc_fence_after();
       uint8_t* stage = smem + L::OFF_STAGE + warp * (32 * 128);
 #pragma unroll
@@ -440,8 +479,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
       float m = -INFINITY, l = 0.f;           // running maximum (scaled log2 domain) and sum
       for (int j = 0; j < n_kv; ++j, ++g) {
-        const int b = g & 1;
-        if (!ptx::mbar_wait(&bar_s[b], (g >> 1) & 1)) {
+        const int b = g % S_BUFS;
+        if (!ptx::mbar_wait(&bar_s[b], (g / S_BUFS) & 1)) {
           ok = false;
           break;
         }
@@ -481,7 +520,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
             // P V issued so far must be complete; the next one is only issued after this
             // warp's arrival on bar_p below.
-            if (!ptx::mbar_wait(&bar_pv[(g - 1) & 1], ((g - 1) >> 1) & 1)) {
+            if (!ptx::mbar_wait(&bar_pv[(g - 1) % S_BUFS], ((g - 1) / S_BUFS) & 1)) {
               ok = false;
               break;
             }
@@ -598,7 +637,7 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
   p.status = a.status;
   const long long total = static_cast<long long>(a.n_work) * a.n_heads;
   if (total > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
-  const long long resident = static_cast<long long>(num_sms()) * (D == 64 ? 2 : 1);
+  const long long resident = static_cast<long long>(num_sms()) * AttnCfg<D>::CTAS_PER_SM;
   const long long grid = total < resident ? total : resident;
   kern<<<static_cast<unsigned>(grid), ATTN_THREADS, L::TOTAL, stream>>>(tm_q, tm_k, tm_v, p);
   return static_cast<int>(cudaGetLastError());
