@@ -265,8 +265,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   auto unit_steps = [&](const int* it) { return (unit_kv_end(it) - it[3] + BKV - 1) / BKV; };
   // Number of keys of step j of a unit that any row can see (CTA-uniform).
   auto keys_in_tile = [&](const int* it, int j) { return min(BKV, unit_kv_end(it) - it[3] - j * BKV); };
+  // The CTA's n-th work unit.  Units are sorted by cost; handing them out in alternating
+  // direction (0..G-1, then G-1..0, ...) keeps the sums per CTA close when the costs fall
+  // steadily, as they do for causal batches.
+  auto unit_at = [&](uint32_t n) {
+    const int G = static_cast<int>(gridDim.x), b = static_cast<int>(blockIdx.x);
+    return static_cast<int>(n) * G + ((n & 1u) ? G - 1 - b : b);
+  };
 
-  // The CTA is persistent: it walks the work units blockIdx.x, blockIdx.x + gridDim.x, ...
+  // The CTA is persistent: it walks the work units unit_at(0), unit_at(1), ...
   // `g` counts key steps over the CTA's whole life, `n` counts units; they drive every buffer
   // index and barrier parity in all three roles.
   if (warp == 5) {
@@ -277,7 +284,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       ptx::prefetch_tmap(&tm_v);
       uint32_t g = 0, n = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
+      for (int w = unit_at(n); w < total && ok; w = unit_at(++n)) {
         const int* it = p.work + (w / p.n_heads) * 4;
         const int head = w % p.n_heads;
         const int kv_head = head / group;
@@ -340,8 +347,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       };
       auto advance = [&](Cursor& c) {
         if (++c.j == c.n_kv) {
-          c.w += static_cast<int>(gridDim.x);
           ++c.n;
+          c.w = unit_at(c.n);
           c.j = 0;
           load_unit(c);
         }
@@ -467,7 +474,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       ptx::tc_fence_before();
       return true;
     };
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++n) {
+    for (int w = unit_at(n); w < total && ok; w = unit_at(++n)) {
       const int* it = p.work + (w / p.n_heads) * 4;
       const int head = w % p.n_heads;
       const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
