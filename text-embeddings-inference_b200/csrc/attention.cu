@@ -3,20 +3,23 @@
 // Replaces the reference's flash_attn_varlen call (backends/candle/src/flash_attn.rs:23-120;
 // call sites models/flash_bert.rs:95-108, flash_nomic.rs:83-96, flash_qwen3.rs:155-169):
 // for every sequence s of the packed batch and head h,
-//     out = softmax(scale * Q_s K_s^T  [- slope_h * |i - j|]  [causal mask]) V_s
-// with q-head h reading kv-head h / (n_heads / n_kv_heads).  Q, K and V are strided views of
-// the projection output (token-major rows), exactly as the reference passes them.
+//     out = softmax(scale * Q_s K_s^T  [- slope_h * |i - j|]  [window / causal mask]) V_s
+// with q-head h reading kv-head h / (n_heads / n_kv_heads); key j counts for query i when
+// i - window_left <= j <= i + window_right (causal: right window 0).  Q, K and V are strided
+// views of the projection output (token-major rows), exactly as the reference passes them.
 //
-// Persistent CTAs (two per SM for D = 64) walk the (sequence, 128-row query tile, head) work
-// units, most expensive first, in steps of 64 keys.  Everything a step needs is double- or
-// triple-buffered, so the three roles of a CTA run decoupled:
-//   warp 5 (one lane)  TMA producer: Q tile per unit (2 buffers), K/V tiles per step (3 stages),
-//                      128-byte swizzle, plain per-CTA loads (no cluster multicast); runs up to
-//                      three steps and one unit ahead.
-//   warp 4 (one lane)  MMA issuer: S = Q K^T of step g+1 into the other of two 64-column score
-//                      buffers in TMEM while the softmax warps still work on step g, then
-//                      O += P V of step g into an output tile in TMEM from column 128 on, with P
-//                      read from TMEM (A operand) and V from shared memory (MN-major operand).
+// Persistent CTAs (two per SM for D = 64, one for D = 128) walk the (sequence, 128-row query
+// tile, head) work units, sorted by cost and handed out in alternating direction, in steps of
+// 64 keys.  Everything a step needs is multi-buffered (AttnCfg), so the three roles of a CTA
+// run decoupled:
+//   warp 5 (one lane)  TMA producer: Q tile per unit, K/V tiles per step (KV_STAGES stages),
+//                      128-byte swizzle, plain per-CTA loads (no cluster multicast); runs ahead
+//                      of the MMAs by the free stages and, with two Q buffers, by one unit.
+//   warp 4 (one lane)  MMA issuer, polling two streams: S = Q K^T of a step into one of S_BUFS
+//                      64-column score tiles in TMEM, up to S_BUFS - 1 steps ahead of the
+//                      softmax and across unit boundaries; O += P V of a step into an output
+//                      tile in TMEM behind the score tiles, with P read from TMEM (A operand)
+//                      and V from shared memory (MN-major operand).
 //   warps 0-3          one query row per thread: the 64 scores of the step are read from TMEM
 //                      into registers once; row maximum, exp2, and P written back as fp16/bf16
 //                      over the row's own scores in TMEM, so P never touches shared memory (the
