@@ -279,6 +279,33 @@ def run_kernel(args):
         fn = lambda: ops.attention(q, k, v, cu, work=work, out=out, status=st)  # noqa: E731
         flops = 4.0 * H * float(sum(n * n for n in lens))
         bytes_ = 2.0 * 4 * T * H
+    elif name in ("attention_long", "attention_causal128", "rope_qwen3"):
+        # 16 x 2048 tokens, 12 heads x 64, bidirectional / 4 x 4096 tokens, 16 query and 8 key-value
+        # heads x 128, causal, bf16 (the Qwen3 shape) / RoPE + q/k RMSNorm on the latter
+        if name == "attention_long":
+            lens, nh, nkv, D, causal = [2048] * 16, 12, 12, 64, False
+        else:
+            lens, nh, nkv, D, causal, dt = [4096] * 4, 16, 8, 128, True, torch.bfloat16
+        T = int(sum(lens))
+        qkv = rnd(T, (nh + 2 * nkv) * D).to(dt)
+        q = qkv[:, : nh * D].view(T, nh, D)
+        k = qkv[:, nh * D: (nh + nkv) * D].view(T, nkv, D)
+        v = qkv[:, (nh + nkv) * D:].view(T, nkv, D)
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        if name == "rope_qwen3":
+            pos = torch.cat([torch.arange(n, device="cuda", dtype=torch.int32) for n in lens])
+            inv = 1.0 / (1e6 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+            ang = torch.arange(max(lens), device="cuda", dtype=torch.float32)[:, None] * inv[None, :]
+            cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+            qg, kg = torch.ones(D, device="cuda", dtype=dt), torch.ones(D, device="cuda", dtype=dt)
+            fn = lambda: ops.qk_norm_rope_(q, k, pos, cos, sin, qg, kg, 1e-6)  # noqa: E731
+            bytes_ = 2.0 * 2 * T * (nh + nkv) * D
+        else:
+            work = torch.from_numpy(ops.attention_plan(cu, causal)).cuda()
+            out = torch.empty(T, nh * D, device="cuda", dtype=dt)
+            fn = lambda: ops.attention(q, k, v, cu, causal=causal, work=work, out=out, status=st)  # noqa: E731
+            flops = (2.0 if causal else 4.0) * nh * D * float(sum(n * (n + 1) if causal else n * n for n in lens))
+            bytes_ = 2.0 * T * (2 * nh + 2 * nkv) * D
     elif name == "add_layernorm":
         x, r, gm, bt = rnd(T, H), rnd(T, H), rnd(H), rnd(H)
         fn = lambda: ops.add_layernorm(x, r, gm, bt, 1e-12)  # noqa: E731
@@ -398,7 +425,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
-                         "add_layernorm | pool_mean")
+                         "attention_long | attention_causal128 | rope_qwen3 | add_layernorm | pool_mean")
     ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
     ap.add_argument("--dtype", default=None, choices=["float16", "bfloat16"],
