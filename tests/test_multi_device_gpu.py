@@ -64,3 +64,26 @@ def test_sharded_predict_and_errors(lib, model_dirs):
         assert again[i] == m[i]
     one.close()
     two.close()
+
+
+@needs_two
+def test_sharded_embed_with_dense_modules(lib, model_dirs, tmp_path):
+    # Dense modules change the width of the pooled rows but not of the raw rows; both kinds are
+    # scattered back from the replicas with their own widths.
+    import shutil
+    import tei_b200
+    d = tmp_path / "bert_dense"
+    shutil.copytree(model_dirs["bert"], d)
+    G.write_dense_dir(d, "2_Dense", 128, 72, seed=31, bias=True, activation="tanh")
+    one = tei_b200.B200Backend(d, "float16", "embedding", "mean", dense_paths=["2_Dense"], devices=[0])
+    two = tei_b200.B200Backend(d, "float16", "embedding", "mean", dense_paths=["2_Dense"], devices=[0, 1])
+    assert two.output_dim == 72 and two.hidden_size == 128
+    lens = [7, 300, 33, 150, 2, 64, 129]
+    b = G.random_batch(8, lens, 0, 1000, pooled=[0, 2, 3, 6], raw=[1, 4, 5], type_vocab=2)
+    a, m = one.embed(b, normalize=True), two.embed(b, normalize=True)
+    for i in range(len(lens)):
+        assert a[i].kind == m[i].kind and a[i].values.shape == m[i].values.shape
+        assert np.abs(a[i].values - m[i].values).max() <= 4e-3
+    assert m[0].values.shape == (72,) and m[1].values.shape == (300, 128)
+    one.close()
+    two.close()
