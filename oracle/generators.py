@@ -108,6 +108,50 @@ def mistral_config(hidden=4096, layers=32, heads=32, kv_heads=8, inter=14336, vo
     return c
 
 
+def modernbert_config(hidden=768, layers=22, heads=12, inter=1152, vocab=50368, max_pos=8192, local_attention=128,
+                      global_every=3, global_theta=160000.0, local_theta=10000.0, eps=1e-5,
+                      num_labels: Optional[int] = None, classifier_pooling: str = "mean") -> dict:
+    """Fields of ModernBertConfig (models/modernbert.rs:12-49)."""
+    c = {
+        "architectures": ["ModernBertModel" if num_labels is None else "ModernBertForSequenceClassification"],
+        "model_type": "modernbert", "vocab_size": vocab, "hidden_size": hidden, "intermediate_size": inter,
+        "num_hidden_layers": layers, "num_attention_heads": heads, "hidden_activation": "gelu",
+        "max_position_embeddings": max_pos, "initializer_range": 0.02, "initializer_cutoff_factor": 2.0,
+        "norm_eps": eps, "norm_bias": False, "pad_token_id": 50283, "eos_token_id": 50282, "bos_token_id": 50281,
+        "cls_token_id": 50281, "sep_token_id": 50282, "global_rope_theta": global_theta, "attention_bias": False,
+        "attention_dropout": 0.0, "global_attn_every_n_layers": global_every, "local_attention": local_attention,
+        "local_rope_theta": local_theta, "mlp_bias": False, "classifier_pooling": classifier_pooling,
+        "classifier_activation": "gelu", "classifier_bias": False,
+    }
+    if num_labels is not None:
+        c["num_labels"] = num_labels
+        c["id2label"] = {str(i): f"LABEL_{i}" for i in range(num_labels)}
+    return c
+
+
+def _modernbert_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    """Names as flash_modernbert.rs:279-293 and modernbert.rs:58-70,88-101,408-432 read them."""
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    t: Dict[str, Tuple[tuple, str]] = {"model.embeddings.tok_embeddings.weight": ((V, H), "normal"),
+                                       "model.embeddings.norm.weight": ((H,), "ones"),
+                                       "model.final_norm.weight": ((H,), "ones")}
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        if i != 0:
+            t[p + "attn_norm.weight"] = ((H,), "ones")
+        t[p + "attn.Wqkv.weight"] = ((3 * H, H), "normal")
+        t[p + "attn.Wo.weight"] = ((H, H), "normal")
+        t[p + "mlp_norm.weight"] = ((H,), "ones")
+        t[p + "mlp.Wi.weight"] = ((2 * I, H), "normal")
+        t[p + "mlp.Wo.weight"] = ((H, I), "normal")
+    if c.get("num_labels") is not None:
+        t["head.dense.weight"] = ((H, H), "normal")
+        t["head.norm.weight"] = ((H,), "ones")
+        t["classifier.weight"] = ((c["num_labels"], H), "normal")
+        t["classifier.bias"] = ((c["num_labels"],), "normal")
+    return t
+
+
 # --------------------------------------------------------------------------- tensor lists
 def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) -> Dict[str, Tuple[tuple, str]]:
     """name -> (shape, kind) with kind in {normal, ones, zeros}."""
@@ -228,6 +272,8 @@ def tensor_shapes(config: dict, classifier: Optional[str] = None, splade: bool =
         return _nomic_shapes(config)
     if mt in ("qwen3", "qwen2", "mistral", "llama"):
         return _qwen3_shapes(config)
+    if mt == "modernbert":
+        return _modernbert_shapes(config)
     raise ValueError(mt)
 
 

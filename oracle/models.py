@@ -121,7 +121,8 @@ def alibi_slopes(n_heads: int) -> Tensor:
 
 
 def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: float, causal: bool,
-                     slopes: Optional[Tensor] = None, window_left: Optional[int] = None) -> Tensor:
+                     slopes: Optional[Tensor] = None, window_left: Optional[int] = None,
+                     window_right: Optional[int] = None) -> Tensor:
     """q [T, nh, D], k/v [T, nkv, D] -> [T, nh*D]; one softmax(QK^T)V per sequence and head.
     window_left: key j counts for query i only when j >= i - window_left (flash-attn's
     window_size_left, as passed by flash_mistral.rs:95-110 through flash_attn.rs:82-95)."""
@@ -148,6 +149,9 @@ def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: flo
         if window_left is not None:
             idx = torch.arange(L)
             sc = sc.masked_fill(idx.view(1, L) < idx.view(L, 1) - window_left, float("-inf"))
+        if window_right is not None:  # and j <= i + window_right (flash_modernbert.rs:92-111)
+            idx = torch.arange(L)
+            sc = sc.masked_fill(idx.view(1, L) > idx.view(L, 1) + window_right, float("-inf"))
         out[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1).reshape(L, nh * D)
     return out
 
@@ -525,6 +529,79 @@ class Qwen3Oracle:
         return pool_outputs(self.hidden_states(batch), batch, self.pool)
 
 
+# --------------------------------------------------------------------------- ModernBERT
+class ModernBertOracle:
+    """models/modernbert.rs (CPU arm) / flash_modernbert.rs: LayerNorm (weight only) after the
+    token embedding; pre-norm blocks x = x + attn(attn_norm(x)), x = x + mlp(mlp_norm(x)) with no
+    attn_norm in layer 0 (flash_modernbert.rs:131-139,161-191); RoPE with `global_rope_theta` on
+    every `global_attn_every_n_layers`-th layer and `local_rope_theta` plus a window of
+    `local_attention / 2` keys on each side elsewhere (`:53-62,92-111,299-313`); feed-forward
+    act(Wi x [:I]) * Wi x [I:] -> Wo (modernbert.rs:115-131) with the tanh GELU every GELU name
+    means on this backend; final LayerNorm.  Head: dense (no bias) + classifier_activation ->
+    LayerNorm -> classifier on the CLS or mean row (modernbert.rs:401-456,481-489)."""
+
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding", pool: str = "cls"):
+        c = config
+        if pool == "splade":
+            raise ValueError("`splade` is not supported for ModernBert")
+        self.cfg = c
+        self.model_type = model_type
+        self.pool = (c.get("classifier_pooling") or "cls") if model_type == "classifier" else pool
+        prefix = "model." if "model.embeddings.tok_embeddings.weight" in tensors else ""
+        self.w = _Weights(tensors, (prefix,))
+        self.all = _Weights(tensors, ("",))
+        self.nh = c["num_attention_heads"]
+        self.hidden = c["hidden_size"]
+        self.dh = self.hidden // self.nh
+        self.inter = c["intermediate_size"]
+        self.eps = float(c["norm_eps"])
+        self.n_layers = c["num_hidden_layers"]
+        self.every = c["global_attn_every_n_layers"]
+        self.window = c["local_attention"] // 2
+        self.act = activation(c["hidden_activation"])
+        n_pos = int(c["max_position_embeddings"])
+        self.rope = {False: rope_tables(self.dh, float(c["global_rope_theta"]), n_pos),
+                     True: rope_tables(self.dh, float(c["local_rope_theta"]), n_pos)}
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        zero = torch.zeros(self.hidden)
+        x = layer_norm(w.get("embeddings.tok_embeddings.weight")[ids], None, w.get("embeddings.norm.weight"), zero, self.eps)
+        T, H = x.shape
+        cu = batch.cumulative_seq_lengths
+        for i in range(self.n_layers):
+            p = f"layers.{i}."
+            local = i % self.every != 0
+            a_in = x if i == 0 else layer_norm(x, None, w.get(p + "attn_norm.weight"), zero, self.eps)
+            qkv = linear(a_in, w.get(p + "attn.Wqkv.weight"), w.get(p + "attn.Wqkv.bias") if w.has(p + "attn.Wqkv.bias") else None)
+            q, k, v = (qkv[:, j * H:(j + 1) * H].reshape(T, self.nh, self.dh) for j in range(3))
+            cos, sin = self.rope[local]
+            q, k = apply_rope(q, cos[pids], sin[pids]), apply_rope(k, cos[pids], sin[pids])
+            win = self.window if local else None
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), False, None, win, win)
+            x = x + linear(a, w.get(p + "attn.Wo.weight"), w.get(p + "attn.Wo.bias") if w.has(p + "attn.Wo.bias") else None)
+            m = layer_norm(x, None, w.get(p + "mlp_norm.weight"), zero, self.eps)
+            h = linear(m, w.get(p + "mlp.Wi.weight"), w.get(p + "mlp.Wi.bias") if w.has(p + "mlp.Wi.bias") else None)
+            f = self.act(h[:, :self.inter]) * h[:, self.inter:]
+            x = x + linear(f, w.get(p + "mlp.Wo.weight"), w.get(p + "mlp.Wo.bias") if w.has(p + "mlp.Wo.bias") else None)
+        return layer_norm(x, None, w.get("final_norm.weight"), zero, self.eps)
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+    def predict(self, batch: Batch) -> Tensor:
+        x = self.hidden_states(batch)
+        all_pooled = Batch(batch.input_ids, batch.token_type_ids, batch.position_ids, batch.cumulative_seq_lengths,
+                           batch.max_length, np.arange(len(batch), dtype=np.uint32), np.zeros(0, dtype=np.uint32))
+        pooled, _ = pool_outputs(x, all_pooled, self.pool)
+        a = self.all
+        h = activation(self.cfg["classifier_activation"])(linear(pooled, a.get("head.dense.weight")))
+        h = layer_norm(h, None, a.get("head.norm.weight"), torch.zeros(self.hidden), self.eps)
+        return linear(h, a.get("classifier.weight"), a.get("classifier.bias"))
+
+
 # --------------------------------------------------------------------------- JinaBERT
 def is_jina_bert(config: dict) -> bool:
     # BertConfigWrapper, backends/candle/src/lib.rs:83-121
@@ -610,4 +687,6 @@ def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
         return NomicOracle(config, tensors, model_type, pool)
     if mt in ("qwen3", "qwen2", "mistral", "llama"):
         return Qwen3Oracle(config, tensors, model_type, pool)
+    if mt == "modernbert":
+        return ModernBertOracle(config, tensors, model_type, pool)
     raise ValueError(f"model_type {mt} is outside the hot path")

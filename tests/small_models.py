@@ -59,6 +59,16 @@ def write_all(base):
         G.mistral_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048,
                          model_type="llama"),
         seed=14, norm_jitter=0.1, std=0.05)
+    dirs["modernbert"] = G.write_model_dir(
+        base / "modernbert",
+        G.modernbert_config(hidden=128, layers=4, heads=2, inter=256, vocab=1000, max_pos=1024, local_attention=64,
+                            global_every=3),
+        seed=15, norm_jitter=0.1, std=0.05)
+    dirs["modernbert_cls"] = G.write_model_dir(
+        base / "modernbert_cls",
+        G.modernbert_config(hidden=256, layers=3, heads=2, inter=384, vocab=1000, max_pos=1024, local_attention=32,
+                            global_every=2, num_labels=3, classifier_pooling="mean"),
+        seed=16, norm_jitter=0.1, std=0.05)
     return dirs
 
 
@@ -80,6 +90,9 @@ GOLDEN_CASES = {
     "mistral_window_last": ("mistral", "embedding", "last_token", dict(seed=113, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
     "mistral_window_mean": ("mistral", "embedding", "mean", dict(seed=114, lens=[400, 101, 100, 99], lo=0, hi=1000, type_vocab=1, offset=0)),
     "llama_cls": ("llama", "embedding", "cls", dict(seed=115, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
+    "modernbert_mean": ("modernbert", "embedding", "mean", dict(seed=116, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "modernbert_cls": ("modernbert", "embedding", "cls", dict(seed=117, lens=[33, 64, 65, 400], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "modernbert_scores": ("modernbert_cls", "classifier", "cls", dict(seed=118, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

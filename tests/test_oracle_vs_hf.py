@@ -127,6 +127,28 @@ def test_mistral_sliding_window_matches_hf(model_dirs):
     assert (o.hidden_states(b)[-1] - hs[-1]).abs().max().item() > 1e-3
 
 
+def test_modernbert_matches_hf(model_dirs):
+    d = model_dirs["modernbert"]
+    cfg = json.load(open(d / "config.json"))
+    # every GELU name means the tanh approximation on the reference's path (layers/linear.rs:5-17)
+    hcfg = dict(cfg, hidden_activation="gelu_pytorch_tanh", attn_implementation="eager", reference_compile=False,
+                pad_token_id=0, bos_token_id=1, eos_token_id=2, cls_token_id=1, sep_token_id=2)
+    hf = transformers.ModernBertModel(transformers.ModernBertConfig(**hcfg)).eval()
+    _, tensors = M.load_model_dir(d)
+    hf.load_state_dict({k[len("model."):]: v for k, v in tensors.items()}, strict=True)
+    o = M.build_oracle(d, "embedding", "mean")
+    assert o.window == 32 and o.every == 3
+    b = G.random_batch(8, [7, 33, 34, 150], 0, 1000)
+    hs = o.hidden_states(b)
+    for s, a, e in _per_sequence(b):
+        with torch.no_grad():
+            ref = hf(input_ids=_t(b.input_ids[a:e])).last_hidden_state[0]
+        assert (ref - hs[a:e]).abs().max().item() < TOL
+    # the local window matters at these lengths
+    o.window = 10 ** 6
+    assert (o.hidden_states(b)[-1] - hs[-1]).abs().max().item() > 1e-3
+
+
 def test_nomic_matches_hf(model_dirs):
     mod = pytest.importorskip("transformers.models.nomic_bert.modeling_nomic_bert")
     d = model_dirs["nomic"]

@@ -103,13 +103,19 @@ struct NormArgs {
   const void* gamma;
   const void* beta;      // LayerNorm only
   void* out;             // normalised rows
-  float* sum_out;        // RMSNorm: fp32 x + residual written here (may alias residual); else nullptr
+  float* sum_out;        // fp32 residual stream: x + residual written here (may alias residual); else nullptr
   int T, H;
   float eps;
   int rms;               // 0 LayerNorm, 1 RMSNorm
   int dtype;
+  // 1: residual and sum_out are fp32 (pre-norm models), 0: residual in the model dtype and no
+  // sum_out, -1: as RMSNorm implies.  gamma == nullptr leaves the sum un-normalised.
+  int residual_f32 = -1;
 };
 int launch_add_norm(const NormArgs& n, cudaStream_t stream);
+// LayerNorm without bias over fp32 rows, in place.
+int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, float eps, int dtype,
+                              cudaStream_t stream);
 
 struct RopeArgs {
   void* q;               // rows of n_heads*head_dim at stride ld_q

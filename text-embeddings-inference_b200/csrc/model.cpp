@@ -203,6 +203,43 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     s.rope = true;
     s.rope_table_len = s.max_pos;
     s.type_vocab = 0;
+  } else if (mt == "modernbert") {
+    // ModernBertConfig (models/modernbert.rs:12-49); it runs on the pre-norm decoder skeleton.
+    s.arch = ARCH_QWEN3;
+    s.modernbert = true;
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for ModernBert");
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "hidden_size"));
+    s.inter = static_cast<int>(need_int(c, "intermediate_size"));
+    s.layers = static_cast<int>(need_int(c, "num_hidden_layers"));
+    s.heads = s.kv_heads = static_cast<int>(need_int(c, "num_attention_heads"));
+    s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
+    s.eps = static_cast<float>(need_double(c, "norm_eps"));
+    if (parse_act(need_string(c, "hidden_activation")) != ACT_GELU) {
+      throw TeiError(ERR_START, "ModernBert expects a GELU hidden_activation");
+    }
+    s.head_dim = s.heads > 0 ? s.hidden / s.heads : 0;
+    s.rope_theta = static_cast<float>(need_double(c, "global_rope_theta"));
+    s.local_theta = static_cast<float>(need_double(c, "local_rope_theta"));
+    s.global_every = static_cast<int>(need_int(c, "global_attn_every_n_layers"));
+    s.local_window = static_cast<int>(need_int(c, "local_attention")) / 2;  // flash_modernbert.rs:61
+    if (s.global_every <= 0) throw TeiError(ERR_START, "global_attn_every_n_layers must be positive");
+    s.gated = true;
+    s.act = ACT_GEGLU;  // act(first half) * second half (modernbert.rs:115-127)
+    s.rope = true;
+    s.rope_table_len = s.max_pos;
+    s.causal = false;
+    s.type_vocab = 0;
+    if (s.classifier) {
+      // modernbert.rs:425-432,482-483: `num_labels` rows (1 when absent), pooling from the config
+      s.n_classes = static_cast<int>(c.get_int("num_labels", c["id2label"].is_object() ? static_cast<int64_t>(c["id2label"].size()) : 1));
+      const std::string cp = c.get_string("classifier_pooling", "cls");
+      if (cp == "cls") s.cls_pool = POOL_CLS;
+      else if (cp == "mean") s.cls_pool = POOL_MEAN;
+      else throw TeiError(ERR_START, "unknown classifier_pooling " + cp);
+      s.head_act = parse_act(need_string(c, "classifier_activation"));
+      if (s.head_act < 0 || s.head_act == ACT_SWIGLU) throw TeiError(ERR_START, "unsupported classifier_activation");
+    }
   } else {
     throw TeiError(ERR_START, "model_type `" + mt + "` is not served by this backend");
   }
@@ -502,7 +539,10 @@ void Replica::load_weights(const SafeTensors& st) {
   switch (spec_.arch) {
     case ARCH_BERT: load_bert(st); break;
     case ARCH_NOMIC: load_nomic(st); break;
-    case ARCH_QWEN3: load_qwen3(st); break;
+    case ARCH_QWEN3:
+      if (spec_.modernbert) load_modernbert(st);
+      else load_qwen3(st);
+      break;
   }
 }
 
@@ -737,6 +777,61 @@ void Replica::load_qwen3(const SafeTensors& st) {
   }
 }
 
+void Replica::load_modernbert(const SafeTensors& st) {
+  const ModelSpec& s = spec_;
+  const int H = s.hidden, I = s.inter;
+  // flash_modernbert.rs:279-293: names under `model.` or bare.
+  Names n{st, st.contains("model.embeddings.tok_embeddings.weight") ? "model." : ""};
+  Names root{st, ""};
+  expect_shape(n.get("embeddings.tok_embeddings.weight"), {s.vocab, H}, "embeddings.tok_embeddings.weight");
+  word_ = upload_new(n.get("embeddings.tok_embeddings.weight"));
+  emb_g_ = upload_new(n.get("embeddings.norm.weight"));  // LayerNormNoBias: weight only
+  for (int i = 0; i < s.layers; ++i) {
+    LayerW& L = layers_[i];
+    const std::string p = "layers." + std::to_string(i) + ".";
+    if (i != 0) L.ln1_g = upload_new(n.get(p + "attn_norm.weight"));  // layer 0 has none (:131-139)
+    expect_shape(n.get(p + "attn.Wqkv.weight"), {3 * H, H}, p + "attn.Wqkv.weight");
+    L.wqkv = upload_new(n.get(p + "attn.Wqkv.weight"));
+    if (n.has(p + "attn.Wqkv.bias")) L.bqkv = upload_new(n.get(p + "attn.Wqkv.bias"));
+    expect_shape(n.get(p + "attn.Wo.weight"), {H, H}, p + "attn.Wo.weight");
+    L.wo = upload_new(n.get(p + "attn.Wo.weight"));
+    if (n.has(p + "attn.Wo.bias")) L.bo = upload_new(n.get(p + "attn.Wo.bias"));
+    L.ln2_g = upload_new(n.get(p + "mlp_norm.weight"));
+    // mlp.Wi [2I, H]: rows [0, I) go through the activation, rows [I, 2I) gate them.
+    const StTensor& wi = n.get(p + "mlp.Wi.weight");
+    expect_shape(wi, {2 * I, H}, p + "mlp.Wi.weight");
+    auto halves = [](const StTensor& t, StTensor& a, StTensor& b) {
+      a = t;
+      b = t;
+      a.shape[0] = b.shape[0] = t.shape[0] / 2;
+      a.nbytes = b.nbytes = t.nbytes / 2;
+      b.data = t.data + t.nbytes / 2;
+    };
+    StTensor ga, up;
+    halves(wi, ga, up);
+    L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+    upload_rows_interleaved(L.w1, ga, up);
+    if (n.has(p + "mlp.Wi.bias")) {
+      StTensor ba, bu;
+      halves(n.get(p + "mlp.Wi.bias"), ba, bu);
+      L.b1 = dev_alloc(static_cast<size_t>(2) * I * 2);
+      upload_rows_interleaved(L.b1, ba, bu);
+    }
+    expect_shape(n.get(p + "mlp.Wo.weight"), {H, I}, p + "mlp.Wo.weight");
+    L.w2 = upload_new(n.get(p + "mlp.Wo.weight"));
+    if (n.has(p + "mlp.Wo.bias")) L.b2 = upload_new(n.get(p + "mlp.Wo.bias"));
+  }
+  final_norm_ = upload_new(n.get("final_norm.weight"));
+  if (s.classifier) {  // ModernBertClassificationHead::load, modernbert.rs:408-440
+    expect_shape(root.get("head.dense.weight"), {H, H}, "head.dense.weight");
+    cls_dense_w_ = upload_new(root.get("head.dense.weight"));
+    cls_norm_g_ = upload_new(root.get("head.norm.weight"));
+    expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
+    cls_out_w_ = upload_new(root.get("classifier.weight"));
+    cls_out_b_ = upload_new(root.get("classifier.bias"));
+  }
+}
+
 void Replica::build_rope_tables() {
   // layers/rotary.rs:29-116: inv_freq_i = 1 / base^(i / dim) for even i, angle = pos * inv_freq,
   // all in f32.  The tables stay in fp32 on the device.
@@ -758,6 +853,8 @@ void Replica::build_rope_tables() {
     TEI_CUDA(cudaMemcpy(*d_sin, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
   };
   fill(spec_.rope_theta, &cos_, &sin_);
+  // ModernBERT: a second pair of tables for the local-attention layers (flash_modernbert.rs:299-313)
+  if (spec_.modernbert) fill(spec_.local_theta, &cos_scaled_, &sin_scaled_);
   if (spec_.arch == ARCH_NOMIC && spec_.rope_scaling_factor > 0.f) {
     // flash_nomic.rs:244-258, including its integer exponent: powi((dim / (dim - 2)) as i32).
     const float sf = spec_.rope_scaling_factor;
@@ -775,7 +872,7 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
                                size_t raw_rows) {
   const ModelSpec& s = spec_;
   // integer inputs
-  const size_t ints_need = 3 * tokens + (seqs + 1) + 2 * seqs + raw_rows + 4 * n_work + 64;
+  const size_t ints_need = 3 * tokens + (seqs + 1) + 2 * seqs + raw_rows + 8 * n_work + 64;
   if (ints_need > ints_cap_) {
     TEI_CUDA(cudaStreamSynchronize(stream_));
     if (d_ints_) cudaFree(d_ints_);
@@ -920,6 +1017,14 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
                                        static_cast<int>(n_work), s.window_left, -1);
   if (static_cast<size_t>(n_planned) != n_work) throw TeiError(ERR_INFERENCE, "attention planning mismatch");
   off += 4 * n_work;
+  size_t o_work_local = 0;
+  if (s.local_window >= 0) {  // the layers with the two-sided window walk their own list
+    o_work_local = off;
+    const int n_local = plan_attention(cu_i.data(), static_cast<int>(B_), 0, h + off, static_cast<int>(n_work),
+                                       s.local_window, s.local_window);
+    if (static_cast<size_t>(n_local) != n_work) throw TeiError(ERR_INFERENCE, "attention planning mismatch");
+    off += 4 * n_work;
+  }
   TEI_CUDA(cudaMemcpyAsync(d_ints_, h_ints_, off * 4, cudaMemcpyHostToDevice, stream_));
   stats_.last_h2d_bytes = static_cast<double>(off * 4);
   d_ids_ = d_ints_ + o_ids;
@@ -930,6 +1035,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   d_all_idx_ = d_ints_ + o_all;
   d_raw_rows_ = d_ints_ + o_raw;
   d_work_ = d_ints_ + o_work;
+  d_work_local_ = s.local_window >= 0 ? d_ints_ + o_work_local : nullptr;
 
   // Output block: [0,64) status word | pooled | raw | scores || scratch (not copied back).
   const size_t D = static_cast<size_t>(output_dim());
@@ -1065,49 +1171,59 @@ void Replica::forward_nomic() {
 }
 
 void Replica::forward_qwen3() {
+  // The pre-norm skeleton: x = x + attn(norm(x)); x = x + mlp(norm(x)), with the running sum in
+  // fp32.  RMSNorm decoders (flash_qwen3.rs, flash_qwen2.rs, flash_mistral.rs) and ModernBERT
+  // (flash_modernbert.rs: LayerNorm without bias, LayerNorm after the embedding, no norm in front
+  // of the first attention, GeGLU, local / global layers) differ by the flags of the spec.
   const ModelSpec& s = spec_;
   const int T = static_cast<int>(T_), H = s.hidden, I = s.inter, Q = s.q_width(), KV = s.kv_width();
   const int W = Q + 2 * KV;
+  const int rms = s.modernbert ? 0 : 1;
   int* status = reinterpret_cast<int*>(d_out_);
   EmbedArgs e;
   e.ids = d_ids_; e.type_ids = nullptr; e.pos_ids = nullptr;
   e.word = word_; e.type_tab = nullptr; e.pos_tab = nullptr;
-  e.gamma = nullptr; e.beta = nullptr; e.out = tmp_; e.T = T; e.H = H; e.eps = 0.f; e.dtype = s.dtype;
+  e.gamma = emb_g_; e.beta = nullptr; e.out = tmp_; e.T = T; e.H = H; e.eps = s.eps; e.dtype = s.dtype;
   LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
   uint8_t* qkv = static_cast<uint8_t*>(qkv_);
   // h (the branch output waiting to be added) lives in tmp_; the fp32 running sum in resid_.
   for (int i = 0; i < s.layers; ++i) {
     const LayerW& L = layers_[i];
+    const bool local = s.modernbert && (i % s.global_every != 0);
     NormArgs n1;
     n1.x = tmp_; n1.residual = (i == 0) ? nullptr : resid_; n1.gamma = L.ln1_g; n1.beta = nullptr;
-    n1.out = x_; n1.sum_out = resid_; n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 1; n1.dtype = s.dtype;
-    LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "input RMSNorm");
+    n1.out = x_; n1.sum_out = resid_; n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = rms; n1.dtype = s.dtype;
+    n1.residual_f32 = 1;
+    LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "input norm");
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status), stream_), "qkv projection");
     RopeArgs r;
-    r.q = qkv; r.k = qkv + static_cast<size_t>(Q) * 2; r.pos_ids = d_pos_; r.cos_tab = cos_; r.sin_tab = sin_;
+    r.q = qkv; r.k = qkv + static_cast<size_t>(Q) * 2; r.pos_ids = d_pos_;
+    r.cos_tab = local ? cos_scaled_ : cos_; r.sin_tab = local ? sin_scaled_ : sin_;
     r.q_gamma = L.q_norm; r.k_gamma = L.k_norm; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
     r.head_dim = s.head_dim; r.ld_q = W; r.ld_k = W; r.eps = s.eps; r.dtype = s.dtype;
     LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "q/k RMSNorm + rotary embedding");
     AttnArgs a;
     a.q = qkv; a.k = qkv + static_cast<size_t>(Q) * 2; a.v = qkv + static_cast<size_t>(Q + KV) * 2;
-    a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
+    a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = local ? d_work_local_ : d_work_;
+    a.n_work = static_cast<int>(n_work_);
     a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
     a.ld_q = a.ld_k = a.ld_v = W; a.ld_o = Q; a.causal = s.causal ? 1 : 0;
-    a.window_left = s.window_left;
+    a.window_left = local ? s.local_window : s.window_left;
+    a.window_right = local ? s.local_window : -1;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
     a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, nullptr, tmp_, T, H, Q, Q, H, ACT_NONE, s.dtype, status), stream_), "o projection");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, Q, Q, H, ACT_NONE, s.dtype, status), stream_), "o projection");
     NormArgs n2 = n1;
     n2.x = tmp_; n2.residual = resid_; n2.gamma = L.ln2_g; n2.out = x1_; n2.sum_out = resid_;
-    LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "post-attention RMSNorm");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, nullptr, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gate/up projection");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, nullptr, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "down projection");
+    LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "post-attention norm");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gate/up projection");
+    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "down projection");
   }
   NormArgs nf;
   nf.x = tmp_; nf.residual = resid_; nf.gamma = final_norm_; nf.beta = nullptr; nf.out = x_; nf.sum_out = resid_;
-  nf.T = T; nf.H = H; nf.eps = s.eps; nf.rms = 1; nf.dtype = s.dtype;
-  LAUNCH(KC_NORM, launch_add_norm(nf, stream_), "final RMSNorm");
+  nf.T = T; nf.H = H; nf.eps = s.eps; nf.rms = rms; nf.dtype = s.dtype; nf.residual_f32 = 1;
+  LAUNCH(KC_NORM, launch_add_norm(nf, stream_), "final norm");
   if (projection_) {
     // Optional `linear.weight` projection applied to every token row (flash_qwen3.rs:430-435).
     if (projection_dim_ > H) throw TeiError(ERR_INFERENCE, "projection wider than the hidden size is not supported");
@@ -1124,10 +1240,15 @@ void Replica::pool_and_heads() {
   if (predict_) {
     PoolArgs p;
     p.x = x_; p.cu_seqlens = d_cu_; p.seq_index = d_all_idx_; p.out = d_cls_;
-    p.n_out = static_cast<int>(B_); p.H = H; p.mode = POOL_CLS; p.normalize = 0; p.dtype = s.dtype;
-    LAUNCH(KC_POOL, launch_pool(p, stream_), "CLS pooling");
+    p.n_out = static_cast<int>(B_); p.H = H; p.mode = s.modernbert ? s.cls_pool : POOL_CLS; p.normalize = 0;
+    p.dtype = s.dtype;
+    LAUNCH(KC_POOL, launch_pool(p, stream_), "pooling for the head");
     const float* head_in = d_cls_;
-    if (cls_dense_w_) {  // dense + tanh (RobertaClassificationHead / BERT pooler, bert.rs:405-465)
+    if (s.modernbert) {  // dense (no bias) + activation -> LayerNorm -> classifier, modernbert.rs:443-456
+      LAUNCH(KC_POOL, launch_head_linear(d_cls_, cls_dense_w_, nullptr, d_head_tmp_, static_cast<int>(B_), H, H, s.head_act, s.dtype, stream_), "head dense");
+      LAUNCH(KC_POOL, launch_layernorm_rows_f32(d_head_tmp_, cls_norm_g_, static_cast<int>(B_), H, s.eps, s.dtype, stream_), "head norm");
+      head_in = d_head_tmp_;
+    } else if (cls_dense_w_) {  // dense + tanh (RobertaClassificationHead / BERT pooler, bert.rs:405-465)
       LAUNCH(KC_POOL, launch_head_linear(d_cls_, cls_dense_w_, cls_dense_b_, d_head_tmp_, static_cast<int>(B_), H, H, ACT_TANH, s.dtype, stream_), "classifier dense");
       head_in = d_head_tmp_;
     }

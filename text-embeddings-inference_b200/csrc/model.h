@@ -54,6 +54,14 @@ struct ModelSpec {
   bool causal = false;
   bool qk_norm = false;    // per-head RMSNorm on q and k before RoPE (Qwen3)
   int window_left = -1;    // sliding window of the decoder families (Mistral), -1: none
+  // ModernBERT (models/flash_modernbert.rs): pre-LayerNorm blocks without biases on the norms,
+  // LayerNorm after the embedding, every `global_every`-th layer attends globally with
+  // rope_theta, the others within `local_window` keys on each side with `local_theta`.
+  bool modernbert = false;
+  int global_every = 0, local_window = -1;
+  float local_theta = 0.f;
+  int head_act = 0;        // activation of the classification head's dense layer
+  int cls_pool = POOL_CLS; // pooling in front of the classification head
   bool rope = false;
   float rope_theta = 10000.f;
   float rope_scaling_factor = 0.f;  // NomicBERT dynamic table switch (flash_nomic.rs:244-258)
@@ -164,6 +172,7 @@ class Replica {
   void load_bert(const SafeTensors& st);
   void load_nomic(const SafeTensors& st);
   void load_qwen3(const SafeTensors& st);
+  void load_modernbert(const SafeTensors& st);
   void build_rope_tables();
   void* dev_alloc(size_t bytes);
   // Converts `src` (any float dtype) into the model dtype at dst + dst_elem_off elements.
@@ -208,7 +217,7 @@ class Replica {
   float* alibi_slopes_ = nullptr;  // [heads], fp32 (alibi.rs:18-47)
   // classification heads
   void *cls_dense_w_ = nullptr, *cls_dense_b_ = nullptr, *cls_out_w_ = nullptr,
-       *cls_out_b_ = nullptr;
+       *cls_out_b_ = nullptr, *cls_norm_g_ = nullptr;
   std::vector<DenseW> dense_;
   // SPLADE head
   void *sp_dense_w_ = nullptr, *sp_dense_b_ = nullptr, *sp_ln_g_ = nullptr, *sp_ln_b_ = nullptr,
@@ -241,7 +250,8 @@ class Replica {
   uint32_t max_length_ = 0;
   bool predict_ = false, normalize_ = false;
   int32_t *d_ids_ = nullptr, *d_types_ = nullptr, *d_pos_ = nullptr, *d_cu_ = nullptr,
-          *d_pooled_idx_ = nullptr, *d_raw_rows_ = nullptr, *d_work_ = nullptr, *d_all_idx_ = nullptr;
+          *d_pooled_idx_ = nullptr, *d_raw_rows_ = nullptr, *d_work_ = nullptr, *d_all_idx_ = nullptr,
+          *d_work_local_ = nullptr;  // work list of the layers with the two-sided local window
   size_t out_floats_ = 0;
 };
 

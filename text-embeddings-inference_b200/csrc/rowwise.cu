@@ -176,7 +176,9 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
 // RMSNorm:   sum = x + residual, out = sum * rsqrt(mean(sum^2) + eps) * gamma
 //            (layers/rms_norm.rs:30-57); the running sum is kept in fp32 so that rounding does
 //            not pile up over the decoder's layers.
-template <class T, int MAXC, bool RMS>
+// F32RES: the residual is fp32 and the sum is written back in fp32 (the pre-norm models: RMSNorm
+// decoders, and ModernBERT with LayerNorm).  gamma == nullptr: no normalisation, out = sum.
+template <class T, int MAXC, bool RMS, bool F32RES>
 __global__ void __launch_bounds__(256, (MAXC <= 3 ? 6 : 1))
 add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restrict__ gamma,
                 const T* __restrict__ beta, T* __restrict__ out, float* sum_out, int T_, int H,
@@ -193,7 +195,7 @@ add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restri
     if (ch < n_chunks) {
       unpack8<T>(ld16(xr + ch * 8), v[c]);
       if (residual) {
-        if (RMS) {
+        if (F32RES) {
           const float* rr = reinterpret_cast<const float*>(residual) + static_cast<size_t>(row) * H;
           const float4 r0 = *reinterpret_cast<const float4*>(rr + ch * 8);
           const float4 r1 = *reinterpret_cast<const float4*>(rr + ch * 8 + 4);
@@ -207,20 +209,38 @@ add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restri
           for (int i = 0; i < 8; ++i) v[c][i] += a[i];
         }
       }
-      if (RMS && sum_out) {
+      if (F32RES && sum_out) {
         float* so = sum_out + static_cast<size_t>(row) * H + ch * 8;
         *reinterpret_cast<float4*>(so) = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
         *reinterpret_cast<float4*>(so + 4) = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
       }
     }
   }
-  normalise_row<T, MAXC, RMS>(v, n_chunks, lane, H, eps, gamma, beta);
+  if (gamma) normalise_row<T, MAXC, RMS>(v, n_chunks, lane, H, eps, gamma, beta);
   T* o = out + static_cast<size_t>(row) * H;
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     const int ch = lane + c * 32;
     if (ch < n_chunks) *reinterpret_cast<uint4*>(o + ch * 8) = pack8<T>(v[c]);
   }
+}
+
+// LayerNorm without bias over fp32 rows, in place (the classification head of ModernBERT,
+// backends/candle/src/models/modernbert.rs:443-456, runs on the few pooled rows).
+template <class T>
+__global__ void __launch_bounds__(256) layernorm_rows_f32_kernel(float* __restrict__ x, const T* __restrict__ gamma,
+                                                                 int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float* r = x + static_cast<size_t>(row) * H;
+  float s = 0.f;
+  for (int j = lane; j < H; j += 32) s += r[j];
+  const float mean = warp_sum(s) / static_cast<float>(H);
+  float q = 0.f;
+  for (int j = lane; j < H; j += 32) q += (r[j] - mean) * (r[j] - mean);
+  const float rstd = rsqrtf(warp_sum(q) / static_cast<float>(H) + eps);
+  for (int j = lane; j < H; j += 32) r[j] = (r[j] - mean) * rstd * ldf<T>(gamma[j]);
 }
 
 // ------------------------------------------------------------------ per-head RMSNorm + RoPE
@@ -503,13 +523,13 @@ int embed_typed(const EmbedArgs& e, cudaStream_t st) {
   return last_error();
 }
 
-template <class T, bool RMS>
+template <class T, bool RMS, bool F32RES>
 int norm_typed(const NormArgs& n, cudaStream_t st) {
   const int warps = 8;
   const int grid = (n.T + warps - 1) / warps;
   const int n_chunks = n.H / 8;
 #define TEI_NORM(MAXC)                                                                           \
-  add_norm_kernel<T, MAXC, RMS><<<grid, warps * 32, 0, st>>>(                                    \
+  add_norm_kernel<T, MAXC, RMS, F32RES><<<grid, warps * 32, 0, st>>>(                                    \
       reinterpret_cast<const T*>(n.x), n.residual, reinterpret_cast<const T*>(n.gamma),          \
       reinterpret_cast<const T*>(n.beta), reinterpret_cast<T*>(n.out),                           \
       reinterpret_cast<float*>(n.sum_out), n.T, n.H, n.eps)
@@ -532,10 +552,28 @@ int launch_embed_layernorm(const EmbedArgs& e, cudaStream_t st) {
 int launch_add_norm(const NormArgs& n, cudaStream_t st) {
   if (n.T <= 0) return 0;
   if (n.H % 8 != 0 || n.H > 4096) return static_cast<int>(cudaErrorInvalidValue);
+  const bool f32res = n.residual_f32 < 0 ? n.rms != 0 : n.residual_f32 != 0;
+  if (n.rms && !f32res) return static_cast<int>(cudaErrorInvalidValue);
   if (n.dtype == DT_F16) {
-    return n.rms ? norm_typed<__half, true>(n, st) : norm_typed<__half, false>(n, st);
+    if (n.rms) return norm_typed<__half, true, true>(n, st);
+    return f32res ? norm_typed<__half, false, true>(n, st) : norm_typed<__half, false, false>(n, st);
   }
-  return n.rms ? norm_typed<__nv_bfloat16, true>(n, st) : norm_typed<__nv_bfloat16, false>(n, st);
+  if (n.rms) return norm_typed<__nv_bfloat16, true, true>(n, st);
+  return f32res ? norm_typed<__nv_bfloat16, false, true>(n, st) : norm_typed<__nv_bfloat16, false, false>(n, st);
+}
+
+int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, float eps, int dtype,
+                              cudaStream_t st) {
+  if (rows <= 0) return 0;
+  const int warps = 8;
+  const int grid = (rows + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    layernorm_rows_f32_kernel<__half><<<grid, warps * 32, 0, st>>>(x, reinterpret_cast<const __half*>(gamma), rows, H, eps);
+  } else {
+    layernorm_rows_f32_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+        x, reinterpret_cast<const __nv_bfloat16*>(gamma), rows, H, eps);
+  }
+  return last_error();
 }
 
 int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
