@@ -91,3 +91,56 @@ def test_cfg5_qwen3_last_token(lib, tmp_path, dtype, cos_min):
     assert _cos(got, ref).min() >= cos_min
     assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
     be.close()
+
+
+def test_mistral_7b_width_two_layers(lib, tmp_path):
+    # e5-mistral-7b-instruct dimensions (hidden 4096, 32/8 heads x 128, FFN 14336, sliding
+    # window 4096) cut to two layers and a 32k-row embedding table; last-token pooling.
+    import tei_b200
+    cfg = G.mistral_config(layers=2, vocab=32000, sliding_window=256)  # window active at these lengths
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=21, store_dtype="float16")
+    rng = np.random.default_rng(61)
+    lens = [5, 300, 777]
+    sub = G.batch_from_encodings([rng.integers(0, 32000, size=n) for n in lens], list(range(len(lens))), [])
+    be = tei_b200.B200Backend(d, "float16", "embedding", "last_token")
+    ref = M.build_oracle(d, "embedding", "last_token").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert got.shape == (3, 4096) and np.isfinite(got).all()
+    assert _cos(got, ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()
+
+
+def test_qwen2_1p5b_width_two_layers(lib, tmp_path):
+    # gte-Qwen2-1.5B dimensions (hidden 1536, 12/2 heads x 128, FFN 8960, q/k/v biases),
+    # bidirectional as that checkpoint is, two layers, 32k-row embedding table.
+    import tei_b200
+    cfg = G.qwen2_config(layers=2, vocab=32000, is_causal=False)
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=22, store_dtype="float16")
+    rng = np.random.default_rng(62)
+    lens = [64, 129, 1000]
+    sub = G.batch_from_encodings([rng.integers(0, 32000, size=n) for n in lens], list(range(len(lens))), [])
+    be = tei_b200.B200Backend(d, "float16", "embedding", "last_token")
+    ref = M.build_oracle(d, "embedding", "last_token").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert got.shape == (3, 1536)
+    assert _cos(got, ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()
+
+
+def test_modernbert_base_width(lib, tmp_path):
+    # ModernBERT-base dimensions (22 x 768, 12 heads x 64, FFN 1152, local window 128 on two of
+    # every three layers), 32k-row embedding table, mean pooling.
+    import tei_b200
+    cfg = G.modernbert_config(vocab=32000)
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=23, store_dtype="float16")
+    rng = np.random.default_rng(63)
+    lens = [40, 200, 900]
+    sub = G.batch_from_encodings([rng.integers(0, 32000, size=n) for n in lens], list(range(len(lens))), [])
+    be = tei_b200.B200Backend(d, "float16", "embedding", "mean")
+    ref = M.build_oracle(d, "embedding", "mean").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert _cos(got, ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()
