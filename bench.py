@@ -416,6 +416,38 @@ def run_config(args):
     be.close()
 
 
+def run_in_handle(args):
+    """`--handle-devices N`: the drop-in mode behind an unchanged router, which keeps one batch in
+    flight: ONE process, ONE handle with a replica on each of N GPUs; every `embed` call splits the
+    packed cfg2 batch at sequence boundaries, runs the shards concurrently and scatters the rows
+    back.  Wall-clock end to end (host buffers in and out), since the call spans several devices."""
+    import torch
+    import tei_b200
+    from oracle import generators as G
+
+    n = args.handle_devices
+    if torch.cuda.device_count() < n:
+        raise SystemExit(f"--handle-devices {n} needs {n} visible GPUs")
+    model_dir = ensure_model_dir(0)
+    be = tei_b200.B200Backend(model_dir, "float16", "embedding", "mean", devices=list(range(n)))
+    batch = G.batch_cfg2()
+    tokens = int(batch.cumulative_seq_lengths[-1])
+    for _ in range(max(args.warmup, 3)):
+        be.embed(batch, normalize=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        be.embed(batch, normalize=True)
+    dt = time.perf_counter() - t0
+    print(json.dumps({
+        "metric": "tokens_per_sec", "value": tokens * args.steps / dt, "unit": "tokens/s", "n_gpus": n,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"one handle, batch split over {n} replicas inside each call",
+                   "timing": "wall clock around embed() with host buffers"},
+    }), flush=True)
+    be.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -430,9 +462,14 @@ def main():
                     help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
     ap.add_argument("--dtype", default=None, choices=["float16", "bfloat16"],
                     help="only with --config cfg1/3/4/5 (cfg5 defaults to bfloat16)")
+    ap.add_argument("--handle-devices", type=int, default=0,
+                    help="one process, one handle with this many replicas: each embed() call splits the batch")
     args = ap.parse_args()
     if args.kernel:
         run_kernel(args)
+        return
+    if args.handle_devices > 0:
+        run_in_handle(args)
         return
     if args.config != "cfg2" and args.impl == "b200":
         run_config(args)

@@ -54,7 +54,18 @@ def jina_config(alibi: bool = True, **kw) -> dict:
 
 
 def nomic_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30528, n_positions=2048,
-                 rotary_base=1000.0, eps=1e-12) -> dict:
+                 rotary_base=1000.0, eps=1e-12, moe_every: int = 0, num_experts: int = 8, moe_top_k: int = 2) -> dict:
+    """moe_every > 0: the mixture-of-experts variant (nomic-embed-text-v2-moe style: GELU
+    feed-forwards, every moe_every-th layer (index % moe_every == 1) routed; nomic.rs:402-414)."""
+    c = _nomic_dense_config(hidden, layers, heads, inter, vocab, n_positions, rotary_base, eps)
+    if moe_every > 0:
+        c.update({"activation_function": "gelu", "mlp_fc1_bias": True, "mlp_fc2_bias": True, "qkv_proj_bias": True,
+                  "moe_every_n_layers": moe_every, "num_experts": num_experts, "moe_top_k": moe_top_k,
+                  "moe_normalize_expert_weights": False})
+    return c
+
+
+def _nomic_dense_config(hidden, layers, heads, inter, vocab, n_positions, rotary_base, eps) -> dict:
     return {
         "architectures": ["NomicBertModel"], "model_type": "nomic_bert", "prenorm": False,
         "rotary_emb_fraction": 1.0, "qkv_proj_bias": False, "rotary_emb_base": rotary_base,
@@ -220,9 +231,27 @@ def _nomic_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
         p = f"encoder.layers.{i}."
         t[p + "attn.Wqkv.weight"] = ((3 * H, H), "normal")
         t[p + "attn.out_proj.weight"] = ((H, H), "normal")
-        t[p + "mlp.fc11.weight"] = ((I, H), "normal")
-        t[p + "mlp.fc12.weight"] = ((I, H), "normal")
-        t[p + "mlp.fc2.weight"] = ((H, I), "normal")
+        if c["qkv_proj_bias"]:
+            t[p + "attn.Wqkv.bias"] = ((3 * H,), "normal")
+            t[p + "attn.out_proj.bias"] = ((H,), "normal")
+        moe_every = c.get("moe_every_n_layers") or 0
+        if moe_every > 0 and i % moe_every == 1:  # nomic.rs:213-219,255-262,289-294
+            E = c["num_experts"]
+            t[p + "mlp.router.layer.weight"] = ((E, H), "normal")
+            t[p + "mlp.experts.mlp.w1"] = ((E * I, H), "normal")
+            t[p + "mlp.experts.mlp.w2"] = ((E * I, H), "normal")
+            t[p + "mlp.experts.bias"] = ((H,), "normal")
+        elif c["activation_function"] == "swiglu":
+            t[p + "mlp.fc11.weight"] = ((I, H), "normal")
+            t[p + "mlp.fc12.weight"] = ((I, H), "normal")
+            t[p + "mlp.fc2.weight"] = ((H, I), "normal")
+        else:
+            t[p + "mlp.fc1.weight"] = ((I, H), "normal")
+            t[p + "mlp.fc2.weight"] = ((H, I), "normal")
+            if c["mlp_fc1_bias"]:
+                t[p + "mlp.fc1.bias"] = ((I,), "normal")
+            if c["mlp_fc2_bias"]:
+                t[p + "mlp.fc2.bias"] = ((H,), "normal")
         for n in ("norm1", "norm2"):
             t[p + n + ".weight"] = ((H,), "ones")
             t[p + n + ".bias"] = ((H,), "zeros")

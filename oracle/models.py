@@ -437,7 +437,10 @@ class NomicOracle:
                        w.get(p + "attn.out_proj.bias") if c["qkv_proj_bias"] else None)
             g1, b1 = w.ln(p + "norm1")
             x1 = layer_norm(x, a, g1, b1, self.eps)
-            if self.act_name == "swiglu":
+            moe_every = c.get("moe_every_n_layers") or 0
+            if moe_every > 0 and i % moe_every == 1:
+                m = self.moe(x1, p + "mlp.")
+            elif self.act_name == "swiglu":
                 # fc1 = cat[fc12; fc11]; swiglu = silu(first half) * second half (nomic.rs:115-121)
                 gate = linear(x1, w.get(p + "mlp.fc12.weight"), w.get(p + "mlp.fc12.bias") if c["mlp_fc1_bias"] else None)
                 up = linear(x1, w.get(p + "mlp.fc11.weight"), w.get(p + "mlp.fc11.bias") if c["mlp_fc1_bias"] else None)
@@ -445,10 +448,32 @@ class NomicOracle:
             else:
                 m = activation(self.act_name)(linear(x1, w.get(p + "mlp.fc1.weight"),
                                                      w.get(p + "mlp.fc1.bias") if c["mlp_fc1_bias"] else None))
-            m = linear(m, w.get(p + "mlp.fc2.weight"), w.get(p + "mlp.fc2.bias") if c["mlp_fc2_bias"] else None)
+            if not (moe_every > 0 and i % moe_every == 1):
+                m = linear(m, w.get(p + "mlp.fc2.weight"), w.get(p + "mlp.fc2.bias") if c["mlp_fc2_bias"] else None)
             g2, b2 = w.ln(p + "norm2")
             x = layer_norm(x1, m, g2, b2, self.eps)
         return x
+
+    def moe(self, x: Tensor, p: str) -> Tensor:
+        """NomicMoELayer (models/nomic.rs:205-394): router logits -> fp32 softmax -> the top-k
+        probabilities as they are (no renormalisation) `:229-243`; expert e computes
+        act(x w1_e^T) w2_e with w1, w2 stored as [E * I, H] `:255-276`; the weighted expert outputs
+        are summed per token and the shared bias is added `:325-355`."""
+        w, c = self.w, self.cfg
+        E, k, I = c["num_experts"], c["moe_top_k"], c["n_inner"]
+        probs = torch.softmax(linear(x, w.get(p + "router.layer.weight")).float(), dim=-1)
+        top_w, top_e = probs.topk(k, dim=-1)
+        w1 = w.get(p + "experts.mlp.w1").view(E, I, self.hidden)
+        w2 = w.get(p + "experts.mlp.w2").view(E, I, self.hidden)
+        act = activation(self.act_name)
+        out = torch.zeros_like(x)
+        for e in range(E):
+            tok, slot = (top_e == e).nonzero(as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            y = act(x[tok] @ w1[e].t()) @ w2[e]
+            out.index_add_(0, tok, y * top_w[tok, slot].unsqueeze(-1))
+        return out + w.get(p + "experts.bias")
 
     def embed(self, batch: Batch):
         return pool_outputs(self.hidden_states(batch), batch, self.pool)

@@ -144,3 +144,25 @@ def test_modernbert_base_width(lib, tmp_path):
     assert _cos(got, ref).min() >= 0.9999
     assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
     be.close()
+
+
+def test_nomic_moe_full_width(lib, tmp_path):
+    # nomic-embed-text-v2-moe dimensions: 12 x 768, GELU feed-forwards of 3072, every second layer
+    # routed to 2 of 8 experts; 32k-row embedding table.  A token whose two best experts are
+    # nearly tied may be routed differently in fp16 than in the fp32 oracle, so the bar is on
+    # the mean-pooled rows, as everywhere.
+    import tei_b200
+    cfg = G.nomic_config(vocab=32000, moe_every=2, num_experts=8, moe_top_k=2)
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=24, store_dtype="float16")
+    rng = np.random.default_rng(64)
+    lens = [40, 300, 1100]
+    sub = G.batch_from_encodings([rng.integers(0, 32000, size=n) for n in lens], list(range(len(lens))), [])
+    be = tei_b200.B200Backend(d, "float16", "embedding", "mean")
+    ref = M.build_oracle(d, "embedding", "mean").embed(sub)[0].numpy()
+    got = _pooled(be.embed(sub), len(sub))
+    assert np.isfinite(got).all()
+    assert _cos(got, ref).min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    # run twice: the rows do not depend on the order in which tokens reached their experts
+    assert np.array_equal(got, _pooled(be.embed(sub), len(sub)))
+    be.close()

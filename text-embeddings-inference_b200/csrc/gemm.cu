@@ -50,7 +50,13 @@ struct GemmParams {
   int ldo, ldr;
   int tma_store;  // 1: outputs leave through the TMA store path
   int* status;
+  const int* m_dev;  // optional device-side row count (see GemmArgs::m_dev)
 };
+
+// Rows the kernel works on.
+__device__ __forceinline__ int effective_rows(const GemmParams& p) {
+  return p.m_dev ? min(p.M, *p.m_dev) : p.M;
+}
 
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
@@ -188,6 +194,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
                                               uint32_t& store_count, int n_out, int part = 0,
                                               int n_parts = 1) {  // part: this warp's share of the columns
   const int row = m0 + quad * 32 + lane;
+  const int m_rows = effective_rows(p);
   if (p.tma_store) {
     // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
     constexpr int STEPS = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? 2 : 4;
@@ -271,7 +278,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
       if (lane == 0) {
         // A box that starts beyond the last row has nothing to write (the tensor map would clip
         // it anyway); the empty group keeps the wait_group accounting uniform.
-        if (m0 + quad * 32 < p.M) ptx::tma_store_2d(tm_c, buf, ocol, m0 + quad * 32);
+        if (m0 + quad * 32 < m_rows) ptx::tma_store_2d(tm_c, buf, ocol, m0 + quad * 32);
         ptx::tma_store_commit();
       }
       ++store_count;
@@ -298,7 +305,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         v[j] = glu_gate<ACT>(gv) * uv;
       }
       const int n_valid = min(32, p.N / 2 - ocol);
-      if (row < p.M && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
+      if (row < m_rows && n_valid > 0) finish_and_store<T, ACT>(v, p, row, ocol, n_valid, vec_ok);
     }
   } else {
 #pragma unroll 1
@@ -316,7 +323,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
         if (bias && j < n_valid) x += to_f32<T>(bias[col + j]);
         v[j] = apply_act<ACT>(x);
       }
-      if (row < p.M) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
+      if (row < m_rows) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
     }
   }
 }
@@ -340,7 +347,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = (effective_rows(p) + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -518,7 +525,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_m = (effective_rows(p) + 2 * BM - 1) / (2 * BM);
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -701,6 +708,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   p.residual = g.residual;
   p.out = g.out;
   p.M = g.M;
+  p.m_dev = g.m_dev;
   p.N = g.N;
   p.K = g.K;
   p.ldo = g.ldo;

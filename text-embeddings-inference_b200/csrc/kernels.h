@@ -45,6 +45,10 @@ struct GemmArgs {
   int act;
   int dtype;
   int* status;          // device int, stays 0 unless a wait ran out
+  // Optional device int: the kernel works on min(M, *m_dev) rows.  M then is the capacity of the
+  // buffers (what the tensor maps cover); the row count is only known on the device, as for the
+  // tokens routed to one expert of a mixture-of-experts layer.
+  const int* m_dev = nullptr;
 };
 
 // out = act(a @ w^T + bias) (+ residual).  tcgen05 + TMEM + TMA, persistent over 128x256 tiles.
@@ -154,6 +158,23 @@ int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int 
 // Small dense head on pooled fp32 rows: out[r, n] = act(sum_k in[r,k] * w[n,k] + b[n]).
 int launch_head_linear(const float* in, const void* w, const void* b, float* out, int rows, int N,
                        int K, int act, int dtype, cudaStream_t stream);
+
+// Mixture-of-experts feed-forward of NomicBERT (backends/candle/src/models/nomic.rs:205-394),
+// without a host round trip: the router's logits stay on the device, every expert gets a
+// fixed-capacity segment of `cap` rows in the gathered buffers, and the expert GEMMs read their
+// row count from `counts` (GemmArgs::m_dev).
+//   route:   fp32 softmax over the E logits of a token, the k largest probabilities (ties: the
+//            lower expert index), rounded to the model dtype as the reference does; for each
+//            pick the expert, the weight and the row it takes in that expert's segment.
+//   gather:  xg[(e * cap + pos) * H ..] = x[t] for every (token, pick).
+//   combine: out[t] = sum over the picks of w * yg[e * cap + pos] + bias, accumulated in fp32.
+int launch_moe_route(const void* logits, int ld_logits, int T, int E, int k, int* topk_e, float* topk_w,
+                     int* pos, int* counts, int dtype, cudaStream_t stream);
+int launch_moe_gather(const void* x, const int* topk_e, const int* pos, void* xg, int T, int k, int H,
+                      long long cap, int dtype, cudaStream_t stream);
+int launch_moe_combine(const void* yg, const int* topk_e, const float* topk_w, const int* pos,
+                       const void* bias, void* out, int T, int k, int H, long long cap, int dtype,
+                       cudaStream_t stream);
 
 // Element-wise dtype conversion used at weight-load time.  src_kind: 0 fp32, 1 fp16, 2 bf16;
 // dst dtype: DT_F16 / DT_BF16, or 2 for fp32.

@@ -122,8 +122,13 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     if (prenorm || frac != 1.0 || interleaved || s.type_vocab <= 0) {
       throw TeiError(ERR_START, "config is not supported");  // NomicConfig::valid(), nomic.rs:49-54
     }
-    if (c.get_int("num_experts", 0) > 1 || c.get_int("moe_every_n_layers", 0) > 0) {
-      throw TeiError(ERR_START, "NomicBERT mixture-of-experts checkpoints are outside this backend");
+    s.moe_every = static_cast<int>(c.get_int("moe_every_n_layers", 0));
+    if (s.moe_every > 0) {  // NomicRouter::load unwraps both (nomic.rs:213-215)
+      s.num_experts = static_cast<int>(need_int(c, "num_experts"));
+      s.moe_top_k = static_cast<int>(need_int(c, "moe_top_k"));
+      if (s.num_experts < 1 || s.num_experts > 64 || s.moe_top_k < 1 || s.moe_top_k > 8 || s.moe_top_k > s.num_experts) {
+        throw TeiError(ERR_START, "mixture of experts: up to 64 experts and a top-k of up to 8 are supported");
+      }
     }
     s.vocab = static_cast<int>(need_int(c, "vocab_size"));
     s.hidden = static_cast<int>(need_int(c, "n_embd"));
@@ -701,6 +706,45 @@ void Replica::load_nomic(const SafeTensors& st) {
     expect_shape(n.get(p + "attn.out_proj.weight"), {H, H}, p + "attn.out_proj.weight");
     L.wo = upload_new(n.get(p + "attn.out_proj.weight"));
     if (s.out_bias) L.bo = upload_new(n.get(p + "attn.out_proj.bias"));
+    if (s.moe_every > 0 && i % s.moe_every == 1) {
+      // NomicMoELayer (nomic.rs:205-296): router.layer.weight [E, H] (rows padded to a multiple
+      // of 8 for the logits' row stride), experts.mlp.w1 / w2 [E * I, H], experts.bias [H].  w2
+      // is used as h [n, I] x w2_e [I, H] (`:268-275`), so each expert's block is transposed
+      // once here to the [N, K] form the GEMM takes.
+      const int E = s.num_experts, Epad = static_cast<int>(align_up(static_cast<size_t>(E), 8));
+      const StTensor& rw = n.get(p + "mlp.router.layer.weight");
+      expect_shape(rw, {E, H}, p + "mlp.router.layer.weight");
+      L.moe_router = dev_alloc(static_cast<size_t>(Epad) * H * 2);
+      TEI_CUDA(cudaMemsetAsync(L.moe_router, 0, static_cast<size_t>(Epad) * H * 2, stream_));
+      upload(L.moe_router, 0, rw);
+      const StTensor& w1 = n.get(p + "mlp.experts.mlp.w1");
+      const StTensor& w2 = n.get(p + "mlp.experts.mlp.w2");
+      expect_shape(w1, {static_cast<int64_t>(E) * I, H}, p + "mlp.experts.mlp.w1");
+      expect_shape(w2, {static_cast<int64_t>(E) * I, H}, p + "mlp.experts.mlp.w2");
+      L.moe_w1 = upload_new(w1);
+      const size_t es = w2.nbytes / static_cast<size_t>(w2.numel());
+      std::vector<uint8_t> tr(w2.nbytes);
+      for (int e = 0; e < E; ++e) {
+        const uint8_t* src = w2.data + static_cast<size_t>(e) * I * H * es;
+        uint8_t* dst = tr.data() + static_cast<size_t>(e) * I * H * es;
+        for (int r = 0; r < I; ++r) {
+          for (int cidx = 0; cidx < H; ++cidx) {
+            std::memcpy(dst + (static_cast<size_t>(cidx) * I + r) * es, src + (static_cast<size_t>(r) * H + cidx) * es, es);
+          }
+        }
+      }
+      StTensor w2t = w2;
+      w2t.data = tr.data();
+      w2t.shape = {static_cast<int64_t>(E) * H, I};
+      L.moe_w2t = upload_new(w2t);
+      TEI_CUDA(cudaStreamSynchronize(stream_));  // `tr` goes out of scope
+      L.moe_bias = upload_new(n.get(p + "mlp.experts.bias"));
+      L.ln1_g = upload_new(n.ln_w(p + "norm1"));
+      L.ln1_b = upload_new(n.ln_b(p + "norm1"));
+      L.ln2_g = upload_new(n.ln_w(p + "norm2"));
+      L.ln2_b = upload_new(n.ln_b(p + "norm2"));
+      continue;
+    }
     if (s.gated) {
       // fc1 = cat[fc12; fc11] and swiglu = silu(first half) * second half (nomic.rs:109-121):
       // fc12 is the gate, fc11 the up projection.
@@ -918,7 +962,16 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
   const size_t sz_res = s.arch == ARCH_QWEN3 ? align_up(cap * H * 4, 1024) : 0;
   const size_t vpad = align_up(static_cast<size_t>(s.vocab), 8);
   const size_t sz_spl = s.pool == POOL_SPLADE ? align_up(cap * vpad * 2, 1024) : 0;
-  const size_t total = 3 * sz_h + sz_qkv + sz_attn + sz_ffn + sz_res + sz_spl;
+  // mixture of experts: every expert owns `cap` rows of the gathered buffers (a token goes to an
+  // expert at most once, so cap rows always suffice)
+  const size_t E = static_cast<size_t>(s.num_experts), topk = static_cast<size_t>(s.moe_top_k);
+  const bool moe = s.moe_every > 0;
+  const size_t sz_xg = moe ? align_up(E * cap * H * 2, 1024) : 0;
+  const size_t sz_hg = moe ? align_up(E * cap * static_cast<size_t>(s.inter) * 2, 1024) : 0;
+  const size_t sz_lg = moe ? align_up(cap * align_up(E, 8) * 2, 1024) : 0;
+  const size_t sz_tk = moe ? align_up(cap * topk * 4, 1024) : 0;
+  const size_t total = 3 * sz_h + sz_qkv + sz_attn + sz_ffn + sz_res + sz_spl + 2 * sz_xg + sz_hg + sz_lg +
+                       3 * sz_tk + (moe ? 1024 : 0);
   TEI_CUDA(cudaMalloc(&arena_, total));
   arena_bytes_ = total;
   uint8_t* p = static_cast<uint8_t*>(arena_);
@@ -931,6 +984,17 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
   resid_ = sz_res ? reinterpret_cast<float*>(p) : nullptr; p += sz_res;
   splade_ = sz_spl ? p : nullptr; p += sz_spl;
   if (sz_spl) TEI_CUDA(cudaMemsetAsync(splade_, 0, sz_spl, stream_));
+  if (moe) {
+    moe_xg_ = p; p += sz_xg;
+    moe_yg_ = p; p += sz_xg;
+    moe_hg_ = p; p += sz_hg;
+    moe_logits_ = p; p += sz_lg;
+    moe_topk_e_ = reinterpret_cast<int*>(p); p += sz_tk;
+    moe_pos_ = reinterpret_cast<int*>(p); p += sz_tk;
+    moe_topk_w_ = reinterpret_cast<float*>(p); p += sz_tk;
+    moe_counts_ = reinterpret_cast<int*>(p); p += 1024;
+    moe_cap_ = cap;
+  }
   cap_tokens_ = cap;
 }
 
@@ -1158,12 +1222,39 @@ void Replica::forward_nomic() {
     n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
     n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "norm1");
-    if (s.gated) {
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gated fc1");
+    if (L.moe_router) {
+      // NomicMoELayer::forward (nomic.rs:384-393): router logits -> fp32 softmax -> top-k; every
+      // expert runs act(x w1_e^T) w2_e on the tokens routed to it; the outputs are summed with
+      // the routing weights and the shared bias.  No host round trip: the expert GEMMs take
+      // their row count from the device.
+      const int E = s.num_experts, K = s.moe_top_k, Epad = static_cast<int>(align_up(static_cast<size_t>(E), 8));
+      const long long cap = static_cast<long long>(moe_cap_);
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.moe_router, nullptr, moe_logits_, T, Epad, H, H, Epad, ACT_NONE, s.dtype, status), stream_), "router");
+      TEI_CUDA(cudaMemsetAsync(moe_counts_, 0, static_cast<size_t>(E) * 4, stream_));
+      LAUNCH(KC_POOL, launch_moe_route(moe_logits_, Epad, T, E, K, moe_topk_e_, moe_topk_w_, moe_pos_, moe_counts_, s.dtype, stream_), "expert routing");
+      LAUNCH(KC_POOL, launch_moe_gather(x1_, moe_topk_e_, moe_pos_, moe_xg_, T, K, H, cap, s.dtype, stream_), "expert gather");
+      for (int e = 0; e < E; ++e) {
+        uint8_t* xg = static_cast<uint8_t*>(moe_xg_) + static_cast<size_t>(e) * cap * H * 2;
+        uint8_t* hg = static_cast<uint8_t*>(moe_hg_) + static_cast<size_t>(e) * cap * I * 2;
+        uint8_t* yg = static_cast<uint8_t*>(moe_yg_) + static_cast<size_t>(e) * cap * H * 2;
+        const uint8_t* w1 = static_cast<const uint8_t*>(L.moe_w1) + static_cast<size_t>(e) * I * H * 2;
+        const uint8_t* w2 = static_cast<const uint8_t*>(L.moe_w2t) + static_cast<size_t>(e) * H * I * 2;
+        GemmArgs g1 = gemm_args(xg, w1, nullptr, hg, static_cast<int>(cap), I, H, H, I, s.act, s.dtype, status);
+        g1.m_dev = moe_counts_ + e;
+        LAUNCH(KC_GEMM, launch_gemm(g1, stream_), "expert fc1");
+        GemmArgs g2 = gemm_args(hg, w2, nullptr, yg, static_cast<int>(cap), H, I, I, H, ACT_NONE, s.dtype, status);
+        g2.m_dev = moe_counts_ + e;
+        LAUNCH(KC_GEMM, launch_gemm(g2, stream_), "expert fc2");
+      }
+      LAUNCH(KC_POOL, launch_moe_combine(moe_yg_, moe_topk_e_, moe_topk_w_, moe_pos_, L.moe_bias, tmp_, T, K, H, cap, s.dtype, stream_), "expert combine");
     } else {
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
+      if (s.gated) {
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gated fc1");
+      } else {
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
+      }
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
     }
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
     NormArgs n2 = n1;
     n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
     LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "norm2");

@@ -57,6 +57,9 @@ struct ModelSpec {
   // ModernBERT (models/flash_modernbert.rs): pre-LayerNorm blocks without biases on the norms,
   // LayerNorm after the embedding, every `global_every`-th layer attends globally with
   // rope_theta, the others within `local_window` keys on each side with `local_theta`.
+  // NomicBERT mixture of experts (models/nomic.rs:205-421): layers with index % moe_every == 1
+  // route every token to moe_top_k of num_experts feed-forwards.
+  int moe_every = 0, num_experts = 0, moe_top_k = 0;
   bool modernbert = false;
   int global_every = 0, local_window = -1;
   float local_theta = 0.f;
@@ -159,6 +162,9 @@ class Replica {
     void *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
     void *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr;
     void *q_norm = nullptr, *k_norm = nullptr;
+    // mixture-of-experts layers: router [E_pad, H], w1 [E*I, H], w2 transposed per expert
+    // [E*H, I], bias [H]
+    void *moe_router = nullptr, *moe_w1 = nullptr, *moe_w2t = nullptr, *moe_bias = nullptr;
   };
 
   struct DenseW {
@@ -237,6 +243,11 @@ class Replica {
   void *x_ = nullptr, *x1_ = nullptr, *qkv_ = nullptr, *attn_ = nullptr, *tmp_ = nullptr,
        *ffn_ = nullptr;
   float* resid_ = nullptr;
+  // mixture-of-experts scratch: gathered inputs / hidden / outputs with `moe_cap_` rows per expert
+  void *moe_xg_ = nullptr, *moe_hg_ = nullptr, *moe_yg_ = nullptr, *moe_logits_ = nullptr;
+  int *moe_topk_e_ = nullptr, *moe_pos_ = nullptr, *moe_counts_ = nullptr;
+  float* moe_topk_w_ = nullptr;
+  size_t moe_cap_ = 0;
   void* splade_ = nullptr;
   float* d_out_ = nullptr;      // status word (as int) | pooled | raw | scores
   float* h_out_ = nullptr;      // pinned mirror

@@ -478,6 +478,85 @@ head_linear_kernel(const float* __restrict__ in, const T* __restrict__ w, const 
   }
 }
 
+// ------------------------------------------------------------------ mixture of experts
+constexpr int kMoeMaxExperts = 64, kMoeMaxTopK = 8;
+
+template <class T>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T* __restrict__ logits, int ld, int T_, int E, int k, int* __restrict__ topk_e,
+                 float* __restrict__ topk_w, int* __restrict__ pos, int* __restrict__ counts) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T_) return;
+  float pr[kMoeMaxExperts];
+  float mx = -INFINITY;
+  for (int e = 0; e < E; ++e) {
+    pr[e] = ldf<T>(logits[static_cast<size_t>(t) * ld + e]);
+    mx = fmaxf(mx, pr[e]);
+  }
+  float sum = 0.f;
+  for (int e = 0; e < E; ++e) {
+    pr[e] = expf(pr[e] - mx);
+    sum += pr[e];
+  }
+  const float inv = 1.0f / sum;
+  for (int s = 0; s < k; ++s) {
+    int best = 0;
+    float bv = -1.f;
+    for (int e = 0; e < E; ++e) {
+      if (pr[e] > bv) {
+        bv = pr[e];
+        best = e;
+      }
+    }
+    pr[best] = -2.f;  // taken
+    topk_e[t * k + s] = best;
+    topk_w[t * k + s] = ldf<T>(stf<T>(bv * inv));  // the reference casts the weights to the model dtype
+    pos[t * k + s] = atomicAdd(&counts[best], 1);
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ topk_e, const int* __restrict__ pos,
+                  T* __restrict__ xg, int n_picks, int k, int H, long long cap) {
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_picks) return;
+  const T* src = x + static_cast<size_t>(w / k) * H;
+  T* dst = xg + (static_cast<size_t>(topk_e[w]) * cap + pos[w]) * H;
+  for (int ch = lane; ch < (H >> 3); ch += 32) {
+    *reinterpret_cast<uint4*>(dst + ch * 8) = ld16(src + ch * 8);
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const T* __restrict__ yg, const int* __restrict__ topk_e, const float* __restrict__ topk_w,
+                   const int* __restrict__ pos, const T* __restrict__ bias, T* __restrict__ out, int T_,
+                   int k, int H, long long cap) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T_) return;
+  for (int ch = lane; ch < (H >> 3); ch += 32) {
+    float acc[8];
+    if (bias) {
+      unpack8<T>(ld16(bias + ch * 8), acc);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    }
+    for (int s = 0; s < k; ++s) {
+      const int p = t * k + s;
+      float v[8];
+      unpack8<T>(ld16(yg + (static_cast<size_t>(topk_e[p]) * cap + pos[p]) * H + ch * 8), v);
+      const float w = topk_w[p];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += w * v[i];
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + ch * 8) = pack8<T>(acc);
+  }
+}
+
 template <class S, class D>
 __global__ void __launch_bounds__(256) convert_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -660,6 +739,56 @@ int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int 
   } else {
     gather_rows_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
         reinterpret_cast<const __nv_bfloat16*>(x), row_index, out, n_rows, H);
+  }
+  return last_error();
+}
+
+int launch_moe_route(const void* logits, int ld_logits, int T, int E, int k, int* topk_e, float* topk_w,
+                     int* pos, int* counts, int dtype, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (E <= 0 || E > kMoeMaxExperts || k <= 0 || k > kMoeMaxTopK || k > E) return static_cast<int>(cudaErrorInvalidValue);
+  const int grid = (T + 255) / 256;
+  if (dtype == DT_F16) {
+    moe_route_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(logits), ld_logits, T, E, k,
+                                                  topk_e, topk_w, pos, counts);
+  } else {
+    moe_route_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
+                                                         ld_logits, T, E, k, topk_e, topk_w, pos, counts);
+  }
+  return last_error();
+}
+
+int launch_moe_gather(const void* x, const int* topk_e, const int* pos, void* xg, int T, int k, int H,
+                      long long cap, int dtype, cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int n = T * k, warps = 8;
+  const int grid = (n + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    moe_gather_kernel<__half><<<grid, warps * 32, 0, st>>>(reinterpret_cast<const __half*>(x), topk_e, pos,
+                                                           reinterpret_cast<__half*>(xg), n, k, H, cap);
+  } else {
+    moe_gather_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), topk_e, pos, reinterpret_cast<__nv_bfloat16*>(xg), n, k, H, cap);
+  }
+  return last_error();
+}
+
+int launch_moe_combine(const void* yg, const int* topk_e, const float* topk_w, const int* pos,
+                       const void* bias, void* out, int T, int k, int H, long long cap, int dtype,
+                       cudaStream_t st) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int warps = 8;
+  const int grid = (T + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    moe_combine_kernel<__half><<<grid, warps * 32, 0, st>>>(
+        reinterpret_cast<const __half*>(yg), topk_e, topk_w, pos, reinterpret_cast<const __half*>(bias),
+        reinterpret_cast<__half*>(out), T, k, H, cap);
+  } else {
+    moe_combine_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(yg), topk_e, topk_w, pos,
+        reinterpret_cast<const __nv_bfloat16*>(bias), reinterpret_cast<__nv_bfloat16*>(out), T, k, H, cap);
   }
   return last_error();
 }
