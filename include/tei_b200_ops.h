@@ -115,6 +115,37 @@ int tei_b200_op_head_linear(const float* in_dev, const void* w_dev, const void* 
                             float* out_dev, int rows, int N, int K, int act, int dtype,
                             void* stream);
 
+/* tei_b200_op_linear on the first min(M, *m_rows_dev) rows only: M is the capacity of the
+ * buffers, the row count lives on the device (the tokens routed to one expert,
+ * backends/candle/src/models/nomic.rs:325-353, where the reference syncs to the host instead). */
+int tei_b200_op_linear_rows_dev(const void* a_dev, const void* w_dev, const void* bias_dev,
+                                void* out_dev, int M, int N, int K, int lda, int ldo, int act,
+                                int dtype, const int32_t* m_rows_dev, int* status_dev, void* stream);
+
+/* Mixture-of-experts routing (NomicRouter::forward, backends/candle/src/models/nomic.rs:229-243,
+ * and the bookkeeping of NomicExperts::forward `:325-341`): per token the fp32 softmax over the
+ * n_experts logits and its top_k largest entries (weights rounded to the model dtype), plus,
+ * for every pick, the row it takes among the tokens of its expert.  counts_dev [n_experts] is
+ * zeroed by the call, counts the picks per expert while the kernel runs and holds those counts
+ * afterwards.  Rows within an expert are handed out in arrival order, so pos_dev may differ
+ * between runs; everything computed from it per token does not.  n_experts <= 64, top_k <= 8. */
+int tei_b200_op_moe_route(const void* logits_dev, int ld_logits, int n_tokens, int n_experts,
+                          int top_k, int32_t* topk_expert_dev, float* topk_weight_dev,
+                          int32_t* pos_dev, int32_t* counts_dev, int dtype, void* stream);
+
+/* xg[(expert * cap + pos) * hidden ..] = x[token] for every pick (the index_select of
+ * nomic.rs:343-345); cap = rows reserved per expert. */
+int tei_b200_op_moe_gather(const void* x_dev, const int32_t* topk_expert_dev, const int32_t* pos_dev,
+                           void* xg_dev, int n_tokens, int top_k, int hidden, long long cap,
+                           int dtype, void* stream);
+
+/* out[token] = sum over its picks of weight * yg[expert * cap + pos] + bias (the index_add and
+ * broadcast_add of nomic.rs:346-355), accumulated in fp32.  bias may be NULL. */
+int tei_b200_op_moe_combine(const void* yg_dev, const int32_t* topk_expert_dev,
+                            const float* topk_weight_dev, const int32_t* pos_dev,
+                            const void* bias_dev, void* out_dev, int n_tokens, int top_k, int hidden,
+                            long long cap, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -301,3 +301,58 @@ def test_pooling_gather_and_heads(lib, dtype):
     b = (torch.randn(5, device="cuda", generator=g) * 0.05).to(dt)
     _close(ops.head_linear(xin, w, b, "tanh"), torch.tanh(xin @ w.float().t() + b.float()), 1e-4)
     _close(ops.head_linear(xin, w, None, "none"), xin @ w.float().t(), 1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_moe_feed_forward_from_its_ops(lib, dtype):
+    # NomicMoELayer::forward (backends/candle/src/models/nomic.rs:205-394) assembled from the
+    # single ops, against the same computation in fp32 torch.
+    from tei_b200 import ops
+    dt = DT[dtype]
+    g = _gen(77)
+    T, H, I, E, K = 1500, 256, 512, 8, 2
+    x = (torch.randn(T, H, device="cuda", generator=g) * 0.5).to(dt)
+    wr = torch.zeros(8, H, device="cuda", dtype=dt)
+    wr[:E] = (torch.randn(E, H, device="cuda", generator=g) * 0.2).to(dt)
+    w1 = (torch.randn(E * I, H, device="cuda", generator=g) * 0.05).to(dt)
+    w2 = (torch.randn(E * I, H, device="cuda", generator=g) * 0.05).to(dt)
+    bias = (torch.randn(H, device="cuda", generator=g) * 0.1).to(dt)
+    logits = ops.linear(x, wr)
+    te, tw, pos, counts = ops.moe_route(logits, E, K)
+    # routing against torch on the same logits
+    probs = torch.softmax(logits[:, :E].float(), dim=-1)
+    ref_w, ref_e = probs.topk(K, dim=-1)
+    # the same probabilities are picked; where two logits tie exactly (they are fp16 / bf16
+    # numbers) the lower expert index wins here, so indices are compared away from ties only
+    assert (tw - ref_w.to(dt).float()).abs().max().item() <= 1e-6
+    assert (probs.gather(1, te.long()) - ref_w).abs().max().item() <= 1e-6
+    srt = probs.sort(dim=-1, descending=True).values
+    no_tie = (srt[:, :K] - srt[:, 1:K + 1]).min(dim=-1).values > 0
+    assert torch.equal(te.long()[no_tie], ref_e[no_tie]) and int(no_tie.sum()) > T // 2
+    assert (te[:, 0] != te[:, 1]).all()
+    ref_e = te.long()  # the reference below follows the picks made here
+    assert int(counts.sum()) == T * K
+    assert torch.equal(counts.long(), torch.bincount(ref_e.flatten(), minlength=E))
+    for e in range(E):  # the rows of an expert are 0 .. count-1, each once
+        p_e = pos[te == e].long().sort().values
+        assert torch.equal(p_e, torch.arange(int(counts[e]), device="cuda"))
+    cap = 1536
+    xg = ops.moe_gather(x, te, pos, cap, E)
+    yg = torch.zeros(E * cap, H, device="cuda", dtype=dt)
+    w2t = w2.view(E, I, H).transpose(1, 2).contiguous()  # [E, H, I]: the [N, K] form of each expert
+    for e in range(E):
+        h = ops.linear_rows_dev(xg[e * cap:(e + 1) * cap], w1[e * I:(e + 1) * I], None, counts[e:e + 1], act="gelu")
+        ops.linear_rows_dev(h, w2t[e], None, counts[e:e + 1], out=yg[e * cap:(e + 1) * cap])
+    out = ops.moe_combine(yg, te, tw, pos, bias, cap)
+    ref = torch.zeros(T, H, device="cuda")
+    xf = x.float()
+    for e in range(E):
+        tok, slot = (ref_e == e).nonzero(as_tuple=True)
+        y = torch.nn.functional.gelu(xf[tok] @ w1[e * I:(e + 1) * I].float().t(), approximate="tanh") @ w2[e * I:(e + 1) * I].float()
+        ref.index_add_(0, tok, y * tw[tok, slot].unsqueeze(-1))
+    ref = ref + bias.float()
+    _close(out, ref, 2e-2 if dtype == "f16" else 8e-2)
+    # a row count of zero leaves the output untouched
+    canary = torch.full((cap, H), 7.0, device="cuda", dtype=dt)
+    ops.linear_rows_dev(xg[:cap], w2t[0][:, :H].contiguous(), None, torch.zeros(1, device="cuda", dtype=torch.int32), out=canary)
+    assert (canary == 7.0).all()

@@ -177,4 +177,52 @@ int tei_b200_op_head_linear(const float* in_dev, const void* w_dev, const void* 
                             static_cast<cudaStream_t>(stream));
 }
 
+int tei_b200_op_linear_rows_dev(const void* a_dev, const void* w_dev, const void* bias_dev,
+                                void* out_dev, int M, int N, int K, int lda, int ldo, int act,
+                                int dtype, const int32_t* m_rows_dev, int* status_dev, void* stream) {
+  GemmArgs g;
+  g.a = a_dev;
+  g.w = w_dev;
+  g.bias = bias_dev;
+  g.residual = nullptr;
+  g.out = out_dev;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = lda;
+  g.ldo = ldo;
+  g.ldr = 0;
+  g.act = act;
+  g.dtype = dtype;
+  g.status = status_dev;
+  g.m_dev = m_rows_dev;
+  return launch_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
+int tei_b200_op_moe_route(const void* logits_dev, int ld_logits, int n_tokens, int n_experts,
+                          int top_k, int32_t* topk_expert_dev, float* topk_weight_dev,
+                          int32_t* pos_dev, int32_t* counts_dev, int dtype, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_experts <= 0 || n_experts > 64) return static_cast<int>(cudaErrorInvalidValue);
+  cudaError_t e = cudaMemsetAsync(counts_dev, 0, static_cast<size_t>(n_experts) * 4, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return launch_moe_route(logits_dev, ld_logits, n_tokens, n_experts, top_k, topk_expert_dev,
+                          topk_weight_dev, pos_dev, counts_dev, dtype, st);
+}
+
+int tei_b200_op_moe_gather(const void* x_dev, const int32_t* topk_expert_dev, const int32_t* pos_dev,
+                           void* xg_dev, int n_tokens, int top_k, int hidden, long long cap,
+                           int dtype, void* stream) {
+  return launch_moe_gather(x_dev, topk_expert_dev, pos_dev, xg_dev, n_tokens, top_k, hidden, cap, dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int tei_b200_op_moe_combine(const void* yg_dev, const int32_t* topk_expert_dev,
+                            const float* topk_weight_dev, const int32_t* pos_dev,
+                            const void* bias_dev, void* out_dev, int n_tokens, int top_k, int hidden,
+                            long long cap, int dtype, void* stream) {
+  return launch_moe_combine(yg_dev, topk_expert_dev, topk_weight_dev, pos_dev, bias_dev, out_dev, n_tokens,
+                            top_k, hidden, cap, dtype, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -6,7 +6,7 @@ if the shared object is missing, `load()` raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_size_t, c_uint32, c_void_p
+from ctypes import c_longlong, POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 PKG_ROOT = Path(__file__).resolve().parent.parent
@@ -34,6 +34,10 @@ _OPS_PROTOTYPES = {
     "tei_b200_op_pool": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
     "tei_b200_op_gather_rows_f32": (c_int, [c_void_p] * 3 + [c_int] * 3 + [c_void_p]),
     "tei_b200_op_head_linear": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
+    "tei_b200_op_linear_rows_dev": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_void_p, c_void_p]),
+    "tei_b200_op_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p]),
+    "tei_b200_op_moe_gather": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
+    "tei_b200_op_moe_combine": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
 }
 
 _BATCH = [POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t,

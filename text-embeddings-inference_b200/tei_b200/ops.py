@@ -192,3 +192,59 @@ def head_linear(x_f32, w, b, act="none"):
                                      _dt(w), _stream())
     _check(rc, "tei_b200_op_head_linear")
     return out
+
+
+def linear_rows_dev(a, w, bias, m_rows_dev, act="none", out=None, status=None):
+    """linear() on the first min(M, m_rows_dev[0]) rows of `a` (int32 device scalar)."""
+    lib = _lib.load()
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if act in ("swiglu", "geglu") else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=a.dtype, device=a.device)
+    own = status is None
+    if own:
+        status = new_status(a.device)
+    rc = lib.tei_b200_op_linear_rows_dev(_p(a), _p(w), _p(bias), _p(out), M, N, K, a.stride(0), out.stride(0),
+                                         ACT[act], _dt(a), _p(m_rows_dev), _p(status), _stream())
+    _check(rc, "tei_b200_op_linear_rows_dev")
+    if own:
+        check_status(status, "linear_rows_dev")
+    return out
+
+
+def moe_route(logits, n_experts: int, top_k: int):
+    """logits [T, >= n_experts] -> (expert int32 [T, k], weight fp32 [T, k], pos int32 [T, k],
+    counts int32 [n_experts])."""
+    lib = _lib.load()
+    T = logits.shape[0]
+    dev = logits.device
+    te = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    tw = torch.empty((T, top_k), dtype=torch.float32, device=dev)
+    pos = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    counts = torch.empty((n_experts,), dtype=torch.int32, device=dev)
+    rc = lib.tei_b200_op_moe_route(_p(logits), logits.stride(0), T, n_experts, top_k, _p(te), _p(tw), _p(pos),
+                                   _p(counts), _dt(logits), _stream())
+    _check(rc, "tei_b200_op_moe_route")
+    return te, tw, pos, counts
+
+
+def moe_gather(x, topk_expert, pos, cap: int, n_experts: int):
+    lib = _lib.load()
+    T, H = x.shape
+    k = topk_expert.shape[1]
+    xg = torch.zeros((n_experts * cap, H), dtype=x.dtype, device=x.device)
+    rc = lib.tei_b200_op_moe_gather(_p(x), _p(topk_expert), _p(pos), _p(xg), T, k, H, cap, _dt(x), _stream())
+    _check(rc, "tei_b200_op_moe_gather")
+    return xg
+
+
+def moe_combine(yg, topk_expert, topk_weight, pos, bias, cap: int):
+    lib = _lib.load()
+    T, k = topk_expert.shape
+    H = yg.shape[1]
+    out = torch.empty((T, H), dtype=yg.dtype, device=yg.device)
+    rc = lib.tei_b200_op_moe_combine(_p(yg), _p(topk_expert), _p(topk_weight), _p(pos), _p(bias), _p(out), T, k, H,
+                                     cap, _dt(yg), _stream())
+    _check(rc, "tei_b200_op_moe_combine")
+    return out
