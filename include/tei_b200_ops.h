@@ -146,6 +146,29 @@ int tei_b200_op_moe_combine(const void* yg_dev, const int32_t* topk_expert_dev,
                             const void* bias_dev, void* out_dev, int n_tokens, int top_k, int hidden,
                             long long cap, int dtype, void* stream);
 
+/* tei_b200_op_moe_route for callers that cannot allocate device memory.  It has no counterpart
+ * in the reference.  The per-expert counters, which tei_b200_op_moe_route takes from the
+ * caller, live in a 256-byte array inside the library instead (held by every GPU that loads
+ * the library, until the process exits), so an embedding host that gave all device memory to
+ * its own arena at start-up and forbids cudaMalloc on the request path - cudaMalloc
+ * synchronises the device and can fail half-way through a request - or an operator plugin that
+ * only receives the tensors of the one operator it implements, can still route.  The call
+ * itself allocates and frees nothing.
+ *   - n_experts <= 64 (the size of the built-in array); more returns an error and a message in
+ *     `err` (may be NULL).
+ *   - counts_out_dev [n_experts] receives the picks per expert; it may be NULL.
+ *   - All calls on one GPU share the array: it is cleared at the start of each call, and calls
+ *     that overlap on the GPU (two streams, two threads) corrupt each other's counts - order
+ *     them.
+ *   - The first call on a device looks up the array's device address; make it before any stream
+ *     capture begins.
+ * Outputs as for tei_b200_op_moe_route. */
+int tei_b200_op_moe_route_noalloc(const void* logits_dev, int ld_logits, int n_tokens,
+                                  int n_experts, int top_k, int32_t* topk_expert_dev,
+                                  float* topk_weight_dev, int32_t* pos_dev,
+                                  int32_t* counts_out_dev, int dtype, void* stream, char* err,
+                                  size_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,8 @@ _OPS_PROTOTYPES = {
     "tei_b200_op_head_linear": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
     "tei_b200_op_linear_rows_dev": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_void_p, c_void_p]),
     "tei_b200_op_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p]),
+    "tei_b200_op_moe_route_noalloc": (
+        c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p, c_char_p, c_size_t]),
     "tei_b200_op_moe_gather": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
     "tei_b200_op_moe_combine": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
 }

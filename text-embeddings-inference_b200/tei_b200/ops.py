@@ -248,3 +248,24 @@ def moe_combine(yg, topk_expert, topk_weight, pos, bias, cap: int):
                                      cap, _dt(yg), _stream())
     _check(rc, "tei_b200_op_moe_combine")
     return out
+
+
+def moe_route_noalloc(logits, n_experts: int, top_k: int, out=None):
+    """moe_route through the entry point that keeps its counters inside the library and never
+    allocates: the four result tensors are the caller's (`out` = (expert, weight, pos, counts),
+    made here when absent - the wrapper may allocate, the library call does not)."""
+    lib = _lib.load()
+    T = logits.shape[0]
+    dev = logits.device
+    if out is None:
+        out = (torch.empty((T, top_k), dtype=torch.int32, device=dev),
+               torch.empty((T, top_k), dtype=torch.float32, device=dev),
+               torch.empty((T, top_k), dtype=torch.int32, device=dev),
+               torch.empty((n_experts,), dtype=torch.int32, device=dev))
+    te, tw, pos, counts = out
+    err = ctypes.create_string_buffer(256)
+    rc = lib.tei_b200_op_moe_route_noalloc(_p(logits), logits.stride(0), T, n_experts, top_k, _p(te), _p(tw),
+                                           _p(pos), _p(counts), _dt(logits), _stream(), err, len(err))
+    if rc != 0:
+        raise RuntimeError(f"tei_b200_op_moe_route_noalloc failed ({rc}): {err.value.decode(errors='replace')}")
+    return te, tw, pos, counts
