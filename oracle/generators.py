@@ -42,6 +42,87 @@ def bert_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30522, max_po
     return c
 
 
+def distilbert_config(hidden=768, layers=6, heads=12, inter=3072, vocab=30522, max_pos=512, act="gelu") -> dict:
+    """Fields of DistilBertConfig (models/distilbert.rs:9-21)."""
+    return {
+        "architectures": ["DistilBertModel"], "model_type": "distilbert", "vocab_size": vocab, "dim": hidden,
+        "n_layers": layers, "n_heads": heads, "hidden_dim": inter, "activation": act,
+        "max_position_embeddings": max_pos, "pad_token_id": 0, "dropout": 0.1, "attention_dropout": 0.1,
+        "sinusoidal_pos_embds": False,
+    }
+
+
+def _distilbert_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    """Names under `distilbert.` as a checkpoint of DistilBertForMaskedLM carries them
+    (flash_distilbert.rs:211-214, models/distilbert.rs:27-56,103-140)."""
+    H, I, V = c["dim"], c["hidden_dim"], c["vocab_size"]
+    e = "distilbert.embeddings."
+    t: Dict[str, Tuple[tuple, str]] = {e + "word_embeddings.weight": ((V, H), "normal"),
+                                       e + "position_embeddings.weight": ((c["max_position_embeddings"], H), "normal"),
+                                       e + "LayerNorm.weight": ((H,), "ones"), e + "LayerNorm.bias": ((H,), "zeros")}
+    for i in range(c["n_layers"]):
+        p = f"distilbert.transformer.layer.{i}."
+        for n in ("q_lin", "k_lin", "v_lin", "out_lin"):
+            t[p + f"attention.{n}.weight"] = ((H, H), "normal")
+            t[p + f"attention.{n}.bias"] = ((H,), "normal")
+        t[p + "sa_layer_norm.weight"] = ((H,), "ones")
+        t[p + "sa_layer_norm.bias"] = ((H,), "zeros")
+        t[p + "ffn.lin1.weight"] = ((I, H), "normal")
+        t[p + "ffn.lin1.bias"] = ((I,), "normal")
+        t[p + "ffn.lin2.weight"] = ((H, I), "normal")
+        t[p + "ffn.lin2.bias"] = ((H,), "normal")
+        t[p + "output_layer_norm.weight"] = ((H,), "ones")
+        t[p + "output_layer_norm.bias"] = ((H,), "zeros")
+    return t
+
+
+def gte_config(hidden=768, layers=12, heads=12, inter=3072, vocab=30528, max_pos=8192, type_vocab=0,
+               theta=500000.0, ntk_factor: Optional[float] = 2.0, eps=1e-12, id2label=None) -> dict:
+    """Fields of GTEConfig (models/gte.rs:14-36); model_type "new" as the Alibaba-NLP checkpoints
+    spell it (backends/candle/src/lib.rs:134-135)."""
+    c = {
+        "architectures": ["NewModel" if id2label is None else "NewForSequenceClassification"], "model_type": "new",
+        "vocab_size": vocab, "hidden_size": hidden, "num_hidden_layers": layers, "num_attention_heads": heads,
+        "intermediate_size": inter, "hidden_act": "gelu", "max_position_embeddings": max_pos,
+        "type_vocab_size": type_vocab, "layer_norm_type": "layer_norm", "layer_norm_eps": eps,
+        "position_embedding_type": "rope", "rope_theta": theta,
+        "rope_scaling": None if ntk_factor is None else {"type": "ntk", "factor": ntk_factor},
+        "logn_attention_scale": False, "logn_attention_clip1": False,
+    }
+    if id2label is not None:
+        c["id2label"] = id2label
+    return c
+
+
+def _gte_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
+    """Names as flash_gte.rs:243-268 and models/gte.rs:52-66,196-205,290-312 read them, under `new.`."""
+    H, I, V = c["hidden_size"], c["intermediate_size"], c["vocab_size"]
+    t: Dict[str, Tuple[tuple, str]] = {"new.embeddings.word_embeddings.weight": ((V, H), "normal"),
+                                       "new.embeddings.LayerNorm.weight": ((H,), "ones"),
+                                       "new.embeddings.LayerNorm.bias": ((H,), "zeros")}
+    if c["type_vocab_size"] > 0:
+        t["new.embeddings.token_type_embeddings.weight"] = ((c["type_vocab_size"], H), "normal")
+    for i in range(c["num_hidden_layers"]):
+        p = f"new.encoder.layer.{i}."
+        t[p + "attention.qkv_proj.weight"] = ((3 * H, H), "normal")
+        t[p + "attention.qkv_proj.bias"] = ((3 * H,), "normal")
+        t[p + "attention.o_proj.weight"] = ((H, H), "normal")
+        t[p + "attention.o_proj.bias"] = ((H,), "normal")
+        t[p + "mlp.up_gate_proj.weight"] = ((2 * I, H), "normal")
+        t[p + "mlp.down_proj.weight"] = ((H, I), "normal")
+        t[p + "mlp.down_proj.bias"] = ((H,), "normal")
+        for n in ("attn_ln", "mlp_ln"):
+            t[p + n + ".weight"] = ((H,), "ones")
+            t[p + n + ".bias"] = ((H,), "zeros")
+    if c.get("id2label") is not None:
+        n_cls = len(c["id2label"])
+        t["new.pooler.dense.weight"] = ((H, H), "normal")
+        t["new.pooler.dense.bias"] = ((H,), "normal")
+        t["classifier.weight"] = ((n_cls, H), "normal")
+        t["classifier.bias"] = ((n_cls,), "normal")
+    return t
+
+
 def jina_config(alibi: bool = True, **kw) -> dict:
     """A JinaBERT config: model_type "bert" plus the markers the reference dispatches on
     (backends/candle/src/lib.rs:83-121) and `position_embedding_type`."""
@@ -303,6 +384,10 @@ def tensor_shapes(config: dict, classifier: Optional[str] = None, splade: bool =
         return _qwen3_shapes(config)
     if mt == "modernbert":
         return _modernbert_shapes(config)
+    if mt == "distilbert":
+        return _distilbert_shapes(config)
+    if mt in ("gte", "new"):
+        return _gte_shapes(config)
     raise ValueError(mt)
 
 

@@ -554,6 +554,143 @@ class Qwen3Oracle:
         return pool_outputs(self.hidden_states(batch), batch, self.pool)
 
 
+# --------------------------------------------------------------------------- GTE
+class GTEOracle:
+    """models/gte.rs (CPU arm) / flash_gte.rs: LN(word [+ token type]) (flash_gte.rs:243-268),
+    post-LayerNorm blocks with biased qkv_proj / o_proj, RoPE whose inverse frequencies may be
+    NTK-scaled - base * factor, divided by factor^(2 / dim) (layers/rotary.rs:86-93) - and the
+    feed-forward act(second half of up_gate_proj x) * first half -> down_proj (gte.rs:216-227).
+    Head: optional pooler.dense + tanh, then classifier, on the CLS row (gte.rs:282-340)."""
+
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding", pool: str = "cls"):
+        c = config
+        if pool == "splade":
+            raise ValueError("`splade` is not supported for GTE")
+        if c.get("logn_attention_scale") or c.get("logn_attention_clip1") or c["position_embedding_type"] != "rope":
+            raise ValueError("config is not supported (flash_gte.rs:177-186)")
+        self.cfg = c
+        self.model_type = model_type
+        self.pool = "cls" if model_type == "classifier" else pool
+        prefix = "new." if "new.embeddings.word_embeddings.weight" in tensors else ""
+        self.w = _Weights(tensors, (prefix,))
+        self.all = _Weights(tensors, ("",))
+        self.nh = c["num_attention_heads"]
+        self.hidden = c["hidden_size"]
+        self.dh = self.hidden // self.nh
+        self.inter = c["intermediate_size"]
+        self.eps = float(c["layer_norm_eps"])
+        self.n_layers = c["num_hidden_layers"]
+        self.act = activation(c["hidden_act"])
+        theta = c.get("rope_theta")
+        if theta is None:
+            theta = c["rope_parameters"]["rope_theta"]
+        theta = float(theta)
+        scaling = c.get("rope_scaling")
+        n_pos = int(c["max_position_embeddings"])
+        if scaling:
+            f = float(scaling["factor"])
+            # inv_freq = 1 / (theta * f)^(i / dim) / f^(2 / dim), angles in f32
+            i = torch.arange(0, self.dh, 2, dtype=torch.float32)
+            inv = (1.0 / torch.pow(torch.tensor(theta * f, dtype=torch.float32), i / self.dh)) / (f ** (2.0 / self.dh))
+            ang = torch.arange(n_pos, dtype=torch.float32)[:, None] * inv[None, :]
+            cos, sin = ang.cos(), ang.sin()
+        else:
+            cos, sin = rope_tables(self.dh, theta, n_pos)
+        self.cos, self.sin = cos, sin
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w, c = self.w, self.cfg
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        g, b = w.ln("embeddings.LayerNorm")
+        typ = None
+        if c["type_vocab_size"] > 0:
+            typ = w.get("embeddings.token_type_embeddings.weight")[torch.from_numpy(batch.token_type_ids.astype(np.int64))]
+        x = layer_norm(w.get("embeddings.word_embeddings.weight")[ids], typ, g, b, self.eps)
+        cos, sin = self.cos[pids], self.sin[pids]
+        T, H = x.shape
+        cu = batch.cumulative_seq_lengths
+        for i in range(self.n_layers):
+            p = f"encoder.layer.{i}."
+            qkv = linear(x, w.get(p + "attention.qkv_proj.weight"), w.get(p + "attention.qkv_proj.bias"))
+            q, k, v = (qkv[:, j * H:(j + 1) * H].reshape(T, self.nh, self.dh) for j in range(3))
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), False)
+            a = linear(a, w.get(p + "attention.o_proj.weight"), w.get(p + "attention.o_proj.bias"))
+            g1, b1 = w.ln(p + "attn_ln")
+            x1 = layer_norm(a, x, g1, b1, self.eps)
+            ug = linear(x1, w.get(p + "mlp.up_gate_proj.weight"))
+            m = self.act(ug[:, self.inter:]) * ug[:, :self.inter]
+            m = linear(m, w.get(p + "mlp.down_proj.weight"), w.get(p + "mlp.down_proj.bias"))
+            g2, b2 = w.ln(p + "mlp_ln")
+            x = layer_norm(m, x1, g2, b2, self.eps)
+        return x
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+    def predict(self, batch: Batch) -> Tensor:
+        x = self.hidden_states(batch)
+        cu = batch.cumulative_seq_lengths.astype(np.int64)
+        h = x[torch.from_numpy(cu[:-1])]
+        if self.w.has("pooler.dense.weight") and self.w.has("pooler.dense.bias"):
+            h = torch.tanh(linear(h, self.w.get("pooler.dense.weight"), self.w.get("pooler.dense.bias")))
+        return linear(h, self.all.get("classifier.weight"), self.all.get("classifier.bias"))
+
+
+# --------------------------------------------------------------------------- DistilBERT
+class DistilBertOracle:
+    """models/distilbert.rs (CPU arm) / flash_distilbert.rs: BERT blocks without token types:
+    LN(word + position) (distilbert.rs:58-70), q_lin / k_lin / v_lin / out_lin, sa_layer_norm on
+    the attention residual, ffn.lin1 -> activation -> ffn.lin2, output_layer_norm; every
+    LayerNorm with eps 1e-12 (flash_distilbert.rs:113-115)."""
+
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding", pool: str = "cls"):
+        if model_type == "classifier" or pool == "splade":
+            raise ValueError("DistilBERT: embedding models with cls / mean / last-token pooling only here")
+        c = config
+        self.cfg = c
+        self.pool = pool
+        if "embeddings.word_embeddings.weight" in tensors and "encoder.layer.0.attention.q_lin.weight" in tensors:
+            self.emb, self.enc = "embeddings.", "encoder."
+        elif "distilbert.embeddings.word_embeddings.weight" in tensors:
+            self.emb, self.enc = "distilbert.embeddings.", "distilbert.transformer."
+        else:
+            self.emb, self.enc = "embeddings.", "transformer."
+        self.w = _Weights(tensors, ("",))
+        self.nh = c["n_heads"]
+        self.hidden = c["dim"]
+        self.dh = self.hidden // self.nh
+        self.eps = 1e-12
+        self.act = activation(c["activation"])
+        self.n_layers = c["n_layers"]
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+        g, b = w.ln(self.emb + "LayerNorm")
+        x = layer_norm(w.get(self.emb + "word_embeddings.weight")[ids],
+                       w.get(self.emb + "position_embeddings.weight")[pids], g, b, self.eps)
+        cu = batch.cumulative_seq_lengths
+        T = x.shape[0]
+        for i in range(self.n_layers):
+            p = f"{self.enc}layer.{i}."
+            q, k, v = (linear(x, w.get(p + f"attention.{n}.weight"), w.get(p + f"attention.{n}.bias")).view(T, self.nh, self.dh)
+                       for n in ("q_lin", "k_lin", "v_lin"))
+            a = attention_varlen(q, k, v, cu, 1.0 / math.sqrt(self.dh), False)
+            g1, b1 = w.ln(p + "sa_layer_norm")
+            x1 = layer_norm(linear(a, w.get(p + "attention.out_lin.weight"), w.get(p + "attention.out_lin.bias")),
+                            x, g1, b1, self.eps)
+            f = self.act(linear(x1, w.get(p + "ffn.lin1.weight"), w.get(p + "ffn.lin1.bias")))
+            g2, b2 = w.ln(p + "output_layer_norm")
+            x = layer_norm(linear(f, w.get(p + "ffn.lin2.weight"), w.get(p + "ffn.lin2.bias")), x1, g2, b2, self.eps)
+        return x
+
+    def embed(self, batch: Batch):
+        return pool_outputs(self.hidden_states(batch), batch, self.pool)
+
+
 # --------------------------------------------------------------------------- ModernBERT
 class ModernBertOracle:
     """models/modernbert.rs (CPU arm) / flash_modernbert.rs: LayerNorm (weight only) after the
@@ -714,4 +851,8 @@ def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
         return Qwen3Oracle(config, tensors, model_type, pool)
     if mt == "modernbert":
         return ModernBertOracle(config, tensors, model_type, pool)
+    if mt == "distilbert":
+        return DistilBertOracle(config, tensors, model_type, pool)
+    if mt in ("gte", "new"):
+        return GTEOracle(config, tensors, model_type, pool)
     raise ValueError(f"model_type {mt} is outside the hot path")

@@ -59,6 +59,17 @@ def write_all(base):
         G.mistral_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048,
                          model_type="llama"),
         seed=14, norm_jitter=0.1, std=0.05)
+    dirs["distilbert"] = G.write_model_dir(
+        base / "distilbert", G.distilbert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+        seed=18, norm_jitter=0.1, std=0.05)
+    dirs["gte"] = G.write_model_dir(
+        base / "gte", G.gte_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=2048, ntk_factor=2.0),
+        seed=19, norm_jitter=0.1, std=0.05)
+    dirs["gte_cls"] = G.write_model_dir(
+        base / "gte_cls",
+        G.gte_config(hidden=256, layers=2, heads=2, inter=256, vocab=1000, max_pos=2048, type_vocab=2, ntk_factor=None,
+                     id2label={"0": "a", "1": "b"}),
+        seed=20, norm_jitter=0.1, std=0.05)
     dirs["nomic_moe"] = G.write_model_dir(
         base / "nomic_moe",
         G.nomic_config(hidden=128, layers=4, heads=2, inter=256, vocab=1000, n_positions=2048, moe_every=2,
@@ -99,6 +110,9 @@ GOLDEN_CASES = {
     "modernbert_cls": ("modernbert", "embedding", "cls", dict(seed=117, lens=[33, 64, 65, 400], lo=0, hi=1000, type_vocab=1, offset=0)),
     "modernbert_scores": ("modernbert_cls", "classifier", "cls", dict(seed=118, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "nomic_moe_mean": ("nomic_moe", "embedding", "mean", dict(seed=119, lens=LENS + [700], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "distilbert_mean": ("distilbert", "embedding", "mean", dict(seed=120, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
+    "gte_cls_pool": ("gte", "embedding", "cls", dict(seed=121, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "gte_scores": ("gte_cls", "classifier", "cls", dict(seed=122, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

@@ -127,6 +127,22 @@ def test_mistral_sliding_window_matches_hf(model_dirs):
     assert (o.hidden_states(b)[-1] - hs[-1]).abs().max().item() > 1e-3
 
 
+def test_distilbert_matches_hf(model_dirs):
+    d = model_dirs["distilbert"]
+    cfg = json.load(open(d / "config.json"))
+    # the reference's "gelu" is the tanh approximation (layers/linear.rs:5-17)
+    hf = transformers.DistilBertModel(transformers.DistilBertConfig(**dict(cfg, activation="gelu_pytorch_tanh"))).eval()
+    _, tensors = M.load_model_dir(d)
+    hf.load_state_dict({k[len("distilbert."):]: v for k, v in tensors.items()}, strict=True)
+    o = M.build_oracle(d, "embedding", "mean")
+    b = G.random_batch(9, [7, 40, 130], 0, 1000)
+    hs = o.hidden_states(b)
+    for s, a, e in _per_sequence(b):
+        with torch.no_grad():
+            ref = hf(input_ids=_t(b.input_ids[a:e])).last_hidden_state[0]
+        assert (ref - hs[a:e]).abs().max().item() < TOL
+
+
 def test_modernbert_matches_hf(model_dirs):
     d = model_dirs["modernbert"]
     cfg = json.load(open(d / "config.json"))

@@ -111,6 +111,65 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
       if (!c["id2label"].is_object()) throw TeiError(ERR_START, "`id2label` must be set for classifier models");
       s.n_classes = static_cast<int>(c["id2label"].size());
     }
+  } else if (mt == "distilbert") {
+    // DistilBertConfig (models/distilbert.rs:9-21); BERT blocks without token types and with a
+    // fixed LayerNorm epsilon of 1e-12 (flash_distilbert.rs:113-115).
+    s.arch = ARCH_BERT;
+    s.distil = true;
+    if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for DistilBert");
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` for DistilBert is outside this backend");
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "dim"));
+    s.layers = static_cast<int>(need_int(c, "n_layers"));
+    s.heads = s.kv_heads = static_cast<int>(need_int(c, "n_heads"));
+    s.inter = static_cast<int>(need_int(c, "hidden_dim"));
+    s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
+    s.type_vocab = 0;
+    s.eps = 1e-12f;
+    s.act = parse_act(need_string(c, "activation"));
+    if (s.act != ACT_GELU && s.act != ACT_RELU) throw TeiError(ERR_START, "unsupported activation for DistilBert");
+    if (s.heads <= 0 || s.hidden % s.heads != 0) throw TeiError(ERR_START, "dim is not a multiple of n_heads");
+    s.head_dim = s.hidden / s.heads;
+    s.qkv_bias = s.out_bias = s.fc1_bias = s.fc2_bias = true;
+  } else if (mt == "gte" || mt == "new") {
+    // GTEConfig (models/gte.rs:14-36); runs on the NomicBERT skeleton (post-LN, RoPE, gated FFN).
+    s.arch = ARCH_NOMIC;
+    s.gte = true;
+    if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for GTE");
+    if (c.get_bool("logn_attention_clip1", false)) throw TeiError(ERR_START, "`logn_attention_clip1` is not supported");
+    if (c.get_bool("logn_attention_scale", false)) throw TeiError(ERR_START, "`logn_attention_scale` is not supported");
+    if (need_string(c, "position_embedding_type") != "rope") throw TeiError(ERR_START, "Only `PositionEmbeddingType::Rope` is supported");
+    s.vocab = static_cast<int>(need_int(c, "vocab_size"));
+    s.hidden = static_cast<int>(need_int(c, "hidden_size"));
+    s.layers = static_cast<int>(need_int(c, "num_hidden_layers"));
+    s.heads = s.kv_heads = static_cast<int>(need_int(c, "num_attention_heads"));
+    s.inter = static_cast<int>(need_int(c, "intermediate_size"));
+    s.max_pos = static_cast<int>(need_int(c, "max_position_embeddings"));
+    s.type_vocab = static_cast<int>(need_int(c, "type_vocab_size"));
+    s.eps = static_cast<float>(need_double(c, "layer_norm_eps"));
+    if (parse_act(need_string(c, "hidden_act")) != ACT_GELU) throw TeiError(ERR_START, "GTE expects a GELU hidden_act");
+    s.gated = true;
+    s.act = ACT_GEGLU;  // act(second half) * first half (gte.rs:216-227)
+    s.qkv_bias = s.out_bias = true;
+    s.fc1_bias = false;
+    s.fc2_bias = true;
+    if (s.heads <= 0 || s.hidden % s.heads != 0) throw TeiError(ERR_START, "hidden_size is not a multiple of num_attention_heads");
+    s.head_dim = s.hidden / s.heads;
+    s.rope = true;
+    if (c["rope_theta"].is_number()) s.rope_theta = static_cast<float>(c["rope_theta"].as_double());
+    else if (c["rope_parameters"]["rope_theta"].is_number()) s.rope_theta = static_cast<float>(c["rope_parameters"]["rope_theta"].as_double());
+    else throw TeiError(ERR_START, "Neither `rope_theta` nor `rope_parameters.rope_theta` are defined in the `config.json`");
+    if (c["rope_scaling"].is_object()) {
+      const std::string rt = c["rope_scaling"].get_string("type", c["rope_scaling"].get_string("rope_type", ""));
+      if (rt != "ntk") throw TeiError(ERR_START, "only the `ntk` rope_scaling of GTE is supported");
+      s.rope_ntk_factor = static_cast<float>(need_double(c["rope_scaling"], "factor"));
+    }
+    s.rope_table_len = s.max_pos;
+    s.nomic_max_pos = s.max_pos;
+    if (s.classifier) {
+      if (!c["id2label"].is_object()) throw TeiError(ERR_START, "`id2label` must be set for classifier models");
+      s.n_classes = static_cast<int>(c["id2label"].size());
+    }
   } else if (mt == "nomic_bert") {
     s.arch = ARCH_NOMIC;
     if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for Nomic");
@@ -543,7 +602,10 @@ void Replica::load_weights(const SafeTensors& st) {
   layers_.resize(spec_.layers);
   switch (spec_.arch) {
     case ARCH_BERT: load_bert(st); break;
-    case ARCH_NOMIC: load_nomic(st); break;
+    case ARCH_NOMIC:
+      if (spec_.gte) load_gte(st);
+      else load_nomic(st);
+      break;
     case ARCH_QWEN3:
       if (spec_.modernbert) load_modernbert(st);
       else load_qwen3(st);
@@ -554,6 +616,54 @@ void Replica::load_weights(const SafeTensors& st) {
 void Replica::load_bert(const SafeTensors& st) {
   const ModelSpec& s = spec_;
   const int H = s.hidden, I = s.inter;
+  if (s.distil) {
+    // flash_distilbert.rs:205-226: `embeddings` + `encoder`, `distilbert.embeddings` +
+    // `distilbert.transformer`, or `embeddings` + `transformer`.
+    std::string emb, enc;
+    if (st.contains("embeddings.word_embeddings.weight") && st.contains("encoder.layer.0.attention.q_lin.weight")) {
+      emb = "embeddings."; enc = "encoder.";
+    } else if (st.contains("distilbert.embeddings.word_embeddings.weight")) {
+      emb = "distilbert.embeddings."; enc = "distilbert.transformer.";
+    } else if (st.contains("embeddings.word_embeddings.weight")) {
+      emb = "embeddings."; enc = "transformer.";
+    } else {
+      throw TeiError(ERR_START, "cannot find tensor embeddings.word_embeddings.weight");
+    }
+    Names n{st, ""};
+    expect_shape(n.get(emb + "word_embeddings.weight"), {s.vocab, H}, emb + "word_embeddings.weight");
+    expect_shape(n.get(emb + "position_embeddings.weight"), {s.max_pos, H}, emb + "position_embeddings.weight");
+    word_ = upload_new(n.get(emb + "word_embeddings.weight"));
+    pos_tab_ = upload_new(n.get(emb + "position_embeddings.weight"));
+    emb_g_ = upload_new(n.ln_w(emb + "LayerNorm"));
+    emb_b_ = upload_new(n.ln_b(emb + "LayerNorm"));
+    for (int i = 0; i < s.layers; ++i) {
+      LayerW& L = layers_[i];
+      const std::string p = enc + "layer." + std::to_string(i) + ".";
+      L.wqkv = dev_alloc(static_cast<size_t>(3) * H * H * 2);
+      L.bqkv = dev_alloc(static_cast<size_t>(3) * H * 2);
+      const char* qkv[3] = {"q_lin", "k_lin", "v_lin"};
+      for (int j = 0; j < 3; ++j) {
+        const StTensor& w = n.get(p + "attention." + qkv[j] + ".weight");
+        expect_shape(w, {H, H}, p + "attention." + qkv[j] + ".weight");
+        upload(L.wqkv, static_cast<size_t>(j) * H * H, w);
+        upload(L.bqkv, static_cast<size_t>(j) * H, n.get(p + "attention." + qkv[j] + ".bias"));
+      }
+      expect_shape(n.get(p + "attention.out_lin.weight"), {H, H}, p + "attention.out_lin.weight");
+      L.wo = upload_new(n.get(p + "attention.out_lin.weight"));
+      L.bo = upload_new(n.get(p + "attention.out_lin.bias"));
+      L.ln1_g = upload_new(n.ln_w(p + "sa_layer_norm"));
+      L.ln1_b = upload_new(n.ln_b(p + "sa_layer_norm"));
+      expect_shape(n.get(p + "ffn.lin1.weight"), {I, H}, p + "ffn.lin1.weight");
+      L.w1 = upload_new(n.get(p + "ffn.lin1.weight"));
+      L.b1 = upload_new(n.get(p + "ffn.lin1.bias"));
+      expect_shape(n.get(p + "ffn.lin2.weight"), {H, I}, p + "ffn.lin2.weight");
+      L.w2 = upload_new(n.get(p + "ffn.lin2.weight"));
+      L.b2 = upload_new(n.get(p + "ffn.lin2.bias"));
+      L.ln2_g = upload_new(n.ln_w(p + "output_layer_norm"));
+      L.ln2_b = upload_new(n.ln_b(p + "output_layer_norm"));
+    }
+    return;
+  }
   // flash_bert.rs:264-279 (bert) and :331-356 (roberta family): bare names, then known prefixes.
   std::vector<std::string> cand = s.roberta ? std::vector<std::string>{"", "roberta.", "xlm-roberta.", "camembert."}
                                             : std::vector<std::string>{"", "bert."};
@@ -771,6 +881,59 @@ void Replica::load_nomic(const SafeTensors& st) {
   }
 }
 
+void Replica::load_gte(const SafeTensors& st) {
+  const ModelSpec& s = spec_;
+  const int H = s.hidden, I = s.inter;
+  // flash_gte.rs:197-199: names under `new.` or bare.
+  Names n{st, st.contains("new.embeddings.word_embeddings.weight") ? "new." : ""};
+  Names root{st, ""};
+  expect_shape(n.get("embeddings.word_embeddings.weight"), {s.vocab, H}, "embeddings.word_embeddings.weight");
+  word_ = upload_new(n.get("embeddings.word_embeddings.weight"));
+  if (s.type_vocab > 0) {
+    expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
+    type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
+  }
+  emb_g_ = upload_new(n.ln_w("embeddings.LayerNorm"));
+  emb_b_ = upload_new(n.ln_b("embeddings.LayerNorm"));
+  for (int i = 0; i < s.layers; ++i) {
+    LayerW& L = layers_[i];
+    const std::string p = "encoder.layer." + std::to_string(i) + ".";
+    expect_shape(n.get(p + "attention.qkv_proj.weight"), {3 * H, H}, p + "attention.qkv_proj.weight");
+    L.wqkv = upload_new(n.get(p + "attention.qkv_proj.weight"));
+    L.bqkv = upload_new(n.get(p + "attention.qkv_proj.bias"));
+    expect_shape(n.get(p + "attention.o_proj.weight"), {H, H}, p + "attention.o_proj.weight");
+    L.wo = upload_new(n.get(p + "attention.o_proj.weight"));
+    L.bo = upload_new(n.get(p + "attention.o_proj.bias"));
+    // mlp.up_gate_proj [2I, H]: rows [0, I) are `up`, rows [I, 2I) the gate that goes through the
+    // activation (gte.rs:219-226).
+    const StTensor& ug = n.get(p + "mlp.up_gate_proj.weight");
+    expect_shape(ug, {2 * I, H}, p + "mlp.up_gate_proj.weight");
+    StTensor up = ug, gate = ug;
+    up.shape = {I, H};
+    gate.shape = {I, H};
+    up.nbytes = gate.nbytes = ug.nbytes / 2;
+    gate.data = ug.data + ug.nbytes / 2;
+    L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+    upload_rows_interleaved(L.w1, gate, up);
+    expect_shape(n.get(p + "mlp.down_proj.weight"), {H, I}, p + "mlp.down_proj.weight");
+    L.w2 = upload_new(n.get(p + "mlp.down_proj.weight"));
+    L.b2 = upload_new(n.get(p + "mlp.down_proj.bias"));
+    L.ln1_g = upload_new(n.ln_w(p + "attn_ln"));
+    L.ln1_b = upload_new(n.ln_b(p + "attn_ln"));
+    L.ln2_g = upload_new(n.ln_w(p + "mlp_ln"));
+    L.ln2_b = upload_new(n.ln_b(p + "mlp_ln"));
+  }
+  if (s.classifier) {  // GTEClassificationHead, gte.rs:282-340: optional pooler.dense + tanh, classifier
+    if (n.has("pooler.dense.weight") && n.has("pooler.dense.bias")) {
+      cls_dense_w_ = upload_new(n.get("pooler.dense.weight"));
+      cls_dense_b_ = upload_new(n.get("pooler.dense.bias"));
+    }
+    expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
+    cls_out_w_ = upload_new(root.get("classifier.weight"));
+    cls_out_b_ = upload_new(root.get("classifier.bias"));
+  }
+}
+
 void Replica::load_qwen3(const SafeTensors& st) {
   const ModelSpec& s = spec_;
   const int H = s.hidden, I = s.inter, Q = s.q_width(), KV = s.kv_width();
@@ -883,6 +1046,14 @@ void Replica::build_rope_tables() {
   auto fill = [&](float base, float** d_cos, float** d_sin) {
     std::vector<float> inv(half);
     for (int i = 0; i < half; ++i) inv[i] = 1.0f / std::pow(base, static_cast<float>(2 * i) / static_cast<float>(dh));
+    if (spec_.rope_ntk_factor > 0.f) {
+      // RopeScaling::Ntk (layers/rotary.rs:86-93): base * factor, then divided by factor^(2 / dim)
+      const float f = spec_.rope_ntk_factor;
+      const float sdiv = std::pow(f, 2.0f / static_cast<float>(dh));
+      for (int i = 0; i < half; ++i) {
+        inv[i] = (1.0f / std::pow(base * f, static_cast<float>(2 * i) / static_cast<float>(dh))) / sdiv;
+      }
+    }
     std::vector<float> c(static_cast<size_t>(len) * half), s(static_cast<size_t>(len) * half);
     for (int p = 0; p < len; ++p) {
       for (int i = 0; i < half; ++i) {
@@ -1018,7 +1189,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   }
   // ALiBi models have no position table to index (flash_jina.rs never reads position_ids then).
   const uint32_t pos_limit = s.alibi ? 0xffffffffu : static_cast<uint32_t>(s.arch == ARCH_BERT ? s.max_pos : s.rope_table_len);
-  const bool use_types = s.arch != ARCH_QWEN3;
+  const bool use_types = s.arch != ARCH_QWEN3 && s.type_vocab > 0;  // DistilBERT and the decoders have no token types
   if (use_types && !b.token_type_ids) throw TeiError(ERR_INFERENCE, "null token_type_ids");
   for (size_t t = 0; t < b.n_tokens; ++t) {
     if (b.input_ids[t] >= static_cast<uint32_t>(s.vocab)) throw TeiError(ERR_INFERENCE, "input id out of the vocabulary");
@@ -1154,7 +1325,7 @@ void Replica::forward_bert() {
   const int T = static_cast<int>(T_), H = s.hidden, I = s.inter;
   int* status = reinterpret_cast<int*>(d_out_);
   EmbedArgs e;
-  e.ids = d_ids_; e.type_ids = d_types_; e.pos_ids = pos_tab_ ? d_pos_ : nullptr;
+  e.ids = d_ids_; e.type_ids = type_tab_ ? d_types_ : nullptr; e.pos_ids = pos_tab_ ? d_pos_ : nullptr;
   e.word = word_; e.type_tab = type_tab_; e.pos_tab = pos_tab_;
   e.gamma = emb_g_; e.beta = emb_b_; e.out = x_; e.T = T; e.H = H; e.eps = s.eps; e.dtype = s.dtype;
   LAUNCH(KC_EMBED, launch_embed_layernorm(e, stream_), "embeddings");
@@ -1249,7 +1420,7 @@ void Replica::forward_nomic() {
       LAUNCH(KC_POOL, launch_moe_combine(moe_yg_, moe_topk_e_, moe_topk_w_, moe_pos_, L.moe_bias, tmp_, T, K, H, cap, s.dtype, stream_), "expert combine");
     } else {
       if (s.gated) {
-        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, ACT_SWIGLU, s.dtype, status), stream_), "gated fc1");
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated fc1");
       } else {
         LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
       }

@@ -43,6 +43,9 @@ struct ModelSpec {
   Arch arch = ARCH_BERT;
   std::string model_type;
   bool roberta = false;
+  bool gte = false;        // GTE ("new"): post-LN blocks with RoPE and a gated feed-forward (models/flash_gte.rs)
+  float rope_ntk_factor = 0.f;  // RopeScaling::Ntk (layers/rotary.rs:86-93), 0: none
+  bool distil = false;     // DistilBERT: no token types, its own tensor names (models/flash_distilbert.rs)
   bool jina = false;       // JinaBERT: gated feed-forward, optional ALiBi (models/flash_jina.rs)
   bool alibi = false;      // ALiBi slopes instead of a position table
   int hidden = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, inter = 0;
@@ -179,6 +182,7 @@ class Replica {
   void load_nomic(const SafeTensors& st);
   void load_qwen3(const SafeTensors& st);
   void load_modernbert(const SafeTensors& st);
+  void load_gte(const SafeTensors& st);
   void build_rope_tables();
   void* dev_alloc(size_t bytes);
   // Converts `src` (any float dtype) into the model dtype at dst + dst_elem_off elements.
