@@ -306,7 +306,9 @@ def run_kernel(args):
             fn = lambda: ops.attention(q, k, v, cu, causal=causal, work=work, out=out, status=st)  # noqa: E731
             flops = (2.0 if causal else 4.0) * nh * D * float(sum(n * (n + 1) if causal else n * n for n in lens))
             bytes_ = 2.0 * T * (2 * nh + 2 * nkv) * D
-    elif name == "add_layernorm":
+    elif name in ("add_layernorm", "add_layernorm_h1024"):
+        if name.endswith("h1024"):  # the XLM-RoBERTa-large / Qwen3 width at the cfg4 token count
+            T, H = 153855, 1024
         x, r, gm, bt = rnd(T, H), rnd(T, H), rnd(H), rnd(H)
         fn = lambda: ops.add_layernorm(x, r, gm, bt, 1e-12)  # noqa: E731
         bytes_ = 3.0 * T * H * 2
@@ -457,7 +459,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
-                         "attention_long | attention_causal128 | rope_qwen3 | add_layernorm | pool_mean")
+                         "attention_long | attention_causal128 | rope_qwen3 | add_layernorm | add_layernorm_h1024 | pool_mean")
     ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
     ap.add_argument("--dtype", default=None, choices=["float16", "bfloat16"],

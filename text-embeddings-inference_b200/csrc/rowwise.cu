@@ -179,7 +179,7 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
 // F32RES: the residual is fp32 and the sum is written back in fp32 (the pre-norm models: RMSNorm
 // decoders, and ModernBERT with LayerNorm).  gamma == nullptr: no normalisation, out = sum.
 template <class T, int MAXC, bool RMS, bool F32RES>
-__global__ void __launch_bounds__(256, (MAXC <= 3 ? 6 : 1))
+__global__ void __launch_bounds__(256, (MAXC <= 3 ? 6 : (MAXC == 4 ? 4 : 1)))
 add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restrict__ gamma,
                 const T* __restrict__ beta, T* __restrict__ out, float* sum_out, int T_, int H,
                 float eps) {  // residual and sum_out may be the same buffer: no __restrict__
