@@ -17,6 +17,10 @@ What is restated (file:line in the reference):
       :474-573, block (post-LN) :605-626; rotary layers/rotary.rs:29-130
   Qwen3                   models/qwen3.rs  attention :137-271, layer :360-385, pooling :639-714;
       RMSNorm layers/rms_norm.rs:30-57
+  further families        JinaBERT models/jina.rs + flash_jina.rs; ModernBERT models/modernbert.rs +
+      flash_modernbert.rs; DistilBERT models/distilbert.rs; GTE models/gte.rs; Qwen2 / Mistral /
+      Llama flash_qwen2.rs, flash_mistral.rs; NomicBERT mixture of experts models/nomic.rs:205-421;
+      Dense modules models/dense.rs - each class below cites its lines
   shared                  LayerNorm layers/layer_norm.rs:108-132; Linear + activations
       layers/linear.rs:5-29,77-101 (every GELU name means the tanh approximation)
   host post-processing    core/src/infer.rs:288-303 (L2 normalise in f64), :458-480 (sigmoid)
