@@ -89,3 +89,69 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cpp", ".cu", ".h", ".cuh", ".rs")):
                 text = open(os.path.join(dirpath, f), errors="replace").read()
                 assert "import oracle" not in text and "from oracle" not in text, os.path.join(dirpath, f)
+
+
+def _start_error(tmp_path, cfg, **kw):
+    import json
+    import tei_b200
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    with pytest.raises(tei_b200.BackendError) as e:
+        tei_b200.B200Backend(tmp_path, **kw)
+    return e.value
+
+
+def test_config_dispatch_refusals_follow_the_reference(lib, tmp_path):
+    """The architecture dispatch and its refusals happen on the host, before any device is
+    touched, so they are checked here without a GPU: every case must end as the error the
+    reference gives, or as 'weights not found' once the config itself was accepted."""
+    from oracle import generators as G
+    # accepted configs of every family get as far as looking for the weights
+    for cfg, kw in [
+        (G.bert_config(), {}),
+        (G.jina_config(alibi=True), dict(pool="mean")),
+        (G.nomic_config(), dict(pool="mean")),
+        (G.nomic_config(moe_every=2), dict(pool="mean")),
+        (G.qwen3_config(), dict(pool="last_token")),
+        (G.qwen2_config(), dict(pool="last_token")),
+        (G.mistral_config(), dict(pool="last_token")),
+        (G.mistral_config(model_type="llama"), dict(pool="mean")),
+        (G.modernbert_config(), dict(pool="mean")),
+        (G.modernbert_config(num_labels=2), dict(model_type="classifier")),
+        (G.distilbert_config(), dict(pool="mean")),
+        (G.gte_config(), dict(pool="cls")),
+    ]:
+        err = _start_error(tmp_path, cfg, **kw)
+        assert err.kind == "WeightsNotFound", (cfg["model_type"], str(err))
+    # refusals (file:line of the reference's bail! in each message's origin)
+    e = _start_error(tmp_path, dict(G.jina_config(), _name_or_path="jinaai/jina-bert-v2-qk-post-norm",
+                                    auto_map={"AutoConfig": "jinaai/jina-bert-v2-qk-post-norm--configuration_bert.JinaBertConfig"}))
+    assert e.kind == "Start" and "JinaCodeBert" in str(e)
+    e = _start_error(tmp_path, G.jina_config(), pool="splade")          # flash_jina.rs:262-264
+    assert "`splade` is not supported for Jina" in str(e)
+    e = _start_error(tmp_path, dict(G.bert_config(), position_embedding_type="relative_key"))  # flash_bert.rs:241-243
+    assert "absolute position embeddings" in str(e)
+    e = _start_error(tmp_path, G.qwen3_config(), model_type="classifier")  # flash_qwen3.rs:312-316
+    assert "`classifier` model type is not supported for Qwen3" in str(e)
+    e = _start_error(tmp_path, dict(G.qwen2_config(), use_sliding_window=True), pool="mean")  # flash_qwen2.rs:26-29
+    assert "Sliding window is not supported for Qwen2" in str(e)
+    e = _start_error(tmp_path, dict(G.mistral_config(model_type="llama"), rope_scaling={"rope_type": "llama3", "factor": 8.0}),
+                     pool="mean")                                         # backends/candle/src/lib.rs:549-553
+    assert "Rope scaling is not supported for FlashLlama yet" in str(e)
+    e = _start_error(tmp_path, G.modernbert_config(), pool="splade")     # flash_modernbert.rs:270-272
+    assert "`splade` is not supported for ModernBert" in str(e)
+    e = _start_error(tmp_path, dict(G.gte_config(), logn_attention_scale=True))  # flash_gte.rs:180-182
+    assert "`logn_attention_scale` is not supported" in str(e)
+    e = _start_error(tmp_path, dict(G.gte_config(), position_embedding_type="absolute"))  # flash_gte.rs:184-186
+    assert "Only `PositionEmbeddingType::Rope` is supported" in str(e)
+    e = _start_error(tmp_path, G.distilbert_config(), model_type="classifier")  # flash_distilbert.rs:199-201
+    assert "`classifier` model type is not supported for DistilBert" in str(e)
+    e = _start_error(tmp_path, dict(G.nomic_config(), prenorm=True), pool="mean")  # nomic.rs:49-54
+    assert "config is not supported" in str(e)
+    e = _start_error(tmp_path, dict(G.nomic_config(moe_every=2), num_experts=128), pool="mean")
+    assert "mixture of experts" in str(e)
+    cfg = G.qwen3_config()
+    del cfg["rope_theta"]                                                 # flash_qwen3.rs:360-366
+    e = _start_error(tmp_path, cfg, pool="last_token")
+    assert "Neither `rope_theta` nor `rope_parameters.rope_theta`" in str(e)
+    e = _start_error(tmp_path, G.bert_config(id2label=None), model_type="classifier")  # bert.rs:376-379
+    assert "`id2label` must be set" in str(e)
