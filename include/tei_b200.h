@@ -103,6 +103,31 @@ int tei_b200_predict(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* t
                      const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
                      float* scores_out, char* err, size_t err_cap);
 
+/* Several batches in flight, one per replica.  The reference runs exactly one backend thread
+ * that takes one command at a time from a channel (backends/src/lib.rs:612-647), so a second
+ * batch waits in core/src/infer.rs:547-625 while the first one computes.  A host that wants N
+ * batches in flight starts N such threads over one handle created with N devices (the same
+ * index may be listed twice: two replicas on one GPU overlap one batch's copies and host work
+ * with the other's kernels) and gives thread i the replica index i:
+ *   tei_b200_num_replicas : how many replicas the handle owns;
+ *   tei_b200_embed_on / tei_b200_predict_on : embed / predict with the WHOLE batch on that one
+ *       replica; same arguments, results and error codes as tei_b200_embed / tei_b200_predict.
+ * Calls with different replica indices may run concurrently; calls with the same index are
+ * serialised inside the library.  They do not touch the staged-batch state of the handle, but
+ * must not overlap with the whole-handle calls (embed, predict, stage, run, sync, fetch), which
+ * use every replica. */
+int tei_b200_num_replicas(const tei_b200_t* h);
+int tei_b200_embed_on(tei_b200_t* h, int replica, const uint32_t* input_ids,
+                      const uint32_t* token_type_ids, const uint32_t* position_ids, size_t n_tokens,
+                      const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                      const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx,
+                      size_t n_raw, int normalize, float* pooled_out, float* raw_out, char* err,
+                      size_t err_cap);
+int tei_b200_predict_on(tei_b200_t* h, int replica, const uint32_t* input_ids,
+                        const uint32_t* token_type_ids, const uint32_t* position_ids, size_t n_tokens,
+                        const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                        float* scores_out, char* err, size_t err_cap);
+
 /* The three phases of embed / predict, exposed separately so that a caller can keep a batch
  * resident in HBM and time the forward alone.  No counterpart in the reference, whose forward
  * always uploads its inputs (flash_bert.rs:376-383).

@@ -6,8 +6,11 @@
 #include "plan.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <fstream>
+#include <memory>
+#include <mutex>
 #include <sstream>
 #include <thread>
 
@@ -49,7 +52,11 @@ struct tei_b200 {
   ModelSpec spec;
   std::string model_dir;
   std::vector<std::unique_ptr<Replica>> replicas;
-  bool healthy = true;
+  // One lock per replica: the per-replica entry points (one caller thread per replica) take it,
+  // so two threads that were given the same index by mistake queue up instead of corrupting the
+  // replica's staging buffers.
+  std::vector<std::unique_ptr<std::mutex>> replica_locks;
+  std::atomic<bool> healthy{true};
   // state of the staged batch (stage / run / sync / fetch)
   bool staged = false;
   bool staged_predict = false;
@@ -322,6 +329,7 @@ int tei_b200_create(const char* model_dir, const char* dtype, int model_type, in
     for (int dv : devs) {
       if (dv < 0 || dv >= count) throw TeiError(ERR_START, "CUDA device index out of range");
       h->replicas.emplace_back(new Replica(dv, h->spec, st));
+      h->replica_locks.emplace_back(new std::mutex());
     }
     // Cost model of the sharding: FLOPs per token of the dense layers, FLOPs per token^2 of
     // attention (half of it when causal).
@@ -417,6 +425,52 @@ int tei_b200_predict(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* t
     do_stage(h, b, true, false);
     do_run(h);
     do_fetch(h, nullptr, nullptr, scores_out);
+  });
+}
+
+int tei_b200_num_replicas(const tei_b200_t* h) { return h ? static_cast<int>(h->replicas.size()) : 0; }
+
+// The whole batch on one replica.  Nothing of the handle's own staged-batch state is touched, so
+// calls with different replica indices may run at the same time from different threads.
+int tei_b200_embed_on(tei_b200_t* h, int replica, const uint32_t* input_ids,
+                      const uint32_t* token_type_ids, const uint32_t* position_ids, size_t n_tokens,
+                      const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                      const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx,
+                      size_t n_raw, int normalize, float* pooled_out, float* raw_out, char* err,
+                      size_t err_cap) {
+  if (!h) return TEI_B200_ERR_UNHEALTHY;
+  return guarded(h, err, err_cap, [&]() {
+    if (replica < 0 || replica >= static_cast<int>(h->replicas.size())) throw TeiError(ERR_INFERENCE, "replica index out of range");
+    if (h->spec.classifier) throw TeiError(ERR_INFERENCE, "`embed` is not implemented for classifier models");
+    if ((n_pooled && !pooled_out) || (n_raw && !raw_out)) throw TeiError(ERR_INFERENCE, "null output buffer");
+    HostBatch b = make_batch(input_ids, token_type_ids, position_ids, n_tokens, cumulative_seq_lengths,
+                             n_seqs, max_length, pooled_idx, n_pooled, raw_idx, n_raw);
+    precheck(b);
+    std::lock_guard<std::mutex> lock(*h->replica_locks[replica]);
+    Replica& r = *h->replicas[replica];
+    r.stage(b, false, normalize != 0);
+    r.run();
+    r.fetch(pooled_out, raw_out, nullptr);
+  });
+}
+
+int tei_b200_predict_on(tei_b200_t* h, int replica, const uint32_t* input_ids,
+                        const uint32_t* token_type_ids, const uint32_t* position_ids, size_t n_tokens,
+                        const uint32_t* cumulative_seq_lengths, size_t n_seqs, uint32_t max_length,
+                        float* scores_out, char* err, size_t err_cap) {
+  if (!h) return TEI_B200_ERR_UNHEALTHY;
+  return guarded(h, err, err_cap, [&]() {
+    if (replica < 0 || replica >= static_cast<int>(h->replicas.size())) throw TeiError(ERR_INFERENCE, "replica index out of range");
+    if (!h->spec.classifier) throw TeiError(ERR_INFERENCE, "`predict` is not implemented for this model");
+    if (!scores_out) throw TeiError(ERR_INFERENCE, "null output buffer");
+    HostBatch b = make_batch(input_ids, token_type_ids, position_ids, n_tokens, cumulative_seq_lengths,
+                             n_seqs, max_length, nullptr, 0, nullptr, 0);
+    precheck(b);
+    std::lock_guard<std::mutex> lock(*h->replica_locks[replica]);
+    Replica& r = *h->replicas[replica];
+    r.stage(b, true, false);
+    r.run();
+    r.fetch(nullptr, nullptr, scores_out);
   });
 }
 

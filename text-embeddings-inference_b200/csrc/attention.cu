@@ -8,11 +8,11 @@
 // i - window_left <= j <= i + window_right (causal: right window 0).  Q, K and V are strided
 // views of the projection output (token-major rows), exactly as the reference passes them.
 //
-// Persistent CTAs (two per SM for D = 64, one for D = 128) walk the (sequence, 128-row query
+// Persistent CTAs (two per SM) walk the (sequence, 128-row query
 // tile, head) work units, sorted by cost and handed out in alternating direction, in steps of
 // 64 keys.  Everything a step needs is multi-buffered (AttnCfg), so the three roles of a CTA
 // run decoupled:
-//   warp 5 (one lane)  TMA producer: Q tile per unit, K/V tiles per step (KV_STAGES stages),
+//   warp 5 (one lane)  TMA producer: Q tile per unit, K and V tiles per step into two rings,
 //                      128-byte swizzle, plain per-CTA loads (no cluster multicast); runs ahead
 //                      of the MMAs by the free stages and, with two Q buffers, by one unit.
 //   warp 4 (one lane)  MMA issuer, polling two streams: S = Q K^T of a step into one of S_BUFS
@@ -41,19 +41,31 @@ constexpr int BQ = 128;  // query rows per CTA
 constexpr int BKV = 64;  // keys per step
 constexpr int ATTN_THREADS = 192;
 
-// Depth of the pipeline per head size.  What bounds the kernel is the latency of the chain
-// "S MMA -> commit -> softmax -> P -> P V MMA" of one step, so the number of steps in flight
-// (score tiles in TMEM) decides the throughput.  D = 64: two CTAs per SM with 256 TMEM columns
-// each hold two score tiles and two output tiles; D = 128: one CTA per SM (shared memory) has
-// all 512 columns: four score tiles and one output tile.
+// Depth of the pipeline per head size.  A softmax warp needs about 1,800 cycles for the 64 keys
+// of a step (512 of them on the exp2 unit alone), the tensor pipe 320 (D = 64) to 640 (D = 128):
+// what bounds the kernel is how many softmax warps an SM keeps busy, so both head sizes run two
+// CTAs per SM (eight softmax warps, two per scheduler), each with half of the TMEM columns and
+// of the shared memory.  D = 64: two score tiles, two output tiles, two Q buffers, three K/V
+// stages.  D = 128: two score tiles, one output tile, one Q buffer and only two K and two V
+// stages (112 KB per CTA), which is enough because the K ring is released early (see K_EARLY).
 template <int D>
 struct AttnCfg {
-  static constexpr int S_BUFS = (D == 64) ? 2 : 4;     // score / P tiles of 64 columns
+  static constexpr int S_BUFS = 2;                     // score / P tiles of 64 columns
   static constexpr int O_BUFS = (D == 64) ? 2 : 1;     // output tiles of D columns
   static constexpr int Q_BUFS = (D == 64) ? 2 : 1;
-  static constexpr int KV_STAGES = S_BUFS + 1;         // the steps in flight plus one being loaded
-  static constexpr int CTAS_PER_SM = (D == 64) ? 2 : 1;
-  static constexpr uint32_t TMEM_COLS = (D == 64) ? 256 : 512;
+  // K and V tiles live in two rings of their own: a K tile is free again as soon as the S MMA
+  // that read it is done, long before the P V of the same step releases the V tile, so with
+  // separate rings two stages each already let the next K arrive a whole step early.
+  static constexpr int K_STAGES = (D == 64) ? 3 : 2;
+  static constexpr int V_STAGES = (D == 64) ? 3 : 2;
+  // With more stages than score tiles (D = 64) the early release buys nothing and its extra
+  // tcgen05.commit per step costs issue time: there a K tile is released together with the V
+  // tile of its step and both are loaded in the same turn.
+  static constexpr bool K_EARLY = K_STAGES <= S_BUFS;
+  static constexpr int K_LEAD = K_EARLY ? 1 : 0;       // steps K is loaded ahead of V
+  static_assert(K_EARLY || K_STAGES == V_STAGES, "shared release needs rings of one length");
+  static constexpr int CTAS_PER_SM = 2;
+  static constexpr uint32_t TMEM_COLS = 256;
   static_assert(S_BUFS * BKV + O_BUFS * D <= TMEM_COLS, "TMEM budget");
 };
 
@@ -65,12 +77,12 @@ struct AttnSmem {
   static constexpr int STAGE_BYTES = BQ * 128;   // output rows, 64 columns at a time
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + C::Q_BUFS * Q_BYTES;
-  static constexpr int OFF_V = OFF_K + C::KV_STAGES * KV_BYTES;
-  static constexpr int OFF_STAGE = OFF_V + C::KV_STAGES * KV_BYTES;
+  static constexpr int OFF_V = OFF_K + C::K_STAGES * KV_BYTES;
+  static constexpr int OFF_STAGE = OFF_V + C::V_STAGES * KV_BYTES;
   static constexpr int OFF_BAR = OFF_STAGE + STAGE_BYTES;
   // No alignment slack: two CTAs of the D = 64 variant must fit in one SM's shared memory.  The
   // kernel checks that the dynamic window is 1024-byte aligned and reports an error otherwise.
-  static constexpr int TOTAL = OFF_BAR + 256;  // up to 26 mbarriers + the TMEM address slot
+  static constexpr int TOTAL = OFF_BAR + 320;  // 32 mbarrier slots + the TMEM address slot
   static_assert(C::CTAS_PER_SM * (TOTAL + 1024) <= 228 * 1024, "shared memory budget");
 };
 
@@ -213,16 +225,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     return;
   }
   using C = AttnCfg<D>;
-  constexpr int S_BUFS = C::S_BUFS, O_BUFS = C::O_BUFS, Q_BUFS = C::Q_BUFS, KV_STAGES = C::KV_STAGES;
+  constexpr int S_BUFS = C::S_BUFS, O_BUFS = C::O_BUFS, Q_BUFS = C::Q_BUFS;
+  constexpr int K_STAGES = C::K_STAGES, V_STAGES = C::V_STAGES;
+  static_assert(Q_BUFS <= 2 && K_STAGES <= 4 && V_STAGES <= 4 && S_BUFS <= 4, "barrier slots");
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-  uint64_t* bar_q = bars;             // [Q_BUFS <= 2] Q buffer landed
+  uint64_t* bar_q = bars;             // [Q_BUFS] Q buffer landed
   uint64_t* bar_qfree = bars + 2;     // [Q_BUFS] last S of the unit that used the Q buffer is done
-  uint64_t* bar_kv = bars + 4;        // [KV_STAGES <= 5] K/V stage landed
-  uint64_t* bar_kvfree = bars + 9;    // [KV_STAGES] the P V that read the stage is done
-  uint64_t* bar_s = bars + 14;        // [S_BUFS <= 4] score tile holds the scores of its step
-  uint64_t* bar_p = bars + 18;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
-  uint64_t* bar_pv = bars + 22;       // [S_BUFS] the P V of the step is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
+  uint64_t* bar_k = bars + 4;         // [K_STAGES] K tile landed
+  uint64_t* bar_kfree = bars + 8;     // [K_STAGES] the S MMA that read the K tile is done
+  uint64_t* bar_v = bars + 12;        // [V_STAGES] V tile landed
+  uint64_t* bar_vfree = bars + 16;    // [V_STAGES] the P V that read the V tile is done
+  uint64_t* bar_s = bars + 20;        // [S_BUFS] score tile holds the scores of its step
+  uint64_t* bar_p = bars + 24;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
+  uint64_t* bar_pv = bars + 28;       // [S_BUFS] the P V of the step is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   constexpr uint32_t TMEM_COLS = C::TMEM_COLS;
 
   const int warp = threadIdx.x >> 5;
@@ -239,9 +255,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       ptx::mbar_init(&bar_p[i], 4);
       ptx::mbar_init(&bar_pv[i], 1);
     }
-    for (int i = 0; i < KV_STAGES; ++i) {
-      ptx::mbar_init(&bar_kv[i], 1);
-      ptx::mbar_init(&bar_kvfree[i], 1);
+    for (int i = 0; i < K_STAGES; ++i) {
+      ptx::mbar_init(&bar_k[i], 1);
+      ptx::mbar_init(&bar_kfree[i], 1);
+    }
+    for (int i = 0; i < V_STAGES; ++i) {
+      ptx::mbar_init(&bar_v[i], 1);
+      ptx::mbar_init(&bar_vfree[i], 1);
     }
     ptx::fence_mbar_init();
   }
@@ -276,6 +296,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     return static_cast<int>(n) * G + ((n & 1u) ? G - 1 - b : b);
   };
 
+  // A cursor walks the CTA's key steps in order, across unit boundaries.  Each role keeps its
+  // own: steps are handed from role to role through the barriers only.
+  struct Cursor {
+    int w, j, n_kv;
+    uint32_t n;
+    const int* it;
+  };
+  auto load_unit = [&](Cursor& c) {
+    if (c.w < total) {
+      c.it = p.work + (c.w / p.n_heads) * 4;
+      c.n_kv = unit_steps(c.it);
+    }
+  };
+  auto advance = [&](Cursor& c) {
+    if (++c.j == c.n_kv) {
+      ++c.n;
+      c.w = unit_at(c.n);
+      c.j = 0;
+      load_unit(c);
+    }
+  };
+
   // The CTA is persistent: it walks the work units unit_at(0), unit_at(1), ...
   // `g` counts key steps over the CTA's whole life, `n` counts units; they drive every buffer
   // index and barrier parity in all three roles.
@@ -285,41 +327,71 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       ptx::prefetch_tmap(&tm_q);
       ptx::prefetch_tmap(&tm_k);
       ptx::prefetch_tmap(&tm_v);
-      uint32_t g = 0, n = 0;
+      // K runs one step ahead of V: K of step t (and Q, at the first step of a unit), then V of
+      // step t - 1.  K(t) only waits for the S MMA of step t - K_STAGES, V(t) for the P V of
+      // step t - V_STAGES, which finishes a whole softmax later.
+      Cursor ck{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cv = ck;
+      load_unit(ck);
+      load_unit(cv);
+      uint32_t gk = 0, gv = 0;
+      int k_col = 0, v_col = 0;  // first column of the unit's K / V head (divisions once per unit)
       bool ok = true;
-      for (int w = unit_at(n); w < total && ok; w = unit_at(++n)) {
-        const int* it = p.work + (w / p.n_heads) * 4;
-        const int head = w % p.n_heads;
-        const int kv_head = head / group;
-        const int n_kv = unit_steps(it);
-        // Q of this unit into buffer n % Q_BUFS, once the unit that used it before is past its
-        // last S.
-        const int qb = n % Q_BUFS;
-        if (n >= Q_BUFS) {
-          ok = ptx::mbar_wait(&bar_qfree[qb], ((n / Q_BUFS) - 1) & 1);
-          if (!ok) break;
-        }
-        ptx::mbar_expect_tx(&bar_q[qb], L::Q_BYTES);
+      while (cv.w < total && ok) {
+        // The cursors move on only after both loads of the turn are out: at a unit boundary
+        // that reads the next work item from global memory.
+        const bool do_k = ck.w < total && gk <= gv + C::K_LEAD;
+        if (do_k) {
+          if (ck.j == 0) {
+            const int head = ck.w % p.n_heads;
+            k_col = (head / group) * D;
+            // Q of this unit into buffer n % Q_BUFS, once the unit that used it before is past
+            // its last S.
+            const int qb = ck.n % Q_BUFS;
+            if (ck.n >= Q_BUFS) {
+              ok = ptx::mbar_wait(&bar_qfree[qb], ((ck.n / Q_BUFS) - 1) & 1);
+              if (!ok) break;
+            }
+            ptx::mbar_expect_tx(&bar_q[qb], L::Q_BYTES);
 #pragma unroll
-        for (int a = 0; a < D_ATOMS; ++a) {
-          ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * 128), &tm_q, &bar_q[qb],
-                           head * D + a * 64, it[0] + it[2]);
-        }
-        for (int j = 0; j < n_kv && ok; ++j, ++g) {
-          const int st = g % KV_STAGES;
-          if (g >= KV_STAGES) {
-            ok = ptx::mbar_wait(&bar_kvfree[st], ((g / KV_STAGES) - 1) & 1);
+            for (int a = 0; a < D_ATOMS; ++a) {
+              ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * 128), &tm_q, &bar_q[qb],
+                               head * D + a * 64, ck.it[0] + ck.it[2]);
+            }
+          }
+          const int st = gk % K_STAGES;
+          if (gk >= K_STAGES) {
+            ok = ptx::mbar_wait(C::K_EARLY ? &bar_kfree[st] : &bar_vfree[st], ((gk / K_STAGES) - 1) & 1);
             if (!ok) break;
           }
-          ptx::mbar_expect_tx(&bar_kv[st], 2 * L::KV_BYTES);
+          // shared release: the V tile of the step follows in the same turn on the same barrier
+          ptx::mbar_expect_tx(&bar_k[st], C::K_EARLY ? L::KV_BYTES : 2 * L::KV_BYTES);
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
-            ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_kv[st],
-                             kv_head * D + a * 64, it[0] + it[3] + j * BKV);
-            ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, &bar_kv[st],
-                             kv_head * D + a * 64, it[0] + it[3] + j * BKV);
+            ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_k[st],
+                             k_col + a * 64, ck.it[0] + ck.it[3] + ck.j * BKV);
           }
+          ++gk;
         }
+        const bool do_v = gv < gk && (gk > gv + C::K_LEAD || !do_k);
+        if (do_v) {
+          if (C::K_LEAD == 0) v_col = k_col;  // same step, same head
+          else if (cv.j == 0) v_col = ((cv.w % p.n_heads) / group) * D;
+          const int st = gv % V_STAGES;
+          if (gv >= V_STAGES) {
+            ok = ptx::mbar_wait(&bar_vfree[st], ((gv / V_STAGES) - 1) & 1);
+            if (!ok) break;
+          }
+          uint64_t* landed = C::K_EARLY ? &bar_v[st] : &bar_k[st];
+          if (C::K_EARLY) ptx::mbar_expect_tx(landed, L::KV_BYTES);
+#pragma unroll
+          for (int a = 0; a < D_ATOMS; ++a) {
+            ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, landed,
+                             v_col + a * 64, cv.it[0] + cv.it[3] + cv.j * BKV);
+          }
+          ++gv;
+        }
+        if (do_k) advance(ck);
+        if (do_v) advance(cv);
       }
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
@@ -334,32 +406,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
       const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
       const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
-      // Two cursors walk the CTA's steps: `cs` is the next step whose S = Q K^T is to be issued,
-      // `cp` the next step whose O (+)= P V is.  S runs up to S_BUFS - 1 steps ahead of P V, across
-      // unit boundaries; whichever of the two has its inputs ready is issued next.
-      struct Cursor {
-        int w, j, n_kv;
-        uint32_t n;
-        const int* it;
-      };
-      auto load_unit = [&](Cursor& c) {
-        if (c.w < total) {
-          c.it = p.work + (c.w / p.n_heads) * 4;
-          c.n_kv = unit_steps(c.it);
-        }
-      };
-      auto advance = [&](Cursor& c) {
-        if (++c.j == c.n_kv) {
-          ++c.n;
-          c.w = unit_at(c.n);
-          c.j = 0;
-          load_unit(c);
-        }
-      };
       Cursor cs{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cp = cs;
       load_unit(cs);
       load_unit(cp);
       uint32_t gs = 0, g = 0;  // steps whose S / P V has been issued
+      uint32_t gvr = 0;        // steps whose V tile is known to have landed (own barrier only)
       uint32_t idle = 0;
       bool ok = true;
       while (cp.w < total) {
@@ -369,14 +420,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (cs.w < total && gs < g + S_BUFS) {
           const int qb = cs.n % Q_BUFS;
           const bool ready = (cs.j != 0 || ptx::mbar_test_wait(&bar_q[qb], (cs.n / Q_BUFS) & 1)) &&
-                             ptx::mbar_test_wait(&bar_kv[gs % KV_STAGES], (gs / KV_STAGES) & 1);
+                             ptx::mbar_test_wait(&bar_k[gs % K_STAGES], (gs / K_STAGES) & 1);
           if (ready) {
             ptx::tc_fence_after();
             const int keys = keys_in_tile(cs.it, cs.j);
             // only ceil(keys / 16) * 16 columns are computed
             const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 15) / 16) * 16, 0, 0);
             const uint64_t dqs = dq + static_cast<uint64_t>((qb * L::Q_BYTES) >> 4);
-            const uint64_t dks = dk + static_cast<uint64_t>(((gs % KV_STAGES) * L::KV_BYTES) >> 4);
+            const uint64_t dks = dk + static_cast<uint64_t>(((gs % K_STAGES) * L::KV_BYTES) >> 4);
             const uint32_t d_s = tmem_base + (gs % S_BUFS) * BKV;
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
@@ -385,6 +436,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
             }
             ptx::umma_commit(&bar_s[gs % S_BUFS]);
+            if (C::K_EARLY) ptx::umma_commit(&bar_kfree[gs % K_STAGES]);
             if (cs.j + 1 == cs.n_kv) ptx::umma_commit(&bar_qfree[qb]);  // last S of the unit
             ++gs;
             advance(cs);
@@ -392,12 +444,18 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
         // O (+)= P V of step g, once its P is written.
-        if (g < gs && ptx::mbar_test_wait(&bar_p[g % S_BUFS], (g / S_BUFS) & 1)) {
+        // V's own barrier is looked at while P is still being written, not after it.
+        if (C::K_EARLY && gvr == g && g < gs &&
+            ptx::mbar_test_wait(&bar_v[g % V_STAGES], (g / V_STAGES) & 1)) {
+          ++gvr;
+        }
+        if (g < gs && (!C::K_EARLY || g < gvr) &&
+            ptx::mbar_test_wait(&bar_p[g % S_BUFS], (g / S_BUFS) & 1)) {
           ptx::tc_fence_after();
           const int k_steps = (keys_in_tile(cp.it, cp.j) + 15) / 16;
           const uint32_t tmem_o = tmem_o0 + (cp.n % O_BUFS) * D;
           const uint32_t t_p = tmem_base + (g % S_BUFS) * BKV;  // P lies over the scores of the step
-          const uint64_t dvs = dv + static_cast<uint64_t>(((g % KV_STAGES) * L::KV_BYTES) >> 4);
+          const uint64_t dvs = dv + static_cast<uint64_t>(((g % V_STAGES) * L::KV_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
             if (k < k_steps) {
@@ -406,7 +464,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
           }
           ptx::umma_commit(&bar_pv[g % S_BUFS]);
-          ptx::umma_commit(&bar_kvfree[g % KV_STAGES]);
+          ptx::umma_commit(&bar_vfree[g % V_STAGES]);
           ++g;
           advance(cp);
           progress = true;

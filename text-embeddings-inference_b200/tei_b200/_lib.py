@@ -64,6 +64,13 @@ _BACKEND_PROTOTYPES = {
                                POINTER(c_float), POINTER(c_float), c_char_p, c_size_t],
     ),
     "tei_b200_predict": (c_int, [c_void_p] + _BATCH + [POINTER(c_float), c_char_p, c_size_t]),
+    "tei_b200_num_replicas": (c_int, [c_void_p]),
+    "tei_b200_embed_on": (
+        c_int,
+        [c_void_p, c_int] + _BATCH + [POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int,
+                                      POINTER(c_float), POINTER(c_float), c_char_p, c_size_t],
+    ),
+    "tei_b200_predict_on": (c_int, [c_void_p, c_int] + _BATCH + [POINTER(c_float), c_char_p, c_size_t]),
     "tei_b200_stage": (
         c_int,
         [c_void_p] + _BATCH + [POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int, c_int,

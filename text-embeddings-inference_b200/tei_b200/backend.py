@@ -129,7 +129,15 @@ class B200Backend:
         raw = _u32(batch.raw_indices)
         return ids, types, pos, cu, pooled, raw
 
-    def embed(self, batch, normalize: bool = False) -> Dict[int, Embedding]:
+    @property
+    def num_replicas(self) -> int:
+        return int(self._lib.tei_b200_num_replicas(self._h))
+
+    def embed(self, batch, normalize: bool = False, replica: Optional[int] = None) -> Dict[int, Embedding]:
+        """`replica=None`: the batch is split over every replica of the handle (one caller at a
+        time).  `replica=i`: the whole batch runs on replica i; callers with different indices may
+        run at the same time from different threads (one backend thread per replica instead of the
+        single one of backends/src/lib.rs:612-647)."""
         ids, types, pos, cu, pooled, raw = self._arrays(batch)
         n_seqs = len(cu) - 1
         lengths = (cu[1:].astype(np.int64) - cu[:-1].astype(np.int64))
@@ -138,10 +146,13 @@ class B200Backend:
         raw_out = np.empty((raw_rows, self.hidden_size), dtype=np.float32)
         err = ctypes.create_string_buffer(1024)
         c_u32, c_f = ctypes.c_uint32, ctypes.c_float
-        rc = self._lib.tei_b200_embed(
-            self._h, _ptr(ids, c_u32), _ptr(types, c_u32), _ptr(pos, c_u32), ids.size, _ptr(cu, c_u32),
-            n_seqs, int(batch.max_length), _ptr(pooled, c_u32), pooled.size, _ptr(raw, c_u32), raw.size,
-            int(normalize), _ptr(pooled_out, c_f), _ptr(raw_out, c_f), err, len(err))
+        tail = (_ptr(ids, c_u32), _ptr(types, c_u32), _ptr(pos, c_u32), ids.size, _ptr(cu, c_u32),
+                n_seqs, int(batch.max_length), _ptr(pooled, c_u32), pooled.size, _ptr(raw, c_u32), raw.size,
+                int(normalize), _ptr(pooled_out, c_f), _ptr(raw_out, c_f), err, len(err))
+        if replica is None:
+            rc = self._lib.tei_b200_embed(self._h, *tail)
+        else:
+            rc = self._lib.tei_b200_embed_on(self._h, int(replica), *tail)
         if rc != 0:
             raise BackendError(rc, err.value.decode(errors="replace"))
         out: Dict[int, Embedding] = {}
@@ -154,15 +165,18 @@ class B200Backend:
             row += n
         return out
 
-    def predict(self, batch) -> Dict[int, List[float]]:
+    def predict(self, batch, replica: Optional[int] = None) -> Dict[int, List[float]]:
         ids, types, pos, cu, _, _ = self._arrays(batch)
         n_seqs = len(cu) - 1
         scores = np.empty((max(n_seqs, 0), max(self.num_classes, 1)), dtype=np.float32)
         err = ctypes.create_string_buffer(1024)
         c_u32, c_f = ctypes.c_uint32, ctypes.c_float
-        rc = self._lib.tei_b200_predict(
-            self._h, _ptr(ids, c_u32), _ptr(types, c_u32), _ptr(pos, c_u32), ids.size, _ptr(cu, c_u32),
-            n_seqs, int(batch.max_length), _ptr(scores, c_f), err, len(err))
+        tail = (_ptr(ids, c_u32), _ptr(types, c_u32), _ptr(pos, c_u32), ids.size, _ptr(cu, c_u32),
+                n_seqs, int(batch.max_length), _ptr(scores, c_f), err, len(err))
+        if replica is None:
+            rc = self._lib.tei_b200_predict(self._h, *tail)
+        else:
+            rc = self._lib.tei_b200_predict_on(self._h, int(replica), *tail)
         if rc != 0:
             raise BackendError(rc, err.value.decode(errors="replace"))
         return {i: scores[i].tolist() for i in range(n_seqs)}
