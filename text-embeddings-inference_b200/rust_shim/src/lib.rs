@@ -73,6 +73,41 @@ extern "C" {
         err: *mut c_char,
         err_cap: usize,
     ) -> c_int;
+    fn tei_b200_num_replicas(h: *const TeiB200) -> c_int;
+    fn tei_b200_embed_on(
+        h: *mut TeiB200,
+        replica: c_int,
+        input_ids: *const u32,
+        token_type_ids: *const u32,
+        position_ids: *const u32,
+        n_tokens: usize,
+        cumulative_seq_lengths: *const u32,
+        n_seqs: usize,
+        max_length: u32,
+        pooled_idx: *const u32,
+        n_pooled: usize,
+        raw_idx: *const u32,
+        n_raw: usize,
+        normalize: c_int,
+        pooled_out: *mut f32,
+        raw_out: *mut f32,
+        err: *mut c_char,
+        err_cap: usize,
+    ) -> c_int;
+    fn tei_b200_predict_on(
+        h: *mut TeiB200,
+        replica: c_int,
+        input_ids: *const u32,
+        token_type_ids: *const u32,
+        position_ids: *const u32,
+        n_tokens: usize,
+        cumulative_seq_lengths: *const u32,
+        n_seqs: usize,
+        max_length: u32,
+        scores_out: *mut f32,
+        err: *mut c_char,
+        err_cap: usize,
+    ) -> c_int;
 }
 
 const ERR_CAP: usize = 1024;
@@ -99,6 +134,9 @@ pub struct B200Backend {
 
 // The handle is owned by the single backend thread (backends/src/lib.rs:612-647).
 unsafe impl Send for B200Backend {}
+// Shared by the backend threads of a multi-replica router: the `_on` entry points may be
+// called concurrently with different replica indices (the library serialises equal ones).
+unsafe impl Sync for B200Backend {}
 
 impl B200Backend {
     /// Same shape as `CandleBackend::new`.  `TEI_B200_DEVICES` (comma-separated CUDA indices)
@@ -205,6 +243,31 @@ impl Backend for B200Backend {
     }
 
     fn embed(&self, batch: Batch) -> Result<Embeddings, BackendError> {
+        self.embed_impl(None, batch)
+    }
+
+    fn predict(&self, batch: Batch) -> Result<Predictions, BackendError> {
+        self.predict_impl(None, batch)
+    }
+}
+
+impl B200Backend {
+    /// Replicas of the handle = backend threads a router may run over it.
+    pub fn num_replicas(&self) -> usize {
+        unsafe { tei_b200_num_replicas(self.handle) }.max(1) as usize
+    }
+
+    /// `embed` with the whole batch on one replica; callers with different indices may overlap.
+    pub fn embed_on(&self, replica: usize, batch: Batch) -> Result<Embeddings, BackendError> {
+        self.embed_impl(Some(replica), batch)
+    }
+
+    /// `predict` with the whole batch on one replica.
+    pub fn predict_on(&self, replica: usize, batch: Batch) -> Result<Predictions, BackendError> {
+        self.predict_impl(Some(replica), batch)
+    }
+
+    fn embed_impl(&self, replica: Option<usize>, batch: Batch) -> Result<Embeddings, BackendError> {
         let batch_size = batch.len();
         let lengths: Vec<usize> = (0..batch_size)
             .map(|i| {
@@ -219,26 +282,49 @@ impl Backend for B200Backend {
         let mut pooled = vec![0f32; batch.pooled_indices.len() * self.output_dim];
         let mut raw = vec![0f32; raw_rows * self.hidden_size];
         let mut err = vec![0 as c_char; ERR_CAP];
+        // normalize = 0: the router normalises on the host (core/src/infer.rs:288-303)
         let rc = unsafe {
-            tei_b200_embed(
-                self.handle,
-                batch.input_ids.as_ptr(),
-                batch.token_type_ids.as_ptr(),
-                batch.position_ids.as_ptr(),
-                batch.input_ids.len(),
-                batch.cumulative_seq_lengths.as_ptr(),
-                batch_size,
-                batch.max_length,
-                batch.pooled_indices.as_ptr(),
-                batch.pooled_indices.len(),
-                batch.raw_indices.as_ptr(),
-                batch.raw_indices.len(),
-                0, // the router normalises on the host (core/src/infer.rs:288-303)
-                pooled.as_mut_ptr(),
-                raw.as_mut_ptr(),
-                err.as_mut_ptr(),
-                ERR_CAP,
-            )
+            match replica {
+                None => tei_b200_embed(
+                    self.handle,
+                    batch.input_ids.as_ptr(),
+                    batch.token_type_ids.as_ptr(),
+                    batch.position_ids.as_ptr(),
+                    batch.input_ids.len(),
+                    batch.cumulative_seq_lengths.as_ptr(),
+                    batch_size,
+                    batch.max_length,
+                    batch.pooled_indices.as_ptr(),
+                    batch.pooled_indices.len(),
+                    batch.raw_indices.as_ptr(),
+                    batch.raw_indices.len(),
+                    0,
+                    pooled.as_mut_ptr(),
+                    raw.as_mut_ptr(),
+                    err.as_mut_ptr(),
+                    ERR_CAP,
+                ),
+                Some(r) => tei_b200_embed_on(
+                    self.handle,
+                    r as c_int,
+                    batch.input_ids.as_ptr(),
+                    batch.token_type_ids.as_ptr(),
+                    batch.position_ids.as_ptr(),
+                    batch.input_ids.len(),
+                    batch.cumulative_seq_lengths.as_ptr(),
+                    batch_size,
+                    batch.max_length,
+                    batch.pooled_indices.as_ptr(),
+                    batch.pooled_indices.len(),
+                    batch.raw_indices.as_ptr(),
+                    batch.raw_indices.len(),
+                    0,
+                    pooled.as_mut_ptr(),
+                    raw.as_mut_ptr(),
+                    err.as_mut_ptr(),
+                    ERR_CAP,
+                ),
+            }
         };
         if rc != 0 {
             return Err(to_error(rc, &err));
@@ -262,24 +348,40 @@ impl Backend for B200Backend {
         Ok(embeddings)
     }
 
-    fn predict(&self, batch: Batch) -> Result<Predictions, BackendError> {
+    fn predict_impl(&self, replica: Option<usize>, batch: Batch) -> Result<Predictions, BackendError> {
         let batch_size = batch.len();
         let mut scores = vec![0f32; batch_size * self.num_classes.max(1)];
         let mut err = vec![0 as c_char; ERR_CAP];
         let rc = unsafe {
-            tei_b200_predict(
-                self.handle,
-                batch.input_ids.as_ptr(),
-                batch.token_type_ids.as_ptr(),
-                batch.position_ids.as_ptr(),
-                batch.input_ids.len(),
-                batch.cumulative_seq_lengths.as_ptr(),
-                batch_size,
-                batch.max_length,
-                scores.as_mut_ptr(),
-                err.as_mut_ptr(),
-                ERR_CAP,
-            )
+            match replica {
+                None => tei_b200_predict(
+                    self.handle,
+                    batch.input_ids.as_ptr(),
+                    batch.token_type_ids.as_ptr(),
+                    batch.position_ids.as_ptr(),
+                    batch.input_ids.len(),
+                    batch.cumulative_seq_lengths.as_ptr(),
+                    batch_size,
+                    batch.max_length,
+                    scores.as_mut_ptr(),
+                    err.as_mut_ptr(),
+                    ERR_CAP,
+                ),
+                Some(r) => tei_b200_predict_on(
+                    self.handle,
+                    r as c_int,
+                    batch.input_ids.as_ptr(),
+                    batch.token_type_ids.as_ptr(),
+                    batch.position_ids.as_ptr(),
+                    batch.input_ids.len(),
+                    batch.cumulative_seq_lengths.as_ptr(),
+                    batch_size,
+                    batch.max_length,
+                    scores.as_mut_ptr(),
+                    err.as_mut_ptr(),
+                    ERR_CAP,
+                ),
+            }
         };
         if rc != 0 {
             return Err(to_error(rc, &err));
