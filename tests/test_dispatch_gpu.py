@@ -115,3 +115,48 @@ def test_predict_on_and_refusals(lib, model_dirs):
     assert be.predict(b, replica=1) == a
     assert be.predict(b, replica=0) == a
     be.close()
+
+
+def test_queue_feeds_two_replicas(lib, model_dirs):
+    """The whole caller side: requests go into the library's queue, two consumer threads (one per
+    replica) take batches and run them; every request's embedding equals the one it gets alone."""
+    import tei_b200
+    be = tei_b200.B200Backend(model_dirs["bert"], "float16", "embedding", "cls", devices=[0, 0])
+    rng = np.random.default_rng(11)
+    reqs = {tag: rng.integers(0, 1000, size=int(rng.integers(2, 120))).astype(np.uint32) for tag in range(60)}
+    alone = {}
+    for tag, ids in reqs.items():
+        b = G.random_batch(0, [len(ids)], 0, 1000)
+        b.input_ids = ids
+        alone[tag] = be.embed(b, replica=0)[0].values
+    q = tei_b200.BatchQueue(max_batch_tokens=400, max_batch_requests=8)
+    for tag, ids in reqs.items():
+        q.append(ids, tag=tag)
+    got, errors, lock = {}, [], threading.Lock()
+
+    def consume(r):
+        try:
+            while True:
+                nb = q.next_batch()
+                if nb is None:
+                    return
+                batch, tags = nb
+                out = be.embed(batch, replica=r)
+                with lock:
+                    for i, tag in enumerate(tags):
+                        got[tag] = out[i].values
+        except Exception as exc:
+            errors.append(exc)
+
+    threads = [threading.Thread(target=consume, args=(r,)) for r in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert sorted(got) == sorted(reqs)
+    for tag in reqs:
+        # batched with neighbours against alone: same kernels, other tile positions
+        assert np.abs(got[tag] - alone[tag]).max() <= 4e-3
+    q.close()
+    be.close()

@@ -6,7 +6,7 @@ if the shared object is missing, `load()` raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_longlong, POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_size_t, c_uint32, c_void_p
+from ctypes import c_longlong, POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_size_t, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
 PKG_ROOT = Path(__file__).resolve().parent.parent
@@ -93,9 +93,28 @@ _BACKEND_PROTOTYPES = {
 }
 
 
+_U32P = POINTER(c_uint32)
+_SZP = POINTER(c_size_t)
+
+# mirrors include/tei_b200_queue.h
+_QUEUE_PROTOTYPES = {
+    "tei_b200_queue_create": (c_int, [c_int, c_size_t, c_size_t, POINTER(c_void_p)]),
+    "tei_b200_queue_destroy": (None, [c_void_p]),
+    "tei_b200_queue_append": (c_int, [c_void_p, _U32P, _U32P, _U32P, c_size_t, c_uint32, c_int, c_uint64]),
+    "tei_b200_queue_cancel": (c_int, [c_void_p, c_uint64, _SZP]),
+    "tei_b200_queue_len": (c_size_t, [c_void_p]),
+    "tei_b200_queue_next_batch": (
+        c_int,
+        [c_void_p, _U32P, _U32P, _U32P, c_size_t, _U32P, _U32P, _U32P, POINTER(c_uint64), c_size_t,
+         _SZP, _SZP, _SZP, _SZP, _U32P],
+    ),
+}
+
+
 def prototypes() -> dict:
     out = dict(_OPS_PROTOTYPES)
     out.update(_BACKEND_PROTOTYPES)
+    out.update(_QUEUE_PROTOTYPES)
     return out
 
 
