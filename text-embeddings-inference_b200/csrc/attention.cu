@@ -205,6 +205,51 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
   return (s0 + s1) + (s2 + s3);
 }
 
+// Pass 2 without pass 1: probabilities relative to the maximum the row already has, and the
+// largest exponent met on the way (amax, relative to m_use).  As long as amax stays below the
+// rescale threshold the result is final; otherwise the caller raises the maximum and runs the
+// two passes again from the scores it still holds in registers.
+template <class T, bool MASKED, bool ALIBI>
+__device__ __forceinline__ float write_probs_tracking(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lo, int lim,
+                                                      int n_chunks, float sl2, float slope, int rel, float m_use,
+                                                      float& amax) {
+  const unsigned span = static_cast<unsigned>(max(0, lim - lo));
+  const uint64_t sl2_2 = ptx::pack_f32x2(sl2, sl2), neg_m2 = ptx::pack_f32x2(-m_use, -m_use);
+  uint64_t acc[2] = {0ull, 0ull};
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < BKV / 32; ++c) {
+    if (c >= n_chunks) break;
+    const uint32_t (&s)[32] = sc[c];
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const int kk = c * 32 + i;
+      float a0, a1;
+      if (ALIBI) {
+        a0 = __uint_as_float(s[i]) * sl2 - slope * fabsf(static_cast<float>(rel - kk)) - m_use;
+        a1 = __uint_as_float(s[i + 1]) * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1)) - m_use;
+      } else {
+        ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sl2_2, neg_m2), a0, a1);
+      }
+      if (MASKED) {  // 2^-inf = 0: a masked key adds nothing and cannot raise the maximum
+        a0 = static_cast<unsigned>(kk - lo) < span ? a0 : -INFINITY;
+        a1 = static_cast<unsigned>(kk + 1 - lo) < span ? a1 : -INFINITY;
+      }
+      mx[(i >> 1) & 1] = ptx::max3(mx[(i >> 1) & 1], a0, a1);
+      const float e0 = ex2_fast(a0), e1 = ex2_fast(a1);
+      acc[(i >> 1) & 1] = ptx::add_f32x2(acc[(i >> 1) & 1], ptx::pack_f32x2(e0, e1));
+      pk[i / 2] = pack2<T>(e0, e1);
+    }
+    ptx::tmem_st16(t_p + c * 16, pk);
+  }
+  amax = fmaxf(mx[0], mx[1]);
+  float s0, s1, s2, s3;
+  ptx::unpack_f32x2(acc[0], s0, s1);
+  ptx::unpack_f32x2(acc[1], s2, s3);
+  return (s0 + s1) + (s2 + s3);
+}
+
 // The running maximum is only raised when it grows by more than this many powers of two; until
 // then probabilities are taken relative to the stale maximum (they stay below 2^8, far inside
 // fp16 / bf16 range) and the accumulator in TMEM needs no rescaling.
@@ -575,13 +620,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (c < n_chunks) ptx::tmem_ld32(t_s + c * 32, sc[c]);
         }
         ptx::tmem_ld_wait();
-        float mx;
-        if (p.alibi_slopes) mx = row_max<true, true>(sc, lo, lim, n_chunks, p.scale_log2, slope, rel);
-        else if (tile_full) mx = row_max<false, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
-        else mx = row_max<true, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+        auto true_max = [&]() {
+          if (p.alibi_slopes) return row_max<true, true>(sc, lo, lim, n_chunks, p.scale_log2, slope, rel);
+          if (tile_full) return row_max<false, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+          return row_max<true, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+        };
+        auto probs = [&](float m_use) {
+          if (p.alibi_slopes) return write_probs<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+          if (tile_full) return write_probs<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+          return write_probs<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+        };
+        // P goes over this step's scores.  Their columns were last read by the P V of step
+        // g-2, which ran before the S MMA of this step wrote them (MMAs run in issue order).
+        float sum;
         if (j == 0) {
-          m = mx;  // P V of the first step overwrites the output tile: nothing to rescale
+          // P V of the first step overwrites the output tile: nothing to rescale
+          m = true_max();
+          sum = probs(m == -INFINITY ? 0.f : m);
         } else {
+          // Later steps first try the maximum the row already has: one pass, no dependency of
+          // the exponentials on a maximum of this step.
+          const float m_old = (m == -INFINITY) ? 0.f : m;
+          float amax;
+          if (p.alibi_slopes) sum = write_probs_tracking<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_old, amax);
+          else if (tile_full) sum = write_probs_tracking<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
+          else sum = write_probs_tracking<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
+          const float mx = amax + m_old;  // this step's maximum in the scaled log2 domain
           const bool grow = mx > m + kRescaleThreshold;
           if (__any_sync(0xffffffffu, grow)) {
             // Raise the maximum of the rows that need it and rescale their partial outputs in
@@ -607,16 +671,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
               ptx::tmem_st16(tmem_o + lane_off + c * 16, t);
             }
-            ptx::tmem_st_wait();
+            // The probabilities again, now relative to the raised maxima (the scores are still
+            // in registers; rows that kept their maximum write the same values once more).
+            sum = probs(m == -INFINITY ? 0.f : m);
           }
         }
-        // P goes over this step's scores.  Their columns were last read by the P V of step
-        // g-2, which ran before the S MMA of this step wrote them (MMAs run in issue order).
-        const float m_use = (m == -INFINITY) ? 0.f : m;
-        float sum;
-        if (p.alibi_slopes) sum = write_probs<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_use);
-        else if (tile_full) sum = write_probs<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
-        else sum = write_probs<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
         l += sum;
         // P and the rescaled O written, S read: hand over to the MMA thread.
         ptx::tmem_st_wait();
