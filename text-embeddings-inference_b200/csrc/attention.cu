@@ -21,7 +21,10 @@
 //                      tile in TMEM behind the score tiles, with P read from TMEM (A operand)
 //                      and V from shared memory (MN-major operand).
 //   warps 0-3          one query row per thread: the 64 scores of the step are read from TMEM
-//                      into registers once; row maximum, exp2, and P written back as fp16/bf16
+//                      into registers once; exp2 against the row's running maximum in one pass
+//                      that also tracks the largest exponent (a row maximum pass first only at
+//                      a unit's first step and when a maximum has to be raised), P written
+//                      back as fp16/bf16
 //                      over the row's own scores in TMEM, so P never touches shared memory (the
 //                      kernel is bound by shared-memory bandwidth otherwise: every MMA operand
 //                      read and every TMA write goes through it).  O stays in TMEM across the
