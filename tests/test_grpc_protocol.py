@@ -97,3 +97,56 @@ def test_classifier_detection(tmp_path):
     assert GS.is_classifier(tmp_path)
     (tmp_path / "config.json").write_text('{"architectures": ["BertModel"]}')
     assert not GS.is_classifier(tmp_path)
+
+
+class _TwoReplicas(_StandIn):
+    """Stand-in with two replicas: records which replica served each call and how many calls
+    were inside `embed` at once."""
+
+    num_replicas = 2
+
+    def __init__(self):
+        super().__init__()
+        import threading
+        self.lock = threading.Lock()
+        self.inside = 0
+        self.peak = 0
+        self.busy = set()
+        self.served = []
+
+    def embed(self, batch, replica=None):
+        import time
+        with self.lock:
+            assert replica in (0, 1) and replica not in self.busy  # a replica serves one call at a time
+            self.busy.add(replica)
+            self.inside += 1
+            self.peak = max(self.peak, self.inside)
+            self.served.append(replica)
+        time.sleep(0.05)
+        out = _StandIn.embed(self, batch)
+        with self.lock:
+            self.busy.discard(replica)
+            self.inside -= 1
+        return out
+
+
+def test_per_replica_dispatch_runs_calls_concurrently(tmp_path):
+    from concurrent.futures import ThreadPoolExecutor
+    uds = str(tmp_path / "sock2")
+    backend = _TwoReplicas()
+    server = GS.serve(GS.EmbeddingService(backend, False, per_replica=True), uds)
+    try:
+        m = GS.message_classes()
+        with grpc.insecure_channel(f"unix://{uds}") as ch:
+            def one(k):
+                req = m["EmbedRequest"](input_ids=[k, k + 1], token_type_ids=[0, 0], position_ids=[0, 1],
+                                        cu_seq_lengths=[0, 2], max_length=2)
+                resp = _call(ch, m, "Embed", req, "EmbedResponse")
+                return list(resp.embeddings[0].values)
+            with ThreadPoolExecutor(max_workers=6) as ex:
+                rows = list(ex.map(one, range(12)))
+        assert rows == [[0.0, 2.0, float(2 * k + 1)] for k in range(12)]
+        assert backend.peak == 2               # both replicas were busy at once, never more
+        assert set(backend.served) == {0, 1}
+    finally:
+        server.stop(grace=None)

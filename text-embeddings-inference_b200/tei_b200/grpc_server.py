@@ -95,13 +95,33 @@ class _Batch:
 class EmbeddingService:
     """The three RPCs on top of any object with the Backend-trait methods `embed`, `predict`
     and `health` (tei_b200.B200Backend, or a stand-in in the protocol tests).  The backend is
-    single-caller (backends/src/lib.rs:618-644), so calls are serialised here."""
+    single-caller (backends/src/lib.rs:618-644), so calls are serialised here; with
+    `per_replica=True` every call instead takes one free replica of the handle and runs its
+    whole batch there, so as many calls as replicas run at once."""
 
-    def __init__(self, backend, classifier: bool):
+    def __init__(self, backend, classifier: bool, per_replica: bool = False):
         self.backend = backend
         self.classifier = classifier
         self.msgs = message_classes()
         self._lock = threading.Lock()
+        self.workers = 1
+        self._free = None
+        if per_replica:
+            import queue
+            self.workers = int(backend.num_replicas)
+            self._free = queue.SimpleQueue()
+            for r in range(self.workers):
+                self._free.put(r)
+
+    def _run(self, method, batch):
+        if self._free is None:
+            with self._lock:
+                return method(batch)
+        r = self._free.get()
+        try:
+            return method(batch, replica=r)
+        finally:
+            self._free.put(r)
 
     def _abort(self, context, exc):
         import grpc
@@ -113,8 +133,7 @@ class EmbeddingService:
             if self.classifier:
                 raise RuntimeError("`embed` is not implemented for classifier models")
             batch = _Batch(request)
-            with self._lock:
-                rows = self.backend.embed(batch)
+            rows = self._run(self.backend.embed, batch)
             resp = m["EmbedResponse"]()
             for i in range(len(batch)):
                 resp.embeddings.add().values.extend(np.asarray(rows[i].values, dtype=np.float32).tolist())
@@ -128,8 +147,7 @@ class EmbeddingService:
             if not self.classifier:
                 raise RuntimeError("`predict` is not implemented for this model")
             batch = _Batch(request)
-            with self._lock:
-                scores = self.backend.predict(batch)
+            scores = self._run(self.backend.predict, batch)
             resp = m["PredictResponse"]()
             for i in range(len(batch)):
                 resp.scores.add().values.extend([float(v) for v in scores[i]])
@@ -166,9 +184,9 @@ def serve(service: EmbeddingService, uds_path: str):
     import grpc
     if os.path.exists(uds_path):
         os.remove(uds_path)
-    # one worker: the backend takes one batch at a time; no message size limit (a packed batch of
-    # 16k tokens is small, but the router's budget is configurable)
-    server = grpc.server(futures.ThreadPoolExecutor(max_workers=1),
+    # one worker per batch the backend can take at a time; no message size limit (a packed batch
+    # of 16k tokens is small, but the router's budget is configurable)
+    server = grpc.server(futures.ThreadPoolExecutor(max_workers=service.workers),
                          options=[("grpc.max_receive_message_length", -1), ("grpc.max_send_message_length", -1)])
     server.add_generic_rpc_handlers((service.handler(),))
     server.add_insecure_port(f"unix://{uds_path}")
@@ -193,7 +211,10 @@ def main(argv: Optional[list] = None) -> int:
     ap.add_argument("--otlp-endpoint", default=None)
     ap.add_argument("--otlp-service-name", default="text-embeddings-inference.server")
     ap.add_argument("--devices", default=os.environ.get("TEI_B200_DEVICES", "0"),
-                    help="comma-separated CUDA indices: one replica each, every batch is split across them")
+                    help="comma-separated CUDA indices: one replica each (an index may repeat)")
+    ap.add_argument("--dispatch", default=os.environ.get("TEI_B200_DISPATCH", "split"), choices=["split", "per-replica"],
+                    help="split: every batch is split across the replicas (one call at a time, what the "
+                         "unmodified router sends); per-replica: concurrent calls each take one free replica")
     args = ap.parse_args(argv)
 
     def log(level, message):
@@ -217,7 +238,7 @@ def main(argv: Optional[list] = None) -> int:
     except tei_b200.BackendError as exc:
         log("ERROR", f"Could not start backend: {exc}")
         return 1
-    server = serve(EmbeddingService(backend, classifier), args.uds_path)
+    server = serve(EmbeddingService(backend, classifier, per_replica=args.dispatch == "per-replica"), args.uds_path)
     log("INFO", f"Server started at unix://{args.uds_path}")
     stop = threading.Event()
     for sig in (signal.SIGTERM, signal.SIGINT):
