@@ -150,6 +150,39 @@ def test_attention(lib, lens, nh, nkv, D, causal, alibi, dtype):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("lens,nh,nkv,D,causal,slope,dtype", [
+    ([700, 130], 2, 2, 64, False, 0.3, "f16"),    # the maximum grows by ~28 powers of two per 64-key step
+    ([700, 130], 2, 2, 64, True, 0.3, "f16"),
+    ([520], 4, 2, 128, True, 0.3, "bf16"),
+    ([700], 2, 2, 64, False, 0.05, "f16"),        # slow growth: raised lazily, every second or third step
+    ([700], 2, 1, 128, False, 0.05, "f16"),
+])
+def test_attention_running_maximum_is_raised(lib, lens, nh, nkv, D, causal, slope, dtype):
+    """Scores that keep growing along the keys for half of the rows and keep falling for the
+    other half: the rows of one warp disagree on whether the maximum has to be raised, the
+    partial outputs are rescaled in place, and the early keys end up with weight ~0."""
+    from tei_b200 import ops
+    dt = DT[dtype]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = _gen(7 * T + D)
+    q = 0.3 * torch.randn(T, nh, D, device="cuda", generator=g)
+    k = 0.3 * torch.randn(T, nkv, D, device="cuda", generator=g)
+    v = torch.randn(T, nkv, D, device="cuda", generator=g)
+    pos = torch.cat([torch.arange(n, device="cuda", dtype=torch.float32) for n in lens])
+    sign = torch.where(torch.arange(T, device="cuda") % 2 == 0, 1.0, -1.0)
+    scale = 1.0 / D ** 0.5
+    # score(i, j) = sign_i * slope * j + small noise
+    q[:, :, 0] = (sign / scale).view(T, 1)
+    k[:, :, 0] = (slope * pos).view(T, 1)
+    q, k, v = q.to(dt), k.to(dt), v.to(dt)
+    out = ops.attention(q, k, v, cu, causal=causal, scale=scale)
+    ref = _ref_attention(q, k, v, cu, causal, scale, None)
+    _close(out, ref, 2e-2 if dtype == "f16" else 6e-2)
+
+
 @pytest.mark.parametrize("lens,nh,nkv,D,causal,wl,wr,dtype", [
     ([300, 40, 129], 4, 4, 64, True, 64, -1, "f16"),      # Mistral-style: causal, left window
     ([1000, 5], 4, 2, 128, True, 100, -1, "bf16"),        # window not a multiple of the tile
