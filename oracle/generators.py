@@ -244,6 +244,17 @@ def _modernbert_shapes(c: dict) -> Dict[str, Tuple[tuple, str]]:
     return t
 
 
+def jina_code_config(alibi: bool = True, **kw) -> dict:
+    """A JinaCodeBert config: model_type "bert" plus the `jina-bert-v2-qk-post-norm` markers
+    (backends/candle/src/lib.rs:83-121)."""
+    c = bert_config(**kw)
+    c["_name_or_path"] = "jinaai/jina-bert-v2-qk-post-norm"
+    c["auto_map"] = {"AutoConfig": "jinaai/jina-bert-v2-qk-post-norm--configuration_bert.JinaBertConfig"}
+    c["position_embedding_type"] = "alibi" if alibi else "absolute"
+    c["feed_forward_type"] = "geglu"
+    return c
+
+
 # --------------------------------------------------------------------------- tensor lists
 def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) -> Dict[str, Tuple[tuple, str]]:
     """name -> (shape, kind) with kind in {normal, ones, zeros}."""
@@ -266,6 +277,17 @@ def _bert_shapes(c: dict, prefix: str, classifier: Optional[str], splade: bool) 
         t[p + "attention.output.dense.bias"] = ((H,), "normal")
         t[p + "attention.output.LayerNorm.weight"] = ((H,), "ones")
         t[p + "attention.output.LayerNorm.bias"] = ((H,), "zeros")
+        if c.get("_name_or_path") == "jinaai/jina-bert-v2-qk-post-norm":  # flash_jina_code.rs:27-212
+            for n in ("layer_norm_q", "layer_norm_k"):
+                t[p + f"attention.self.{n}.weight"] = ((H,), "ones")
+                t[p + f"attention.self.{n}.bias"] = ((H,), "zeros")
+            t[p + "mlp.up_gated_layer.weight"] = ((2 * I, H), "normal")
+            t[p + "mlp.down_layer.weight"] = ((H, I), "normal")
+            t[p + "mlp.down_layer.bias"] = ((H,), "normal")
+            for n in ("layer_norm_1", "layer_norm_2"):
+                t[p + f"{n}.weight"] = ((H,), "ones")
+                t[p + f"{n}.bias"] = ((H,), "zeros")
+            continue
         if jina:  # flash_jina.rs:133-155
             t[p + "mlp.gated_layers.weight"] = ((2 * I, H), "normal")
             t[p + "mlp.wo.weight"] = ((H, I), "normal")

@@ -92,11 +92,45 @@ def rms_norm(x: Tensor, residual: Optional[Tensor], gamma: Tensor, eps: float) -
     return x / torch.sqrt(ms + eps) * gamma, x
 
 
-def rope_tables(head_dim: int, base: float, max_pos: int) -> Tuple[Tensor, Tensor]:
+def scaled_inv_freqs(head_dim: int, base: float, scaling: Optional[dict]) -> np.ndarray:
+    """get_inv_freqs (layers/rotary.rs:29-98) in f32.  `scaling` is the config's `rope_scaling`
+    object; as in the reference's untagged enum (:11-27) its FIELDS pick the variant: with
+    high_freq_factor, low_freq_factor and original_max_position_embeddings it is the Llama3 rule
+    (:46-85), with `factor` alone the NTK rule (:86-93), whatever its type string says."""
+    f32 = np.float32
+    dim = f32(head_dim)
+
+    def plain(b):
+        return np.array([f32(1.0) / np.power(f32(b), f32(i) / dim, dtype=np.float32)
+                         for i in range(0, head_dim, 2)], dtype=np.float32)
+
+    if not scaling:
+        return plain(base)
+    factor = f32(scaling["factor"])
+    if all(k in scaling for k in ("high_freq_factor", "low_freq_factor", "original_max_position_embeddings")):
+        old = f32(scaling["original_max_position_embeddings"])
+        lo_f, hi_f = f32(scaling["low_freq_factor"]), f32(scaling["high_freq_factor"])
+        low_wavelen, high_wavelen = old / lo_f, old / hi_f
+        out = []
+        for i in range(0, head_dim, 2):
+            inv_base = f32(1.0) / np.power(f32(base), f32(i) / dim, dtype=np.float32)
+            wavelen = f32(2.0) * f32(np.pi) / inv_base
+            if wavelen < high_wavelen:
+                out.append(inv_base)
+            elif wavelen > low_wavelen:
+                out.append(inv_base / factor)
+            else:
+                smooth = (old / wavelen - lo_f) / (hi_f - lo_f)
+                out.append((f32(1.0) - smooth) * (inv_base / factor) + smooth * inv_base)
+        return np.array(out, dtype=np.float32)
+    # NTK: base * factor in f32, then divided by factor^(2/dim) computed in f32, applied as f64
+    s = float(np.power(factor, f32(2.0) / dim, dtype=np.float32))
+    return (plain(f32(base) * factor).astype(np.float64) / s).astype(np.float32)
+
+
+def rope_tables(head_dim: int, base: float, max_pos: int, scaling: Optional[dict] = None) -> Tuple[Tensor, Tensor]:
     # layers/rotary.rs:29-116: inv_freq_i = 1 / base^(i/dim) for even i, all in f32.
-    base32 = np.float32(base)
-    inv = np.array([np.float32(1.0) / np.power(base32, np.float32(i) / np.float32(head_dim), dtype=np.float32)
-                    for i in range(0, head_dim, 2)], dtype=np.float32)
+    inv = scaled_inv_freqs(head_dim, base, scaling)
     t = np.arange(max_pos, dtype=np.float32)[:, None]
     freqs = (t * inv[None, :]).astype(np.float32)
     return torch.from_numpy(np.cos(freqs).astype(np.float32)), torch.from_numpy(np.sin(freqs).astype(np.float32))
@@ -498,8 +532,8 @@ class Qwen3Oracle:
         mt = c["model_type"]
         if mt in ("qwen3", "qwen2") and c.get("use_sliding_window"):
             raise ValueError("sliding window is not supported (flash_qwen3.rs:32-34, flash_qwen2.rs:26-29)")
-        if mt in ("mistral", "llama") and c.get("rope_scaling") is not None:
-            raise ValueError("rope scaling is outside this restatement")
+        if mt == "llama" and c.get("rope_scaling") is not None:
+            raise ValueError("Rope scaling is not supported for FlashLlama yet")  # lib.rs:549-553
         self.qk_norm = mt == "qwen3"
         self.qkv_bias = mt == "qwen2"
         self.window_left = c.get("sliding_window") if mt == "mistral" else None
@@ -521,7 +555,9 @@ class Qwen3Oracle:
             self.causal = bool(c.get("is_causal", True))  # qwen2.rs:4-7,26-27
         else:
             self.causal = not c.get("use_bidirectional_attention", False)
-        self.cos, self.sin = rope_tables(self.dh, float(theta), int(c["max_position_embeddings"]))
+        # only Mistral passes its `rope_scaling` on (flash_mistral.rs:278-283); Qwen2 / Qwen3 do not
+        scaling = c.get("rope_scaling") if mt == "mistral" else None
+        self.cos, self.sin = rope_tables(self.dh, float(theta), int(c["max_position_embeddings"]), scaling)
 
     def hidden_states(self, batch: Batch) -> Tensor:
         w = self.w
@@ -841,10 +877,75 @@ class JinaBertOracle(BertOracle):
         return linear(h, a.get("classifier.weight"), a.get("classifier.bias"))
 
 
+def is_jina_code_bert(config: dict) -> bool:
+    # BertConfigWrapper, backends/candle/src/lib.rs:83-121
+    name = config.get("_name_or_path", "") or ""
+    auto = (config.get("auto_map") or {}).get("AutoConfig", "") or ""
+    return config.get("model_type") == "bert" and (
+        name == "jinaai/jina-bert-v2-qk-post-norm" or "jinaai/jina-bert-v2-qk-post-norm" in auto)
+
+
+class JinaCodeBertOracle(JinaBertOracle):
+    """models/jina_code.rs / flash_jina_code.rs: JinaBERT's embeddings and ALiBi, with
+      * LayerNorm over the whole q row and the whole k row before attention
+        (flash_jina_code.rs:112-120),
+      * a = LN_out(dense(attention) + x)  (:147-150), h = layer_norm_1(a + x)  (:226-230: the
+        residual is the layer's input again),
+      * up_gated_layer without bias, first half * act(second half)  (:234-240), down_layer,
+        layer_norm_2(down + h)  (:243-245).
+    Embedding models only (no classifier, no splade, :305-315)."""
+
+    def __init__(self, config: dict, tensors: Dict[str, Tensor], model_type: str = "embedding",
+                 pool: str = "cls"):
+        if model_type == "classifier":
+            raise ValueError("`classifier` model type is not supported for Jina Code")
+        super().__init__(config, tensors, model_type, pool)
+
+    def hidden_states(self, batch: Batch) -> Tensor:
+        w = self.w
+        ids = torch.from_numpy(batch.input_ids.astype(np.int64))
+        tids = torch.from_numpy(batch.token_type_ids.astype(np.int64))
+        g, b = w.ln("embeddings.LayerNorm")
+        word = w.get("embeddings.word_embeddings.weight")[ids]
+        typ = w.get("embeddings.token_type_embeddings.weight")[tids]
+        if self.alibi:
+            x = layer_norm(word, typ, g, b, self.eps)
+        else:
+            pids = torch.from_numpy(batch.position_ids.astype(np.int64))
+            x = layer_norm(word + typ, w.get("embeddings.position_embeddings.weight")[pids], g, b, self.eps)
+        slopes = alibi_slopes(self.nh) if self.alibi else None
+        cu = batch.cumulative_seq_lengths
+        T = x.shape[0]
+        for i in range(self.n_layers):
+            p = f"encoder.layer.{i}."
+            q = linear(x, w.get(p + "attention.self.query.weight"), w.get(p + "attention.self.query.bias"))
+            k = linear(x, w.get(p + "attention.self.key.weight"), w.get(p + "attention.self.key.bias"))
+            v = linear(x, w.get(p + "attention.self.value.weight"), w.get(p + "attention.self.value.bias"))
+            gq, bq = w.ln(p + "attention.self.layer_norm_q")
+            gk, bk = w.ln(p + "attention.self.layer_norm_k")
+            q = layer_norm(q, None, gq, bq, self.eps)
+            k = layer_norm(k, None, gk, bk, self.eps)
+            a = attention_varlen(q.view(T, self.nh, self.dh), k.view(T, self.nh, self.dh),
+                                 v.view(T, self.nh, self.dh), cu, 1.0 / math.sqrt(self.dh), False, slopes)
+            go, bo = w.ln(p + "attention.output.LayerNorm")
+            a = layer_norm(linear(a, w.get(p + "attention.output.dense.weight"),
+                                  w.get(p + "attention.output.dense.bias")), x, go, bo, self.eps)
+            g1, b1 = w.ln(p + "layer_norm_1")
+            h = layer_norm(a, x, g1, b1, self.eps)
+            u = linear(h, w.get(p + "mlp.up_gated_layer.weight"), None)
+            f = u[:, :self.inter] * self.act(u[:, self.inter:])
+            g2, b2 = w.ln(p + "layer_norm_2")
+            x = layer_norm(linear(f, w.get(p + "mlp.down_layer.weight"), w.get(p + "mlp.down_layer.bias")),
+                           h, g2, b2, self.eps)
+        return x
+
+
 def build_oracle(model_dir, model_type: str = "embedding", pool: str = "cls"):
     """Dispatch on config.json's model_type like backends/candle/src/lib.rs:124-154,282-577."""
     config, tensors = load_model_dir(model_dir)
     mt = config["model_type"]
+    if is_jina_code_bert(config):
+        return JinaCodeBertOracle(config, tensors, model_type, pool)
     if is_jina_bert(config):
         return JinaBertOracle(config, tensors, model_type, pool)
     if mt in ("bert", "roberta", "xlm-roberta", "camembert"):

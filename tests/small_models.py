@@ -34,6 +34,14 @@ def write_all(base):
         G.jina_config(alibi=False, hidden=384, layers=2, heads=6, inter=512, vocab=1000, max_pos=512,
                       id2label={"0": "a", "1": "b"}),
         seed=9, classifier="bert", norm_jitter=0.1, std=0.05, prefix="bert.")
+    dirs["jina_code"] = G.write_model_dir(
+        base / "jina_code",
+        G.jina_code_config(alibi=True, hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+        seed=21, norm_jitter=0.1, std=0.05)
+    dirs["jina_code_abs"] = G.write_model_dir(
+        base / "jina_code_abs",
+        G.jina_code_config(alibi=False, hidden=384, layers=2, heads=6, inter=512, vocab=1000, max_pos=512),
+        seed=22, norm_jitter=0.1, std=0.05, prefix="bert.")
     dirs["nomic"] = G.write_model_dir(
         base / "nomic", G.nomic_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, n_positions=2048),
         seed=4, norm_jitter=0.1, std=0.05)
@@ -54,6 +62,21 @@ def write_all(base):
         G.mistral_config(hidden=512, layers=2, heads=4, kv_heads=2, inter=512, vocab=1000, max_pos=2048,
                          sliding_window=100),
         seed=13, norm_jitter=0.1, std=0.05)
+    # rope scaling: the Llama3 rule (original context 64, so that low, middle and high bands all
+    # occur at head_dim 128) and the NTK rule
+    dirs["mistral_rope_l3"] = G.write_model_dir(
+        base / "mistral_rope_l3",
+        dict(G.mistral_config(hidden=512, layers=2, heads=4, kv_heads=2, inter=512, vocab=1000, max_pos=2048,
+                              sliding_window=None),
+             rope_scaling={"rope_type": "llama3", "factor": 8.0, "high_freq_factor": 4.0, "low_freq_factor": 1.0,
+                           "original_max_position_embeddings": 64}),
+        seed=23, norm_jitter=0.1, std=0.05)
+    dirs["mistral_rope_ntk"] = G.write_model_dir(
+        base / "mistral_rope_ntk",
+        dict(G.mistral_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048,
+                              sliding_window=None),
+             rope_scaling={"type": "ntk", "factor": 4.0}),
+        seed=24, norm_jitter=0.1, std=0.05)
     dirs["llama"] = G.write_model_dir(
         base / "llama",
         G.mistral_config(hidden=256, layers=2, heads=4, kv_heads=4, inter=512, vocab=1000, max_pos=2048,
@@ -105,6 +128,8 @@ GOLDEN_CASES = {
     "qwen2_bidir_mean": ("qwen2_bidir", "embedding", "mean", dict(seed=112, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "mistral_window_last": ("mistral", "embedding", "last_token", dict(seed=113, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
     "mistral_window_mean": ("mistral", "embedding", "mean", dict(seed=114, lens=[400, 101, 100, 99], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "mistral_rope_l3_last": ("mistral_rope_l3", "embedding", "last_token", dict(seed=125, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
+    "mistral_rope_ntk_mean": ("mistral_rope_ntk", "embedding", "mean", dict(seed=126, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "llama_cls": ("llama", "embedding", "cls", dict(seed=115, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "modernbert_mean": ("modernbert", "embedding", "mean", dict(seed=116, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
     "modernbert_cls": ("modernbert", "embedding", "cls", dict(seed=117, lens=[33, 64, 65, 400], lo=0, hi=1000, type_vocab=1, offset=0)),
@@ -113,6 +138,8 @@ GOLDEN_CASES = {
     "distilbert_mean": ("distilbert", "embedding", "mean", dict(seed=120, lens=LENS, lo=0, hi=1000, type_vocab=1, offset=0)),
     "gte_cls_pool": ("gte", "embedding", "cls", dict(seed=121, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
     "gte_scores": ("gte_cls", "classifier", "cls", dict(seed=122, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "jina_code_mean": ("jina_code", "embedding", "mean", dict(seed=123, lens=LENS + [511], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "jina_code_abs_cls": ("jina_code_abs", "embedding", "cls", dict(seed=124, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

@@ -109,6 +109,7 @@ def test_config_dispatch_refusals_follow_the_reference(lib, tmp_path):
     for cfg, kw in [
         (G.bert_config(), {}),
         (G.jina_config(alibi=True), dict(pool="mean")),
+        (G.jina_code_config(alibi=True), dict(pool="mean")),
         (G.nomic_config(), dict(pool="mean")),
         (G.nomic_config(moe_every=2), dict(pool="mean")),
         (G.qwen3_config(), dict(pool="last_token")),
@@ -123,9 +124,10 @@ def test_config_dispatch_refusals_follow_the_reference(lib, tmp_path):
         err = _start_error(tmp_path, cfg, **kw)
         assert err.kind == "WeightsNotFound", (cfg["model_type"], str(err))
     # refusals (file:line of the reference's bail! in each message's origin)
-    e = _start_error(tmp_path, dict(G.jina_config(), _name_or_path="jinaai/jina-bert-v2-qk-post-norm",
-                                    auto_map={"AutoConfig": "jinaai/jina-bert-v2-qk-post-norm--configuration_bert.JinaBertConfig"}))
-    assert e.kind == "Start" and "JinaCodeBert" in str(e)
+    e = _start_error(tmp_path, dict(G.jina_code_config(), id2label={"0": "a"}), model_type="classifier")  # flash_jina_code.rs:305-307
+    assert e.kind == "Start" and "not supported for Jina Code" in str(e)
+    e = _start_error(tmp_path, G.jina_code_config(), pool="splade")     # flash_jina_code.rs:309-311
+    assert "`splade` is not supported for Jina Code" in str(e)
     e = _start_error(tmp_path, G.jina_config(), pool="splade")          # flash_jina.rs:262-264
     assert "`splade` is not supported for Jina" in str(e)
     e = _start_error(tmp_path, dict(G.bert_config(), position_embedding_type="relative_key"))  # flash_bert.rs:241-243

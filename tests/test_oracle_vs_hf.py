@@ -223,3 +223,28 @@ def test_alibi_slopes_known_values():
     s12 = M.alibi_slopes(12).numpy()
     assert np.allclose(s12[:8], [2.0 ** -(i + 1) for i in range(8)])
     assert np.allclose(s12[8:], [2.0 ** -(0.5 + i) for i in range(4)])
+
+
+def test_mistral_llama3_rope_scaling_matches_hf(model_dirs):
+    """The Llama3 frequency rule (layers/rotary.rs:46-85) against Hugging Face's `llama3` rope
+    type on the same weights."""
+    d = model_dirs["mistral_rope_l3"]
+    cfg = json.load(open(d / "config.json"))
+    hcfg = {k: v for k, v in cfg.items() if k not in ("rope_scaling", "rope_theta")}
+    hcfg["rope_parameters"] = dict(cfg["rope_scaling"], rope_theta=cfg["rope_theta"])
+    hcfg["attn_implementation"] = "eager"
+    hf = transformers.MistralModel(transformers.MistralConfig(**hcfg)).eval()
+    _, tensors = M.load_model_dir(d)
+    hf.load_state_dict(tensors, strict=True)
+    inv = M.scaled_inv_freqs(cfg["hidden_size"] // cfg["num_attention_heads"], cfg["rope_theta"], cfg["rope_scaling"])
+    plain = M.scaled_inv_freqs(cfg["hidden_size"] // cfg["num_attention_heads"], cfg["rope_theta"], None)
+    ratio = plain / inv
+    # all three bands occur: untouched, blended, divided by the factor
+    assert (ratio == 1.0).any() and (np.abs(ratio - 8.0) < 1e-4).any() and ((ratio > 1.01) & (ratio < 7.9)).any()
+    o = M.build_oracle(d, "embedding", "last_token")
+    b = G.random_batch(17, [7, 101, 230], 0, 1000)
+    hs = o.hidden_states(b)
+    for s, a, e in _per_sequence(b):
+        with torch.no_grad():
+            ref = hf(input_ids=_t(b.input_ids[a:e])).last_hidden_state[0]
+        assert (ref - hs[a:e]).abs().max().item() < TOL

@@ -117,6 +117,9 @@ struct NormArgs {
   int residual_f32 = -1;
 };
 int launch_add_norm(const NormArgs& n, cudaStream_t stream);
+// LayerNorm with bias over whole q rows and whole k rows (width H, stride ld), in place.
+int launch_layernorm_qk(void* q, void* k, int ld, const void* gq, const void* bq, const void* gk,
+                        const void* bk, int T, int H, float eps, int dtype, cudaStream_t stream);
 // LayerNorm without bias over fp32 rows, in place.
 int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, float eps, int dtype,
                               cudaStream_t stream);

@@ -89,7 +89,11 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
       if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Jina");
     } else if (mt == "bert" && (name_or_path == "jinaai/jina-bert-v2-qk-post-norm" ||
                                 auto_config.find("jinaai/jina-bert-v2-qk-post-norm") != std::string::npos)) {
-      throw TeiError(ERR_START, "JinaCodeBert checkpoints are outside this backend");
+      s.jina = s.jina_code = true;
+      if (pos_type == "alibi") s.alibi = true;
+      else if (pos_type != "absolute") throw TeiError(ERR_START, "not supported");  // flash_jina_code.rs:296
+      if (s.classifier) throw TeiError(ERR_START, "`classifier` model type is not supported for Jina Code");
+      if (s.pool == POOL_SPLADE) throw TeiError(ERR_START, "`splade` is not supported for Jina Code");
     } else if (pos_type != "absolute") {
       throw TeiError(ERR_START, "FlashBert only supports absolute position embeddings");
     }
@@ -248,9 +252,25 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
       s.qkv_bias = true;
       s.causal = c.get_bool("is_causal", true);
     } else {
-      // flash_mistral.rs:56,95-110: `sliding_window` is the left window of the attention;
-      // Llama's rope_scaling is refused (lib.rs:549-553), so is Mistral's here.
-      if (!c["rope_scaling"].is_null()) throw TeiError(ERR_START, "Rope scaling is not supported for " + std::string(mt == "llama" ? "FlashLlama yet" : "this Mistral backend"));
+      // flash_mistral.rs:56,95-110: `sliding_window` is the left window of the attention.
+      // Llama's rope_scaling is refused (lib.rs:549-553); Mistral hands its own to get_inv_freqs
+      // (flash_mistral.rs:278-283), whose untagged enum picks the variant by the fields present
+      // (layers/rotary.rs:11-27): Llama3 with all four numbers, NTK with `factor` alone.
+      if (!c["rope_scaling"].is_null()) {
+        if (mt == "llama") throw TeiError(ERR_START, "Rope scaling is not supported for FlashLlama yet");
+        const Json& rs = c["rope_scaling"];
+        if (!rs.is_object() || !rs["factor"].is_number()) throw TeiError(ERR_START, "config.json: unsupported `rope_scaling`");
+        const float factor = static_cast<float>(rs["factor"].as_double());
+        if (rs["high_freq_factor"].is_number() && rs["low_freq_factor"].is_number() &&
+            rs["original_max_position_embeddings"].is_number()) {
+          s.rope_l3_factor = factor;
+          s.rope_l3_high = static_cast<float>(rs["high_freq_factor"].as_double());
+          s.rope_l3_low = static_cast<float>(rs["low_freq_factor"].as_double());
+          s.rope_l3_orig_max = static_cast<float>(rs["original_max_position_embeddings"].as_double());
+        } else {
+          s.rope_ntk_factor = factor;
+        }
+      }
       s.head_dim = s.heads > 0 ? s.hidden / s.heads : 0;
       if (mt == "mistral" && c["sliding_window"].is_number()) s.window_left = static_cast<int>(c["sliding_window"].as_int());
       s.causal = !c.get_bool("use_bidirectional_attention", false);
@@ -728,6 +748,33 @@ void Replica::load_bert(const SafeTensors& st) {
     L.bo = upload_new(n.get(p + "attention.output.dense.bias"));
     L.ln1_g = upload_new(n.ln_w(p + "attention.output.LayerNorm"));
     L.ln1_b = upload_new(n.ln_b(p + "attention.output.LayerNorm"));
+    if (s.jina_code) {
+      // JinaCodeAttention::load / JinaCodeBertLayer::load (flash_jina_code.rs:27-90,170-212):
+      // `attention.self.layer_norm_q` / `_k` over the whole hidden width; `mlp.up_gated_layer`
+      // [2I, H] without bias whose rows [0, I) are NOT gated and rows [I, 2I) go through the
+      // activation (:236-240); `mlp.down_layer`; `layer_norm_1`, `layer_norm_2`.
+      L.lnq_g = upload_new(n.ln_w(p + "attention.self.layer_norm_q"));
+      L.lnq_b = upload_new(n.ln_b(p + "attention.self.layer_norm_q"));
+      L.lnk_g = upload_new(n.ln_w(p + "attention.self.layer_norm_k"));
+      L.lnk_b = upload_new(n.ln_b(p + "attention.self.layer_norm_k"));
+      const StTensor& gw = n.get(p + "mlp.up_gated_layer.weight");
+      expect_shape(gw, {2 * I, H}, p + "mlp.up_gated_layer.weight");
+      StTensor gate = gw, up = gw;
+      gate.shape = {I, H};
+      up.shape = {I, H};
+      gate.nbytes = up.nbytes = gw.nbytes / 2;
+      gate.data = gw.data + gw.nbytes / 2;
+      L.w1 = dev_alloc(static_cast<size_t>(2) * I * H * 2);
+      upload_rows_interleaved(L.w1, gate, up);
+      expect_shape(n.get(p + "mlp.down_layer.weight"), {H, I}, p + "mlp.down_layer.weight");
+      L.w2 = upload_new(n.get(p + "mlp.down_layer.weight"));
+      L.b2 = upload_new(n.get(p + "mlp.down_layer.bias"));
+      L.lnm_g = upload_new(n.ln_w(p + "layer_norm_1"));
+      L.lnm_b = upload_new(n.ln_b(p + "layer_norm_1"));
+      L.ln2_g = upload_new(n.ln_w(p + "layer_norm_2"));
+      L.ln2_b = upload_new(n.ln_b(p + "layer_norm_2"));
+      continue;
+    }
     if (s.jina) {
       // JinaBertLayer::load (flash_jina.rs:133-155): `mlp.gated_layers.weight` [2I, H] without
       // bias, rows [0, I) gated by the activation, rows [I, 2I) not; `mlp.wo`; `mlp.layernorm`.
@@ -1054,6 +1101,23 @@ void Replica::build_rope_tables() {
         inv[i] = (1.0f / std::pow(base * f, static_cast<float>(2 * i) / static_cast<float>(dh))) / sdiv;
       }
     }
+    if (spec_.rope_l3_factor > 0.f) {
+      // RopeScaling::Llama3 (layers/rotary.rs:46-85): short wavelengths keep their frequency,
+      // long ones are divided by the factor, the band between is blended; all in f32.
+      const float old_len = spec_.rope_l3_orig_max;
+      const float low_wavelen = old_len / spec_.rope_l3_low, high_wavelen = old_len / spec_.rope_l3_high;
+      for (int i = 0; i < half; ++i) {
+        const float inv_base = inv[i];
+        const float wavelen = 2.0f * 3.14159265358979323846f / inv_base;
+        if (wavelen < high_wavelen) continue;
+        if (wavelen > low_wavelen) {
+          inv[i] = inv_base / spec_.rope_l3_factor;
+        } else {
+          const float smooth = (old_len / wavelen - spec_.rope_l3_low) / (spec_.rope_l3_high - spec_.rope_l3_low);
+          inv[i] = (1.0f - smooth) * (inv_base / spec_.rope_l3_factor) + smooth * inv_base;
+        }
+      }
+    }
     std::vector<float> c(static_cast<size_t>(len) * half), s(static_cast<size_t>(len) * half);
     for (int p = 0; p < len; ++p) {
       for (int i = 0; i < half; ++i) {
@@ -1340,12 +1404,30 @@ void Replica::forward_bert() {
     a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
     a.alibi_slopes = alibi_slopes_; a.dtype = s.dtype; a.status = status;
+    if (s.jina_code) {
+      LAUNCH(KC_NORM, launch_layernorm_qk(qkv, qkv + static_cast<size_t>(H) * 2, 3 * H, L.lnq_g, L.lnq_b, L.lnk_g,
+                                          L.lnk_b, T, H, s.eps, s.dtype, stream_), "q / k LayerNorm");
+    }
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
     NormArgs n1;
     n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
     n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "attention LayerNorm");
+    if (s.jina_code) {
+      // flash_jina_code.rs:226-247: h = layer_norm_1(attention block output + layer input), the
+      // gated feed-forward on h, then layer_norm_2(down + h).  h goes to tmp_ (free again), the
+      // down projection to x1_ (consumed by then).
+      NormArgs nm = n1;
+      nm.x = x1_; nm.residual = x_; nm.gamma = L.lnm_g; nm.beta = L.lnm_b; nm.out = tmp_;
+      LAUNCH(KC_NORM, launch_add_norm(nm, stream_), "pre-MLP LayerNorm");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(tmp_, L.w1, nullptr, ffn_, T, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated projection");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, x1_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "down projection");
+      NormArgs n2 = n1;
+      n2.x = x1_; n2.residual = tmp_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
+      LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "post-MLP LayerNorm");
+      continue;
+    }
     if (s.gated) {  // JinaBERT: act(gate) * up in the epilogue of one [T, 2I] projection
       LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, nullptr, ffn_, T, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated projection");
     } else {

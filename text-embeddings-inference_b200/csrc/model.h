@@ -45,8 +45,13 @@ struct ModelSpec {
   bool roberta = false;
   bool gte = false;        // GTE ("new"): post-LN blocks with RoPE and a gated feed-forward (models/flash_gte.rs)
   float rope_ntk_factor = 0.f;  // RopeScaling::Ntk (layers/rotary.rs:86-93), 0: none
+  // RopeScaling::Llama3 (layers/rotary.rs:46-85), factor 0: none
+  float rope_l3_factor = 0.f, rope_l3_high = 0.f, rope_l3_low = 0.f, rope_l3_orig_max = 0.f;
   bool distil = false;     // DistilBERT: no token types, its own tensor names (models/flash_distilbert.rs)
   bool jina = false;       // JinaBERT: gated feed-forward, optional ALiBi (models/flash_jina.rs)
+  // JinaCodeBert (models/flash_jina_code.rs): LayerNorm on q and k, a second LayerNorm with the
+  // layer's input as residual before the feed-forward, gate in the second half of the rows
+  bool jina_code = false;
   bool alibi = false;      // ALiBi slopes instead of a position table
   int hidden = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, inter = 0;
   int vocab = 0, max_pos = 0, type_vocab = 0;
@@ -165,6 +170,9 @@ class Replica {
     void *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
     void *w1 = nullptr, *b1 = nullptr, *w2 = nullptr, *b2 = nullptr;
     void *q_norm = nullptr, *k_norm = nullptr;
+    // JinaCodeBert: LayerNorm of q, of k, and `layer_norm_1`
+    void *lnq_g = nullptr, *lnq_b = nullptr, *lnk_g = nullptr, *lnk_b = nullptr;
+    void *lnm_g = nullptr, *lnm_b = nullptr;
     // mixture-of-experts layers: router [E_pad, H], w1 [E*I, H], w2 transposed per expert
     // [E*H, I], bias [H]
     void *moe_router = nullptr, *moe_w1 = nullptr, *moe_w2t = nullptr, *moe_bias = nullptr;

@@ -243,6 +243,37 @@ __global__ void __launch_bounds__(256) layernorm_rows_f32_kernel(float* __restri
   for (int j = lane; j < H; j += 32) r[j] = (r[j] - mean) * rstd * ldf<T>(gamma[j]);
 }
 
+// LayerNorm over whole q rows and whole k rows (all heads together), in place, on strided views
+// of the fused projection output: JinaCodeBert normalises q and k before attention
+// (backends/candle/src/models/flash_jina_code.rs:112-120).  One warp per row; rows [0, T) are
+// q, rows [T, 2T) are k.  Statistics in fp32 from the values as stored, like layer_norm.rs:108-132.
+template <class T>
+__global__ void __launch_bounds__(256)
+layernorm_qk_kernel(T* q, T* k, int ld, const T* __restrict__ gq, const T* __restrict__ bq,
+                    const T* __restrict__ gk, const T* __restrict__ bk, int T_, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= 2 * T_) return;
+  const bool is_k = idx >= T_;
+  T* r = (is_k ? k : q) + static_cast<size_t>(is_k ? idx - T_ : idx) * ld;
+  const T* g = is_k ? gk : gq;
+  const T* b = is_k ? bk : bq;
+  float s = 0.f;
+  for (int j = lane; j < H; j += 32) s += ldf<T>(r[j]);
+  const float mean = warp_sum(s) / static_cast<float>(H);
+  float v = 0.f;
+  for (int j = lane; j < H; j += 32) {
+    const float d = ldf<T>(r[j]) - mean;
+    v += d * d;
+  }
+  const float rstd = rsqrtf(warp_sum(v) / static_cast<float>(H) + eps);
+  for (int j = lane; j < H; j += 32) {
+    // cast back to the model dtype before the affine part (layer_norm.rs:127-131)
+    const float n = ldf<T>(stf<T>((ldf<T>(r[j]) - mean) * rstd));
+    r[j] = stf<T>(n * ldf<T>(g[j]) + ldf<T>(b[j]));
+  }
+}
+
 // ------------------------------------------------------------------ per-head RMSNorm + RoPE
 // One warp per (token, head).  Optional RMSNorm over the head (flash_qwen3.rs:150-151), then
 // x*cos + rotate_half(x)*sin with the half-rotation pairing (j, j + head_dim/2)
@@ -651,6 +682,25 @@ int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, floa
   } else {
     layernorm_rows_f32_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
         x, reinterpret_cast<const __nv_bfloat16*>(gamma), rows, H, eps);
+  }
+  return last_error();
+}
+
+int launch_layernorm_qk(void* q, void* k, int ld, const void* gq, const void* bq, const void* gk,
+                        const void* bk, int T, int H, float eps, int dtype, cudaStream_t st) {
+  if (T <= 0) return 0;
+  const int warps = 8;
+  const int grid = (2 * T + warps - 1) / warps;
+  if (dtype == DT_F16) {
+    using X = __half;
+    layernorm_qk_kernel<X><<<grid, warps * 32, 0, st>>>(
+        static_cast<X*>(q), static_cast<X*>(k), ld, static_cast<const X*>(gq), static_cast<const X*>(bq),
+        static_cast<const X*>(gk), static_cast<const X*>(bk), T, H, eps);
+  } else {
+    using X = __nv_bfloat16;
+    layernorm_qk_kernel<X><<<grid, warps * 32, 0, st>>>(
+        static_cast<X*>(q), static_cast<X*>(k), ld, static_cast<const X*>(gq), static_cast<const X*>(bq),
+        static_cast<const X*>(gk), static_cast<const X*>(bk), T, H, eps);
   }
   return last_error();
 }
