@@ -1,7 +1,7 @@
 /* C ABI of libtei_b200.so: a B200 (sm_100a) implementation of the `Backend` trait of Text
- * Embeddings Inference (backends/core/src/lib.rs:37-48) for the BERT / RoBERTa / XLM-R,
- * NomicBERT and Qwen3 model paths that backends/candle serves with flash_bert / flash_nomic /
- * flash_qwen3.  A Rust shim (`text-embeddings-inference_b200/rust_shim`) binds these functions
+ * Embeddings Inference (backends/core/src/lib.rs:37-48) for the model paths that backends/candle
+ * serves with its flash models (flash_bert, flash_distilbert, flash_gte, flash_jina,
+ * flash_jina_code, flash_mistral, flash_modernbert, flash_nomic, flash_qwen2, flash_qwen3).  A Rust shim (`text-embeddings-inference_b200/rust_shim`) binds these functions
  * and implements `text_embeddings_backend_core::Backend` on top of them.
  *
  * Conventions
@@ -12,7 +12,8 @@
  *   - All batch pointers are HOST pointers borrowed for the duration of the call
  *     (`Batch`, backends/core/src/lib.rs:9-17); output buffers are caller-allocated host memory.
  *   - A handle is used by one thread at a time, as the reference's single backend thread does
- *     (backends/src/lib.rs:612-647).  Nothing throws or aborts across this boundary.
+ *     (backends/src/lib.rs:612-647), except through the per-replica entry points below.
+ *     Nothing throws or aborts across this boundary.
  *   - The library owns all device memory: weights, a workspace that grows only when a larger
  *     batch than ever before arrives, and pinned staging buffers.
  */
@@ -80,6 +81,10 @@ int tei_b200_output_dim(const tei_b200_t* h);
 int tei_b200_hidden_size(const tei_b200_t* h);
 /* Number of classes of a classifier (0 for embedding models). */
 int tei_b200_num_classes(const tei_b200_t* h);
+/* First position id of every sequence: what the router adds when it builds position_ids
+ * (router/src/lib.rs:184-192 -> core/src/tokenization.rs:406-411): pad_token_id + 1 for the
+ * RoBERTa family, else 0.  For hosts that build batches themselves (tei_b200_queue_append). */
+int tei_b200_position_offset(const tei_b200_t* h);
 
 /* Backend::embed (backends/candle/src/lib.rs:656-709).
  *   pooled_out [n_pooled, output_dim]: row i is the embedding of batch position pooled_idx[i]

@@ -128,6 +128,8 @@ def test_config_dispatch_refusals_follow_the_reference(lib, tmp_path):
     assert e.kind == "Start" and "not supported for Jina Code" in str(e)
     e = _start_error(tmp_path, G.jina_code_config(), pool="splade")     # flash_jina_code.rs:309-311
     assert "`splade` is not supported for Jina Code" in str(e)
+    e = _start_error(tmp_path, dict(G.qwen3_config(), model_type="bidirectional_pplx_qwen3"), pool="mean")  # lib.rs:537-542
+    assert e.kind == "Start" and "Pplx1 is only supported in fp32 precision" in str(e)
     e = _start_error(tmp_path, G.jina_config(), pool="splade")          # flash_jina.rs:262-264
     assert "`splade` is not supported for Jina" in str(e)
     e = _start_error(tmp_path, dict(G.bert_config(), position_embedding_type="relative_key"))  # flash_bert.rs:241-243

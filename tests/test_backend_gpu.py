@@ -203,6 +203,10 @@ def test_trait_surface_and_health(lib, model_dirs):
     clf = _backend(model_dirs, "bert_cls3", "classifier", "cls")
     assert clf.num_classes == 3
     clf.health()
+    # position ids start at pad_token_id + 1 for the RoBERTa family (router/src/lib.rs:184-192)
+    x = _backend(model_dirs, "xlmr", "classifier", "cls")
+    assert be.position_offset == 0 and x.position_offset == 2
+    x.close()
     be.close()
     clf.close()
 

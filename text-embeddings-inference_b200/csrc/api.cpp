@@ -393,6 +393,7 @@ int tei_b200_hidden_size(const tei_b200_t* h) {
   return h->spec.pool == POOL_SPLADE ? h->spec.hidden : h->replicas[0]->raw_dim();
 }
 int tei_b200_num_classes(const tei_b200_t* h) { return h ? h->spec.n_classes : 0; }
+int tei_b200_position_offset(const tei_b200_t* h) { return h ? h->spec.position_offset : 0; }
 
 int tei_b200_embed(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* token_type_ids,
                    const uint32_t* position_ids, size_t n_tokens,

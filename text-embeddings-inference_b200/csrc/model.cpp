@@ -68,6 +68,7 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
   if (mt == "bert" || mt == "roberta" || mt == "xlm-roberta" || mt == "camembert") {
     s.arch = ARCH_BERT;
     s.roberta = mt != "bert";
+    if (s.roberta) s.position_offset = static_cast<int>(c.get_int("pad_token_id", 0)) + 1;
     s.vocab = static_cast<int>(need_int(c, "vocab_size"));
     s.hidden = static_cast<int>(need_int(c, "hidden_size"));
     s.layers = static_cast<int>(need_int(c, "num_hidden_layers"));
@@ -325,6 +326,8 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
       if (s.head_act < 0 || s.head_act == ACT_SWIGLU) throw TeiError(ERR_START, "unsupported classifier_activation");
     }
   } else {
+    // backends/candle/src/lib.rs:537-542: the reference itself refuses this model in half precision
+    if (mt == "bidirectional_pplx_qwen3") throw TeiError(ERR_START, "Pplx1 is only supported in fp32 precision");
     throw TeiError(ERR_START, "model_type `" + mt + "` is not served by this backend");
   }
   if (s.head_dim != 64 && s.head_dim != 128) {

@@ -48,6 +48,9 @@ struct ModelSpec {
   // RopeScaling::Llama3 (layers/rotary.rs:46-85), factor 0: none
   float rope_l3_factor = 0.f, rope_l3_high = 0.f, rope_l3_low = 0.f, rope_l3_orig_max = 0.f;
   bool distil = false;     // DistilBERT: no token types, its own tensor names (models/flash_distilbert.rs)
+  // What the router adds to every position id (router/src/lib.rs:184-192): pad_token_id + 1 for
+  // model_type roberta / xlm-roberta / camembert, else 0.
+  int position_offset = 0;
   bool jina = false;       // JinaBERT: gated feed-forward, optional ALiBi (models/flash_jina.rs)
   // JinaCodeBert (models/flash_jina_code.rs): LayerNorm on q and k, a second LayerNorm with the
   // layer's input as residual before the feed-forward, gate in the second half of the rows

@@ -58,6 +58,7 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_output_dim": (c_int, [c_void_p]),
     "tei_b200_hidden_size": (c_int, [c_void_p]),
     "tei_b200_num_classes": (c_int, [c_void_p]),
+    "tei_b200_position_offset": (c_int, [c_void_p]),
     "tei_b200_embed": (
         c_int,
         [c_void_p] + _BATCH + [POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int,

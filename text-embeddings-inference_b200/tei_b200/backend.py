@@ -94,6 +94,8 @@ class B200Backend:
         self.output_dim = self._lib.tei_b200_output_dim(self._h)
         self.hidden_size = self._lib.tei_b200_hidden_size(self._h)
         self.num_classes = self._lib.tei_b200_num_classes(self._h)
+        # first position id of every sequence (router/src/lib.rs:184-192)
+        self.position_offset = int(self._lib.tei_b200_position_offset(self._h))
         self._keep = None
 
     def close(self):
