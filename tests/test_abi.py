@@ -159,3 +159,39 @@ def test_config_dispatch_refusals_follow_the_reference(lib, tmp_path):
     assert "Neither `rope_theta` nor `rope_parameters.rope_theta`" in str(e)
     e = _start_error(tmp_path, G.bert_config(id2label=None), model_type="classifier")  # bert.rs:376-379
     assert "`id2label` must be set" in str(e)
+
+
+def test_headers_are_plain_c(tmp_path):
+    """The boundary is a C ABI: every header compiles as C99 on its own and together, and a C
+    program that uses a few entry points links against the library."""
+    import subprocess
+    hdrs = sorted(glob.glob(os.path.join(ROOT, "include", "*.h")))
+    assert len(hdrs) >= 3
+    for h in hdrs:
+        subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", h], check=True)
+    src = tmp_path / "use.c"
+    src.write_text(
+        "".join(f'#include "{os.path.basename(h)}"\n' for h in hdrs) +
+        "#include <stdio.h>\n"
+        "int main(void) {\n"
+        "  tei_b200_queue_t* q = NULL;\n"
+        "  if (tei_b200_queue_create(0, 16, 0, &q) != TEI_B200_OK) return 1;\n"
+        "  uint32_t ids[3] = {7, 8, 9};\n"
+        "  if (tei_b200_queue_append(q, ids, NULL, NULL, 3, 2, 1, 42) != TEI_B200_OK) return 2;\n"
+        "  uint32_t a[16], b[16], c[16], cu[5], p[4], r[4], mx; uint64_t tags[4]; size_t nt, ns, np, nr;\n"
+        "  if (tei_b200_queue_next_batch(q, a, b, c, 16, cu, p, r, tags, 4, &nt, &ns, &np, &nr, &mx)) return 3;\n"
+        "  if (nt != 3 || ns != 1 || np != 1 || nr != 0 || mx != 3 || tags[0] != 42 || c[0] != 2 || c[2] != 4) return 4;\n"
+        "  tei_b200_queue_destroy(q);\n"
+        "  tei_b200_t* h = NULL; char err[256];\n"
+        "  int rc = tei_b200_create(\"/nonexistent\", \"float16\", TEI_B200_EMBEDDING, TEI_B200_POOL_CLS, NULL, 0, &h, err, sizeof err);\n"
+        "  if (rc != TEI_B200_ERR_START || h != NULL) return 5;\n"
+        "  puts(err);\n"
+        "  return 0;\n"
+        "}\n")
+    lib_dir = os.path.join(ROOT, "text-embeddings-inference_b200", "lib")
+    exe = tmp_path / "use"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", lib_dir, "-ltei_b200", f"-Wl,-rpath,{lib_dir}"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
+    assert "config.json" in out.stdout
