@@ -259,7 +259,9 @@ __device__ __forceinline__ float write_probs_tracking(const uint32_t (&sc)[BKV /
 constexpr float kRescaleThreshold = 8.0f;
 
 
-template <class T, int D>
+// ALIBI is a compile-time switch: the softmax code of the models without a positional bias
+// (all but JinaBERT with ALiBi) then holds two variants of each pass instead of three.
+template <class T, int D, bool ALIBI>
 __global__ void __launch_bounds__(ATTN_THREADS, AttnCfg<D>::CTAS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_k,
@@ -592,7 +594,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int kv_end = unit_kv_end(it);
       const int n_kv = (kv_end - kv_begin + BKV - 1) / BKV;
       const int qi = q0 + r;                  // position inside the sequence
-      const float slope = p.alibi_slopes ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+      const float slope = ALIBI ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
       float m = -INFINITY, l = 0.f;           // running maximum (scaled log2 domain) and sum
       for (int j = 0; j < n_kv; ++j, ++g) {
         const int b = g % S_BUFS;
@@ -624,28 +626,36 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         ptx::tmem_ld_wait();
         auto true_max = [&]() {
-          if (p.alibi_slopes) return row_max<true, true>(sc, lo, lim, n_chunks, p.scale_log2, slope, rel);
-          if (tile_full) return row_max<false, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
-          return row_max<true, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+          if constexpr (ALIBI) {
+            return row_max<true, true>(sc, lo, lim, n_chunks, p.scale_log2, slope, rel);
+          } else {
+            if (tile_full) return row_max<false, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+            return row_max<true, false>(sc, lo, lim, n_chunks, p.scale_log2, 0.f, 0);
+          }
         };
         auto probs = [&](float m_use) {
-          if (p.alibi_slopes) return write_probs<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_use);
-          if (tile_full) return write_probs<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
-          return write_probs<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+          if constexpr (ALIBI) {
+            return write_probs<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_use);
+          } else {
+            if (tile_full) return write_probs<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+            return write_probs<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_use);
+          }
         };
         // P goes over this step's scores.  Their columns were last read by the P V of step
         // g-2, which ran before the S MMA of this step wrote them (MMAs run in issue order).
-        float sum;
+        // The two-pass form has ONE call site (warp-uniform flag): the unrolled passes are long,
+        // and the instruction footprint of the step is what the warps wait for most.
+        float sum = 0.f;
+        bool two_pass = j == 0;
         if (j == 0) {
           // P V of the first step overwrites the output tile: nothing to rescale
           m = true_max();
-          sum = probs(m == -INFINITY ? 0.f : m);
         } else {
           // Later steps first try the maximum the row already has: one pass, no dependency of
           // the exponentials on a maximum of this step.
           const float m_old = (m == -INFINITY) ? 0.f : m;
           float amax;
-          if (p.alibi_slopes) sum = write_probs_tracking<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_old, amax);
+          if constexpr (ALIBI) sum = write_probs_tracking<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_old, amax);
           else if (tile_full) sum = write_probs_tracking<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
           else sum = write_probs_tracking<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
           const float mx = amax + m_old;  // this step's maximum in the scaled log2 domain
@@ -676,9 +686,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             // The probabilities again, now relative to the raised maxima (the scores are still
             // in registers; rows that kept their maximum write the same values once more).
-            sum = probs(m == -INFINITY ? 0.f : m);
+            two_pass = true;
           }
         }
+        if (two_pass) sum = probs(m == -INFINITY ? 0.f : m);
         l += sum;
         // P and the rescaled O written, S read: hand over to the MMA thread.
         ptx::tmem_st_wait();
@@ -728,8 +739,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   }
 }
 
-template <class T, int D>
-int launch_typed(const AttnArgs& a, cudaStream_t stream) {
+template <class T, int D, bool ALIBI>
+int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
   using L = AttnSmem<D>;
   const CUtensorMapDataType dt =
       a.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -744,7 +755,7 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
                     static_cast<uint64_t>(a.ld_v) * 2, 64, BKV);
   if (rc) return rc;
   static bool attr_set[64] = {};
-  auto kern = attention_tcgen05_kernel<T, D>;
+  auto kern = attention_tcgen05_kernel<T, D, ALIBI>;
   const int dev = current_device() & 63;
   if (!attr_set[dev]) {
     cudaError_t e =
@@ -771,6 +782,11 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
   const long long grid = total < resident ? total : resident;
   kern<<<static_cast<unsigned>(grid), ATTN_THREADS, L::TOTAL, stream>>>(tm_q, tm_k, tm_v, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+template <class T, int D>
+int launch_typed(const AttnArgs& a, cudaStream_t stream) {
+  return a.alibi_slopes ? launch_alibi<T, D, true>(a, stream) : launch_alibi<T, D, false>(a, stream);
 }
 
 }  // namespace
