@@ -116,6 +116,9 @@ def test_pooled_and_raw_bookkeeping(lib, model_dirs):
     all_pooled = G.random_batch(41, lens, 0, 1000, type_vocab=2)
     mixed = G.random_batch(41, lens, 0, 1000, pooled=[0, 2, 3], raw=[1, 4, 5], type_vocab=2)
     only_raw = G.random_batch(41, lens, 0, 1000, pooled=[], raw=list(range(6)), type_vocab=2)
+    # all_pooled takes the last-layer shortcut (only the first rows are computed after the
+    # scores), mixed and only_raw the full path: the comparisons below also pin the two against
+    # each other, bit for bit.
     ep = be.embed(all_pooled)
     em = be.embed(mixed)
     er = be.embed(only_raw)

@@ -1,5 +1,7 @@
 #include "model.h"
 
+#include <cstdlib>
+
 #include "kernels.h"
 #include "plan.h"
 
@@ -1327,8 +1329,30 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
     if (static_cast<size_t>(n_local) != n_work) throw TeiError(ERR_INFERENCE, "attention planning mismatch");
     off += 4 * n_work;
   }
+  // Last-layer shortcut of the post-LN BERT family (see forward_bert): needs room for five packed
+  // [B, H] blocks inside one [T, H] buffer.
+  size_t o_work_first = 0;
+  // TEI_B200_FIRST_ROWS=0 switches the shortcut off (for A/B timing).
+  static const bool first_rows_enabled = [] {
+    const char* v = std::getenv("TEI_B200_FIRST_ROWS");
+    return !(v && v[0] == '0');
+  }();
+  first_rows_only_ = first_rows_enabled && s.arch == ARCH_BERT && !s.jina && s.layers > 0 && s.local_window < 0 &&
+                     n_raw == 0 && (predict || s.pool == POOL_CLS) && 5 * B_ <= T_;
+  n_work_first_ = 0;
+  if (first_rows_only_) {
+    o_work_first = off;
+    const int32_t* all = h + o_work;
+    for (size_t i = 0; i < n_work; ++i) {
+      if (all[4 * i + 2] != 0) continue;  // not the first query tile of its sequence
+      std::memcpy(h + off, all + 4 * i, 16);
+      off += 4;
+      ++n_work_first_;
+    }
+  }
   TEI_CUDA(cudaMemcpyAsync(d_ints_, h_ints_, off * 4, cudaMemcpyHostToDevice, stream_));
   stats_.last_h2d_bytes = static_cast<double>(off * 4);
+  d_work_first_ = first_rows_only_ ? d_ints_ + o_work_first : nullptr;
   d_ids_ = d_ints_ + o_ids;
   d_types_ = d_ints_ + o_types;
   d_pos_ = d_ints_ + o_pos;
@@ -1400,6 +1424,39 @@ void Replica::forward_bert() {
   for (int i = 0; i < s.layers; ++i) {
     const LayerW& L = layers_[i];
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, 3 * H, H, H, 3 * H, ACT_NONE, s.dtype, status), stream_), "qkv projection");
+    if (first_rows_only_ && i + 1 == s.layers) {
+      // Only the first row of every sequence is read after this layer.  Keys and values are
+      // there for every token; the scores are taken for the first query tile of each sequence
+      // only, and the output projection, both LayerNorms and the feed-forward run on the B
+      // first rows, packed into x1_ (five [B, H] blocks) and ffn_; the result goes back to the
+      // rows' places in x_, where pooling and the heads look for it.
+      const int B = static_cast<int>(B_);
+      const size_t blk = static_cast<size_t>(B) * H * 2;
+      uint8_t* c0 = static_cast<uint8_t*>(x1_);
+      void *attn_c = c0, *res_c = c0 + blk, *tmp_c = c0 + 2 * blk, *x1_c = c0 + 3 * blk, *out_c = c0 + 4 * blk;
+      AttnArgs a;
+      a.q = qkv; a.k = qkv + static_cast<size_t>(H) * 2; a.v = qkv + static_cast<size_t>(2 * H) * 2;
+      a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_first_; a.n_work = static_cast<int>(n_work_first_);
+      a.total_tokens = T; a.n_heads = s.heads; a.n_kv_heads = s.kv_heads; a.head_dim = s.head_dim;
+      a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
+      a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
+      a.alibi_slopes = alibi_slopes_; a.dtype = s.dtype; a.status = status;
+      LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention, first query tiles");
+      LAUNCH(KC_POOL, launch_first_rows(attn_, attn_c, d_cu_, B, H, 0, stream_), "first rows of the attention output");
+      LAUNCH(KC_POOL, launch_first_rows(x_, res_c, d_cu_, B, H, 0, stream_), "first rows of the layer input");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_c, L.wo, L.bo, tmp_c, B, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
+      NormArgs n1;
+      n1.x = tmp_c; n1.residual = res_c; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_c; n1.sum_out = nullptr;
+      n1.T = B; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
+      LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "attention LayerNorm");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
+      NormArgs n2 = n1;
+      n2.x = tmp_c; n2.residual = x1_c; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = out_c;
+      LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "output LayerNorm");
+      LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H, 1, stream_), "first rows back in place");
+      break;
+    }
     AttnArgs a;
     a.q = qkv; a.k = qkv + static_cast<size_t>(H) * 2; a.v = qkv + static_cast<size_t>(2 * H) * 2;
     a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);

@@ -278,6 +278,12 @@ class Replica {
   int32_t *d_ids_ = nullptr, *d_types_ = nullptr, *d_pos_ = nullptr, *d_cu_ = nullptr,
           *d_pooled_idx_ = nullptr, *d_raw_rows_ = nullptr, *d_work_ = nullptr, *d_all_idx_ = nullptr,
           *d_work_local_ = nullptr;  // work list of the layers with the two-sided local window
+  // When only the first row of every sequence leaves the model (CLS pooling or a classifier head,
+  // no raw rows), the last layer needs its keys and values for every token but everything after
+  // the scores only for that row: a work list with just the first query tile of every sequence.
+  int32_t* d_work_first_ = nullptr;
+  size_t n_work_first_ = 0;
+  bool first_rows_only_ = false;
   size_t out_floats_ = 0;
 };
 
