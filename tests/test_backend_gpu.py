@@ -300,3 +300,29 @@ def test_bert_base_full_width_against_oracle(lib, tmp_path):
     for i in range(6):
         assert _cos(m[i][None], ref[i][None]).min() >= COS_MIN
     be.close()
+
+
+@pytest.mark.parametrize("key,model_type,pool", [
+    ("jina_alibi6", "embedding", "cls"),       # gated feed-forward, ALiBi
+    ("bert", "embedding", "cls"),
+    ("distilbert", "embedding", "cls"),
+])
+def test_first_rows_shortcut_equals_the_full_path(lib, model_dirs, key, model_type, pool):
+    """CLS pooling without raw requests runs the last layer on the first rows only; one raw
+    request in the batch forces every row.  Same pooled rows either way, bit for bit; a batch too
+    short for the shortcut (fewer than five tokens per sequence) gives the oracle's rows too."""
+    be = _backend(model_dirs, key, model_type, pool)
+    lens = [7, 33, 150, 2, 64, 129, 300]
+    tv = 1 if key == "distilbert" else 2
+    short = G.random_batch(51, lens, 0, 1000, type_vocab=tv)
+    full = G.random_batch(51, lens, 0, 1000, pooled=list(range(6)), raw=[6], type_vocab=tv)
+    a, b = be.embed(short), be.embed(full)
+    for i in range(6):
+        assert np.array_equal(a[i].values, b[i].values)
+    assert np.array_equal(a[6].values, b[6].values[0])
+    tiny = G.random_batch(52, [2, 3, 1, 4], 0, 1000, type_vocab=tv)  # 10 tokens < 5 * 4
+    o = M.build_oracle(model_dirs[key], model_type, pool)
+    ref, _ = o.embed(tiny)
+    got = be.embed(tiny)
+    _check_embeddings(np.stack([got[i].values for i in range(4)]), ref.numpy())
+    be.close()

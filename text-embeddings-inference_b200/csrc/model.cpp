@@ -1337,7 +1337,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
     const char* v = std::getenv("TEI_B200_FIRST_ROWS");
     return !(v && v[0] == '0');
   }();
-  first_rows_only_ = first_rows_enabled && s.arch == ARCH_BERT && !s.jina && s.layers > 0 && s.local_window < 0 &&
+  first_rows_only_ = first_rows_enabled && s.arch == ARCH_BERT && !s.jina_code && s.layers > 0 && s.local_window < 0 &&
                      n_raw == 0 && (predict || s.pool == POOL_CLS) && 5 * B_ <= T_;
   n_work_first_ = 0;
   if (first_rows_only_) {
@@ -1449,7 +1449,11 @@ void Replica::forward_bert() {
       n1.x = tmp_c; n1.residual = res_c; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_c; n1.sum_out = nullptr;
       n1.T = B; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
       LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "attention LayerNorm");
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+      if (s.gated) {  // JinaBERT
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, nullptr, ffn_, B, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated projection");
+      } else {
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
+      }
       LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
       NormArgs n2 = n1;
       n2.x = tmp_c; n2.residual = x1_c; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = out_c;
