@@ -326,3 +326,25 @@ def test_first_rows_shortcut_equals_the_full_path(lib, model_dirs, key, model_ty
     got = be.embed(tiny)
     _check_embeddings(np.stack([got[i].values for i in range(4)]), ref.numpy())
     be.close()
+
+
+@pytest.mark.parametrize("key,pool,dtype", [
+    ("qwen3", "last_token", "float16"),
+    ("qwen3", "last_token", "bfloat16"),
+    ("mistral", "last_token", "float16"),      # left window
+    ("llama", "cls", "float16"),
+    ("qwen2_bidir", "cls", "float16"),
+])
+def test_one_row_shortcut_of_the_decoders_equals_the_full_path(lib, model_dirs, key, pool, dtype):
+    """Last-token / CLS pooling without raw requests runs the decoders' last layer on one row per
+    sequence; a raw request in the batch forces every row.  Same pooled rows, bit for bit."""
+    be = _backend(model_dirs, key, "embedding", pool, dtype)
+    lens = [7, 33, 150, 2, 64, 129, 300, 128]
+    short = G.random_batch(61, lens, 0, 1000)
+    full = G.random_batch(61, lens, 0, 1000, pooled=list(range(7)), raw=[7])
+    a, b = be.embed(short), be.embed(full)
+    for i in range(7):
+        assert np.array_equal(a[i].values, b[i].values), i
+    row = -1 if pool == "last_token" else 0
+    assert np.array_equal(a[7].values, b[7].values[row])
+    be.close()

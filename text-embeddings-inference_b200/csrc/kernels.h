@@ -117,10 +117,11 @@ struct NormArgs {
   int residual_f32 = -1;
 };
 int launch_add_norm(const NormArgs& n, cudaStream_t stream);
-// The first row of every sequence (the CLS token) of a [T, H] matrix of 16-bit values, packed
-// into [B, H] (scatter = 0) or written back from it (scatter = 1).
-int launch_first_rows(const void* src, void* dst, const int* cu_seqlens, int B, int H, int scatter,
-                      cudaStream_t stream);
+// One row per sequence of a [T, row_bytes] matrix, the first (last = 0: the CLS token) or the
+// last one (last = 1), packed into [B, row_bytes] (scatter = 0) or written back from it
+// (scatter = 1).  row_bytes is a multiple of 16.
+int launch_first_rows(const void* src, void* dst, const int* cu_seqlens, int B, int row_bytes, int scatter,
+                      int last, cudaStream_t stream);
 // LayerNorm with bias over whole q rows and whole k rows (width H, stride ld), in place.
 int launch_layernorm_qk(void* q, void* k, int ld, const void* gq, const void* bq, const void* gk,
                         const void* bk, int T, int H, float eps, int dtype, cudaStream_t stream);

@@ -1339,12 +1339,23 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   }();
   first_rows_only_ = first_rows_enabled && s.arch == ARCH_BERT && !s.jina_code && s.layers > 0 && s.local_window < 0 &&
                      n_raw == 0 && (predict || s.pool == POOL_CLS) && 5 * B_ <= T_;
+  // The pre-norm decoders (forward_qwen3) do the same for CLS and last-token pooling; their
+  // packed blocks are [B, Q] + four [B, H] inside x1_ and [B, 2I] + an fp32 [B, H] inside ffn_.
+  const bool one_row_decoder =
+      first_rows_enabled && s.arch == ARCH_QWEN3 && !s.modernbert && !projection_ && s.layers > 0 && n_raw == 0 &&
+      !predict && (s.pool == POOL_CLS || s.pool == POOL_LAST) &&
+      B_ * (static_cast<size_t>(s.q_width()) + 4 * s.hidden) <= T_ * static_cast<size_t>(s.hidden) &&
+      B_ * (static_cast<size_t>(s.inter) * 4 + static_cast<size_t>(s.hidden) * 4 + 64) <= T_ * static_cast<size_t>(s.inter) * 2;
+  const bool last_row = one_row_decoder && s.pool == POOL_LAST;
+  first_rows_only_ = first_rows_only_ || one_row_decoder;
   n_work_first_ = 0;
   if (first_rows_only_) {
     o_work_first = off;
     const int32_t* all = h + o_work;
     for (size_t i = 0; i < n_work; ++i) {
-      if (all[4 * i + 2] != 0) continue;  // not the first query tile of its sequence
+      // keep the query tile that holds the row: the first one, or the last one of the sequence
+      const bool keep = last_row ? all[4 * i + 2] + 128 >= all[4 * i + 1] : all[4 * i + 2] == 0;
+      if (!keep) continue;
       std::memcpy(h + off, all + 4 * i, 16);
       off += 4;
       ++n_work_first_;
@@ -1442,8 +1453,8 @@ void Replica::forward_bert() {
       a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
       a.alibi_slopes = alibi_slopes_; a.dtype = s.dtype; a.status = status;
       LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention, first query tiles");
-      LAUNCH(KC_POOL, launch_first_rows(attn_, attn_c, d_cu_, B, H, 0, stream_), "first rows of the attention output");
-      LAUNCH(KC_POOL, launch_first_rows(x_, res_c, d_cu_, B, H, 0, stream_), "first rows of the layer input");
+      LAUNCH(KC_POOL, launch_first_rows(attn_, attn_c, d_cu_, B, H * 2, 0, 0, stream_), "first rows of the attention output");
+      LAUNCH(KC_POOL, launch_first_rows(x_, res_c, d_cu_, B, H * 2, 0, 0, stream_), "first rows of the layer input");
       LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_c, L.wo, L.bo, tmp_c, B, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
       NormArgs n1;
       n1.x = tmp_c; n1.residual = res_c; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_c; n1.sum_out = nullptr;
@@ -1458,7 +1469,7 @@ void Replica::forward_bert() {
       NormArgs n2 = n1;
       n2.x = tmp_c; n2.residual = x1_c; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = out_c;
       LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "output LayerNorm");
-      LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H, 1, stream_), "first rows back in place");
+      LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H * 2, 1, 0, stream_), "first rows back in place");
       break;
     }
     AttnArgs a;
@@ -1620,6 +1631,37 @@ void Replica::forward_qwen3() {
     a.window_right = local ? s.local_window : -1;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
     a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    if (first_rows_only_ && i + 1 == s.layers) {
+      // Only one row per sequence is pooled (the first or the last token) and nothing else is
+      // read after this layer: scores for the query tile that holds the row, then the output
+      // projection, the post-attention norm, the feed-forward and the final norm on the B rows,
+      // packed into x1_ / ffn_, and back to the rows' places in x_.
+      const int B = static_cast<int>(B_);
+      const int last = s.pool == POOL_LAST ? 1 : 0;
+      uint8_t* c0 = static_cast<uint8_t*>(x1_);
+      const size_t blk = static_cast<size_t>(B) * H * 2;
+      void* attn_c = c0;
+      uint8_t* c1 = c0 + static_cast<size_t>(B) * Q * 2;
+      void *tmp_c = c1, *x1_c = c1 + blk, *out_c = c1 + 2 * blk;
+      float* resid_c = reinterpret_cast<float*>(static_cast<uint8_t*>(ffn_) +
+                                                align_up(static_cast<size_t>(B) * 2 * I * 2, 64));
+      a.work_items = d_work_first_;
+      a.n_work = static_cast<int>(n_work_first_);
+      LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention, one query tile per sequence");
+      LAUNCH(KC_POOL, launch_first_rows(attn_, attn_c, d_cu_, B, Q * 2, 0, last, stream_), "rows of the attention output");
+      LAUNCH(KC_POOL, launch_first_rows(resid_, resid_c, d_cu_, B, H * 4, 0, last, stream_), "rows of the running sum");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_c, L.wo, L.bo, tmp_c, B, H, Q, Q, H, ACT_NONE, s.dtype, status), stream_), "o projection");
+      NormArgs m2 = n1;
+      m2.x = tmp_c; m2.residual = resid_c; m2.gamma = L.ln2_g; m2.out = x1_c; m2.sum_out = resid_c; m2.T = B;
+      LAUNCH(KC_NORM, launch_add_norm(m2, stream_), "post-attention norm");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gate/up projection");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "down projection");
+      NormArgs mf = m2;
+      mf.x = tmp_c; mf.gamma = final_norm_; mf.out = out_c;
+      LAUNCH(KC_NORM, launch_add_norm(mf, stream_), "final norm");
+      LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H * 2, 1, last, stream_), "rows back in place");
+      return;
+    }
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, Q, Q, H, ACT_NONE, s.dtype, status), stream_), "o projection");
     NormArgs n2 = n1;

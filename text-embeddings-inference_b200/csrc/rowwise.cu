@@ -686,27 +686,27 @@ int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, floa
   return last_error();
 }
 
-// First rows of the sequences: gather (dst[b] = src[cu[b]]) or scatter (dst[cu[b]] = src[b]) of
-// H 16-bit values per row, 16 bytes per thread.
+// One row per sequence, the first (last = 0) or the last (last = 1): gather
+// (dst[b] = src[row_b]) or scatter (dst[row_b] = src[b]), 16 bytes per thread.
 __global__ void __launch_bounds__(256) first_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                          const int* __restrict__ cu, int B, int vec_per_row,
-                                                         int scatter) {
+                                                         int scatter, int last) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<long long>(B) * vec_per_row) return;
   const int b = static_cast<int>(i / vec_per_row), v = static_cast<int>(i % vec_per_row);
   const size_t packed = static_cast<size_t>(b) * vec_per_row + v;
-  const size_t in_batch = static_cast<size_t>(cu[b]) * vec_per_row + v;
+  const size_t in_batch = static_cast<size_t>(last ? cu[b + 1] - 1 : cu[b]) * vec_per_row + v;
   if (scatter) dst[in_batch] = src[packed];
   else dst[packed] = src[in_batch];
 }
 
-int launch_first_rows(const void* src, void* dst, const int* cu_seqlens, int B, int H, int scatter,
-                      cudaStream_t st) {
+int launch_first_rows(const void* src, void* dst, const int* cu_seqlens, int B, int row_bytes, int scatter,
+                      int last, cudaStream_t st) {
   if (B <= 0) return 0;
-  if (H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
-  const long long n = static_cast<long long>(B) * (H / 8);
+  if (row_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const long long n = static_cast<long long>(B) * (row_bytes / 16);
   first_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
-      static_cast<const uint4*>(src), static_cast<uint4*>(dst), cu_seqlens, B, H / 8, scatter);
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), cu_seqlens, B, row_bytes / 16, scatter, last);
   return last_error();
 }
 
