@@ -306,6 +306,8 @@ def test_bert_base_full_width_against_oracle(lib, tmp_path):
     ("jina_alibi6", "embedding", "cls"),       # gated feed-forward, ALiBi
     ("bert", "embedding", "cls"),
     ("distilbert", "embedding", "cls"),
+    ("gte", "embedding", "cls"),               # NomicBERT skeleton: RoPE, gated feed-forward
+    ("nomic", "embedding", "cls"),
 ])
 def test_first_rows_shortcut_equals_the_full_path(lib, model_dirs, key, model_type, pool):
     """CLS pooling without raw requests runs the last layer on the first rows only; one raw
@@ -313,7 +315,7 @@ def test_first_rows_shortcut_equals_the_full_path(lib, model_dirs, key, model_ty
     short for the shortcut (fewer than five tokens per sequence) gives the oracle's rows too."""
     be = _backend(model_dirs, key, model_type, pool)
     lens = [7, 33, 150, 2, 64, 129, 300]
-    tv = 1 if key == "distilbert" else 2
+    tv = 1 if key in ("distilbert", "gte") else 2
     short = G.random_batch(51, lens, 0, 1000, type_vocab=tv)
     full = G.random_batch(51, lens, 0, 1000, pooled=list(range(6)), raw=[6], type_vocab=tv)
     a, b = be.embed(short), be.embed(full)

@@ -1337,7 +1337,9 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
     const char* v = std::getenv("TEI_B200_FIRST_ROWS");
     return !(v && v[0] == '0');
   }();
-  first_rows_only_ = first_rows_enabled && s.arch == ARCH_BERT && !s.jina_code && s.layers > 0 && s.local_window < 0 &&
+  const bool post_ln_family = (s.arch == ARCH_BERT && !s.jina_code) ||
+                              (s.arch == ARCH_NOMIC && !layers_.empty() && !layers_.back().moe_router);
+  first_rows_only_ = first_rows_enabled && post_ln_family && s.layers > 0 && s.local_window < 0 &&
                      n_raw == 0 && (predict || s.pool == POOL_CLS) && 5 * B_ <= T_;
   // The pre-norm decoders (forward_qwen3) do the same for CLS and last-token pooling; their
   // packed blocks are [B, Q] + four [B, H] inside x1_ and [B, 2I] + an fp32 [B, H] inside ffn_.
@@ -1544,6 +1546,35 @@ void Replica::forward_nomic() {
     a.ld_q = a.ld_k = a.ld_v = 3 * H; a.ld_o = H; a.causal = 0;
     a.scale = static_cast<float>(1.0 / std::sqrt(static_cast<double>(s.head_dim)));
     a.alibi_slopes = nullptr; a.dtype = s.dtype; a.status = status;
+    if (first_rows_only_ && i + 1 == s.layers) {
+      // Only the first row of every sequence is read after this layer (see forward_bert): scores
+      // for the first query tiles, everything behind them on the B first rows, packed into x1_.
+      const int B = static_cast<int>(B_);
+      const size_t blk = static_cast<size_t>(B) * H * 2;
+      uint8_t* c0 = static_cast<uint8_t*>(x1_);
+      void *attn_c = c0, *res_c = c0 + blk, *tmp_c = c0 + 2 * blk, *x1_c = c0 + 3 * blk, *out_c = c0 + 4 * blk;
+      a.work_items = d_work_first_;
+      a.n_work = static_cast<int>(n_work_first_);
+      LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention, first query tiles");
+      LAUNCH(KC_POOL, launch_first_rows(attn_, attn_c, d_cu_, B, H * 2, 0, 0, stream_), "first rows of the attention output");
+      LAUNCH(KC_POOL, launch_first_rows(x_, res_c, d_cu_, B, H * 2, 0, 0, stream_), "first rows of the layer input");
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_c, L.wo, L.bo, tmp_c, B, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
+      NormArgs m1;
+      m1.x = tmp_c; m1.residual = res_c; m1.gamma = L.ln1_g; m1.beta = L.ln1_b; m1.out = x1_c; m1.sum_out = nullptr;
+      m1.T = B; m1.H = H; m1.eps = s.eps; m1.rms = 0; m1.dtype = s.dtype;
+      LAUNCH(KC_NORM, launch_add_norm(m1, stream_), "norm1");
+      if (s.gated) {
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, 2 * I, H, H, I, s.act, s.dtype, status), stream_), "gated fc1");
+      } else {
+        LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
+      }
+      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
+      NormArgs m2 = m1;
+      m2.x = tmp_c; m2.residual = x1_c; m2.gamma = L.ln2_g; m2.beta = L.ln2_b; m2.out = out_c;
+      LAUNCH(KC_NORM, launch_add_norm(m2, stream_), "norm2");
+      LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H * 2, 1, 0, stream_), "first rows back in place");
+      break;
+    }
     LAUNCH(KC_ATTENTION, launch_attention(a, stream_), "attention");
     LAUNCH(KC_GEMM, launch_gemm(gemm_args(attn_, L.wo, L.bo, tmp_, T, H, H, H, H, ACT_NONE, s.dtype, status), stream_), "attention output projection");
     NormArgs n1;
