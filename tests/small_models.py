@@ -98,6 +98,12 @@ def write_all(base):
         G.nomic_config(hidden=128, layers=4, heads=2, inter=256, vocab=1000, n_positions=2048, moe_every=2,
                        num_experts=8, moe_top_k=2),
         seed=17, norm_jitter=0.1, std=0.05)
+    # three layers: the last one is a local-attention layer (index 2 with a global layer every 3)
+    dirs["modernbert_local_last"] = G.write_model_dir(
+        base / "modernbert_local_last",
+        G.modernbert_config(hidden=128, layers=3, heads=2, inter=256, vocab=1000, max_pos=1024, local_attention=64,
+                            global_every=3),
+        seed=25, norm_jitter=0.1, std=0.05)
     dirs["modernbert"] = G.write_model_dir(
         base / "modernbert",
         G.modernbert_config(hidden=128, layers=4, heads=2, inter=256, vocab=1000, max_pos=1024, local_attention=64,

@@ -336,6 +336,8 @@ def test_first_rows_shortcut_equals_the_full_path(lib, model_dirs, key, model_ty
     ("mistral", "last_token", "float16"),      # left window
     ("llama", "cls", "float16"),
     ("qwen2_bidir", "cls", "float16"),
+    ("modernbert", "cls", "float16"),          # LayerNorm, local / global layers with their own work lists
+    ("modernbert_local_last", "cls", "float16"),   # the last layer walks the local-window list
 ])
 def test_one_row_shortcut_of_the_decoders_equals_the_full_path(lib, model_dirs, key, pool, dtype):
     """Last-token / CLS pooling without raw requests runs the decoders' last layer on one row per

@@ -1156,7 +1156,7 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
                                size_t raw_rows) {
   const ModelSpec& s = spec_;
   // integer inputs
-  const size_t ints_need = 3 * tokens + (seqs + 1) + 2 * seqs + raw_rows + 8 * n_work + 64;
+  const size_t ints_need = 3 * tokens + (seqs + 1) + 2 * seqs + raw_rows + 12 * n_work + 64;  // up to three work lists
   if (ints_need > ints_cap_) {
     TEI_CUDA(cudaStreamSynchronize(stream_));
     if (d_ints_) cudaFree(d_ints_);
@@ -1344,7 +1344,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   // The pre-norm decoders (forward_qwen3) do the same for CLS and last-token pooling; their
   // packed blocks are [B, Q] + four [B, H] inside x1_ and [B, 2I] + an fp32 [B, H] inside ffn_.
   const bool one_row_decoder =
-      first_rows_enabled && s.arch == ARCH_QWEN3 && !s.modernbert && !projection_ && s.layers > 0 && n_raw == 0 &&
+      first_rows_enabled && s.arch == ARCH_QWEN3 && !projection_ && s.layers > 0 && n_raw == 0 &&
       !predict && (s.pool == POOL_CLS || s.pool == POOL_LAST) &&
       B_ * (static_cast<size_t>(s.q_width()) + 4 * s.hidden) <= T_ * static_cast<size_t>(s.hidden) &&
       B_ * (static_cast<size_t>(s.inter) * 4 + static_cast<size_t>(s.hidden) * 4 + 64) <= T_ * static_cast<size_t>(s.inter) * 2;
@@ -1353,7 +1353,9 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   n_work_first_ = 0;
   if (first_rows_only_) {
     o_work_first = off;
-    const int32_t* all = h + o_work;
+    // ModernBERT: the last layer may be one of those with the two-sided window and its own list
+    const bool last_is_local = s.modernbert && s.local_window >= 0 && ((s.layers - 1) % s.global_every != 0);
+    const int32_t* all = h + (last_is_local ? o_work_local : o_work);
     for (size_t i = 0; i < n_work; ++i) {
       // keep the query tile that holds the row: the first one, or the last one of the sequence
       const bool keep = last_row ? all[4 * i + 2] + 128 >= all[4 * i + 1] : all[4 * i + 2] == 0;
