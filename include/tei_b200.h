@@ -118,9 +118,10 @@ int tei_b200_predict(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* t
  *   tei_b200_embed_on / tei_b200_predict_on : embed / predict with the WHOLE batch on that one
  *       replica; same arguments, results and error codes as tei_b200_embed / tei_b200_predict.
  * Calls with different replica indices may run concurrently; calls with the same index are
- * serialised inside the library.  They do not touch the staged-batch state of the handle, but
- * must not overlap with the whole-handle calls (embed, predict, stage, run, sync, fetch), which
- * use every replica. */
+ * serialised inside the library.  They do not touch the staged-batch state of the handle.  The
+ * whole-handle calls (embed, predict, stage, run, sync, fetch) use every replica and wait for
+ * per-replica calls in flight; tei_b200_health runs its probe on replica 0 under that
+ * replica's lock, so it is safe next to per-replica callers. */
 int tei_b200_num_replicas(const tei_b200_t* h);
 int tei_b200_embed_on(tei_b200_t* h, int replica, const uint32_t* input_ids,
                       const uint32_t* token_type_ids, const uint32_t* position_ids, size_t n_tokens,
@@ -175,6 +176,29 @@ int tei_b200_stats(const tei_b200_t* h, double* out, int n);
  * quadratic_cost * L * L, balanced longest-first.  shard_of_seq has n_seqs entries. */
 int tei_b200_plan_shards(const uint32_t* cumulative_seq_lengths, size_t n_seqs, int n_shards,
                          double linear_cost, double quadratic_cost, int* shard_of_seq);
+
+/* Host-only, no GPU needed: the split of one packed batch over n_shards replicas and the way
+ * back, with a stand-in for the forward.  The batch is split exactly as tei_b200_embed /
+ * tei_b200_predict split it on a handle with n_shards devices (same planner, same gather of
+ * the tokens, same renumbering of the pooled / raw index lists, same scatter of the rows); in
+ * place of a model every shard echoes its own sub-batch: a pooled row (and, with predict != 0,
+ * a score row) is (sum of the sequence's input ids mod 65521) + column, a raw row is
+ * id mod 4096 + 7 * type id + 13 * (position id mod 4096) + column, `width` columns each.  The
+ * rows come back in the layout of Backend::embed / predict (backends/candle/src/lib.rs:694-706,
+ * 718-722), so a caller can check the whole bookkeeping of the split against the unsplit batch.
+ * shard_tokens_out (optional, n_shards entries) receives the tokens each shard got. */
+int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_ids, const uint32_t* position_ids,
+                        size_t n_tokens, const uint32_t* cumulative_seq_lengths, size_t n_seqs,
+                        const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx, size_t n_raw,
+                        int predict, int n_shards, double linear_cost, double quadratic_cost, int width,
+                        float* pooled_out, float* raw_out, float* scores_out, int* shard_tokens_out);
+
+/* The last-layer shortcut, on by default: when only one row per sequence leaves the model (CLS
+ * or last-token pooling, or a classifier head, and no raw request in the batch), everything
+ * behind the last layer's attention scores runs on those rows only.  on == 0 makes every call
+ * compute every row, as the reference does (flash_bert.rs:169-185); the results are the same
+ * bit for bit.  No counterpart in the reference. */
+int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on);
 
 #ifdef __cplusplus
 }

@@ -55,7 +55,7 @@ int tei_b200_attention_plan_windowed(const int32_t* cu_seqlens_host, int n_seqs,
 /* Variable-length attention over a packed batch.  Replaces flash_attn_varlen
  * (backends/candle/src/flash_attn.rs:23-120).  q/k/v are token-major strided views
  * (row stride ld_* elements, head h at column h*head_dim); work_dev holds the quadruples from
- * tei_b200_attention_plan copied to the device.  head_dim 64 or 128.  alibi_slopes_dev: fp32
+ * tei_b200_attention_plan copied to the device.  head_dim 32, 64 or 128.  alibi_slopes_dev: fp32
  * [n_heads] or NULL. */
 int tei_b200_op_attention(const void* q_dev, const void* k_dev, const void* v_dev, void* out_dev,
                           const int32_t* work_dev, int n_work, int total_tokens, int n_heads,

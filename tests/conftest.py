@@ -47,7 +47,7 @@ def lib():
 
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
-    """Small seeded model directories of every family (head_dim 64 / 128 as the kernels need)."""
+    """Small seeded model directories of every family (head_dim 32, 64 and 128)."""
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     import small_models
     return small_models.write_all(tmp_path_factory.mktemp("models"))

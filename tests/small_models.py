@@ -93,6 +93,19 @@ def write_all(base):
         G.gte_config(hidden=256, layers=2, heads=2, inter=256, vocab=1000, max_pos=2048, type_vocab=2, ntk_factor=None,
                      id2label={"0": "a", "1": "b"}),
         seed=20, norm_jitter=0.1, std=0.05)
+    # head_dim 32: the shape of all-MiniLM-L6-v2 (384 wide, 12 heads), the model of the reference's
+    # own flash-BERT test (backends/candle/tests/test_flash_bert.rs:18), and the same head size
+    # behind RoPE and behind q/k RMSNorm + GQA
+    dirs["minilm"] = G.write_model_dir(
+        base / "minilm", G.bert_config(hidden=384, layers=2, heads=12, inter=1536, vocab=1000, max_pos=512),
+        seed=26, norm_jitter=0.1, std=0.05)
+    dirs["nomic_d32"] = G.write_model_dir(
+        base / "nomic_d32", G.nomic_config(hidden=128, layers=2, heads=4, inter=256, vocab=1000, n_positions=2048),
+        seed=27, norm_jitter=0.1, std=0.05)
+    dirs["qwen3_d32"] = G.write_model_dir(
+        base / "qwen3_d32",
+        G.qwen3_config(hidden=128, layers=2, heads=4, kv_heads=2, head_dim=32, inter=256, vocab=1000, max_pos=2048),
+        seed=28, norm_jitter=0.1, std=0.05)
     dirs["nomic_moe"] = G.write_model_dir(
         base / "nomic_moe",
         G.nomic_config(hidden=128, layers=4, heads=2, inter=256, vocab=1000, n_positions=2048, moe_every=2,
@@ -146,6 +159,10 @@ GOLDEN_CASES = {
     "gte_scores": ("gte_cls", "classifier", "cls", dict(seed=122, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
     "jina_code_mean": ("jina_code", "embedding", "mean", dict(seed=123, lens=LENS + [511], lo=0, hi=1000, type_vocab=2, offset=0)),
     "jina_code_abs_cls": ("jina_code_abs", "embedding", "cls", dict(seed=124, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "minilm_mean": ("minilm", "embedding", "mean", dict(seed=127, lens=LENS + [511], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "minilm_cls": ("minilm", "embedding", "cls", dict(seed=128, lens=LENS, lo=0, hi=1000, type_vocab=2, offset=0)),
+    "nomic_d32_mean": ("nomic_d32", "embedding", "mean", dict(seed=129, lens=LENS + [700], lo=0, hi=1000, type_vocab=2, offset=0)),
+    "qwen3_d32_last": ("qwen3_d32", "embedding", "last_token", dict(seed=130, lens=LENS + [700], lo=0, hi=1000, type_vocab=1, offset=0)),
     "splade": ("splade", "embedding", "splade", dict(seed=107, lens=[5, 1, 130, 40], lo=0, hi=1003, type_vocab=2, offset=0)),
 }
 

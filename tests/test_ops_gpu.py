@@ -39,6 +39,10 @@ def _close(got, ref, tol):
     (1000, 768, 3072, "none", True, True, "bf16"),
     (700, 256, 256, "tanh", True, False, "f16"),
     (20000, 2304, 768, "none", True, False, "f16"),   # many waves of the persistent loop
+    (300, 512, 200, "none", True, False, "f16"),      # K tail: the last k-block is 8 of 64 wide, zero-filled by TMA
+    (300, 512, 1000, "gelu", True, False, "f16"),     # K tail behind 15 full k-blocks (a Dense module of 1000 inputs)
+    (100, 256, 1000, "none", False, False, "bf16"),   # the same on the single-CTA kernel
+    (64, 384, 8, "none", True, False, "f16"),         # K smaller than one MMA step
 ])
 def test_linear(lib, M, N, K, act, bias, res, dtype):
     from tei_b200 import ops
@@ -122,6 +126,16 @@ def _ref_attention(q, k, v, cu, causal, scale, slopes=None):
     ([200, 130], 2, 2, 128, False, False, "f16"),
     ([200, 130], 4, 4, 64, False, True, "f16"),        # ALiBi
     ([1000], 4, 1, 128, True, False, "f16"),           # MQA, 8 query tiles
+    # head_dim 32 (64-byte swizzle): all-MiniLM-L6-v2, bge-small, e5-small, gte-small
+    ([1], 1, 1, 32, False, False, "f16"),
+    ([15, 16, 17], 2, 2, 32, False, False, "f16"),
+    ([63, 64, 65], 2, 2, 32, False, False, "f16"),
+    ([127, 128, 129], 2, 2, 32, False, False, "f16"),
+    ([127, 128, 129], 2, 2, 32, True, False, "f16"),
+    ([512, 5, 300], 12, 12, 32, False, False, "f16"),
+    ([512, 77], 12, 12, 32, True, False, "bf16"),
+    ([300, 40], 4, 2, 32, True, False, "bf16"),        # GQA
+    ([200, 130], 4, 4, 32, False, True, "f16"),        # ALiBi
 ])
 def test_attention(lib, lens, nh, nkv, D, causal, alibi, dtype):
     from tei_b200 import ops
@@ -156,6 +170,9 @@ def test_attention(lib, lens, nh, nkv, D, causal, alibi, dtype):
     ([520], 4, 2, 128, True, 0.3, "bf16"),
     ([700], 2, 2, 64, False, 0.05, "f16"),        # slow growth: raised lazily, every second or third step
     ([700], 2, 1, 128, False, 0.05, "f16"),
+    ([700, 130], 2, 2, 32, False, 0.3, "f16"),
+    ([700], 2, 2, 32, True, 0.05, "bf16"),
+    ([4096], 2, 1, 64, False, 0.02, "f16"),       # 64 key steps: the maximum keeps growing over the whole unit
 ])
 def test_attention_running_maximum_is_raised(lib, lens, nh, nkv, D, causal, slope, dtype):
     """Scores that keep growing along the keys for half of the rows and keep falling for the
@@ -190,6 +207,8 @@ def test_attention_running_maximum_is_raised(lib, lens, nh, nkv, D, causal, slop
     ([513, 64, 200], 4, 4, 64, False, 64, 64, "f16"),     # ModernBERT-style local attention
     ([400], 2, 2, 128, False, 17, 130, "f16"),            # asymmetric
     ([300, 130], 4, 4, 64, True, 4096, -1, "f16"),        # window wider than the sequences
+    ([300, 40, 129], 4, 4, 32, True, 64, -1, "f16"),
+    ([513, 64], 4, 2, 32, False, 64, 64, "bf16"),
 ])
 def test_attention_sliding_window(lib, lens, nh, nkv, D, causal, wl, wr, dtype):
     # flash_attn.rs:23-36,72-95: key j counts for query i when i - wl <= j <= i + wr.
@@ -231,6 +250,36 @@ def test_attention_sliding_window(lib, lens, nh, nkv, D, causal, wl, wr, dtype):
     assert torch.equal(out, ops.attention(q, k, v, cu, causal=causal, scale=scale, window_left=wl, window_right=wr))
 
 
+@pytest.mark.parametrize("lens,nh,nkv,D,causal,dtype", [
+    ([8192, 100], 4, 2, 128, True, "bf16"),     # 64 query tiles, 128 key steps, the K/V rings wrap > 40 times
+    ([8055], 2, 1, 128, True, "f16"),           # the longest sequence of the Qwen3-style benchmark batch
+    ([2048, 2008, 513], 4, 4, 64, False, "f16"),  # the NomicBERT-style benchmark lengths
+    ([4096], 2, 2, 64, False, "f16"),
+    ([3000], 4, 4, 32, True, "f16"),
+])
+def test_attention_long_sequences(lib, lens, nh, nkv, D, causal, dtype):
+    """The lengths the benchmark configurations run (up to 8,055 and 8,192 tokens) against fp32
+    softmax on the same device, one head at a time so that the reference fits."""
+    from tei_b200 import ops
+    dt = DT[dtype]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = _gen(T + nh + D)
+    qkv = torch.randn(T, (nh + 2 * nkv) * D, device="cuda", generator=g).to(dt)
+    q = qkv[:, : nh * D].view(T, nh, D)
+    k = qkv[:, nh * D: (nh + nkv) * D].view(T, nkv, D)
+    v = qkv[:, (nh + nkv) * D:].view(T, nkv, D)
+    scale = 1.0 / D ** 0.5
+    out = ops.attention(q, k, v, cu, causal=causal, scale=scale).view(T, nh, D)
+    tol = 1e-2 if dtype == "f16" else 4e-2
+    for h in range(nh):
+        hk = h // (nh // nkv)
+        ref = _ref_attention(q[:, h:h + 1], k[:, hk:hk + 1], v[:, hk:hk + 1], cu, causal, scale, None)
+        _close(out[:, h].reshape(T, D), ref, tol)
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_embedding_and_norms(lib, dtype):
     from tei_b200 import ops
@@ -268,7 +317,8 @@ def test_embedding_and_norms(lib, dtype):
 
 
 @pytest.mark.parametrize("nh,nkv,D,use_norm,dtype", [(12, 12, 64, False, "f16"), (16, 8, 128, True, "bf16"),
-                                                     (16, 8, 128, True, "f16")])
+                                                     (16, 8, 128, True, "f16"), (12, 12, 32, False, "f16"),
+                                                     (4, 2, 32, True, "bf16"), (3, 3, 48, True, "f16")])
 def test_qk_norm_rope(lib, nh, nkv, D, use_norm, dtype):
     from tei_b200 import ops
     dt = DT[dtype]

@@ -4,11 +4,14 @@
 
 #include "model.h"
 #include "plan.h"
+#include "split.h"
 
 #include <algorithm>
 #include <atomic>
+#include <condition_variable>
 #include <cstring>
 #include <fstream>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <sstream>
@@ -17,19 +20,6 @@
 using namespace tei;
 
 namespace {
-
-// A sub-batch for one replica plus where its rows go in the caller's buffers.
-struct Shard {
-  std::vector<uint32_t> ids, types, pos, cu, pooled_idx, raw_idx;
-  uint32_t max_length = 0;
-  std::vector<size_t> seqs;             // original batch positions, in shard order
-  std::vector<size_t> pooled_dst_row;   // caller's pooled row of each pooled entry of the shard
-  std::vector<size_t> raw_dst_row;      // caller's first raw row of each raw entry
-  std::vector<size_t> raw_len;
-  std::vector<float> pooled, raw, scores;
-  int err_kind = 0;
-  std::string err_msg;
-};
 
 void set_err(char* err, size_t cap, const std::string& msg) {
   if (!err || cap == 0) return;
@@ -46,26 +36,90 @@ std::string read_file(const std::string& path) {
   return ss.str();
 }
 
+// The thread that drives one replica of a multi-replica handle.  It lives as long as the handle
+// and sleeps on a condition variable between calls, so a split embed / predict costs one wake-up
+// per replica instead of thread creations.  Jobs never throw (the posting code wraps them).
+class Worker {
+ public:
+  Worker() : thread_([this]() { loop(); }) {}
+  ~Worker() {
+    {
+      std::lock_guard<std::mutex> g(m_);
+      stop_ = true;
+    }
+    cv_.notify_all();
+    thread_.join();
+  }
+  Worker(const Worker&) = delete;
+  Worker& operator=(const Worker&) = delete;
+  void post(std::function<void()> job) {
+    {
+      std::lock_guard<std::mutex> g(m_);
+      job_ = std::move(job);
+      pending_ = true;
+      done_ = false;
+    }
+    cv_.notify_all();
+  }
+  void wait() {
+    std::unique_lock<std::mutex> g(m_);
+    cv_.wait(g, [this]() { return done_; });
+  }
+
+ private:
+  void loop() {
+    std::unique_lock<std::mutex> g(m_);
+    for (;;) {
+      cv_.wait(g, [this]() { return pending_ || stop_; });
+      if (stop_) return;
+      std::function<void()> job = std::move(job_);
+      pending_ = false;
+      g.unlock();
+      job();
+      g.lock();
+      done_ = true;
+      cv_.notify_all();
+    }
+  }
+  std::mutex m_;
+  std::condition_variable cv_;
+  std::function<void()> job_;
+  bool pending_ = false, done_ = true, stop_ = false;
+  std::thread thread_;  // last member: the loop reads the others
+};
+
 }  // namespace
 
 struct tei_b200 {
   ModelSpec spec;
   std::string model_dir;
   std::vector<std::unique_ptr<Replica>> replicas;
-  // One lock per replica: the per-replica entry points (one caller thread per replica) take it,
-  // so two threads that were given the same index by mistake queue up instead of corrupting the
-  // replica's staging buffers.
+  // One lock per replica.  The per-replica entry points (one caller thread per replica) take
+  // their replica's; the whole-handle entry points take all of them, in index order.  Two
+  // threads that were given the same index by mistake, or a health probe next to per-replica
+  // callers, queue up instead of corrupting a replica's staging buffers.
   std::vector<std::unique_ptr<std::mutex>> replica_locks;
+  std::vector<std::unique_ptr<Worker>> workers;  // one per replica when there are several
   std::atomic<bool> healthy{true};
   // state of the staged batch (stage / run / sync / fetch)
   bool staged = false;
   bool staged_predict = false;
-  std::vector<Shard> shards;   // empty when a single replica took the whole batch
+  std::vector<Shard> shards;   // all empty when a single replica took the whole batch
+  bool split = false;          // the staged batch is spread over `shards`
   size_t staged_n_pooled = 0, staged_raw_rows = 0, staged_n_seqs = 0;
   double linear_cost = 1.0, quadratic_cost = 0.0;
 };
 
 namespace {
+
+// Every replica lock of the handle, taken in index order.
+struct AllReplicas {
+  std::vector<std::unique_lock<std::mutex>> held;
+  explicit AllReplicas(tei_b200* h) {
+    held.reserve(h->replica_locks.size());
+    for (auto& m : h->replica_locks) held.emplace_back(*m);
+  }
+};
 
 template <class F>
 int guarded(tei_b200* h, char* err, size_t cap, F&& fn) {
@@ -126,65 +180,33 @@ void precheck(const HostBatch& b) {
   }
 }
 
-void build_shards(tei_b200* h, const HostBatch& b, bool predict) {
-  const int n = static_cast<int>(h->replicas.size());
-  std::vector<int> shard_of(b.n_seqs, 0);
-  plan_shards(b.cu_seqlens, static_cast<int>(b.n_seqs), n, h->linear_cost, h->quadratic_cost,
-              shard_of.data());
-  h->shards.assign(n, Shard());
-  std::vector<size_t> local_index(b.n_seqs, 0);
-  for (size_t s = 0; s < b.n_seqs; ++s) {
-    Shard& sh = h->shards[shard_of[s]];
-    if (sh.cu.empty()) sh.cu.push_back(0);
-    const uint32_t a = b.cu_seqlens[s], e = b.cu_seqlens[s + 1];
-    sh.ids.insert(sh.ids.end(), b.input_ids + a, b.input_ids + e);
-    if (b.token_type_ids) sh.types.insert(sh.types.end(), b.token_type_ids + a, b.token_type_ids + e);
-    else sh.types.insert(sh.types.end(), e - a, 0u);
-    sh.pos.insert(sh.pos.end(), b.position_ids + a, b.position_ids + e);
-    sh.cu.push_back(sh.cu.back() + (e - a));
-    sh.max_length = std::max(sh.max_length, e - a);
-    local_index[s] = sh.seqs.size();
-    sh.seqs.push_back(s);
-  }
-  if (!predict) {
-    for (size_t i = 0; i < b.n_pooled; ++i) {
-      const uint32_t s = b.pooled_indices[i];
-      Shard& sh = h->shards[shard_of[s]];
-      sh.pooled_idx.push_back(static_cast<uint32_t>(local_index[s]));
-      sh.pooled_dst_row.push_back(i);
-    }
-    size_t row = 0;
-    for (size_t i = 0; i < b.n_raw; ++i) {
-      const uint32_t s = b.raw_indices[i];
-      Shard& sh = h->shards[shard_of[s]];
-      const size_t len = b.cu_seqlens[s + 1] - b.cu_seqlens[s];
-      sh.raw_idx.push_back(static_cast<uint32_t>(local_index[s]));
-      sh.raw_dst_row.push_back(row);
-      sh.raw_len.push_back(len);
-      row += len;
-    }
-  }
-}
-
+// Runs fn(replica, shard) for every shard that holds sequences, each on its replica's own
+// thread, and waits for all of them.  The first error of a shard is rethrown here.
 template <class F>
 void for_each_shard_parallel(tei_b200* h, F&& fn) {
-  std::vector<std::thread> threads;
+  std::vector<size_t> posted;
   for (size_t d = 0; d < h->shards.size(); ++d) {
     if (h->shards[d].seqs.empty()) continue;
-    threads.emplace_back([h, d, &fn]() {
-      Shard& sh = h->shards[d];
+    Shard* sh = &h->shards[d];
+    Replica* r = h->replicas[d].get();
+    sh->err_kind = 0;
+    h->workers[d]->post([sh, r, &fn]() {
       try {
-        fn(*h->replicas[d], sh);
+        fn(*r, *sh);
       } catch (const TeiError& e) {
-        sh.err_kind = e.kind;
-        sh.err_msg = e.what();
+        sh->err_kind = e.kind;
+        sh->err_msg = e.what();
       } catch (const std::exception& e) {
-        sh.err_kind = ERR_INFERENCE;
-        sh.err_msg = e.what();
+        sh->err_kind = ERR_INFERENCE;
+        sh->err_msg = e.what();
+      } catch (...) {
+        sh->err_kind = ERR_INFERENCE;
+        sh->err_msg = "unknown error";
       }
     });
+    posted.push_back(d);
   }
-  for (auto& t : threads) t.join();
+  for (size_t d : posted) h->workers[d]->wait();
   for (auto& sh : h->shards) {
     if (sh.err_kind) {
       const int k = sh.err_kind;
@@ -195,9 +217,9 @@ void for_each_shard_parallel(tei_b200* h, F&& fn) {
   }
 }
 
-void do_stage(tei_b200* h, const HostBatch& b, bool predict, bool normalize) {
-  precheck(b);
-  h->staged = false;
+bool wants_split(const tei_b200* h, const HostBatch& b) { return h->replicas.size() > 1 && b.n_seqs > 1; }
+
+void note_staged(tei_b200* h, const HostBatch& b, bool predict) {
   h->staged_predict = predict;
   h->staged_n_pooled = predict ? 0 : b.n_pooled;
   h->staged_n_seqs = b.n_seqs;
@@ -206,16 +228,20 @@ void do_stage(tei_b200* h, const HostBatch& b, bool predict, bool normalize) {
     for (size_t i = 0; i < b.n_raw; ++i) raw_rows += b.cu_seqlens[b.raw_indices[i] + 1] - b.cu_seqlens[b.raw_indices[i]];
   }
   h->staged_raw_rows = raw_rows;
-  if (h->replicas.size() == 1 || b.n_seqs == 1) {
-    h->shards.clear();
+}
+
+void do_stage(tei_b200* h, const HostBatch& b, bool predict, bool normalize) {
+  precheck(b);
+  h->staged = false;
+  note_staged(h, b, predict);
+  h->split = wants_split(h, b);
+  if (!h->split) {
     h->replicas[0]->stage(b, predict, normalize);
   } else {
-    build_shards(h, b, predict);
+    assign_shards(b, predict, static_cast<int>(h->replicas.size()), h->linear_cost, h->quadratic_cost, h->shards);
     for_each_shard_parallel(h, [&](Replica& r, Shard& sh) {
-      HostBatch sb = make_batch(sh.ids.data(), sh.types.data(), sh.pos.data(), sh.ids.size(), sh.cu.data(),
-                                sh.seqs.size(), sh.max_length, sh.pooled_idx.data(), sh.pooled_idx.size(),
-                                sh.raw_idx.data(), sh.raw_idx.size());
-      r.stage(sb, predict, normalize);
+      gather_shard_tokens(b, sh);
+      r.stage(sh.view(), predict, normalize);
     });
   }
   h->staged = true;
@@ -223,7 +249,7 @@ void do_stage(tei_b200* h, const HostBatch& b, bool predict, bool normalize) {
 
 void do_run(tei_b200* h) {
   if (!h->staged) throw TeiError(ERR_INFERENCE, "no staged batch");
-  if (h->shards.empty()) {
+  if (!h->split) {
     h->replicas[0]->run();
   } else {
     for_each_shard_parallel(h, [](Replica& r, Shard&) { r.run(); });
@@ -232,52 +258,65 @@ void do_run(tei_b200* h) {
 
 void do_sync(tei_b200* h) {
   if (!h->staged) throw TeiError(ERR_INFERENCE, "no staged batch");
-  if (h->shards.empty()) {
+  if (!h->split) {
     h->replicas[0]->sync_and_check();
   } else {
     for_each_shard_parallel(h, [](Replica& r, Shard&) { r.sync_and_check(); });
   }
 }
 
+struct RowWidths {
+  size_t D, DR, C;
+};
+RowWidths row_widths(const tei_b200* h) {
+  return {static_cast<size_t>(h->replicas[0]->output_dim()), static_cast<size_t>(h->replicas[0]->raw_dim()),
+          static_cast<size_t>(std::max(h->spec.n_classes, 1))};
+}
+
 void do_fetch(tei_b200* h, float* pooled_out, float* raw_out, float* scores_out) {
   if (!h->staged) throw TeiError(ERR_INFERENCE, "no staged batch");
-  if (h->shards.empty()) {
+  if (!h->split) {
     h->replicas[0]->fetch(pooled_out, raw_out, scores_out);
     return;
   }
-  const size_t D = static_cast<size_t>(h->replicas[0]->output_dim());
-  const size_t DR = static_cast<size_t>(h->replicas[0]->raw_dim());
-  const size_t C = static_cast<size_t>(std::max(h->spec.n_classes, 1));
+  const RowWidths w = row_widths(h);
   const bool predict = h->staged_predict;
   for_each_shard_parallel(h, [&](Replica& r, Shard& sh) {
-    size_t raw_rows = 0;
-    for (size_t l : sh.raw_len) raw_rows += l;
-    sh.pooled.resize(sh.pooled_idx.size() * D);
-    sh.raw.resize(raw_rows * DR);
-    sh.scores.resize(predict ? sh.seqs.size() * C : 0);
+    size_shard_results(sh, predict, w.D, w.DR, w.C);
     r.fetch(sh.pooled.data(), sh.raw.data(), sh.scores.data());
+    // every shard's rows go back to their original batch positions
+    scatter_shard(sh, predict, w.D, w.DR, w.C, pooled_out, raw_out, scores_out);
   });
-  // Host-side gather: every shard's rows go back to their original batch positions.
-  for (auto& sh : h->shards) {
-    if (sh.seqs.empty()) continue;
-    if (pooled_out) {
-      for (size_t i = 0; i < sh.pooled_dst_row.size(); ++i) {
-        std::memcpy(pooled_out + sh.pooled_dst_row[i] * D, sh.pooled.data() + i * D, D * 4);
-      }
-    }
-    if (raw_out) {
-      size_t src_row = 0;
-      for (size_t i = 0; i < sh.raw_dst_row.size(); ++i) {
-        std::memcpy(raw_out + sh.raw_dst_row[i] * DR, sh.raw.data() + src_row * DR, sh.raw_len[i] * DR * 4);
-        src_row += sh.raw_len[i];
-      }
-    }
-    if (predict && scores_out) {
-      for (size_t i = 0; i < sh.seqs.size(); ++i) {
-        std::memcpy(scores_out + sh.seqs[i] * C, sh.scores.data() + i * C, C * 4);
-      }
-    }
+}
+
+// embed / predict in one pass: with several replicas each replica's thread gathers its tokens,
+// stages, runs, waits once, copies back and scatters its rows; the calling thread only plans the
+// split and sleeps.
+void do_all(tei_b200* h, const HostBatch& b, bool predict, bool normalize, float* pooled_out,
+            float* raw_out, float* scores_out) {
+  precheck(b);
+  h->staged = false;
+  note_staged(h, b, predict);
+  h->split = wants_split(h, b);
+  if (!h->split) {
+    Replica& r = *h->replicas[0];
+    r.stage(b, predict, normalize);
+    h->staged = true;
+    r.run();
+    r.fetch(pooled_out, raw_out, scores_out);
+    return;
   }
+  assign_shards(b, predict, static_cast<int>(h->replicas.size()), h->linear_cost, h->quadratic_cost, h->shards);
+  const RowWidths w = row_widths(h);
+  for_each_shard_parallel(h, [&](Replica& r, Shard& sh) {
+    gather_shard_tokens(b, sh);
+    r.stage(sh.view(), predict, normalize);
+    r.run();
+    size_shard_results(sh, predict, w.D, w.DR, w.C);
+    r.fetch(sh.pooled.data(), sh.raw.data(), sh.scores.data());
+    scatter_shard(sh, predict, w.D, w.DR, w.C, pooled_out, raw_out, scores_out);
+  });
+  h->staged = true;
 }
 
 }  // namespace
@@ -331,6 +370,9 @@ int tei_b200_create(const char* model_dir, const char* dtype, int model_type, in
       h->replicas.emplace_back(new Replica(dv, h->spec, st));
       h->replica_locks.emplace_back(new std::mutex());
     }
+    if (h->replicas.size() > 1) {
+      for (size_t i = 0; i < h->replicas.size(); ++i) h->workers.emplace_back(new Worker());
+    }
     // Cost model of the sharding: FLOPs per token of the dense layers, FLOPs per token^2 of
     // attention (half of it when causal).
     const ModelSpec& s = h->spec;
@@ -360,6 +402,7 @@ int tei_b200_add_dense(tei_b200_t* h, const char* dense_path, char* err, size_t 
       set_err(err, err_cap, "Dense module files not found for path: " + std::string(dense_path));
       return;
     }
+    AllReplicas all(h);
     for (auto& r : h->replicas) r->add_dense(dir);
     h->staged = false;
   });
@@ -371,16 +414,18 @@ void tei_b200_destroy(tei_b200_t* h) { delete h; }
 int tei_b200_health(tei_b200_t* h) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
   if (h->healthy) return TEI_B200_OK;
-  // One-token probe, like backends/src/lib.rs:393-409.
+  // One-token probe, like backends/src/lib.rs:393-409.  It runs on replica 0 under that
+  // replica's lock and leaves the handle's staged-batch state alone, so it may be called while
+  // other threads are inside the per-replica entry points.
   const uint32_t ids[1] = {0}, types[1] = {0}, pos[1] = {0}, cu[2] = {0, 1}, idx[1] = {0};
   const ModelSpec& s = h->spec;
   int rc;
   if (s.classifier) {
     std::vector<float> scores(std::max(s.n_classes, 1));
-    rc = tei_b200_predict(h, ids, types, pos, 1, cu, 1, 1, scores.data(), nullptr, 0);
+    rc = tei_b200_predict_on(h, 0, ids, types, pos, 1, cu, 1, 1, scores.data(), nullptr, 0);
   } else {
     std::vector<float> outv(static_cast<size_t>(h->replicas[0]->output_dim()));
-    rc = tei_b200_embed(h, ids, types, pos, 1, cu, 1, 1, idx, 1, nullptr, 0, 0, outv.data(), nullptr, nullptr, 0);
+    rc = tei_b200_embed_on(h, 0, ids, types, pos, 1, cu, 1, 1, idx, 1, nullptr, 0, 0, outv.data(), nullptr, nullptr, 0);
   }
   return rc == TEI_B200_OK ? TEI_B200_OK : TEI_B200_ERR_UNHEALTHY;
 }
@@ -407,9 +452,8 @@ int tei_b200_embed(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* tok
     if ((n_pooled && !pooled_out) || (n_raw && !raw_out)) throw TeiError(ERR_INFERENCE, "null output buffer");
     HostBatch b = make_batch(input_ids, token_type_ids, position_ids, n_tokens, cumulative_seq_lengths,
                              n_seqs, max_length, pooled_idx, n_pooled, raw_idx, n_raw);
-    do_stage(h, b, false, normalize != 0);
-    do_run(h);
-    do_fetch(h, pooled_out, raw_out, nullptr);
+    AllReplicas all(h);
+    do_all(h, b, false, normalize != 0, pooled_out, raw_out, nullptr);
   });
 }
 
@@ -423,9 +467,8 @@ int tei_b200_predict(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* t
     if (!scores_out) throw TeiError(ERR_INFERENCE, "null output buffer");
     HostBatch b = make_batch(input_ids, token_type_ids, position_ids, n_tokens, cumulative_seq_lengths,
                              n_seqs, max_length, nullptr, 0, nullptr, 0);
-    do_stage(h, b, true, false);
-    do_run(h);
-    do_fetch(h, nullptr, nullptr, scores_out);
+    AllReplicas all(h);
+    do_all(h, b, true, false, nullptr, nullptr, scores_out);
   });
 }
 
@@ -486,24 +529,34 @@ int tei_b200_stage(tei_b200_t* h, const uint32_t* input_ids, const uint32_t* tok
                              n_seqs, max_length, pooled_idx, n_pooled, raw_idx, n_raw);
     if (predict && !h->spec.classifier) throw TeiError(ERR_INFERENCE, "`predict` is not implemented for this model");
     if (!predict && h->spec.classifier) throw TeiError(ERR_INFERENCE, "`embed` is not implemented for classifier models");
+    AllReplicas all(h);
     do_stage(h, b, predict != 0, normalize != 0);
   });
 }
 
 int tei_b200_run_staged(tei_b200_t* h, char* err, size_t err_cap) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
-  return guarded(h, err, err_cap, [&]() { do_run(h); });
+  return guarded(h, err, err_cap, [&]() {
+    AllReplicas all(h);
+    do_run(h);
+  });
 }
 
 int tei_b200_sync(tei_b200_t* h, char* err, size_t err_cap) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
-  return guarded(h, err, err_cap, [&]() { do_sync(h); });
+  return guarded(h, err, err_cap, [&]() {
+    AllReplicas all(h);
+    do_sync(h);
+  });
 }
 
 int tei_b200_fetch(tei_b200_t* h, float* pooled_out, float* raw_out, float* scores_out, char* err,
                    size_t err_cap) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
-  return guarded(h, err, err_cap, [&]() { do_fetch(h, pooled_out, raw_out, scores_out); });
+  return guarded(h, err, err_cap, [&]() {
+    AllReplicas all(h);
+    do_fetch(h, pooled_out, raw_out, scores_out);
+  });
 }
 
 int tei_b200_run_staged_timed(tei_b200_t* h, int steps, double* device_ms, char* err, size_t err_cap) {
@@ -511,8 +564,9 @@ int tei_b200_run_staged_timed(tei_b200_t* h, int steps, double* device_ms, char*
   return guarded(h, err, err_cap, [&]() {
     if (!h->staged) throw TeiError(ERR_INFERENCE, "no staged batch");
     if (steps <= 0) throw TeiError(ERR_INFERENCE, "steps must be positive");
+    AllReplicas all(h);
     double worst = 0.0;
-    if (h->shards.empty()) {
+    if (!h->split) {
       worst = h->replicas[0]->timed_runs(steps);
     } else {
       std::vector<double> ms(h->shards.size(), 0.0);
@@ -526,6 +580,7 @@ int tei_b200_run_staged_timed(tei_b200_t* h, int steps, double* device_ms, char*
 int tei_b200_set_profiling(tei_b200_t* h, int on) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
   return guarded(h, nullptr, 0, [&]() {
+    AllReplicas all(h);
     for (auto& r : h->replicas) r->set_profiling(on != 0);
   });
 }
@@ -565,6 +620,66 @@ int tei_b200_stats(const tei_b200_t* h, double* out, int n) {
   const int m = std::min(n, 8);
   for (int i = 0; i < m; ++i) out[i] = v[i];
   return m;
+}
+
+int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on) {
+  if (!h) return TEI_B200_ERR_UNHEALTHY;
+  AllReplicas all(h);
+  for (auto& r : h->replicas) r->set_last_layer_shortcut(on != 0);
+  return TEI_B200_OK;
+}
+
+int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_ids, const uint32_t* position_ids,
+                        size_t n_tokens, const uint32_t* cumulative_seq_lengths, size_t n_seqs,
+                        const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx, size_t n_raw,
+                        int predict, int n_shards, double linear_cost, double quadratic_cost, int width,
+                        float* pooled_out, float* raw_out, float* scores_out, int* shard_tokens_out) {
+  if (n_shards <= 0 || width <= 0) return TEI_B200_ERR_INFERENCE;
+  try {
+    HostBatch b = make_batch(input_ids, token_type_ids, position_ids, n_tokens, cumulative_seq_lengths, n_seqs, 0,
+                             pooled_idx, n_pooled, raw_idx, n_raw);
+    precheck(b);
+    std::vector<Shard> shards;
+    assign_shards(b, predict != 0, n_shards, linear_cost, quadratic_cost, shards);
+    const size_t W = static_cast<size_t>(width);
+    for (size_t d = 0; d < shards.size(); ++d) {
+      Shard& sh = shards[d];
+      if (shard_tokens_out) shard_tokens_out[d] = 0;
+      if (sh.seqs.empty()) continue;
+      gather_shard_tokens(b, sh);
+      const HostBatch v = sh.view();
+      precheck(v);  // the sub-batch is a well-formed batch of its own
+      if (shard_tokens_out) shard_tokens_out[d] = static_cast<int>(v.n_tokens);
+      size_shard_results(sh, predict != 0, W, W, W);
+      // Stand-in for the forward, computed from the SUB-batch alone: a pooled or score row is
+      // (sum of the sequence's ids mod 65521) + column, a raw row id + 7 type + 13 position + column.
+      auto seq_value = [&](uint32_t local) {
+        uint64_t acc = 0;
+        for (uint32_t t = v.cu_seqlens[local]; t < v.cu_seqlens[local + 1]; ++t) acc += v.input_ids[t];
+        return static_cast<float>(acc % 65521u);
+      };
+      for (size_t i = 0; i < v.n_pooled; ++i) {
+        for (size_t j = 0; j < W; ++j) sh.pooled[i * W + j] = seq_value(v.pooled_indices[i]) + static_cast<float>(j);
+      }
+      size_t row = 0;
+      for (size_t i = 0; i < v.n_raw; ++i) {
+        const uint32_t l = v.raw_indices[i];
+        for (uint32_t t = v.cu_seqlens[l]; t < v.cu_seqlens[l + 1]; ++t, ++row) {
+          const float base = static_cast<float>(v.input_ids[t] % 4096u + 7u * v.token_type_ids[t] + 13u * (v.position_ids[t] % 4096u));
+          for (size_t j = 0; j < W; ++j) sh.raw[row * W + j] = base + static_cast<float>(j);
+        }
+      }
+      if (predict) {
+        for (size_t i = 0; i < v.n_seqs; ++i) {
+          for (size_t j = 0; j < W; ++j) sh.scores[i * W + j] = seq_value(static_cast<uint32_t>(i)) + static_cast<float>(j);
+        }
+      }
+      scatter_shard(sh, predict != 0, W, W, W, pooled_out, raw_out, scores_out);
+    }
+    return TEI_B200_OK;
+  } catch (...) {
+    return TEI_B200_ERR_INFERENCE;
+  }
 }
 
 int tei_b200_plan_shards(const uint32_t* cumulative_seq_lengths, size_t n_seqs, int n_shards,

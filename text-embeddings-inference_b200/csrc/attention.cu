@@ -37,6 +37,8 @@
 #include "ptx.cuh"
 #include "tmap.h"
 
+#include <atomic>
+
 namespace tei {
 namespace {
 
@@ -48,19 +50,19 @@ constexpr int ATTN_THREADS = 192;
 // of a step (512 of them on the exp2 unit alone), the tensor pipe 320 (D = 64) to 640 (D = 128):
 // what bounds the kernel is how many softmax warps an SM keeps busy, so both head sizes run two
 // CTAs per SM (eight softmax warps, two per scheduler), each with half of the TMEM columns and
-// of the shared memory.  D = 64: two score tiles, two output tiles, two Q buffers, three K/V
-// stages.  D = 128: two score tiles, one output tile, one Q buffer and only two K and two V
+// of the shared memory.  D = 64 (and 32): two score tiles, two output tiles, two Q buffers, three
+// K/V stages.  D = 128: two score tiles, one output tile, one Q buffer and only two K and two V
 // stages (112 KB per CTA), which is enough because the K ring is released early (see K_EARLY).
 template <int D>
 struct AttnCfg {
   static constexpr int S_BUFS = 2;                     // score / P tiles of 64 columns
-  static constexpr int O_BUFS = (D == 64) ? 2 : 1;     // output tiles of D columns
-  static constexpr int Q_BUFS = (D == 64) ? 2 : 1;
+  static constexpr int O_BUFS = (D <= 64) ? 2 : 1;     // output tiles of D columns
+  static constexpr int Q_BUFS = (D <= 64) ? 2 : 1;
   // K and V tiles live in two rings of their own: a K tile is free again as soon as the S MMA
   // that read it is done, long before the P V of the same step releases the V tile, so with
   // separate rings two stages each already let the next K arrive a whole step early.
-  static constexpr int K_STAGES = (D == 64) ? 3 : 2;
-  static constexpr int V_STAGES = (D == 64) ? 3 : 2;
+  static constexpr int K_STAGES = (D <= 64) ? 3 : 2;
+  static constexpr int V_STAGES = (D <= 64) ? 3 : 2;
   // With more stages than score tiles (D = 64) the early release buys nothing and its extra
   // tcgen05.commit per step costs issue time: there a K tile is released together with the V
   // tile of its step and both are loaded in the same turn.
@@ -72,9 +74,14 @@ struct AttnCfg {
   static_assert(S_BUFS * BKV + O_BUFS * D <= TMEM_COLS, "TMEM budget");
 };
 
+// Head sizes of 64 and more are held as 64-element atoms (128-byte rows, 128-byte swizzle), one
+// after the other; head_dim 32 is one atom of 64-byte rows with the 64-byte swizzle.
 template <int D>
 struct AttnSmem {
   using C = AttnCfg<D>;
+  static constexpr int ATOM = D < 64 ? D : 64;   // elements per swizzle row
+  static constexpr int ROW_BYTES = ATOM * 2;
+  static constexpr int D_ATOMS = D / ATOM;
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int KV_BYTES = BKV * D * 2;   // one K or one V tile
   static constexpr int STAGE_BYTES = BQ * 128;   // output rows, 64 columns at a time
@@ -267,7 +274,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_k,
                          const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using L = AttnSmem<D>;
-  constexpr int D_ATOMS = D / 64;  // 64-element (128-byte) swizzle atoms per head
+  constexpr int D_ATOMS = L::D_ATOMS;  // swizzle atoms per head
+  constexpr int ATOM = L::ATOM, ROW_BYTES = L::ROW_BYTES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (ptx::smem_u32(smem) & 1023u) {  // swizzled operand tiles need 1024-byte alignment
@@ -404,8 +412,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             ptx::mbar_expect_tx(&bar_q[qb], L::Q_BYTES);
 #pragma unroll
             for (int a = 0; a < D_ATOMS; ++a) {
-              ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * 128), &tm_q, &bar_q[qb],
-                               head * D + a * 64, ck.it[0] + ck.it[2]);
+              ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * ROW_BYTES), &tm_q, &bar_q[qb],
+                               head * D + a * ATOM, ck.it[0] + ck.it[2]);
             }
           }
           const int st = gk % K_STAGES;
@@ -417,8 +425,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           ptx::mbar_expect_tx(&bar_k[st], C::K_EARLY ? L::KV_BYTES : 2 * L::KV_BYTES);
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
-            ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * 128), &tm_k, &bar_k[st],
-                             k_col + a * 64, ck.it[0] + ck.it[3] + ck.j * BKV);
+            ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * ROW_BYTES), &tm_k, &bar_k[st],
+                             k_col + a * ATOM, ck.it[0] + ck.it[3] + ck.j * BKV);
           }
           ++gk;
         }
@@ -435,8 +443,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (C::K_EARLY) ptx::mbar_expect_tx(landed, L::KV_BYTES);
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
-            ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * 128), &tm_v, landed,
-                             v_col + a * 64, cv.it[0] + cv.it[3] + cv.j * BKV);
+            ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * ROW_BYTES), &tm_v, landed,
+                             v_col + a * ATOM, cv.it[0] + cv.it[3] + cv.j * BKV);
           }
           ++gv;
         }
@@ -453,9 +461,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       constexpr uint32_t idesc_o = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, D, 0, 1);
       // Operand descriptors are built once; each MMA adds a constant to the address field
       // (units of 16 bytes; every operand sits below 256 KB, so the 14-bit field cannot carry).
-      const uint64_t dq = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_Q), 16, 1024);
-      const uint64_t dk = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_K), 16, 1024);
-      const uint64_t dv = ptx::make_smem_desc_sw128(ptx::smem_u32(smem + L::OFF_V), BKV * 128, 1024);
+      // The swizzle pattern repeats every 8 rows (sbo); for V, lbo is the distance between the
+      // atoms of one key row group.
+      constexpr uint64_t SWZ = D < 64 ? 4 : 2;  // SWIZZLE_64B : SWIZZLE_128B
+      const uint64_t dq = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_Q), 16, 8 * ROW_BYTES, SWZ);
+      const uint64_t dk = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_K), 16, 8 * ROW_BYTES, SWZ);
+      const uint64_t dv = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_V), BKV * ROW_BYTES, 8 * ROW_BYTES, SWZ);
       Cursor cs{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cp = cs;
       load_unit(cs);
       load_unit(cp);
@@ -481,8 +492,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             const uint32_t d_s = tmem_base + (gs % S_BUFS) * BKV;
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
-              const uint64_t qoff = static_cast<uint64_t>(((k / 4) * (BQ * 128) + (k % 4) * 32) >> 4);
-              const uint64_t koff = static_cast<uint64_t>(((k / 4) * (BKV * 128) + (k % 4) * 32) >> 4);
+              const uint64_t qoff = static_cast<uint64_t>(((k / 4) * (BQ * ROW_BYTES) + (k % 4) * 32) >> 4);
+              const uint64_t koff = static_cast<uint64_t>(((k / 4) * (BKV * ROW_BYTES) + (k % 4) * 32) >> 4);
               ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
             }
             ptx::umma_commit(&bar_s[gs % S_BUFS]);
@@ -509,7 +520,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
             if (k < k_steps) {
-              ptx::umma_ts(tmem_o, t_p + k * 8, dvs + static_cast<uint64_t>((k * 2048) >> 4), idesc_o,
+              ptx::umma_ts(tmem_o, t_p + k * 8, dvs + static_cast<uint64_t>((k * 16 * ROW_BYTES) >> 4), idesc_o,
                            (cp.j | k) != 0 ? 1u : 0u);
             }
           }
@@ -552,6 +563,35 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (!ptx::mbar_wait(&bar_pv[g_last % S_BUFS], (g_last / S_BUFS) & 1)) return false;
       ptx::tc_fence_after();
       uint8_t* stage = smem + L::OFF_STAGE + warp * (32 * 128);
+      if constexpr (D == 32) {
+        // 64-byte rows: four 16-byte chunks per row, chunk index XORed with bits 1-2 of the row;
+        // written back with 4 lanes per row.
+        uint32_t t[32];
+        ptx::tmem_ld32(t_o, t);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint4 v;
+          v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
+          v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
+          v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
+          v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((q8 ^ ((lane >> 1) & 3)) * 16)) = v;
+        }
+        __syncwarp();
+        const int sub = lane >> 2, ch = lane & 3;
+#pragma unroll
+        for (int i8 = 0; i8 < 4; ++i8) {
+          const int row = i8 * 8 + sub;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 64 + ((ch ^ ((row >> 1) & 3)) * 16));
+          if (row < rows_valid) {
+            *reinterpret_cast<uint4*>(warp_dst + static_cast<size_t>(row) * p.ld_o + ch * 8) = v;
+          }
+        }
+        __syncwarp();
+        ptx::tc_fence_before();
+        return true;
+      }
 #pragma unroll
       for (int c2 = 0; c2 < D / 64; ++c2) {
 #pragma unroll
@@ -746,22 +786,24 @@ int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
       a.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tm_q, tm_k, tm_v;
   int rc = make_tmap_2d(&tm_q, a.q, dt, 2, static_cast<uint64_t>(a.n_heads) * D, a.total_tokens,
-                        static_cast<uint64_t>(a.ld_q) * 2, 64, BQ);
+                        static_cast<uint64_t>(a.ld_q) * 2, L::ATOM, BQ);
   if (rc) return rc;
   rc = make_tmap_2d(&tm_k, a.k, dt, 2, static_cast<uint64_t>(a.n_kv_heads) * D, a.total_tokens,
-                    static_cast<uint64_t>(a.ld_k) * 2, 64, BKV);
+                    static_cast<uint64_t>(a.ld_k) * 2, L::ATOM, BKV);
   if (rc) return rc;
   rc = make_tmap_2d(&tm_v, a.v, dt, 2, static_cast<uint64_t>(a.n_kv_heads) * D, a.total_tokens,
-                    static_cast<uint64_t>(a.ld_v) * 2, 64, BKV);
+                    static_cast<uint64_t>(a.ld_v) * 2, L::ATOM, BKV);
   if (rc) return rc;
-  static bool attr_set[64] = {};
+  // The opt-in shared-memory size is a per-device function attribute; setting it twice is
+  // harmless, so replicas on several threads may race to set it, but not on the flag itself.
+  static std::atomic<bool> attr_set[64];
   auto kern = attention_tcgen05_kernel<T, D, ALIBI>;
   const int dev = current_device() & 63;
-  if (!attr_set[dev]) {
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   AttnParams p;
   p.out = a.out;
@@ -792,12 +834,18 @@ int launch_typed(const AttnArgs& a, cudaStream_t stream) {
 }  // namespace
 
 int launch_attention(const AttnArgs& a, cudaStream_t stream) {
+  // The kernel reports a wait that ran out through *status: without it there is nowhere to write.
+  if (a.status == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   if (a.n_work <= 0 || a.total_tokens <= 0) return 0;
   if (a.n_kv_heads <= 0 || a.n_heads % a.n_kv_heads != 0) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
   if (a.ld_q % 8 || a.ld_k % 8 || a.ld_v % 8 || a.ld_o % 8) {
     return static_cast<int>(cudaErrorInvalidValue);
+  }
+  if (a.head_dim == 32) {
+    return a.dtype == DT_F16 ? launch_typed<__half, 32>(a, stream)
+                             : launch_typed<__nv_bfloat16, 32>(a, stream);
   }
   if (a.head_dim == 64) {
     return a.dtype == DT_F16 ? launch_typed<__half, 64>(a, stream)

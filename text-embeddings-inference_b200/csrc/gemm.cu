@@ -23,7 +23,7 @@
 #include "ptx.cuh"
 #include "tmap.h"
 
-#include <cstdlib>
+#include <atomic>
 
 namespace tei {
 namespace {
@@ -669,15 +669,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
-// TEI_B200_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel (for A/B timing).
-inline bool pair_mode_enabled() {
-  static const bool on = [] {
-    const char* v = std::getenv("TEI_B200_GEMM_PAIR");
-    return !(v && v[0] == '0');
-  }();
-  return on;
-}
-
 template <class T, int ACT>
 int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   CUtensorMap tm_a, tm_b;
@@ -699,9 +690,9 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   }
 
   // The opt-in shared-memory size is a per-device function attribute; setting it twice is
-  // harmless, so a plain flag per device (and per instantiation) is enough.
-  static bool attr_set[64] = {};
-  static bool attr_set_pair[64] = {};
+  // harmless, so replicas on several threads may race to set it, but not on the flag itself.
+  static std::atomic<bool> attr_set[64];
+  static std::atomic<bool> attr_set_pair[64];
   const int dev = current_device() & 63;
   GemmParams p;
   p.bias = g.bias;
@@ -715,16 +706,16 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   p.ldr = g.ldr;
   p.tma_store = tma_store ? 1 : 0;
   p.status = g.status;
-  if (g.M > BM && pair_mode_enabled()) {
+  if (g.M > BM) {
     // CTA pairs: 256 x 256 tiles, W loaded in halves of 128 rows.
     CUtensorMap tm_b2;
     rc = make_tmap_2d(&tm_b2, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, 128);
     if (rc) return rc;
     auto kern2 = gemm_tcgen05_pair_kernel<T, ACT>;
-    if (!attr_set_pair[dev]) {
+    if (!attr_set_pair[dev].load(std::memory_order_acquire)) {
       cudaError_t e = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
       if (e != cudaSuccess) return static_cast<int>(e);
-      attr_set_pair[dev] = true;
+      attr_set_pair[dev].store(true, std::memory_order_release);
     }
     const int tiles2 = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
     const int max_pairs = num_sms() / 2;
@@ -733,11 +724,11 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     return static_cast<int>(cudaGetLastError());
   }
   auto kern = gemm_tcgen05_kernel<T, ACT>;
-  if (!attr_set[dev]) {
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
@@ -764,6 +755,8 @@ int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
 int gemm_smem_bytes() { return SMEM_BYTES; }
 
 int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
+  // The kernels report a wait that ran out through *status: without it there is nowhere to write.
+  if (g.status == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   if (g.M <= 0) return 0;
   if (g.N <= 0 || g.K <= 0 || g.K % 8 != 0 || g.lda % 8 != 0) {
     return static_cast<int>(cudaErrorInvalidValue);

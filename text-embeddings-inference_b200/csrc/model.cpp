@@ -332,8 +332,8 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
     if (mt == "bidirectional_pplx_qwen3") throw TeiError(ERR_START, "Pplx1 is only supported in fp32 precision");
     throw TeiError(ERR_START, "model_type `" + mt + "` is not served by this backend");
   }
-  if (s.head_dim != 64 && s.head_dim != 128) {
-    throw TeiError(ERR_START, "head_dim must be 64 or 128 for the sm_100a attention kernel");
+  if (s.head_dim != 32 && s.head_dim != 64 && s.head_dim != 128) {
+    throw TeiError(ERR_START, "head_dim must be 32, 64 or 128 for the sm_100a attention kernel");
   }
   if (s.kv_heads <= 0 || s.heads % s.kv_heads != 0) throw TeiError(ERR_START, "heads must be a multiple of kv heads");
   if (s.hidden % 8 != 0 || s.inter % 8 != 0 || s.hidden > 4096) {
@@ -1241,6 +1241,10 @@ void Replica::ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t
 // ------------------------------------------------------------------------------ stage
 void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   TEI_CUDA(cudaSetDevice(device_));
+  // The pinned block is rewritten below: an earlier batch's copy or forward that is still in
+  // flight (stage, run, stage again without a sync or fetch between) must be through with it.
+  // After a fetch or sync the stream is idle and this returns at once.
+  TEI_CUDA(cudaStreamSynchronize(stream_));
   const ModelSpec& s = spec_;
   if (b.n_seqs == 0 || b.n_tokens == 0) throw TeiError(ERR_INFERENCE, "empty batch");
   if (!b.input_ids || !b.cu_seqlens || !b.position_ids) throw TeiError(ERR_INFERENCE, "null batch pointer");
@@ -1332,11 +1336,7 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   // Last-layer shortcut of the post-LN BERT family (see forward_bert): needs room for five packed
   // [B, H] blocks inside one [T, H] buffer.
   size_t o_work_first = 0;
-  // TEI_B200_FIRST_ROWS=0 switches the shortcut off (for A/B timing).
-  static const bool first_rows_enabled = [] {
-    const char* v = std::getenv("TEI_B200_FIRST_ROWS");
-    return !(v && v[0] == '0');
-  }();
+  const bool first_rows_enabled = last_layer_shortcut_;
   const bool post_ln_family = (s.arch == ARCH_BERT && !s.jina_code) ||
                               (s.arch == ARCH_NOMIC && !layers_.empty() && !layers_.back().moe_router);
   first_rows_only_ = first_rows_enabled && post_ln_family && s.layers > 0 && s.local_window < 0 &&

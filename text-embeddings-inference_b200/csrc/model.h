@@ -161,6 +161,11 @@ class Replica {
   // sequence, measured with events on the launching stream.
   double timed_runs(int steps);
 
+  // The last-layer shortcut (on by default): when only one row per sequence leaves the model,
+  // everything behind the last layer's scores runs on those rows alone.  Off: every row is
+  // computed, as the reference does.  Takes effect with the next stage().
+  void set_last_layer_shortcut(bool on) { last_layer_shortcut_ = on; }
+
   const ReplicaStats& stats() const { return stats_; }
   cudaStream_t stream() const { return stream_; }
   // Device pointers of the last outputs (valid until the next stage()).
@@ -284,6 +289,7 @@ class Replica {
   int32_t* d_work_first_ = nullptr;
   size_t n_work_first_ = 0;
   bool first_rows_only_ = false;
+  bool last_layer_shortcut_ = true;
   size_t out_floats_ = 0;
 };
 

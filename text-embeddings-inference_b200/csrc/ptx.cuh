@@ -337,15 +337,26 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
 //   lbo unused.  Advancing K by 16 elements = start + 32 B.
 //   MN-major operand (row = K index, 64 fp16 of MN per row): sbo = 1024 (8 K rows), lbo = byte
 //   distance between 64-element MN atoms.  Advancing K by 16 rows = start + 2048 B.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t start, uint32_t lbo,
-                                                        uint32_t sbo) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t start, uint32_t lbo, uint32_t sbo,
+                                                  uint64_t layout_type) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((start & 0x3FFFF) >> 4);
   d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFF) << 16;
   d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFF) << 32;
   d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // SWIZZLE_128B
+  d |= layout_type << 61;
   return d;
+}
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t start, uint32_t lbo,
+                                                        uint32_t sbo) {
+  return make_smem_desc(start, lbo, sbo, 2);  // SWIZZLE_128B
+}
+// 64-byte swizzle: rows of 32 fp16 (64 B); the pattern repeats every 8 rows = 512 B, which is
+// also sbo for a densely packed tile, K-major (8 M/N rows) or MN-major (8 K rows) alike.
+// Advancing K by 16 elements: start + 32 B (K-major), start + 1024 B (MN-major, 16 rows).
+__device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t start, uint32_t lbo,
+                                                       uint32_t sbo) {
+  return make_smem_desc(start, lbo, sbo, 4);  // SWIZZLE_64B
 }
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A and B both of `fmt`

@@ -331,7 +331,7 @@ qk_norm_rope_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restrict_
   }
 }
 
-// The same for head_dim 64 and 128 with 16-byte accesses: DH / 16 lanes share one (token, head);
+// The same for head_dim 32, 64 and 128 with 16-byte accesses: DH / 16 lanes share one (token, head);
 // each lane owns 8 consecutive elements of the first half and the 8 they pair with in the
 // second half, so every load and store is a full 16 bytes and a warp covers 8 (or 4) heads of a
 // token at once.  The RMSNorm sum is reduced across the lanes of the group.
@@ -736,7 +736,7 @@ int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
   const bool aligned = r.ld_q % 8 == 0 && r.ld_k % 8 == 0 &&
                        (reinterpret_cast<uintptr_t>(r.q) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.k) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(r.q_gamma) & 15) == 0 && (reinterpret_cast<uintptr_t>(r.k_gamma) & 15) == 0;
-  if (aligned && (r.head_dim == 64 || r.head_dim == 128)) {
+  if (aligned && (r.head_dim == 32 || r.head_dim == 64 || r.head_dim == 128)) {
     const long long threads = warps_total * (r.head_dim / 16);
     const unsigned grid_v = static_cast<unsigned>((threads + 255) / 256);
 #define TEI_ROPE_VEC(TYPE, DH)                                                                     \
@@ -745,10 +745,12 @@ int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
       reinterpret_cast<const TYPE*>(r.q_gamma), reinterpret_cast<const TYPE*>(r.k_gamma), r.T,     \
       r.n_heads, r.n_kv_heads, r.ld_q, r.ld_k, r.eps)
     if (r.dtype == DT_F16) {
-      if (r.head_dim == 64) TEI_ROPE_VEC(__half, 64);
+      if (r.head_dim == 32) TEI_ROPE_VEC(__half, 32);
+      else if (r.head_dim == 64) TEI_ROPE_VEC(__half, 64);
       else TEI_ROPE_VEC(__half, 128);
     } else {
-      if (r.head_dim == 64) TEI_ROPE_VEC(__nv_bfloat16, 64);
+      if (r.head_dim == 32) TEI_ROPE_VEC(__nv_bfloat16, 32);
+      else if (r.head_dim == 64) TEI_ROPE_VEC(__nv_bfloat16, 64);
       else TEI_ROPE_VEC(__nv_bfloat16, 128);
     }
 #undef TEI_ROPE_VEC

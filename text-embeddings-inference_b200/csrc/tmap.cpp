@@ -34,15 +34,18 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
   std::call_once(g_once, resolve_encode);
   if (!g_encode) return static_cast<int>(cudaErrorNotSupported);
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) ||
-      box_inner * elem_bytes != 128 || box_outer == 0 || box_outer > 256) {
+      (box_inner * elem_bytes != 128 && box_inner * elem_bytes != 64) || box_outer == 0 || box_outer > 256) {
     return static_cast<int>(cudaErrorInvalidValue);
   }
+  // The swizzle span equals the box row: 128-byte rows for head sizes and GEMM tiles of 64
+  // elements and more, 64-byte rows for head_dim 32.
+  const CUtensorMapSwizzle swz = box_inner * elem_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {row_stride_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return static_cast<int>(r);
 }

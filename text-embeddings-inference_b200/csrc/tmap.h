@@ -8,10 +8,11 @@
 
 namespace tei {
 
-// Encodes a 2-D row-major tensor map with 128-byte swizzle and zero fill outside the tensor.
+// Encodes a 2-D row-major tensor map with zero fill outside the tensor; the swizzle span is the
+// box row (128 or 64 bytes).
 //   inner / outer: extent in elements of the contiguous dimension / number of rows;
 //   row_stride_bytes: distance between rows (multiple of 16);
-//   box_inner * elem_bytes must be 128 (one swizzle row); box_outer <= 256.
+//   box_inner * elem_bytes must be 128 or 64 (one swizzle row); box_outer <= 256.
 // Returns 0 or a non-zero error code (CUresult or cudaError_t value).
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
                  uint64_t inner, uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner,

@@ -87,6 +87,13 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_set_profiling": (c_int, [c_void_p, c_int]),
     "tei_b200_kernel_times": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), c_int]),
     "tei_b200_stats": (c_int, [c_void_p, POINTER(c_double), c_int]),
+    "tei_b200_set_last_layer_shortcut": (c_int, [c_void_p, c_int]),
+    "tei_b200_split_echo": (
+        c_int,
+        [POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t,
+         POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int, c_int, c_double, c_double, c_int,
+         POINTER(c_float), POINTER(c_float), POINTER(c_float), POINTER(c_int)],
+    ),
     "tei_b200_plan_shards": (
         c_int,
         [POINTER(c_uint32), c_size_t, c_int, c_double, c_double, POINTER(c_int)],
