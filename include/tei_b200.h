@@ -193,6 +193,14 @@ int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_id
                         int predict, int n_shards, double linear_cost, double quadratic_cost, int width,
                         float* pooled_out, float* raw_out, float* scores_out, int* shard_tokens_out);
 
+/* Self-test of the TIMEOUT path; no counterpart in the reference.  The next forward on
+ * `replica` ends with a kernel that writes `device_code` (> 0, e.g. 104) to the status word, which
+ * is all a kernel whose bounded wait ran out leaves behind; nothing hangs or faults.  That call
+ * then returns TEI_B200_ERR_TIMEOUT (-> BackendError::Inference, backends/candle/src/lib.rs:728-740),
+ * the handle turns unhealthy (backends/src/lib.rs:621-642) and the next tei_b200_health runs its
+ * one-token probe (backends/src/lib.rs:393-409).  One shot. */
+int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code);
+
 /* The last-layer shortcut, on by default: when only one row per sequence leaves the model (CLS
  * or last-token pooling, or a classifier head, and no raw request in the batch), everything
  * behind the last layer's attention scores runs on those rows only.  on == 0 makes every call

@@ -169,6 +169,16 @@ int tei_b200_op_moe_route_noalloc(const void* logits_dev, int ld_logits, int n_t
                                   int32_t* counts_out_dev, int dtype, void* stream, char* err,
                                   size_t err_cap);
 
+/* Self-test of the bounded waits; no counterpart in the reference.  Every wait inside the GEMM
+ * and attention kernels gives up after a fixed number of probes, writes a code to *status_dev
+ * and lets the kernel return.  This launches one CTA that waits, with that same primitive, on a
+ * barrier nobody arrives at, with a limit of `limit` probes (1 .. 4096, a few microseconds to
+ * milliseconds): afterwards *status_dev holds 101 and *gave_up_dev (optional) 1.  The kernel
+ * cannot spin longer than its limit, trap or fault.  status_dev is mandatory here and in
+ * tei_b200_op_linear / tei_b200_op_attention: a NULL status pointer is refused with
+ * cudaErrorInvalidValue before anything is launched. */
+int tei_b200_op_bounded_wait_probe(int* status_dev, int limit, int* gave_up_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

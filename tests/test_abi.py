@@ -195,3 +195,24 @@ def test_headers_are_plain_c(tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
     assert "config.json" in out.stdout
+
+
+def test_the_c_backend_thread_program_compiles_and_links(tmp_path):
+    """tests/c/router_threads.c (run by the GPU tests) builds as C99 against include/*.h."""
+    import subprocess
+    lib_dir = os.path.join(ROOT, "text-embeddings-inference_b200", "lib")
+    exe = tmp_path / "router_threads"
+    subprocess.run(["gcc", "-std=c99", "-D_POSIX_C_SOURCE=200809L", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "c", "router_threads.c"), "-o", str(exe), "-L", lib_dir, "-ltei_b200",
+                    f"-Wl,-rpath,{lib_dir}", "-lpthread", "-lm"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 64 and "usage" in out.stderr
+
+
+def test_kernel_entry_points_refuse_a_null_status_word(lib):
+    """The GEMM and attention kernels report a wait that ran out through *status; without it the
+    report would be a write to address 0.  Refused on the host, before any CUDA call."""
+    assert lib.tei_b200_op_linear(None, None, None, None, None, 128, 256, 64, 64, 256, 0, 0, 0, None, None) == 1
+    assert lib.tei_b200_op_attention(None, None, None, None, None, 1, 128, 1, 1, 64, 64, 64, 64, 64, 0, 0.125,
+                                     None, 0, None, None) == 1
+    assert lib.tei_b200_op_bounded_wait_probe(None, 10, None, None) == 1

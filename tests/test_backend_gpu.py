@@ -352,3 +352,24 @@ def test_one_row_shortcut_of_the_decoders_equals_the_full_path(lib, model_dirs, 
     row = -1 if pool == "last_token" else 0
     assert np.array_equal(a[7].values, b[7].values[row])
     be.close()
+
+
+@pytest.mark.parametrize("key", ["xlmr", "bert_cls3", "gte_cls", "jina_abs_cls"])
+def test_classifier_scores_are_the_same_with_and_without_the_shortcut(lib, model_dirs, key):
+    """predict always pools the first rows, so it takes the last-layer shortcut whenever the batch
+    has five tokens per sequence; switched off through the handle, every row is computed as the
+    reference does (flash_bert.rs:169-185,538-547).  Same scores, bit for bit."""
+    be = _backend(model_dirs, key, "classifier", "cls")
+    off = 2 if key == "xlmr" else 0
+    tv = 1 if key == "xlmr" else 2
+    b = G.random_batch(71, [7, 33, 150, 12, 64, 129, 300], 5, 1000, type_vocab=tv, position_offset=off)
+    fast = be.predict(b)
+    launches_fast = be.stats()["launches"]
+    be.set_last_layer_shortcut(False)
+    full = be.predict(b)
+    launches_full = be.stats()["launches"]
+    be.set_last_layer_shortcut(True)
+    assert fast == full
+    assert launches_fast != launches_full  # the two paths really differ
+    assert be.predict(b) == fast
+    be.close()

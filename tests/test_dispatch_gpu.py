@@ -160,3 +160,22 @@ def test_queue_feeds_two_replicas(lib, model_dirs):
         assert np.abs(got[tag] - alone[tag]).max() <= 4e-3
     q.close()
     be.close()
+
+
+def test_n_backend_threads_in_c_over_the_queue(lib, model_dirs, tmp_path):
+    """tests/c/router_threads.c: the reference's backend-thread loop (backends/src/lib.rs:612-647)
+    run N times over one handle, in C over the C ABI, fed by the library's queue."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_dir = os.path.join(root, "text-embeddings-inference_b200", "lib")
+    exe = tmp_path / "router_threads"
+    subprocess.run(["gcc", "-std=c99", "-D_POSIX_C_SOURCE=200809L", "-Wall", "-Werror", "-I", os.path.join(root, "include"),
+                    os.path.join(root, "tests", "c", "router_threads.c"), "-o", str(exe), "-L", lib_dir, "-ltei_b200",
+                    f"-Wl,-rpath,{lib_dir}", "-lpthread", "-lm"], check=True)
+    for n_replicas in (1, 3):
+        out = subprocess.run([str(exe), str(model_dirs["bert"]), str(n_replicas), "200", "1000", "2048"],
+                             capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
+        assert out.stdout.startswith("ok batches=")
+        n_batches = int(out.stdout.split("batches=")[1].split()[0])
+        assert n_batches >= 200 * 150 // 2048  # the requests did not all fit one batch

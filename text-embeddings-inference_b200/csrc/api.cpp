@@ -629,6 +629,15 @@ int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on) {
   return TEI_B200_OK;
 }
 
+int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code) {
+  if (!h || replica < 0 || replica >= static_cast<int>(h->replicas.size()) || device_code <= 0) {
+    return TEI_B200_ERR_INFERENCE;
+  }
+  std::lock_guard<std::mutex> lock(*h->replica_locks[replica]);
+  h->replicas[replica]->report_status_once(device_code);
+  return TEI_B200_OK;
+}
+
 int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_ids, const uint32_t* position_ids,
                         size_t n_tokens, const uint32_t* cumulative_seq_lengths, size_t n_seqs,
                         const uint32_t* pooled_idx, size_t n_pooled, const uint32_t* raw_idx, size_t n_raw,

@@ -184,6 +184,12 @@ int launch_moe_combine(const void* yg, const int* topk_e, const float* topk_w, c
                        const void* bias, void* out, int T, int k, int H, long long cap, int dtype,
                        cudaStream_t stream);
 
+// Self-test of the failure path (selftest.cu): a kernel that only writes `code` to *status, as a
+// kernel whose bounded wait ran out would, and a one-CTA kernel whose wait on a barrier nobody
+// arrives at gives up after `limit` (<= 4096) probes and reports DEV_TIMEOUT_PRODUCER.
+int launch_report_status(int* status, int code, cudaStream_t stream);
+int launch_bounded_wait_probe(int* status, int limit, int* gave_up, cudaStream_t stream);
+
 // Element-wise dtype conversion used at weight-load time.  src_kind: 0 fp32, 1 fp16, 2 bf16;
 // dst dtype: DT_F16 / DT_BF16, or 2 for fp32.
 int launch_convert(const void* src, int src_kind, void* dst, int dst_kind, size_t n,

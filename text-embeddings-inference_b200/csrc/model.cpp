@@ -1410,6 +1410,11 @@ void Replica::run() {
     case ARCH_QWEN3: forward_qwen3(); break;
   }
   pool_and_heads();
+  if (inject_status_ != 0) {
+    const int code = inject_status_;
+    inject_status_ = 0;
+    launch(launch_report_status(reinterpret_cast<int*>(d_out_), code, stream_), "status report");
+  }
   TEI_CUDA(cudaEventRecord(ev_stop_, stream_));
   stats_.last_launches = launches_;
   stats_.last_tokens = static_cast<double>(T_);

@@ -166,6 +166,10 @@ class Replica {
   // computed, as the reference does.  Takes effect with the next stage().
   void set_last_layer_shortcut(bool on) { last_layer_shortcut_ = on; }
 
+  // Self-test hook: the next run() ends with a kernel that writes `code` to the status word,
+  // exactly what a kernel whose bounded wait ran out leaves behind.  One shot.
+  void report_status_once(int code) { inject_status_ = code; }
+
   const ReplicaStats& stats() const { return stats_; }
   cudaStream_t stream() const { return stream_; }
   // Device pointers of the last outputs (valid until the next stage()).
@@ -290,6 +294,7 @@ class Replica {
   size_t n_work_first_ = 0;
   bool first_rows_only_ = false;
   bool last_layer_shortcut_ = true;
+  int inject_status_ = 0;
   size_t out_floats_ = 0;
 };
 

@@ -225,4 +225,8 @@ int tei_b200_op_moe_combine(const void* yg_dev, const int32_t* topk_expert_dev,
                             top_k, hidden, cap, dtype, static_cast<cudaStream_t>(stream));
 }
 
+int tei_b200_op_bounded_wait_probe(int* status_dev, int limit, int* gave_up_dev, void* stream) {
+  return launch_bounded_wait_probe(status_dev, limit, gave_up_dev, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -88,11 +88,14 @@ __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
   return mbar_wait(bar, parity);
 }
 // Bounded wait.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, kSpinLimit);
 }
 
 // ---------------------------------------------------------------- packed fp32 pairs

@@ -38,6 +38,7 @@ _OPS_PROTOTYPES = {
     "tei_b200_op_moe_route": (c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p]),
     "tei_b200_op_moe_route_noalloc": (
         c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p, c_char_p, c_size_t]),
+    "tei_b200_op_bounded_wait_probe": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
     "tei_b200_op_moe_gather": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
     "tei_b200_op_moe_combine": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
 }
@@ -88,6 +89,7 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_kernel_times": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), c_int]),
     "tei_b200_stats": (c_int, [c_void_p, POINTER(c_double), c_int]),
     "tei_b200_set_last_layer_shortcut": (c_int, [c_void_p, c_int]),
+    "tei_b200_selftest_report_timeout": (c_int, [c_void_p, c_int, c_int]),
     "tei_b200_split_echo": (
         c_int,
         [POINTER(c_uint32), POINTER(c_uint32), POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t,

@@ -239,6 +239,17 @@ class B200Backend:
         n = self._lib.tei_b200_kernel_times(self._h, ms, ln, 6)
         return {self.KERNEL_CLASSES[i]: {"ms": ms[i], "launches": ln[i]} for i in range(n)}
 
+    def set_last_layer_shortcut(self, on: bool) -> None:
+        """Off: every call computes every row of the last layer, as the reference does."""
+        self._lib.tei_b200_set_last_layer_shortcut(self._h, int(on))
+
+    def selftest_report_timeout(self, replica: int = 0, device_code: int = 104) -> None:
+        """The next forward on `replica` reports `device_code` through the status word, like a
+        kernel whose bounded wait ran out (self-test of the TIMEOUT path; nothing hangs)."""
+        rc = self._lib.tei_b200_selftest_report_timeout(self._h, int(replica), int(device_code))
+        if rc != 0:
+            raise BackendError(rc, "selftest_report_timeout")
+
     def stats(self) -> dict:
         buf = (ctypes.c_double * 8)()
         n = self._lib.tei_b200_stats(self._h, buf, 8)
