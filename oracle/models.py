@@ -178,19 +178,26 @@ def attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu: np.ndarray, scale: flo
         if nkv != nh:  # GQA: q-head i reads kv-head i // group (models/qwen3.rs:189-205)
             ks = ks.repeat_interleave(nh // nkv, dim=0)
             vs = vs.repeat_interleave(nh // nkv, dim=0)
-        sc = (qs @ ks.transpose(1, 2)) * scale
-        if slopes is not None:
-            idx = torch.arange(L)
-            sc = sc - slopes.view(nh, 1, 1) * (idx.view(1, L, 1) - idx.view(1, 1, L)).abs()
-        if causal:
-            sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf"))
-        if window_left is not None:
-            idx = torch.arange(L)
-            sc = sc.masked_fill(idx.view(1, L) < idx.view(L, 1) - window_left, float("-inf"))
-        if window_right is not None:  # and j <= i + window_right (flash_modernbert.rs:92-111)
-            idx = torch.arange(L)
-            sc = sc.masked_fill(idx.view(1, L) > idx.view(L, 1) + window_right, float("-inf"))
-        out[a:b] = (torch.softmax(sc, dim=-1) @ vs).transpose(0, 1).reshape(L, nh * D)
+        # Heads are independent: long sequences go through a few heads at a time so that the
+        # [heads, L, L] score tensor stays below about 1 GB (same arithmetic per head).
+        step = nh if nh * L * L <= (1 << 28) else max(1, (1 << 28) // (L * L))
+        o_s = torch.empty(nh, L, D, dtype=q.dtype)
+        for h0 in range(0, nh, step):
+            h1 = min(nh, h0 + step)
+            sc = (qs[h0:h1] @ ks[h0:h1].transpose(1, 2)) * scale
+            if slopes is not None:
+                idx = torch.arange(L)
+                sc = sc - slopes[h0:h1].view(h1 - h0, 1, 1) * (idx.view(1, L, 1) - idx.view(1, 1, L)).abs()
+            if causal:
+                sc = sc.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf"))
+            if window_left is not None:
+                idx = torch.arange(L)
+                sc = sc.masked_fill(idx.view(1, L) < idx.view(L, 1) - window_left, float("-inf"))
+            if window_right is not None:  # and j <= i + window_right (flash_modernbert.rs:92-111)
+                idx = torch.arange(L)
+                sc = sc.masked_fill(idx.view(1, L) > idx.view(L, 1) + window_right, float("-inf"))
+            o_s[h0:h1] = torch.softmax(sc, dim=-1) @ vs[h0:h1]
+        out[a:b] = o_s.transpose(0, 1).reshape(L, nh * D)
     return out
 
 

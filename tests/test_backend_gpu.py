@@ -74,8 +74,10 @@ def test_bf16_qwen3_against_oracle(lib, model_dirs):
     got = be.embed(b)
     g = np.stack([got[i].values for i in range(len(b))])
     ref = o.embed(b)[0].numpy()
-    # bf16 keeps 8 mantissa bits in every stored activation; 0.999 is the reference's own bar
-    # (backends/candle/tests/common.rs:57-73), the 0.9999 bar is checked in fp16 above.
+    # bf16 keeps 8 mantissa bits in every stored activation: held to its measured floor (the
+    # reference's own bar for half precision is 0.999, backends/candle/tests/common.rs:57-73);
+    # the 0.9999 bar is checked in fp16 above.
+    print(f"bf16 qwen3, 3 layers: cos per sequence {_cos(g, ref)}")
     assert _cos(g, ref).min() >= 0.9995
     assert np.abs(M.l2_normalise(g) - M.l2_normalise(ref)).max() <= MAX_ABS
     be.close()
@@ -373,3 +375,25 @@ def test_classifier_scores_are_the_same_with_and_without_the_shortcut(lib, model
     assert launches_fast != launches_full  # the two paths really differ
     assert be.predict(b) == fast
     be.close()
+
+
+@pytest.mark.parametrize("name", ["encoder.layer.1.output.dense.bias", "encoder.layer.0.attention.output.LayerNorm.weight",
+                                  "encoder.layer.0.attention.self.key.bias", "embeddings.LayerNorm.bias"])
+def test_vector_parameters_of_the_wrong_length_are_refused_at_load(lib, tmp_path, name):
+    """A bias or norm weight shorter than the config implies would be read past its end by the
+    kernels; it is a Start error at load, like a matrix of the wrong shape, before any kernel runs."""
+    import shutil
+    from safetensors.numpy import load_file, save_file
+    import tei_b200
+    from tei_b200.backend import BackendError
+    d = G.write_model_dir(tmp_path / "m", G.bert_config(hidden=128, layers=2, heads=2, inter=256, vocab=1000, max_pos=512),
+                          seed=1)
+    tensors = load_file(str(d / "model.safetensors"))
+    tensors[name] = tensors[name][:-8].copy()
+    bad = tmp_path / "bad"
+    shutil.copytree(d, bad)
+    save_file(tensors, str(bad / "model.safetensors"))
+    with pytest.raises(BackendError) as e:
+        tei_b200.B200Backend(bad, "float16", "embedding", "mean")
+    assert e.value.kind == "Start" and "unexpected shape" in str(e.value)
+    tei_b200.B200Backend(d, "float16", "embedding", "mean").close()  # the intact directory loads

@@ -1,11 +1,14 @@
 """Full-width architectures of the benchmark configurations (BERT-base, NomicBERT-768,
-XLM-RoBERTa-large reranker, Qwen3-0.6B-style), random-init, against the fp32 CPU oracle on
-subsets of their seeded batches that the oracle finishes in seconds.
+XLM-RoBERTa-large reranker, Qwen3-0.6B-style), random-init, against the fp32 CPU oracle: the
+whole headline batch (256 ragged sequences), the reranker with its real 250,002-row table on 32
+pairs, the longest sequence of the Qwen3-style batch (8,055 tokens), and subsets of the other
+seeded batches that the oracle finishes in seconds.
 
-Vocabularies of the two large models are cut to 32k rows for the test (the embedding table is a
-plain gather; every other dimension is the real one).  Tolerances: pooled embeddings after L2
-normalisation cosine >= 0.9999 and max-abs <= 2e-2 (fp16); reranker logits abs <= 1e-2; bf16
-cosine >= 0.999 (8 mantissa bits per stored activation; the reference's own bar).
+Tolerances: pooled embeddings after L2 normalisation cosine >= 0.9999 and max-abs <= 2e-2
+(fp16); reranker logits abs <= 1e-2.  bf16 (8 mantissa bits in every stored activation) is held
+to the floor it measures, cosine >= 0.9995 over 28 layers, and the per-sequence cosines are
+printed; the reference's own bar for any half precision is 0.999
+(backends/candle/tests/common.rs:57-73).
 """
 import numpy as np
 import pytest
@@ -75,7 +78,73 @@ def test_cfg4_xlm_roberta_large_reranker(lib, tmp_path):
     be.close()
 
 
-@pytest.mark.parametrize("dtype,cos_min", [("float16", 0.9999), ("bfloat16", 0.999)])
+def test_cfg2_the_whole_headline_batch(lib, tmp_path):
+    """All 256 sequences (68,576 tokens) of the benchmark batch, every row against the oracle."""
+    import tei_b200
+    d = G.write_model_dir(tmp_path / "m", G.bert_config(), seed=0)
+    full = G.batch_cfg2()
+    assert len(full) == 256 and int(full.cumulative_seq_lengths[-1]) == 68576
+    be = tei_b200.B200Backend(d, "float16", "embedding", "mean")
+    got = _pooled(be.embed(full), 256)
+    ref = M.build_oracle(d, "embedding", "mean").embed(full)[0].numpy()
+    c = _cos(got, ref)
+    print(f"cfg2 full batch: min cos {c.min():.7f}, max abs {np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max():.5f}")
+    assert c.min() >= 0.9999
+    assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+    be.close()
+
+
+def test_cfg4_real_vocabulary_32_pairs(lib, tmp_path):
+    """The reranker with its 250,002-row embedding table (stored fp16) on the first 32 pairs."""
+    import tei_b200
+    cfg = G.bert_config(hidden=1024, layers=24, heads=16, inter=4096, vocab=250002, max_pos=514, type_vocab=1,
+                        model_type="xlm-roberta", pad_token_id=1, id2label={"0": "LABEL_0"})
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=4, classifier="roberta", store_dtype="float16")
+    b = G.batch_cfg4(n_pairs=32)
+    assert int(b.input_ids.max()) > 200000  # ids reach the far end of the table
+    be = tei_b200.B200Backend(d, "float16", "classifier")
+    got = be.predict(b)
+    g = np.array([got[i] for i in range(len(b))], dtype=np.float32)
+    ref = M.build_oracle(d, "classifier").predict(b).numpy()
+    assert g.shape == ref.shape == (32, 1)
+    print(f"cfg4 32 pairs: max abs logit diff {np.abs(g - ref).max():.5f}")
+    assert np.abs(g - ref).max() <= 1e-2
+    be.close()
+
+
+@pytest.fixture(scope="module")
+def cfg5_longest(tmp_path_factory):
+    """Two Qwen3-0.6B-width layers, the 8,055-token sequence of the benchmark batch next to two
+    shorter ones, and the oracle's hidden states for them (computed once: 8055^2 scores per head)."""
+    assert int(G.lengths_cfg5().max()) == 8055
+    cfg = G.qwen3_config(layers=2, vocab=32000, max_pos=8192)
+    d = G.write_model_dir(tmp_path_factory.mktemp("cfg5_longest") / "m", cfg, seed=5)
+    rng = np.random.default_rng(65)
+    lens = [8055, 128, 1000]
+    sub = G.batch_from_encodings([rng.integers(1000, 32000, size=n) for n in lens], [0, 1, 2], [])
+    hidden = M.build_oracle(d, "embedding", "last_token").hidden_states(sub)
+    return d, sub, hidden
+
+
+@pytest.mark.parametrize("dtype,cos_min", [("float16", 0.9999), ("bfloat16", 0.9995)])
+def test_cfg5_longest_sequence_two_layers(lib, cfg5_longest, dtype, cos_min):
+    """126 key steps per query tile, the K / V rings wrap more than 40 times, the running
+    maximum is carried across all of them; last-token pooling (one-row shortcut) and mean pooling
+    (every row)."""
+    import tei_b200
+    d, sub, hidden = cfg5_longest
+    for pool in ("last_token", "mean"):
+        be = tei_b200.B200Backend(d, dtype, "embedding", pool)
+        got = _pooled(be.embed(sub), 3)
+        ref = M.pool_outputs(hidden, sub, pool)[0].numpy()
+        c = _cos(got, ref)
+        print(f"cfg5 longest sequence, {dtype}, {pool}: cos per sequence {c}")
+        assert np.isfinite(got).all() and c.min() >= cos_min
+        assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
+        be.close()
+
+
+@pytest.mark.parametrize("dtype,cos_min", [("float16", 0.9999), ("bfloat16", 0.9995)])
 def test_cfg5_qwen3_last_token(lib, tmp_path, dtype, cos_min):
     import tei_b200
     cfg = G.qwen3_config(vocab=32000)
@@ -88,6 +157,7 @@ def test_cfg5_qwen3_last_token(lib, tmp_path, dtype, cos_min):
     ref = M.build_oracle(d, "embedding", "last_token").embed(sub)[0].numpy()
     got = _pooled(be.embed(sub), len(sub))
     assert np.isfinite(got).all()
+    print(f"cfg5 28 layers, {dtype}: cos per sequence {_cos(got, ref)}")
     assert _cos(got, ref).min() >= cos_min
     assert np.abs(M.l2_normalise(got) - M.l2_normalise(ref)).max() <= 2e-2
     be.close()

@@ -615,6 +615,15 @@ struct Names {
   const StTensor& ln_b(const std::string& p) const { return has(p + ".bias") ? get(p + ".bias") : get(p + ".beta"); }
 };
 
+// A vector parameter (bias, norm weight) must have exactly the length the kernels will read.
+const StTensor& vec(const StTensor& t, int64_t n, const char* what) {
+  if (t.numel() != n) {
+    throw TeiError(ERR_START, std::string("unexpected shape for a ") + what + " vector: " + std::to_string(t.numel()) +
+                                  " elements where the config implies " + std::to_string(n));
+  }
+  return t;
+}
+
 void expect_shape(const StTensor& t, std::initializer_list<int64_t> shape, const std::string& name) {
   if (t.shape != std::vector<int64_t>(shape)) {
     throw TeiError(ERR_START, "unexpected shape for tensor " + name);
@@ -659,8 +668,8 @@ void Replica::load_bert(const SafeTensors& st) {
     expect_shape(n.get(emb + "position_embeddings.weight"), {s.max_pos, H}, emb + "position_embeddings.weight");
     word_ = upload_new(n.get(emb + "word_embeddings.weight"));
     pos_tab_ = upload_new(n.get(emb + "position_embeddings.weight"));
-    emb_g_ = upload_new(n.ln_w(emb + "LayerNorm"));
-    emb_b_ = upload_new(n.ln_b(emb + "LayerNorm"));
+    emb_g_ = upload_new(vec(n.ln_w(emb + "LayerNorm"), H, "hidden-size"));
+    emb_b_ = upload_new(vec(n.ln_b(emb + "LayerNorm"), H, "hidden-size"));
     for (int i = 0; i < s.layers; ++i) {
       LayerW& L = layers_[i];
       const std::string p = enc + "layer." + std::to_string(i) + ".";
@@ -671,21 +680,21 @@ void Replica::load_bert(const SafeTensors& st) {
         const StTensor& w = n.get(p + "attention." + qkv[j] + ".weight");
         expect_shape(w, {H, H}, p + "attention." + qkv[j] + ".weight");
         upload(L.wqkv, static_cast<size_t>(j) * H * H, w);
-        upload(L.bqkv, static_cast<size_t>(j) * H, n.get(p + "attention." + qkv[j] + ".bias"));
+        upload(L.bqkv, static_cast<size_t>(j) * H, vec(n.get(p + "attention." + qkv[j] + ".bias"), H, "q/k/v bias"));
       }
       expect_shape(n.get(p + "attention.out_lin.weight"), {H, H}, p + "attention.out_lin.weight");
       L.wo = upload_new(n.get(p + "attention.out_lin.weight"));
-      L.bo = upload_new(n.get(p + "attention.out_lin.bias"));
-      L.ln1_g = upload_new(n.ln_w(p + "sa_layer_norm"));
-      L.ln1_b = upload_new(n.ln_b(p + "sa_layer_norm"));
+      L.bo = upload_new(vec(n.get(p + "attention.out_lin.bias"), H, "hidden-size"));
+      L.ln1_g = upload_new(vec(n.ln_w(p + "sa_layer_norm"), H, "hidden-size"));
+      L.ln1_b = upload_new(vec(n.ln_b(p + "sa_layer_norm"), H, "hidden-size"));
       expect_shape(n.get(p + "ffn.lin1.weight"), {I, H}, p + "ffn.lin1.weight");
       L.w1 = upload_new(n.get(p + "ffn.lin1.weight"));
-      L.b1 = upload_new(n.get(p + "ffn.lin1.bias"));
+      L.b1 = upload_new(vec(n.get(p + "ffn.lin1.bias"), I, "feed-forward bias"));
       expect_shape(n.get(p + "ffn.lin2.weight"), {H, I}, p + "ffn.lin2.weight");
       L.w2 = upload_new(n.get(p + "ffn.lin2.weight"));
-      L.b2 = upload_new(n.get(p + "ffn.lin2.bias"));
-      L.ln2_g = upload_new(n.ln_w(p + "output_layer_norm"));
-      L.ln2_b = upload_new(n.ln_b(p + "output_layer_norm"));
+      L.b2 = upload_new(vec(n.get(p + "ffn.lin2.bias"), H, "hidden-size"));
+      L.ln2_g = upload_new(vec(n.ln_w(p + "output_layer_norm"), H, "hidden-size"));
+      L.ln2_b = upload_new(vec(n.ln_b(p + "output_layer_norm"), H, "hidden-size"));
     }
     return;
   }
@@ -733,8 +742,8 @@ void Replica::load_bert(const SafeTensors& st) {
     TEI_CUDA(cudaMemcpy(alibi_slopes_, slf.data(), slf.size() * 4, cudaMemcpyHostToDevice));
   }
   type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
-  emb_g_ = upload_new(n.ln_w("embeddings.LayerNorm"));
-  emb_b_ = upload_new(n.ln_b("embeddings.LayerNorm"));
+  emb_g_ = upload_new(vec(n.ln_w("embeddings.LayerNorm"), H, "hidden-size"));
+  emb_b_ = upload_new(vec(n.ln_b("embeddings.LayerNorm"), H, "hidden-size"));
   for (int i = 0; i < s.layers; ++i) {
     LayerW& L = layers_[i];
     const std::string p = "encoder.layer." + std::to_string(i) + ".";
@@ -746,22 +755,22 @@ void Replica::load_bert(const SafeTensors& st) {
       const StTensor& w = n.get(p + "attention.self." + qkv[j] + ".weight");
       expect_shape(w, {H, H}, p + "attention.self." + qkv[j] + ".weight");
       upload(L.wqkv, static_cast<size_t>(j) * H * H, w);
-      upload(L.bqkv, static_cast<size_t>(j) * H, n.get(p + "attention.self." + qkv[j] + ".bias"));
+      upload(L.bqkv, static_cast<size_t>(j) * H, vec(n.get(p + "attention.self." + qkv[j] + ".bias"), H, "q/k/v bias"));
     }
     expect_shape(n.get(p + "attention.output.dense.weight"), {H, H}, p + "attention.output.dense.weight");
     L.wo = upload_new(n.get(p + "attention.output.dense.weight"));
-    L.bo = upload_new(n.get(p + "attention.output.dense.bias"));
-    L.ln1_g = upload_new(n.ln_w(p + "attention.output.LayerNorm"));
-    L.ln1_b = upload_new(n.ln_b(p + "attention.output.LayerNorm"));
+    L.bo = upload_new(vec(n.get(p + "attention.output.dense.bias"), H, "hidden-size"));
+    L.ln1_g = upload_new(vec(n.ln_w(p + "attention.output.LayerNorm"), H, "hidden-size"));
+    L.ln1_b = upload_new(vec(n.ln_b(p + "attention.output.LayerNorm"), H, "hidden-size"));
     if (s.jina_code) {
       // JinaCodeAttention::load / JinaCodeBertLayer::load (flash_jina_code.rs:27-90,170-212):
       // `attention.self.layer_norm_q` / `_k` over the whole hidden width; `mlp.up_gated_layer`
       // [2I, H] without bias whose rows [0, I) are NOT gated and rows [I, 2I) go through the
       // activation (:236-240); `mlp.down_layer`; `layer_norm_1`, `layer_norm_2`.
-      L.lnq_g = upload_new(n.ln_w(p + "attention.self.layer_norm_q"));
-      L.lnq_b = upload_new(n.ln_b(p + "attention.self.layer_norm_q"));
-      L.lnk_g = upload_new(n.ln_w(p + "attention.self.layer_norm_k"));
-      L.lnk_b = upload_new(n.ln_b(p + "attention.self.layer_norm_k"));
+      L.lnq_g = upload_new(vec(n.ln_w(p + "attention.self.layer_norm_q"), H, "hidden-size"));
+      L.lnq_b = upload_new(vec(n.ln_b(p + "attention.self.layer_norm_q"), H, "hidden-size"));
+      L.lnk_g = upload_new(vec(n.ln_w(p + "attention.self.layer_norm_k"), H, "hidden-size"));
+      L.lnk_b = upload_new(vec(n.ln_b(p + "attention.self.layer_norm_k"), H, "hidden-size"));
       const StTensor& gw = n.get(p + "mlp.up_gated_layer.weight");
       expect_shape(gw, {2 * I, H}, p + "mlp.up_gated_layer.weight");
       StTensor gate = gw, up = gw;
@@ -773,11 +782,11 @@ void Replica::load_bert(const SafeTensors& st) {
       upload_rows_interleaved(L.w1, gate, up);
       expect_shape(n.get(p + "mlp.down_layer.weight"), {H, I}, p + "mlp.down_layer.weight");
       L.w2 = upload_new(n.get(p + "mlp.down_layer.weight"));
-      L.b2 = upload_new(n.get(p + "mlp.down_layer.bias"));
-      L.lnm_g = upload_new(n.ln_w(p + "layer_norm_1"));
-      L.lnm_b = upload_new(n.ln_b(p + "layer_norm_1"));
-      L.ln2_g = upload_new(n.ln_w(p + "layer_norm_2"));
-      L.ln2_b = upload_new(n.ln_b(p + "layer_norm_2"));
+      L.b2 = upload_new(vec(n.get(p + "mlp.down_layer.bias"), H, "hidden-size"));
+      L.lnm_g = upload_new(vec(n.ln_w(p + "layer_norm_1"), H, "hidden-size"));
+      L.lnm_b = upload_new(vec(n.ln_b(p + "layer_norm_1"), H, "hidden-size"));
+      L.ln2_g = upload_new(vec(n.ln_w(p + "layer_norm_2"), H, "hidden-size"));
+      L.ln2_b = upload_new(vec(n.ln_b(p + "layer_norm_2"), H, "hidden-size"));
       continue;
     }
     if (s.jina) {
@@ -794,56 +803,65 @@ void Replica::load_bert(const SafeTensors& st) {
       upload_rows_interleaved(L.w1, gate, up);
       expect_shape(n.get(p + "mlp.wo.weight"), {H, I}, p + "mlp.wo.weight");
       L.w2 = upload_new(n.get(p + "mlp.wo.weight"));
-      L.b2 = upload_new(n.get(p + "mlp.wo.bias"));
-      L.ln2_g = upload_new(n.ln_w(p + "mlp.layernorm"));
-      L.ln2_b = upload_new(n.ln_b(p + "mlp.layernorm"));
+      L.b2 = upload_new(vec(n.get(p + "mlp.wo.bias"), H, "hidden-size"));
+      L.ln2_g = upload_new(vec(n.ln_w(p + "mlp.layernorm"), H, "hidden-size"));
+      L.ln2_b = upload_new(vec(n.ln_b(p + "mlp.layernorm"), H, "hidden-size"));
       continue;
     }
     expect_shape(n.get(p + "intermediate.dense.weight"), {I, H}, p + "intermediate.dense.weight");
     L.w1 = upload_new(n.get(p + "intermediate.dense.weight"));
-    L.b1 = upload_new(n.get(p + "intermediate.dense.bias"));
+    L.b1 = upload_new(vec(n.get(p + "intermediate.dense.bias"), I, "feed-forward bias"));
     expect_shape(n.get(p + "output.dense.weight"), {H, I}, p + "output.dense.weight");
     L.w2 = upload_new(n.get(p + "output.dense.weight"));
-    L.b2 = upload_new(n.get(p + "output.dense.bias"));
-    L.ln2_g = upload_new(n.ln_w(p + "output.LayerNorm"));
-    L.ln2_b = upload_new(n.ln_b(p + "output.LayerNorm"));
+    L.b2 = upload_new(vec(n.get(p + "output.dense.bias"), H, "hidden-size"));
+    L.ln2_g = upload_new(vec(n.ln_w(p + "output.LayerNorm"), H, "hidden-size"));
+    L.ln2_b = upload_new(vec(n.ln_b(p + "output.LayerNorm"), H, "hidden-size"));
   }
   if (s.classifier) {
     if (s.roberta) {  // RobertaClassificationHead, bert.rs:434-444
       expect_shape(root.get("classifier.dense.weight"), {H, H}, "classifier.dense.weight");
       expect_shape(root.get("classifier.out_proj.weight"), {s.n_classes, H}, "classifier.out_proj.weight");
       cls_dense_w_ = upload_new(root.get("classifier.dense.weight"));
-      cls_dense_b_ = upload_new(root.get("classifier.dense.bias"));
+      cls_dense_b_ = upload_new(vec(root.get("classifier.dense.bias"), H, "hidden-size"));
       cls_out_w_ = upload_new(root.get("classifier.out_proj.weight"));
-      cls_out_b_ = upload_new(root.get("classifier.out_proj.bias"));
+      cls_out_b_ = upload_new(vec(root.get("classifier.out_proj.bias"), s.n_classes, "classifier bias"));
     } else {  // BertClassificationHead, bert.rs:381-395
       if (root.has("bert.pooler.dense.weight")) {
+        expect_shape(root.get("bert.pooler.dense.weight"), {H, H}, "bert.pooler.dense.weight");
         cls_dense_w_ = upload_new(root.get("bert.pooler.dense.weight"));
-        cls_dense_b_ = upload_new(root.get("bert.pooler.dense.bias"));
+        cls_dense_b_ = upload_new(vec(root.get("bert.pooler.dense.bias"), H, "hidden-size"));
       }
       expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
       cls_out_w_ = upload_new(root.get("classifier.weight"));
-      cls_out_b_ = upload_new(root.get("classifier.bias"));
+      cls_out_b_ = upload_new(vec(root.get("classifier.bias"), s.n_classes, "classifier bias"));
     }
   }
   if (s.pool == POOL_SPLADE) {
     if (s.roberta) {  // bert.rs:519-541
+      expect_shape(root.get("lm_head.dense.weight"), {H, H}, "lm_head.dense.weight");
+      expect_shape(root.get("lm_head.decoder.weight"), {s.vocab, H}, "lm_head.decoder.weight");
       sp_dense_w_ = upload_new(root.get("lm_head.dense.weight"));
-      sp_dense_b_ = upload_new(root.get("lm_head.dense.bias"));
-      sp_ln_g_ = upload_new(root.ln_w("lm_head.layer_norm"));
-      sp_ln_b_ = upload_new(root.ln_b("lm_head.layer_norm"));
+      sp_dense_b_ = upload_new(vec(root.get("lm_head.dense.bias"), H, "hidden-size"));
+      sp_ln_g_ = upload_new(vec(root.ln_w("lm_head.layer_norm"), H, "hidden-size"));
+      sp_ln_b_ = upload_new(vec(root.ln_b("lm_head.layer_norm"), H, "hidden-size"));
       sp_dec_w_ = upload_new(root.get("lm_head.decoder.weight"));
-      sp_dec_b_ = upload_new(root.get("lm_head.bias"));
+      sp_dec_b_ = upload_new(vec(root.get("lm_head.bias"), s.vocab, "decoder bias"));
       sp_act_ = ACT_GELU;
     } else {  // bert.rs:477-509
+      expect_shape(root.get("cls.predictions.transform.dense.weight"), {H, H}, "cls.predictions.transform.dense.weight");
+      {
+        const char* dec = root.has("cls.predictions.decoder.weight") ? "cls.predictions.decoder.weight"
+                                                                      : "bert.embeddings.word_embeddings.weight";
+        expect_shape(root.get(dec), {s.vocab, H}, dec);
+      }
       sp_dense_w_ = upload_new(root.get("cls.predictions.transform.dense.weight"));
-      sp_dense_b_ = upload_new(root.get("cls.predictions.transform.dense.bias"));
-      sp_ln_g_ = upload_new(root.ln_w("cls.predictions.transform.LayerNorm"));
-      sp_ln_b_ = upload_new(root.ln_b("cls.predictions.transform.LayerNorm"));
+      sp_dense_b_ = upload_new(vec(root.get("cls.predictions.transform.dense.bias"), H, "hidden-size"));
+      sp_ln_g_ = upload_new(vec(root.ln_w("cls.predictions.transform.LayerNorm"), H, "hidden-size"));
+      sp_ln_b_ = upload_new(vec(root.ln_b("cls.predictions.transform.LayerNorm"), H, "hidden-size"));
       sp_dec_w_ = root.has("cls.predictions.decoder.weight")
                       ? upload_new(root.get("cls.predictions.decoder.weight"))
                       : upload_new(root.get("bert.embeddings.word_embeddings.weight"));
-      sp_dec_b_ = upload_new(root.get("cls.predictions.bias"));
+      sp_dec_b_ = upload_new(vec(root.get("cls.predictions.bias"), s.vocab, "decoder bias"));
       sp_act_ = s.act;
     }
   }
@@ -857,17 +875,17 @@ void Replica::load_nomic(const SafeTensors& st) {
   word_ = upload_new(n.get("embeddings.word_embeddings.weight"));
   expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
   type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
-  emb_g_ = upload_new(n.ln_w("emb_ln"));
-  emb_b_ = upload_new(n.ln_b("emb_ln"));
+  emb_g_ = upload_new(vec(n.ln_w("emb_ln"), H, "hidden-size"));
+  emb_b_ = upload_new(vec(n.ln_b("emb_ln"), H, "hidden-size"));
   for (int i = 0; i < s.layers; ++i) {
     LayerW& L = layers_[i];
     const std::string p = "encoder.layers." + std::to_string(i) + ".";
     expect_shape(n.get(p + "attn.Wqkv.weight"), {3 * H, H}, p + "attn.Wqkv.weight");
     L.wqkv = upload_new(n.get(p + "attn.Wqkv.weight"));
-    if (s.qkv_bias) L.bqkv = upload_new(n.get(p + "attn.Wqkv.bias"));
+    if (s.qkv_bias) L.bqkv = upload_new(vec(n.get(p + "attn.Wqkv.bias"), s.qkv_width(), "qkv bias"));
     expect_shape(n.get(p + "attn.out_proj.weight"), {H, H}, p + "attn.out_proj.weight");
     L.wo = upload_new(n.get(p + "attn.out_proj.weight"));
-    if (s.out_bias) L.bo = upload_new(n.get(p + "attn.out_proj.bias"));
+    if (s.out_bias) L.bo = upload_new(vec(n.get(p + "attn.out_proj.bias"), H, "hidden-size"));
     if (s.moe_every > 0 && i % s.moe_every == 1) {
       // NomicMoELayer (nomic.rs:205-296): router.layer.weight [E, H] (rows padded to a multiple
       // of 8 for the logits' row stride), experts.mlp.w1 / w2 [E * I, H], experts.bias [H].  w2
@@ -900,11 +918,11 @@ void Replica::load_nomic(const SafeTensors& st) {
       w2t.shape = {static_cast<int64_t>(E) * H, I};
       L.moe_w2t = upload_new(w2t);
       TEI_CUDA(cudaStreamSynchronize(stream_));  // `tr` goes out of scope
-      L.moe_bias = upload_new(n.get(p + "mlp.experts.bias"));
-      L.ln1_g = upload_new(n.ln_w(p + "norm1"));
-      L.ln1_b = upload_new(n.ln_b(p + "norm1"));
-      L.ln2_g = upload_new(n.ln_w(p + "norm2"));
-      L.ln2_b = upload_new(n.ln_b(p + "norm2"));
+      L.moe_bias = upload_new(vec(n.get(p + "mlp.experts.bias"), H, "hidden-size"));
+      L.ln1_g = upload_new(vec(n.ln_w(p + "norm1"), H, "hidden-size"));
+      L.ln1_b = upload_new(vec(n.ln_b(p + "norm1"), H, "hidden-size"));
+      L.ln2_g = upload_new(vec(n.ln_w(p + "norm2"), H, "hidden-size"));
+      L.ln2_b = upload_new(vec(n.ln_b(p + "norm2"), H, "hidden-size"));
       continue;
     }
     if (s.gated) {
@@ -916,20 +934,20 @@ void Replica::load_nomic(const SafeTensors& st) {
       upload_rows_interleaved(L.w1, n.get(p + "mlp.fc12.weight"), n.get(p + "mlp.fc11.weight"));
       if (s.fc1_bias) {
         L.b1 = dev_alloc(static_cast<size_t>(2) * I * 2);
-        upload_rows_interleaved(L.b1, n.get(p + "mlp.fc12.bias"), n.get(p + "mlp.fc11.bias"));
+        upload_rows_interleaved(L.b1, vec(n.get(p + "mlp.fc12.bias"), I, "fc12 bias"), vec(n.get(p + "mlp.fc11.bias"), I, "fc11 bias"));
       }
     } else {
       expect_shape(n.get(p + "mlp.fc1.weight"), {I, H}, p + "mlp.fc1.weight");
       L.w1 = upload_new(n.get(p + "mlp.fc1.weight"));
-      if (s.fc1_bias) L.b1 = upload_new(n.get(p + "mlp.fc1.bias"));
+      if (s.fc1_bias) L.b1 = upload_new(vec(n.get(p + "mlp.fc1.bias"), I, "feed-forward bias"));
     }
     expect_shape(n.get(p + "mlp.fc2.weight"), {H, I}, p + "mlp.fc2.weight");
     L.w2 = upload_new(n.get(p + "mlp.fc2.weight"));
-    if (s.fc2_bias) L.b2 = upload_new(n.get(p + "mlp.fc2.bias"));
-    L.ln1_g = upload_new(n.ln_w(p + "norm1"));
-    L.ln1_b = upload_new(n.ln_b(p + "norm1"));
-    L.ln2_g = upload_new(n.ln_w(p + "norm2"));
-    L.ln2_b = upload_new(n.ln_b(p + "norm2"));
+    if (s.fc2_bias) L.b2 = upload_new(vec(n.get(p + "mlp.fc2.bias"), H, "hidden-size"));
+    L.ln1_g = upload_new(vec(n.ln_w(p + "norm1"), H, "hidden-size"));
+    L.ln1_b = upload_new(vec(n.ln_b(p + "norm1"), H, "hidden-size"));
+    L.ln2_g = upload_new(vec(n.ln_w(p + "norm2"), H, "hidden-size"));
+    L.ln2_b = upload_new(vec(n.ln_b(p + "norm2"), H, "hidden-size"));
   }
 }
 
@@ -945,17 +963,17 @@ void Replica::load_gte(const SafeTensors& st) {
     expect_shape(n.get("embeddings.token_type_embeddings.weight"), {s.type_vocab, H}, "embeddings.token_type_embeddings.weight");
     type_tab_ = upload_new(n.get("embeddings.token_type_embeddings.weight"));
   }
-  emb_g_ = upload_new(n.ln_w("embeddings.LayerNorm"));
-  emb_b_ = upload_new(n.ln_b("embeddings.LayerNorm"));
+  emb_g_ = upload_new(vec(n.ln_w("embeddings.LayerNorm"), H, "hidden-size"));
+  emb_b_ = upload_new(vec(n.ln_b("embeddings.LayerNorm"), H, "hidden-size"));
   for (int i = 0; i < s.layers; ++i) {
     LayerW& L = layers_[i];
     const std::string p = "encoder.layer." + std::to_string(i) + ".";
     expect_shape(n.get(p + "attention.qkv_proj.weight"), {3 * H, H}, p + "attention.qkv_proj.weight");
     L.wqkv = upload_new(n.get(p + "attention.qkv_proj.weight"));
-    L.bqkv = upload_new(n.get(p + "attention.qkv_proj.bias"));
+    L.bqkv = upload_new(vec(n.get(p + "attention.qkv_proj.bias"), s.qkv_width(), "qkv bias"));
     expect_shape(n.get(p + "attention.o_proj.weight"), {H, H}, p + "attention.o_proj.weight");
     L.wo = upload_new(n.get(p + "attention.o_proj.weight"));
-    L.bo = upload_new(n.get(p + "attention.o_proj.bias"));
+    L.bo = upload_new(vec(n.get(p + "attention.o_proj.bias"), H, "hidden-size"));
     // mlp.up_gate_proj [2I, H]: rows [0, I) are `up`, rows [I, 2I) the gate that goes through the
     // activation (gte.rs:219-226).
     const StTensor& ug = n.get(p + "mlp.up_gate_proj.weight");
@@ -969,20 +987,21 @@ void Replica::load_gte(const SafeTensors& st) {
     upload_rows_interleaved(L.w1, gate, up);
     expect_shape(n.get(p + "mlp.down_proj.weight"), {H, I}, p + "mlp.down_proj.weight");
     L.w2 = upload_new(n.get(p + "mlp.down_proj.weight"));
-    L.b2 = upload_new(n.get(p + "mlp.down_proj.bias"));
-    L.ln1_g = upload_new(n.ln_w(p + "attn_ln"));
-    L.ln1_b = upload_new(n.ln_b(p + "attn_ln"));
-    L.ln2_g = upload_new(n.ln_w(p + "mlp_ln"));
-    L.ln2_b = upload_new(n.ln_b(p + "mlp_ln"));
+    L.b2 = upload_new(vec(n.get(p + "mlp.down_proj.bias"), H, "hidden-size"));
+    L.ln1_g = upload_new(vec(n.ln_w(p + "attn_ln"), H, "hidden-size"));
+    L.ln1_b = upload_new(vec(n.ln_b(p + "attn_ln"), H, "hidden-size"));
+    L.ln2_g = upload_new(vec(n.ln_w(p + "mlp_ln"), H, "hidden-size"));
+    L.ln2_b = upload_new(vec(n.ln_b(p + "mlp_ln"), H, "hidden-size"));
   }
   if (s.classifier) {  // GTEClassificationHead, gte.rs:282-340: optional pooler.dense + tanh, classifier
     if (n.has("pooler.dense.weight") && n.has("pooler.dense.bias")) {
+      expect_shape(n.get("pooler.dense.weight"), {H, H}, "pooler.dense.weight");
       cls_dense_w_ = upload_new(n.get("pooler.dense.weight"));
-      cls_dense_b_ = upload_new(n.get("pooler.dense.bias"));
+      cls_dense_b_ = upload_new(vec(n.get("pooler.dense.bias"), H, "hidden-size"));
     }
     expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
     cls_out_w_ = upload_new(root.get("classifier.weight"));
-    cls_out_b_ = upload_new(root.get("classifier.bias"));
+    cls_out_b_ = upload_new(vec(root.get("classifier.bias"), s.n_classes, "classifier bias"));
   }
 }
 
@@ -1009,13 +1028,13 @@ void Replica::load_qwen3(const SafeTensors& st) {
     L.wo = upload_new(n.get(p + "self_attn.o_proj.weight"));
     if (s.qkv_bias) {  // flash_qwen2.rs:37-57
       L.bqkv = dev_alloc(static_cast<size_t>(Q + 2 * KV) * 2);
-      upload(L.bqkv, 0, n.get(p + "self_attn.q_proj.bias"));
-      upload(L.bqkv, static_cast<size_t>(Q), n.get(p + "self_attn.k_proj.bias"));
-      upload(L.bqkv, static_cast<size_t>(Q + KV), n.get(p + "self_attn.v_proj.bias"));
+      upload(L.bqkv, 0, vec(n.get(p + "self_attn.q_proj.bias"), Q, "q bias"));
+      upload(L.bqkv, static_cast<size_t>(Q), vec(n.get(p + "self_attn.k_proj.bias"), KV, "k bias"));
+      upload(L.bqkv, static_cast<size_t>(Q + KV), vec(n.get(p + "self_attn.v_proj.bias"), KV, "v bias"));
     }
     if (s.qk_norm) {
-      L.q_norm = upload_new(n.get(p + "self_attn.q_norm.weight"));
-      L.k_norm = upload_new(n.get(p + "self_attn.k_norm.weight"));
+      L.q_norm = upload_new(vec(n.get(p + "self_attn.q_norm.weight"), s.head_dim, "q_norm"));
+      L.k_norm = upload_new(vec(n.get(p + "self_attn.k_norm.weight"), s.head_dim, "k_norm"));
     }
     expect_shape(n.get(p + "mlp.gate_proj.weight"), {I, H}, p + "mlp.gate_proj.weight");
     expect_shape(n.get(p + "mlp.up_proj.weight"), {I, H}, p + "mlp.up_proj.weight");
@@ -1023,10 +1042,10 @@ void Replica::load_qwen3(const SafeTensors& st) {
     upload_rows_interleaved(L.w1, n.get(p + "mlp.gate_proj.weight"), n.get(p + "mlp.up_proj.weight"));
     expect_shape(n.get(p + "mlp.down_proj.weight"), {H, I}, p + "mlp.down_proj.weight");
     L.w2 = upload_new(n.get(p + "mlp.down_proj.weight"));
-    L.ln1_g = upload_new(n.get(p + "input_layernorm.weight"));
-    L.ln2_g = upload_new(n.get(p + "post_attention_layernorm.weight"));
+    L.ln1_g = upload_new(vec(n.get(p + "input_layernorm.weight"), H, "hidden-size"));
+    L.ln2_g = upload_new(vec(n.get(p + "post_attention_layernorm.weight"), H, "hidden-size"));
   }
-  final_norm_ = upload_new(n.get("norm.weight"));
+  final_norm_ = upload_new(vec(n.get("norm.weight"), H, "hidden-size"));
   if (st.contains("linear.weight")) {  // flash_qwen3.rs:344-357
     const StTensor& w = st.get("linear.weight");
     if (w.shape.size() != 2 || w.shape[1] != H) throw TeiError(ERR_START, "unexpected shape for tensor linear.weight");
@@ -1044,18 +1063,18 @@ void Replica::load_modernbert(const SafeTensors& st) {
   Names root{st, ""};
   expect_shape(n.get("embeddings.tok_embeddings.weight"), {s.vocab, H}, "embeddings.tok_embeddings.weight");
   word_ = upload_new(n.get("embeddings.tok_embeddings.weight"));
-  emb_g_ = upload_new(n.get("embeddings.norm.weight"));  // LayerNormNoBias: weight only
+  emb_g_ = upload_new(vec(n.get("embeddings.norm.weight"), H, "hidden-size"));  // LayerNormNoBias: weight only
   for (int i = 0; i < s.layers; ++i) {
     LayerW& L = layers_[i];
     const std::string p = "layers." + std::to_string(i) + ".";
-    if (i != 0) L.ln1_g = upload_new(n.get(p + "attn_norm.weight"));  // layer 0 has none (:131-139)
+    if (i != 0) L.ln1_g = upload_new(vec(n.get(p + "attn_norm.weight"), H, "hidden-size"));  // layer 0 has none (:131-139)
     expect_shape(n.get(p + "attn.Wqkv.weight"), {3 * H, H}, p + "attn.Wqkv.weight");
     L.wqkv = upload_new(n.get(p + "attn.Wqkv.weight"));
-    if (n.has(p + "attn.Wqkv.bias")) L.bqkv = upload_new(n.get(p + "attn.Wqkv.bias"));
+    if (n.has(p + "attn.Wqkv.bias")) L.bqkv = upload_new(vec(n.get(p + "attn.Wqkv.bias"), s.qkv_width(), "qkv bias"));
     expect_shape(n.get(p + "attn.Wo.weight"), {H, H}, p + "attn.Wo.weight");
     L.wo = upload_new(n.get(p + "attn.Wo.weight"));
-    if (n.has(p + "attn.Wo.bias")) L.bo = upload_new(n.get(p + "attn.Wo.bias"));
-    L.ln2_g = upload_new(n.get(p + "mlp_norm.weight"));
+    if (n.has(p + "attn.Wo.bias")) L.bo = upload_new(vec(n.get(p + "attn.Wo.bias"), H, "hidden-size"));
+    L.ln2_g = upload_new(vec(n.get(p + "mlp_norm.weight"), H, "hidden-size"));
     // mlp.Wi [2I, H]: rows [0, I) go through the activation, rows [I, 2I) gate them.
     const StTensor& wi = n.get(p + "mlp.Wi.weight");
     expect_shape(wi, {2 * I, H}, p + "mlp.Wi.weight");
@@ -1072,22 +1091,22 @@ void Replica::load_modernbert(const SafeTensors& st) {
     upload_rows_interleaved(L.w1, ga, up);
     if (n.has(p + "mlp.Wi.bias")) {
       StTensor ba, bu;
-      halves(n.get(p + "mlp.Wi.bias"), ba, bu);
+      halves(vec(n.get(p + "mlp.Wi.bias"), 2 * I, "Wi bias"), ba, bu);
       L.b1 = dev_alloc(static_cast<size_t>(2) * I * 2);
       upload_rows_interleaved(L.b1, ba, bu);
     }
     expect_shape(n.get(p + "mlp.Wo.weight"), {H, I}, p + "mlp.Wo.weight");
     L.w2 = upload_new(n.get(p + "mlp.Wo.weight"));
-    if (n.has(p + "mlp.Wo.bias")) L.b2 = upload_new(n.get(p + "mlp.Wo.bias"));
+    if (n.has(p + "mlp.Wo.bias")) L.b2 = upload_new(vec(n.get(p + "mlp.Wo.bias"), H, "hidden-size"));
   }
-  final_norm_ = upload_new(n.get("final_norm.weight"));
+  final_norm_ = upload_new(vec(n.get("final_norm.weight"), H, "hidden-size"));
   if (s.classifier) {  // ModernBertClassificationHead::load, modernbert.rs:408-440
     expect_shape(root.get("head.dense.weight"), {H, H}, "head.dense.weight");
     cls_dense_w_ = upload_new(root.get("head.dense.weight"));
-    cls_norm_g_ = upload_new(root.get("head.norm.weight"));
+    cls_norm_g_ = upload_new(vec(root.get("head.norm.weight"), H, "hidden-size"));
     expect_shape(root.get("classifier.weight"), {s.n_classes, H}, "classifier.weight");
     cls_out_w_ = upload_new(root.get("classifier.weight"));
-    cls_out_b_ = upload_new(root.get("classifier.bias"));
+    cls_out_b_ = upload_new(vec(root.get("classifier.bias"), s.n_classes, "classifier bias"));
   }
 }
 
