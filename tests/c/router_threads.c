@@ -152,12 +152,13 @@ int main(int argc, char** argv) {
   /* every request again, alone, through the whole-handle call */
   float* one = malloc((size_t)dim * 4);
   uint32_t* pos = malloc(300 * 4);
+  uint32_t* zeros = calloc(300, 4); /* token type ids: the queue fills zeros in, here they are explicit */
   for (uint32_t t = 0; t < 300; ++t) pos[t] = t;
   double worst = 0.0;
   for (int r = 0; r < n_req; ++r) {
     const uint32_t cu[2] = {0, (uint32_t)req_len[r]};
     const uint32_t idx[1] = {0};
-    rc = tei_b200_embed(h, req_ids[r], NULL, pos, req_len[r], cu, 1, (uint32_t)req_len[r], idx, 1, NULL, 0, 0, one,
+    rc = tei_b200_embed(h, req_ids[r], zeros, pos, req_len[r], cu, 1, (uint32_t)req_len[r], idx, 1, NULL, 0, 0, one,
                         NULL, err, sizeof err);
     if (rc != TEI_B200_OK) {
       fprintf(stderr, "single embed: %d %s\n", rc, err);

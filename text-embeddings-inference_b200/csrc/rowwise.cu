@@ -5,6 +5,7 @@
 // All of them move each byte once with 16-byte accesses, keep the row in registers between the
 // statistics pass and the normalisation pass, and do their arithmetic in fp32.
 #include "kernels.h"
+#include "rope_math.cuh"
 #include "tmap.h"
 
 #include <cuda_bf16.h>
@@ -359,19 +360,17 @@ qk_norm_rope_vec_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restr
   unpack8<T>(ld16(base), a);
   unpack8<T>(ld16(base + HALF), b);
   if (gamma) {
-    float ss = 0.f;
+    float ss = ropemath::ss8(a, b);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float r = rsqrtf(ss / static_cast<float>(DH) + eps);
+    for (int o = G / 2; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    const float r = ropemath::rms_scale(ss, DH, eps);
     float ga[8], gb[8];
     unpack8<T>(ld16(gamma + sub * 8), ga);
     unpack8<T>(ld16(gamma + HALF + sub * 8), gb);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      a[i] = a[i] * r * ga[i];
-      b[i] = b[i] * r * gb[i];
+      a[i] = ropemath::normed(a[i], r, ga[i]);
+      b[i] = ropemath::normed(b[i], r, gb[i]);
     }
   }
   const size_t trow = static_cast<size_t>(pos_ids[tok]) * HALF + sub * 8;
@@ -384,8 +383,8 @@ qk_norm_rope_vec_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restr
   float oa[8], ob[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    oa[i] = a[i] * c[i] - b[i] * sn[i];
-    ob[i] = b[i] * c[i] + a[i] * sn[i];
+    oa[i] = ropemath::rot_lo(a[i], b[i], c[i], sn[i]);
+    ob[i] = ropemath::rot_hi(a[i], b[i], c[i], sn[i]);
   }
   if (valid) {
     *reinterpret_cast<uint4*>(base) = pack8<T>(oa);
