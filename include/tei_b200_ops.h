@@ -115,6 +115,21 @@ int tei_b200_op_head_linear(const float* in_dev, const void* w_dev, const void* 
                             float* out_dev, int rows, int N, int K, int act, int dtype,
                             void* stream);
 
+/* The fused q/k/v projection with its rotary epilogue: out[M, N] = a @ w^T + bias, then on the
+ * output's q heads (columns [0, q_cols)) and k heads (columns [q_cols, q_cols + k_cols)), heads of
+ * head_dim (32, 64 or 128) columns: per-head RMSNorm with q_gamma / k_gamma when they are not
+ * NULL (flash_qwen3.rs:150-151), then the rotary embedding with the cos / sin row of
+ * pos_ids[row] (flash_nomic.rs:81, flash_qwen3.rs:153; tables [max_pos, head_dim / 2] fp32, as
+ * for tei_b200_op_qk_norm_rope).  The remaining columns (v) are the plain projection.  Same
+ * result, bit for bit, as tei_b200_op_linear followed by tei_b200_op_qk_norm_rope on its
+ * output, without the second pass over q and k.  ldo must be a multiple of 8 and out 16-byte
+ * aligned. */
+int tei_b200_op_linear_rope(const void* a_dev, const void* w_dev, const void* bias_dev, void* out_dev, int M,
+                            int N, int K, int lda, int ldo, const int32_t* pos_ids_dev, const float* cos_dev,
+                            const float* sin_dev, const void* q_gamma_dev, const void* k_gamma_dev,
+                            int head_dim, int q_cols, int k_cols, float eps, int dtype, int* status_dev,
+                            void* stream);
+
 /* tei_b200_op_linear on the first min(M, *m_rows_dev) rows only: M is the capacity of the
  * buffers, the row count lives on the device (the tokens routed to one expert,
  * backends/candle/src/models/nomic.rs:325-353, where the reference syncs to the host instead). */

@@ -397,3 +397,32 @@ def test_vector_parameters_of_the_wrong_length_are_refused_at_load(lib, tmp_path
         tei_b200.B200Backend(bad, "float16", "embedding", "mean")
     assert e.value.kind == "Start" and "unexpected shape" in str(e.value)
     tei_b200.B200Backend(d, "float16", "embedding", "mean").close()  # the intact directory loads
+
+
+@pytest.mark.parametrize("key,pool,dtype", [
+    ("nomic", "mean", "float16"),
+    ("nomic_d32", "mean", "float16"),
+    ("gte", "cls", "float16"),
+    ("qwen3", "last_token", "bfloat16"),       # q/k RMSNorm + RoPE, head_dim 128, GQA
+    ("qwen3_d32", "last_token", "float16"),
+    ("qwen2", "last_token", "float16"),        # q/k/v biases
+    ("mistral", "mean", "float16"),
+    ("modernbert", "mean", "float16"),         # two RoPE tables (local / global layers)
+])
+def test_rope_in_the_projection_epilogue_equals_the_separate_kernel(lib, model_dirs, key, pool, dtype):
+    """RoPE (and Qwen3's q/k RMSNorm) fused into the q/k/v projection against the reference's form,
+    a separate pass over q and k (flash_nomic.rs:81, flash_qwen3.rs:150-153): identical rows, one
+    kernel launch per layer fewer."""
+    be = _backend(model_dirs, key, "embedding", pool, dtype)
+    b = G.random_batch(81, [7, 33, 150, 2, 64, 129, 300, 700], 0, 1000, pooled=list(range(7)), raw=[7],
+                       type_vocab=2 if key.startswith("nomic") else 1)
+    fused = be.embed(b)
+    n_fused = be.stats()["launches"]
+    be.set_fused_rope(False)
+    split = be.embed(b)
+    n_split = be.stats()["launches"]
+    be.set_fused_rope(True)
+    for i in fused:
+        assert np.array_equal(fused[i].values, split[i].values), i
+    assert n_split > n_fused
+    be.close()

@@ -349,6 +349,58 @@ def test_qk_norm_rope(lib, nh, nkv, D, use_norm, dtype):
     assert torch.equal(qkv[:, (nh + nkv) * D:], v0)  # V untouched
 
 
+@pytest.mark.parametrize("M,nh,nkv,D,use_norm,bias,dtype", [
+    (333, 12, 12, 64, False, False, "f16"),     # NomicBERT: 768 -> 2304, no bias
+    (1000, 16, 8, 128, True, False, "bf16"),    # Qwen3: 1024 -> 4096, q/k RMSNorm, GQA
+    (1000, 16, 8, 128, True, False, "f16"),
+    (77, 16, 8, 128, True, False, "bf16"),      # one row tile: the single-CTA kernel
+    (300, 12, 2, 128, False, True, "f16"),      # Qwen2: q/k/v biases
+    (300, 3, 1, 128, True, True, "f16"),        # q and k heads share a tile; 640 columns: the last tile is partial
+    (520, 12, 12, 32, False, True, "f16"),      # head_dim 32; q and k heads share a tile
+    (200, 4, 2, 32, True, False, "bf16"),
+    (130, 6, 6, 64, True, True, "f16"),         # q region of 384 columns: tile 1 holds q and k heads
+    (100, 3, 1, 64, False, False, "bf16"),      # 320 columns: the last tile is partial
+])
+def test_linear_with_the_rotary_epilogue_equals_linear_then_rope(lib, M, nh, nkv, D, use_norm, bias, dtype):
+    """The q/k/v projection with RMSNorm + RoPE in its epilogue against the two-kernel form
+    (projection, then the in-place RoPE kernel): the same bits, and both against fp32 torch."""
+    from tei_b200 import ops
+    dt = DT[dtype]
+    g = _gen(M + nh * D)
+    K = 256 if D == 32 else 768
+    Q, KV = nh * D, nkv * D
+    N = Q + 2 * KV
+    a = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dt)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dt)
+    b = (torch.randn(N, device="cuda", generator=g) * 0.1).to(dt) if bias else None
+    posi = torch.randint(0, 2048, (M,), device="cuda", dtype=torch.int32)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(2048, device="cuda").float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    qg = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dt) if use_norm else None
+    kg = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).to(dt) if use_norm else None
+    two = ops.linear(a, w, b)
+    plain = two.clone()
+    ops.qk_norm_rope_(two[:, :Q].view(M, nh, D), two[:, Q:Q + KV].view(M, nkv, D), posi, cos, sin, qg, kg, 1e-6)
+    canary = torch.full((M + 8, N), float("nan"), device="cuda", dtype=dt)
+    one = ops.linear_rope(a, w, b, posi, cos, sin, qg, kg, D, Q, KV, 1e-6, out=canary[:M])
+    assert torch.isnan(canary[M:]).all()
+    assert torch.equal(one, two)
+    assert torch.equal(one[:, Q + KV:], plain[:, Q + KV:])  # v is the plain projection
+    # and the pair against fp32
+    y = a.float() @ w.float().t() + (b.float() if bias else 0.0)
+
+    def ref(x, gamma):
+        if gamma is not None:
+            x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * gamma.float()
+        c, s_ = cos[posi.long()][:, None, :], sin[posi.long()][:, None, :]
+        x1, x2 = x[..., : D // 2], x[..., D // 2:]
+        return torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_], dim=-1)
+    tol = 3e-2 if dtype == "f16" else 1e-1
+    _close(one[:, :Q], ref(y[:, :Q].view(M, nh, D), qg).reshape(M, Q), tol)
+    _close(one[:, Q:Q + KV], ref(y[:, Q:Q + KV].view(M, nkv, D), kg).reshape(M, KV), tol)
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_pooling_gather_and_heads(lib, dtype):
     from tei_b200 import ops

@@ -10,8 +10,9 @@ inside the library instead.
 
 What is checked: the new entry point gives what the existing one gives on the same logits, twice
 in a row (the built-in counters keep the previous call's contents and must be cleared by the
-call), with different sizes in between, and it refuses more experts than its array holds.  The
-file is named so that pytest collects it last: if it fails, `-x` has already run everything else.
+call), with different sizes in between, and it refuses more experts than its array holds.  It
+shares one device array with every other caller in the process, so it runs after the other GPU
+tests (pytest collects this file last) and alone in a fresh process alike.
 """
 import ctypes
 import os

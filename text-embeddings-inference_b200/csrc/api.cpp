@@ -629,6 +629,13 @@ int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on) {
   return TEI_B200_OK;
 }
 
+int tei_b200_set_fused_rope(tei_b200_t* h, int on) {
+  if (!h) return TEI_B200_ERR_UNHEALTHY;
+  AllReplicas all(h);
+  for (auto& r : h->replicas) r->set_fused_rope(on != 0);
+  return TEI_B200_OK;
+}
+
 int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code) {
   if (!h || replica < 0 || replica >= static_cast<int>(h->replicas.size()) || device_code <= 0) {
     return TEI_B200_ERR_INFERENCE;

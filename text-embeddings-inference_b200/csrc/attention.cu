@@ -63,9 +63,8 @@ struct AttnCfg {
   // separate rings two stages each already let the next K arrive a whole step early.
   static constexpr int K_STAGES = (D <= 64) ? 3 : 2;
   static constexpr int V_STAGES = (D <= 64) ? 3 : 2;
-  // With more stages than score tiles (D = 64) the early release buys nothing and its extra
-  // tcgen05.commit per step costs issue time: there a K tile is released together with the V
-  // tile of its step and both are loaded in the same turn.
+  // With more stages than score tiles (D = 64) the early release buys nothing: there a K tile is
+  // released together with the V tile of its step and both are loaded in the same turn.
   static constexpr bool K_EARLY = K_STAGES <= S_BUFS;
   static constexpr int K_LEAD = K_EARLY ? 1 : 0;       // steps K is loaded ahead of V
   static_assert(K_EARLY || K_STAGES == V_STAGES, "shared release needs rings of one length");
@@ -287,15 +286,25 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   constexpr int K_STAGES = C::K_STAGES, V_STAGES = C::V_STAGES;
   static_assert(Q_BUFS <= 2 && K_STAGES <= 4 && V_STAGES <= 4 && S_BUFS <= 4, "barrier slots");
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  // Every tcgen05.commit costs the issuing thread 100 to 180 cycles, and that thread is the
+  // busiest of the CTA, so each MMA group signals ONE barrier and everybody who depends on it
+  // waits there: bar_s (S of a step done) tells the softmax warps that the scores are in TMEM
+  // and, with the early K release, the producer that the K stage is free (K_STAGES == S_BUFS, so
+  // stage and score tile share their index); bar_done (P V of a step done) serves the output
+  // read-out, the rescale, the V stage and, without the early release, the K stage.  bar_done
+  // is a ring of DONE_RING barriers indexed by the step: nobody waits for a step more than three
+  // steps after its P V can have finished, so a phase is always looked at before it comes round.
   uint64_t* bar_q = bars;             // [Q_BUFS] Q buffer landed
   uint64_t* bar_qfree = bars + 2;     // [Q_BUFS] last S of the unit that used the Q buffer is done
   uint64_t* bar_k = bars + 4;         // [K_STAGES] K tile landed
-  uint64_t* bar_kfree = bars + 8;     // [K_STAGES] the S MMA that read the K tile is done
-  uint64_t* bar_v = bars + 12;        // [V_STAGES] V tile landed
-  uint64_t* bar_vfree = bars + 16;    // [V_STAGES] the P V that read the V tile is done
-  uint64_t* bar_s = bars + 20;        // [S_BUFS] score tile holds the scores of its step
-  uint64_t* bar_p = bars + 24;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
-  uint64_t* bar_pv = bars + 28;       // [S_BUFS] the P V of the step is done
+  uint64_t* bar_v = bars + 8;         // [V_STAGES] V tile landed
+  uint64_t* bar_s = bars + 12;        // [S_BUFS] score tile holds the scores of its step
+  uint64_t* bar_p = bars + 16;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
+  uint64_t* bar_done = bars + 20;     // [DONE_RING] the P V of step g is done: slot g % DONE_RING
+  constexpr uint32_t DONE_RING = 6;
+  static_assert(!C::K_EARLY || K_STAGES == S_BUFS, "the early K release shares bar_s with the score tile");
+  auto done_bar = [&](uint32_t step) { return &bar_done[step % DONE_RING]; };
+  auto done_parity = [](uint32_t step) { return (step / DONE_RING) & 1u; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   constexpr uint32_t TMEM_COLS = C::TMEM_COLS;
 
@@ -311,16 +320,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < S_BUFS; ++i) {
       ptx::mbar_init(&bar_s[i], 1);
       ptx::mbar_init(&bar_p[i], 4);
-      ptx::mbar_init(&bar_pv[i], 1);
     }
-    for (int i = 0; i < K_STAGES; ++i) {
-      ptx::mbar_init(&bar_k[i], 1);
-      ptx::mbar_init(&bar_kfree[i], 1);
-    }
-    for (int i = 0; i < V_STAGES; ++i) {
-      ptx::mbar_init(&bar_v[i], 1);
-      ptx::mbar_init(&bar_vfree[i], 1);
-    }
+    for (int i = 0; i < K_STAGES; ++i) ptx::mbar_init(&bar_k[i], 1);
+    for (int i = 0; i < V_STAGES; ++i) ptx::mbar_init(&bar_v[i], 1);
+    for (uint32_t i = 0; i < DONE_RING; ++i) ptx::mbar_init(&bar_done[i], 1);
     ptx::fence_mbar_init();
   }
   if (warp == 4) {
@@ -418,7 +421,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           const int st = gk % K_STAGES;
           if (gk >= K_STAGES) {
-            ok = ptx::mbar_wait(C::K_EARLY ? &bar_kfree[st] : &bar_vfree[st], ((gk / K_STAGES) - 1) & 1);
+            // the stage held the K tile of step gk - K_STAGES: free after that step's S (early
+            // release) or after its P V
+            ok = C::K_EARLY ? ptx::mbar_wait(&bar_s[st], ((gk / K_STAGES) - 1) & 1)
+                            : ptx::mbar_wait(done_bar(gk - K_STAGES), done_parity(gk - K_STAGES));
             if (!ok) break;
           }
           // shared release: the V tile of the step follows in the same turn on the same barrier
@@ -436,7 +442,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           else if (cv.j == 0) v_col = ((cv.w % p.n_heads) / group) * D;
           const int st = gv % V_STAGES;
           if (gv >= V_STAGES) {
-            ok = ptx::mbar_wait(&bar_vfree[st], ((gv / V_STAGES) - 1) & 1);
+            ok = ptx::mbar_wait(done_bar(gv - V_STAGES), done_parity(gv - V_STAGES));
             if (!ok) break;
           }
           uint64_t* landed = C::K_EARLY ? &bar_v[st] : &bar_k[st];
@@ -497,7 +503,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               ptx::umma_ss(d_s, dqs + qoff, dks + koff, idesc_s, k != 0 ? 1u : 0u);
             }
             ptx::umma_commit(&bar_s[gs % S_BUFS]);
-            if (C::K_EARLY) ptx::umma_commit(&bar_kfree[gs % K_STAGES]);
             if (cs.j + 1 == cs.n_kv) ptx::umma_commit(&bar_qfree[qb]);  // last S of the unit
             ++gs;
             advance(cs);
@@ -524,8 +529,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                            (cp.j | k) != 0 ? 1u : 0u);
             }
           }
-          ptx::umma_commit(&bar_pv[g % S_BUFS]);
-          ptx::umma_commit(&bar_vfree[g % V_STAGES]);
+          ptx::umma_commit(done_bar(g));
           ++g;
           advance(cp);
           progress = true;
@@ -538,7 +542,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
       // Nothing may be in flight when the CTA frees its TMEM.
-      if (ok && g > 0) ok = ptx::mbar_wait(&bar_pv[(g - 1) % S_BUFS], ((g - 1) / S_BUFS) & 1);
+      if (ok && g > 0) ok = ptx::mbar_wait(done_bar(g - 1), done_parity(g - 1));
       if (!ok) atomicExch(p.status, DEV_TIMEOUT_ATTN);
     }
   } else {
@@ -560,7 +564,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     // written back with 8 lanes per row.  warp_dst: row 0 of the warp; rows_valid: how many of
     // the 32 rows belong to the sequence.
     auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* warp_dst, int rows_valid) -> bool {
-      if (!ptx::mbar_wait(&bar_pv[g_last % S_BUFS], (g_last / S_BUFS) & 1)) return false;
+      if (!ptx::mbar_wait(done_bar(g_last), done_parity(g_last))) return false;
       ptx::tc_fence_after();
       uint8_t* stage = smem + L::OFF_STAGE + warp * (32 * 128);
       if constexpr (D == 32) {
@@ -705,7 +709,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
             // P V issued so far must be complete; the next one is only issued after this
             // warp's arrival on bar_p below.
-            if (!ptx::mbar_wait(&bar_pv[(g - 1) % S_BUFS], ((g - 1) / S_BUFS) & 1)) {
+            if (!ptx::mbar_wait(done_bar(g - 1), done_parity(g - 1))) {
               ok = false;
               break;
             }

@@ -21,6 +21,7 @@
 // drains and exits.
 #include "kernels.h"
 #include "ptx.cuh"
+#include "rope_math.cuh"
 #include "tmap.h"
 
 #include <atomic>
@@ -51,6 +52,7 @@ struct GemmParams {
   int tma_store;  // 1: outputs leave through the TMA store path
   int* status;
   const int* m_dev;  // optional device-side row count (see GemmArgs::m_dev)
+  RopeFusion rope;   // used by the ROPE_D != 0 instantiations only
 };
 
 // Rows the kernel works on.
@@ -328,7 +330,211 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
   }
 }
 
-template <class T, int ACT>
+template <class T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+
+// 32 accumulator columns of one row plus bias, rounded to T and widened again: the values the
+// plain projection would have stored and the standalone RoPE kernel would have read back.
+template <class T>
+__device__ __forceinline__ void rounded_chunk(uint32_t taddr, const T* bias, int col, int N, float (&x)[32]) {
+  uint32_t r[32];
+  ptx::tmem_ld32(taddr, r);
+  ptx::tmem_ld_wait();
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
+    if (bias) {
+      // the same packed add as the plain epilogue
+      ptx::unpack_f32x2(ptx::add_f32x2(ptx::pack_f32x2(v0, v1),
+                                       ptx::pack_f32x2(col + j < N ? to_f32<T>(bias[col + j]) : 0.f,
+                                                       col + j + 1 < N ? to_f32<T>(bias[col + j + 1]) : 0.f)),
+                        v0, v1);
+    }
+    const float2 f = unpack2<T>(pack2<T>(v0, v1));
+    x[j] = f.x;
+    x[j + 1] = f.y;
+  }
+}
+
+// Writes 32 values of row `lane` into 16-byte chunks chunk0 .. chunk0 + 3 of a 32 x 64 staging
+// tile (128-byte rows, chunk index XORed with row & 7: the tensor map's 128-byte swizzle).
+template <class T>
+__device__ __forceinline__ void stage32(uint8_t* buf, int lane, int chunk0, const float (&v)[32]) {
+  uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    *reinterpret_cast<uint4*>(rowp + (((chunk0 + q) ^ (lane & 7)) * 16)) =
+        make_uint4(pack2<T>(v[q * 8 + 0], v[q * 8 + 1]), pack2<T>(v[q * 8 + 2], v[q * 8 + 3]),
+                   pack2<T>(v[q * 8 + 4], v[q * 8 + 5]), pack2<T>(v[q * 8 + 6], v[q * 8 + 7]));
+  }
+}
+
+// cos / sin of 8 consecutive pair indices of one table row.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// NP pairs (a[i], b[i]) = (x[j0 + i], x[j0 + i + D/2]) of one head: optional RMSNorm scale r with
+// the gammas of both halves, then the rotation with the table entries j0 .. j0 + NP - 1.
+template <class T, int NP>
+__device__ __forceinline__ void norm_rotate(float* a, float* b, bool norm, float r, const T* gamma, int j0,
+                                            int half, const float* cos_row, const float* sin_row) {
+#pragma unroll
+  for (int s = 0; s < NP / 8; ++s) {
+    float c[8], sn[8];
+    load8(cos_row + j0 + s * 8, c);
+    load8(sin_row + j0 + s * 8, sn);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float x = a[s * 8 + i], y = b[s * 8 + i];
+      if (norm) {
+        x = ropemath::normed(x, r, to_f32<T>(gamma[j0 + s * 8 + i]));
+        y = ropemath::normed(y, r, to_f32<T>(gamma[half + j0 + s * 8 + i]));
+      }
+      a[s * 8 + i] = ropemath::rot_lo(x, y, c[i], sn[i]);
+      b[s * 8 + i] = ropemath::rot_hi(x, y, c[i], sn[i]);
+    }
+  }
+}
+
+// Epilogue of a fused q/k/v projection (flash_qwen3.rs:119-153, flash_nomic.rs:60-81): bias, then
+// on the q and k heads the per-head RMSNorm (Qwen3) and the rotary embedding, v as it is.  A
+// thread owns one row; a head of D columns never straddles a 256-column tile, and in the CTA-pair
+// kernel each warp's half of the tile (128 columns) holds whole heads.  The arithmetic is that of
+// qk_norm_rope_vec_kernel on the rounded projection, operation for operation, so both paths give
+// the same bits.  Outputs leave through the same staging tiles and TMA stores as the plain path.
+template <class T, int D>
+__device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
+                                                   int m0, int n0, int quad, int lane, const T* bias,
+                                                   uint8_t* stage_buf, uint32_t& store_count, int part,
+                                                   int n_parts) {
+  constexpr int HALF = D / 2;
+  const int row = m0 + quad * 32 + lane;
+  const int m_rows = effective_rows(p);
+  const RopeFusion& rp = p.rope;
+  const int pos = row < m_rows ? rp.pos_ids[row] : 0;
+  const float* cos_row = rp.cos_tab + static_cast<size_t>(pos) * HALF;
+  const float* sin_row = rp.sin_tab + static_cast<size_t>(pos) * HALF;
+  const int rope_end = rp.q_cols + rp.k_cols;
+  const bool store_rows = m0 + quad * 32 < m_rows;
+  auto store = [&](uint8_t* buf, int ocol) {
+    // A box that starts beyond the last row has nothing to write; the empty group keeps the
+    // wait_group accounting uniform.
+    if (lane == 0) {
+      if (store_rows) ptx::tma_store_2d(tm_c, buf, ocol, m0 + quad * 32);
+      ptx::tma_store_commit();
+    }
+    ++store_count;
+  };
+  constexpr int STEPS = 4;  // 64 output columns each
+  const int c_begin = part * (STEPS / n_parts), c_end = (part + 1) * (STEPS / n_parts);
+  if constexpr (D == 128) {
+    // One head = two steps: the first half of the head in one staging tile, the second half in
+    // the other.
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; c += 2) {
+      const int col0 = n0 + c * 64;
+      if (col0 >= p.N) break;  // uniform across the CTA
+      const bool rotate = col0 < rope_end;
+      const T* gamma = reinterpret_cast<const T*>(col0 < rp.q_cols ? rp.q_gamma : rp.k_gamma);
+      const bool norm = rotate && gamma != nullptr;
+      float r = 1.f;
+      if (norm) {
+        float part_ss[8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          float a[32], b[32];
+          rounded_chunk<T>(t_row + c * 64 + u * 32, bias, col0 + u * 32, p.N, a);
+          rounded_chunk<T>(t_row + c * 64 + 64 + u * 32, bias, col0 + 64 + u * 32, p.N, b);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) part_ss[u * 4 + t] = ropemath::ss8(a + t * 8, b + t * 8);
+        }
+        r = ropemath::rms_scale(ropemath::combine<8>(part_ss), D, rp.eps);
+      }
+      // both staging tiles must have been read out by their TMA stores
+      if (lane == 0) ptx::tma_store_wait_read<0>();
+      __syncwarp();
+      uint8_t* buf0 = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
+      uint8_t* buf1 = stage_buf + ((store_count + 1) & 1) * EPI_BUF_BYTES;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        float a[32], b[32];
+        rounded_chunk<T>(t_row + c * 64 + u * 32, bias, col0 + u * 32, p.N, a);
+        rounded_chunk<T>(t_row + c * 64 + 64 + u * 32, bias, col0 + 64 + u * 32, p.N, b);
+        if (rotate) norm_rotate<T, 32>(a, b, norm, r, gamma, u * 32, HALF, cos_row, sin_row);
+        stage32<T>(buf0, lane, u * 4, a);
+        stage32<T>(buf1, lane, u * 4, b);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      store(buf0, col0);
+      store(buf1, col0 + 64);
+    }
+  } else {
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; ++c) {
+      const int col0 = n0 + c * 64;
+      if (col0 >= p.N) break;  // uniform across the CTA
+      float x0[32], x1[32];
+      rounded_chunk<T>(t_row + c * 64, bias, col0, p.N, x0);
+      rounded_chunk<T>(t_row + c * 64 + 32, bias, col0 + 32, p.N, x1);
+      if constexpr (D == 64) {
+        // the step is one head: x0 its first half, x1 the second
+        if (col0 < rope_end) {
+          const T* gamma = reinterpret_cast<const T*>(col0 < rp.q_cols ? rp.q_gamma : rp.k_gamma);
+          float r = 1.f;
+          if (gamma) {
+            float part_ss[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) part_ss[t] = ropemath::ss8(x0 + t * 8, x1 + t * 8);
+            r = ropemath::rms_scale(ropemath::combine<4>(part_ss), D, rp.eps);
+          }
+          norm_rotate<T, 32>(x0, x1, gamma != nullptr, r, gamma, 0, HALF, cos_row, sin_row);
+        }
+      } else {
+        // D == 32: each 32-column chunk is one head, elements [0, 16) pair with [16, 32)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          float* x = hlf ? x1 : x0;
+          const int hcol = col0 + hlf * 32;
+          if (hcol < rope_end) {
+            const T* gamma = reinterpret_cast<const T*>(hcol < rp.q_cols ? rp.q_gamma : rp.k_gamma);
+            float r = 1.f;
+            if (gamma) {
+              float part_ss[2];
+#pragma unroll
+              for (int t = 0; t < 2; ++t) part_ss[t] = ropemath::ss8(x + t * 8, x + 16 + t * 8);
+              r = ropemath::rms_scale(ropemath::combine<2>(part_ss), D, rp.eps);
+            }
+            norm_rotate<T, 16>(x, x + 16, gamma != nullptr, r, gamma, 0, HALF, cos_row, sin_row);
+          }
+        }
+      }
+      // The staging buffer used two stores ago must have been read out by its TMA store.
+      uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
+      if (lane == 0) ptx::tma_store_wait_read<1>();
+      __syncwarp();
+      stage32<T>(buf, lane, 0, x0);
+      stage32<T>(buf, lane, 4, x1);
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      store(buf, col0);
+    }
+  }
+}
+
+template <class T, int ACT, int ROPE_D>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
@@ -466,8 +672,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
-                            n_out);
+      if constexpr (ROPE_D != 0) {
+        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, 0, 1);
+      } else {
+        epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
+                              n_out);
+      }
       // Hand the accumulator back to the MMA warp.
       ptx::tc_fence_before();
       __syncwarp();
@@ -503,7 +713,7 @@ constexpr int P_B_BYTES = 128 * BK * 2;
 constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;
 constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + P_EPI_BYTES + 1024 + 256;
 
-template <class T, int ACT>
+template <class T, int ACT, int ROPE_D>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
@@ -648,8 +858,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       }
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
-                            n_out, part, 2);
+      if constexpr (ROPE_D != 0) {
+        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, part, 2);
+      } else {
+        epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
+                              n_out, part, 2);
+      }
       // Hand the accumulator back to the MMA thread of the even CTA.
       ptx::tc_fence_before();
       __syncwarp();
@@ -669,7 +883,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
-template <class T, int ACT>
+template <class T, int ACT, int ROPE_D = 0>
 int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   CUtensorMap tm_a, tm_b;
   const CUtensorMapDataType dt =
@@ -706,12 +920,17 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   p.ldr = g.ldr;
   p.tma_store = tma_store ? 1 : 0;
   p.status = g.status;
+  p.rope = RopeFusion{};
+  if (ROPE_D != 0) {
+    if (!tma_store || g.rope == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+    p.rope = *g.rope;
+  }
   if (g.M > BM) {
     // CTA pairs: 256 x 256 tiles, W loaded in halves of 128 rows.
     CUtensorMap tm_b2;
     rc = make_tmap_2d(&tm_b2, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, 128);
     if (rc) return rc;
-    auto kern2 = gemm_tcgen05_pair_kernel<T, ACT>;
+    auto kern2 = gemm_tcgen05_pair_kernel<T, ACT, ROPE_D>;
     if (!attr_set_pair[dev].load(std::memory_order_acquire)) {
       cudaError_t e = cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
       if (e != cudaSuccess) return static_cast<int>(e);
@@ -723,7 +942,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     kern2<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b2, tm_c, p);
     return static_cast<int>(cudaGetLastError());
   }
-  auto kern = gemm_tcgen05_kernel<T, ACT>;
+  auto kern = gemm_tcgen05_kernel<T, ACT, ROPE_D>;
   if (!attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -738,6 +957,19 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
 
 template <class T>
 int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
+  if (g.rope) {
+    const RopeFusion& r = *g.rope;
+    if (g.act != ACT_NONE || g.residual || !r.pos_ids || !r.cos_tab || !r.sin_tab || r.q_cols < 0 || r.k_cols < 0 ||
+        r.q_cols + r.k_cols > g.N || (r.head_dim != 32 && r.head_dim != 64 && r.head_dim != 128) ||
+        r.q_cols % r.head_dim || r.k_cols % r.head_dim || g.N % r.head_dim || (g.bias && g.N % 2)) {
+      return static_cast<int>(cudaErrorInvalidValue);
+    }
+    switch (r.head_dim) {
+      case 32: return launch_typed<T, ACT_NONE, 32>(g, stream);
+      case 64: return launch_typed<T, ACT_NONE, 64>(g, stream);
+      default: return launch_typed<T, ACT_NONE, 128>(g, stream);
+    }
+  }
   switch (g.act) {
     case ACT_NONE: return launch_typed<T, ACT_NONE>(g, stream);
     case ACT_GELU: return launch_typed<T, ACT_GELU>(g, stream);

@@ -34,6 +34,20 @@ enum DevStatus : int {
   DEV_SMEM_ALIGN = 105,
 };
 
+// Optional epilogue of a fused q/k/v projection: per-head RMSNorm (when the gammas are given) and
+// rotary embedding on the q and k heads of the output, the v columns untouched.  The output
+// columns are [q heads | k heads | rest], heads of head_dim (32, 64 or 128) columns.
+struct RopeFusion {
+  const int* pos_ids;    // [M] position of every row
+  const float* cos_tab;  // [max_pos, head_dim/2] fp32
+  const float* sin_tab;
+  const void* q_gamma;   // [head_dim] in the activation dtype, or nullptr: no norm
+  const void* k_gamma;
+  int head_dim;
+  int q_cols, k_cols;    // widths of the q and of the k region in columns
+  float eps;
+};
+
 struct GemmArgs {
   const void* a;        // [M, K] row-major activations, lda elements between rows
   const void* w;        // [N, K] row-major weights (as stored in safetensors)
@@ -49,6 +63,9 @@ struct GemmArgs {
   // buffers (what the tensor maps cover); the row count is only known on the device, as for the
   // tokens routed to one expert of a mixture-of-experts layer.
   const int* m_dev = nullptr;
+  // Optional: q/k RMSNorm + RoPE in the epilogue (act must be ACT_NONE, no residual, output rows
+  // 16-byte aligned).  Same bits as launch_qk_norm_rope applied to the plain projection.
+  const RopeFusion* rope = nullptr;
 };
 
 // out = act(a @ w^T + bias) (+ residual).  tcgen05 + TMEM + TMA, persistent over 128x256 tiles.

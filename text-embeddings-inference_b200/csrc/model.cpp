@@ -1450,6 +1450,24 @@ GemmArgs gemm_args(const void* a, const void* w, const void* bias, void* out, in
 }
 }  // namespace
 
+// The fused q/k/v projection of the rotary models.  q/k RMSNorm and RoPE run in the epilogue of
+// the GEMM (head sizes 32, 64, 128); otherwise, or with the fusion switched off, as a second
+// in-place kernel over the q and k columns.  Both give the same bits.
+void Replica::qkv_projection(const void* x, const LayerW& L, int T, int W, int H, const RopeArgs& r, int* status) {
+  const ModelSpec& s = spec_;
+  GemmArgs g = gemm_args(x, L.wqkv, L.bqkv, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status);
+  const bool fuse = fused_rope_ && (r.head_dim == 32 || r.head_dim == 64 || r.head_dim == 128);
+  RopeFusion f;
+  if (fuse) {
+    f.pos_ids = r.pos_ids; f.cos_tab = r.cos_tab; f.sin_tab = r.sin_tab;
+    f.q_gamma = r.q_gamma; f.k_gamma = r.k_gamma; f.head_dim = r.head_dim;
+    f.q_cols = r.n_heads * r.head_dim; f.k_cols = r.n_kv_heads * r.head_dim; f.eps = r.eps;
+    g.rope = &f;
+  }
+  LAUNCH(KC_GEMM, launch_gemm(g, stream_), "qkv projection");
+  if (!fuse) LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "q/k RMSNorm + rotary embedding");
+}
+
 void Replica::forward_bert() {
   const ModelSpec& s = spec_;
   const int T = static_cast<int>(T_), H = s.hidden, I = s.inter;
@@ -1558,13 +1576,12 @@ void Replica::forward_nomic() {
   uint8_t* qkv = static_cast<uint8_t*>(qkv_);
   for (int i = 0; i < s.layers; ++i) {
     const LayerW& L = layers_[i];
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, 3 * H, H, H, 3 * H, ACT_NONE, s.dtype, status), stream_), "qkv projection");
     RopeArgs r;
     r.q = qkv; r.k = qkv + static_cast<size_t>(H) * 2; r.pos_ids = d_pos_;
     r.cos_tab = scaled ? cos_scaled_ : cos_; r.sin_tab = scaled ? sin_scaled_ : sin_;
     r.q_gamma = nullptr; r.k_gamma = nullptr; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
     r.head_dim = s.head_dim; r.ld_q = 3 * H; r.ld_k = 3 * H; r.eps = 0.f; r.dtype = s.dtype;
-    LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "rotary embedding");
+    qkv_projection(x_, L, T, 3 * H, H, r, status);  // flash_nomic.rs:60-81
     AttnArgs a;
     a.q = qkv; a.k = qkv + static_cast<size_t>(H) * 2; a.v = qkv + static_cast<size_t>(2 * H) * 2;
     a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = d_work_; a.n_work = static_cast<int>(n_work_);
@@ -1671,13 +1688,12 @@ void Replica::forward_qwen3() {
     n1.out = x_; n1.sum_out = resid_; n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = rms; n1.dtype = s.dtype;
     n1.residual_f32 = 1;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "input norm");
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(x_, L.wqkv, L.bqkv, qkv_, T, W, H, H, W, ACT_NONE, s.dtype, status), stream_), "qkv projection");
     RopeArgs r;
     r.q = qkv; r.k = qkv + static_cast<size_t>(Q) * 2; r.pos_ids = d_pos_;
     r.cos_tab = local ? cos_scaled_ : cos_; r.sin_tab = local ? sin_scaled_ : sin_;
     r.q_gamma = L.q_norm; r.k_gamma = L.k_norm; r.T = T; r.n_heads = s.heads; r.n_kv_heads = s.kv_heads;
     r.head_dim = s.head_dim; r.ld_q = W; r.ld_k = W; r.eps = s.eps; r.dtype = s.dtype;
-    LAUNCH(KC_ROPE, launch_qk_norm_rope(r, stream_), "q/k RMSNorm + rotary embedding");
+    qkv_projection(x_, L, T, W, H, r, status);  // flash_qwen3.rs:119-153
     AttnArgs a;
     a.q = qkv; a.k = qkv + static_cast<size_t>(Q) * 2; a.v = qkv + static_cast<size_t>(Q + KV) * 2;
     a.out = attn_; a.cu_seqlens = d_cu_; a.work_items = local ? d_work_local_ : d_work_;

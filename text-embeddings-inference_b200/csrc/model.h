@@ -19,6 +19,8 @@
 
 namespace tei {
 
+struct RopeArgs;
+
 // Error kinds that map onto the reference's BackendError (backends/core/src/lib.rs:84-95).
 enum ErrKind : int {
   ERR_OK = 0,
@@ -166,6 +168,10 @@ class Replica {
   // computed, as the reference does.  Takes effect with the next stage().
   void set_last_layer_shortcut(bool on) { last_layer_shortcut_ = on; }
 
+  // RoPE (and the q/k RMSNorm) in the epilogue of the q/k/v projection (on by default) or as a
+  // kernel of its own behind it.  Same results bit for bit; takes effect with the next run().
+  void set_fused_rope(bool on) { fused_rope_ = on; }
+
   // Self-test hook: the next run() ends with a kernel that writes `code` to the status word,
   // exactly what a kernel whose bounded wait ran out leaves behind.  One shot.
   void report_status_once(int code) { inject_status_ = code; }
@@ -211,6 +217,7 @@ class Replica {
   void upload_rows_interleaved(void* dst, const StTensor& gate, const StTensor& up);
   void ensure_workspace(size_t tokens, size_t seqs, size_t n_work, size_t n_pooled,
                         size_t raw_rows);
+  void qkv_projection(const void* x, const LayerW& L, int T, int W, int H, const RopeArgs& r, int* status);
   void forward_bert();
   void forward_nomic();
   void forward_qwen3();
@@ -294,6 +301,7 @@ class Replica {
   size_t n_work_first_ = 0;
   bool first_rows_only_ = false;
   bool last_layer_shortcut_ = true;
+  bool fused_rope_ = true;
   int inject_status_ = 0;
   size_t out_floats_ = 0;
 };

@@ -225,6 +225,40 @@ int tei_b200_op_moe_combine(const void* yg_dev, const int32_t* topk_expert_dev,
                             top_k, hidden, cap, dtype, static_cast<cudaStream_t>(stream));
 }
 
+int tei_b200_op_linear_rope(const void* a_dev, const void* w_dev, const void* bias_dev, void* out_dev, int M,
+                            int N, int K, int lda, int ldo, const int32_t* pos_ids_dev, const float* cos_dev,
+                            const float* sin_dev, const void* q_gamma_dev, const void* k_gamma_dev,
+                            int head_dim, int q_cols, int k_cols, float eps, int dtype, int* status_dev,
+                            void* stream) {
+  RopeFusion r;
+  r.pos_ids = pos_ids_dev;
+  r.cos_tab = cos_dev;
+  r.sin_tab = sin_dev;
+  r.q_gamma = q_gamma_dev;
+  r.k_gamma = k_gamma_dev;
+  r.head_dim = head_dim;
+  r.q_cols = q_cols;
+  r.k_cols = k_cols;
+  r.eps = eps;
+  GemmArgs g;
+  g.a = a_dev;
+  g.w = w_dev;
+  g.bias = bias_dev;
+  g.residual = nullptr;
+  g.out = out_dev;
+  g.M = M;
+  g.N = N;
+  g.K = K;
+  g.lda = lda;
+  g.ldo = ldo;
+  g.ldr = 0;
+  g.act = ACT_NONE;
+  g.dtype = dtype;
+  g.status = status_dev;
+  g.rope = &r;
+  return launch_gemm(g, static_cast<cudaStream_t>(stream));
+}
+
 int tei_b200_op_bounded_wait_probe(int* status_dev, int limit, int* gave_up_dev, void* stream) {
   return launch_bounded_wait_probe(status_dev, limit, gave_up_dev, static_cast<cudaStream_t>(stream));
 }

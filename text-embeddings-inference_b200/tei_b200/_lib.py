@@ -17,6 +17,8 @@ _lib = None
 # name -> (restype, argtypes); mirrors include/tei_b200_ops.h and include/tei_b200.h
 _OPS_PROTOTYPES = {
     "tei_b200_op_linear": (c_int, [c_void_p] * 5 + [c_int] * 8 + [c_void_p, c_void_p]),
+    "tei_b200_op_linear_rope": (
+        c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p] * 5 + [c_int] * 3 + [c_float, c_int, c_void_p, c_void_p]),
     "tei_b200_attention_plan": (c_int, [POINTER(c_int32), c_int, c_int, POINTER(c_int32), c_int]),
     "tei_b200_attention_plan_windowed": (
         c_int, [POINTER(c_int32), c_int, c_int, c_int, c_int, POINTER(c_int32), c_int]),
@@ -89,6 +91,7 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_kernel_times": (c_int, [c_void_p, POINTER(c_double), POINTER(c_double), c_int]),
     "tei_b200_stats": (c_int, [c_void_p, POINTER(c_double), c_int]),
     "tei_b200_set_last_layer_shortcut": (c_int, [c_void_p, c_int]),
+    "tei_b200_set_fused_rope": (c_int, [c_void_p, c_int]),
     "tei_b200_selftest_report_timeout": (c_int, [c_void_p, c_int, c_int]),
     "tei_b200_split_echo": (
         c_int,
