@@ -338,6 +338,7 @@ def run_kernel(args):
 
     name = args.kernel
     flops = bytes_ = 0.0
+    extra = []
     st = ops.new_status()
     if name.startswith("gemm_"):
         N, K, act = {"gemm_qkv": (3 * H, H, "none"), "gemm_out": (H, H, "none"),
@@ -383,6 +384,42 @@ def run_kernel(args):
             fn = lambda: ops.attention(q, k, v, cu, causal=causal, work=work, out=out, status=st)  # noqa: E731
             flops = (2.0 if causal else 4.0) * nh * D * float(sum(n * (n + 1) if causal else n * n for n in lens))
             bytes_ = 2.0 * T * (2 * nh + 2 * nkv) * D
+    elif name in ("qkv_rope_nomic", "qkv_rope_qwen3"):
+        # The fused q/k/v projection with RoPE (and Qwen3's q/k RMSNorm) in its epilogue against the
+        # projection followed by the in-place RoPE kernel: NomicBERT (78,106 tokens, 768 -> 2304,
+        # 12 heads x 64, fp16) / Qwen3-0.6B (131,072 tokens, 1024 -> 4096, 16 + 8 heads x 128, bf16).
+        if name == "qkv_rope_nomic":
+            T, K, nh, nkv, D, norm = 78106, 768, 12, 12, 64, False
+        else:
+            T, K, nh, nkv, D, norm, dt = 131072, 1024, 16, 8, 128, True, torch.bfloat16
+        Q, KV = nh * D, nkv * D
+        N = Q + 2 * KV
+        a, w = rnd(T, K, scale=0.5).to(dt), rnd(N, K, scale=0.05).to(dt)
+        pos = (torch.arange(T, device="cuda", dtype=torch.int32) % 2048).contiguous()
+        inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, device="cuda", dtype=torch.float32) / D))
+        ang = torch.arange(2048, device="cuda", dtype=torch.float32)[:, None] * inv[None, :]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        qg = torch.ones(D, device="cuda", dtype=dt) if norm else None
+        kg = torch.ones(D, device="cuda", dtype=dt) if norm else None
+        out = torch.empty(T, N, device="cuda", dtype=dt)
+
+        def split():
+            ops.linear(a, w, None, out=out, status=st)
+            ops.qk_norm_rope_(out[:, :Q].view(T, nh, D), out[:, Q:Q + KV].view(T, nkv, D), pos, cos, sin, qg, kg, 1e-6)
+        fn = lambda: ops.linear_rope(a, w, None, pos, cos, sin, qg, kg, D, Q, KV, 1e-6, out=out, status=st)  # noqa: E731
+        flops = 2.0 * T * N * K
+        bytes_ = 2.0 * (T * K + N * K + T * N)
+        for f in (split, lambda: ops.linear(a, w, None, out=out, status=st)):
+            for _ in range(3):
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                f()
+            e1.record()
+            torch.cuda.synchronize()
+            extra.append(e0.elapsed_time(e1) / args.steps)
     elif name in ("add_layernorm", "add_layernorm_h1024"):
         if name.endswith("h1024"):  # the XLM-RoBERTa-large / Qwen3 width at the cfg4 token count
             T, H = 153855, 1024
@@ -410,6 +447,8 @@ def run_kernel(args):
     ops.check_status(st, name)
     line = {"kernel": name, "ms_per_launch": ms, "tokens": T,
             "tflops": flops / ms / 1e9 if flops else None, "algorithmic_gbs": bytes_ / ms / 1e6}
+    if extra:
+        line["ms_projection_then_rope_kernel"], line["ms_projection_alone"] = extra
     print(json.dumps(line), flush=True)
 
 
@@ -613,7 +652,8 @@ def main():
                     help="skip the flash_attn + cuBLASLt proxy forward that follows the main arm at N = 1")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
-                         "attention_long | attention_causal128 | rope_qwen3 | add_layernorm | add_layernorm_h1024 | pool_mean")
+                         "attention_long | attention_causal128 | rope_qwen3 | qkv_rope_nomic | qkv_rope_qwen3 | add_layernorm | "
+                         "add_layernorm_h1024 | pool_mean")
     ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
     ap.add_argument("--dtype", default=None, choices=["float16", "bfloat16"],

@@ -209,9 +209,11 @@ int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code
 int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on);
 
 /* Rotary models (NomicBERT, GTE, Qwen3 / Qwen2 / Mistral / Llama, ModernBERT): the rotary
- * embedding and Qwen3's per-head q/k RMSNorm run in the epilogue of the q/k/v projection (on,
- * the default) or, with on == 0, as a kernel of their own behind it, the form the reference has
- * (flash_nomic.rs:81, flash_qwen3.rs:150-153).  The results are the same bit for bit. */
+ * embedding and Qwen3's per-head q/k RMSNorm run in the epilogue of the q/k/v projection
+ * (on == 1) or as a kernel of their own behind it, the form the reference has (on == 0;
+ * flash_nomic.rs:81, flash_qwen3.rs:150-153).  on < 0, the default, picks per model whichever
+ * measured faster: the epilogue for RoPE alone, the separate kernel when the q/k RMSNorm comes
+ * with it.  The results are the same bit for bit in every mode. */
 int tei_b200_set_fused_rope(tei_b200_t* h, int on);
 
 #ifdef __cplusplus

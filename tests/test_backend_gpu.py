@@ -416,13 +416,18 @@ def test_rope_in_the_projection_epilogue_equals_the_separate_kernel(lib, model_d
     be = _backend(model_dirs, key, "embedding", pool, dtype)
     b = G.random_batch(81, [7, 33, 150, 2, 64, 129, 300, 700], 0, 1000, pooled=list(range(7)), raw=[7],
                        type_vocab=2 if key.startswith("nomic") else 1)
+    be.set_fused_rope(True)
     fused = be.embed(b)
     n_fused = be.stats()["launches"]
     be.set_fused_rope(False)
     split = be.embed(b)
     n_split = be.stats()["launches"]
-    be.set_fused_rope(True)
+    be.set_fused_rope(None)  # the default: fused unless the model has a q/k RMSNorm
+    auto = be.embed(b)
+    n_auto = be.stats()["launches"]
     for i in fused:
         assert np.array_equal(fused[i].values, split[i].values), i
+        assert np.array_equal(fused[i].values, auto[i].values), i
     assert n_split > n_fused
+    assert n_auto == (n_split if key.startswith("qwen3") else n_fused)
     be.close()

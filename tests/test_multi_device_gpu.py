@@ -1,7 +1,9 @@
 """One handle, several replicas: the packed batch is split at sequence boundaries across the
-GPUs inside a single embed / predict call and the rows come back in their original places.
-Needs at least two GPUs (skipped otherwise).  No collective runs: each replica computes its
-sequences independently."""
+replicas inside a single embed / predict call and the rows come back in their original places.
+No collective runs: each replica computes its sequences independently.  The tests over several
+GPUs need at least two (skipped otherwise); the same split, gather and scatter also run with
+several replicas of ONE GPU (each with its own stream, workspace and pinned buffers), which is
+how a single-GPU box exercises them."""
 import os
 import sys
 
@@ -87,3 +89,55 @@ def test_sharded_embed_with_dense_modules(lib, model_dirs, tmp_path):
     assert m[0].values.shape == (72,) and m[1].values.shape == (300, 128)
     one.close()
     two.close()
+
+
+@pytest.mark.parametrize("n_replicas", [2, 3])
+def test_split_over_replicas_of_one_gpu(lib, model_dirs, n_replicas):
+    """embed / predict on a handle with n replicas of device 0 against a single replica: pooled
+    and raw requests interleaved, every row back at its place; a malformed batch is an error for
+    the whole call and the handle recovers."""
+    import tei_b200
+    one = tei_b200.B200Backend(model_dirs["bert"], "float16", "embedding", "mean", devices=[0])
+    many = tei_b200.B200Backend(model_dirs["bert"], "float16", "embedding", "mean", devices=[0] * n_replicas)
+    assert many.num_replicas == n_replicas
+    lens = [7, 300, 33, 150, 2, 64, 129, 511, 90, 18, 1]
+    b = G.random_batch(15, lens, 0, 1000, pooled=[9, 0, 2, 3, 6, 8], raw=[10, 1, 4, 5, 7], type_vocab=2)
+    a = one.embed(b, normalize=True)
+    for _ in range(3):  # the per-replica threads and buffers are reused from call to call
+        m = many.embed(b, normalize=True)
+        assert sorted(a) == sorted(m) == list(range(len(lens)))
+        for i in range(len(lens)):
+            assert a[i].kind == m[i].kind and a[i].values.shape == m[i].values.shape
+            assert np.abs(a[i].values - m[i].values).max() <= 4e-3
+    assert many.stats()["tokens"] == sum(lens)
+    bad = G.random_batch(15, lens, 0, 1000, type_vocab=2)
+    bad.input_ids = bad.input_ids.copy()
+    bad.input_ids[400] = 5000  # beyond the vocabulary, inside one shard only
+    with pytest.raises(tei_b200.BackendError):
+        many.embed(bad)
+    many.health()
+    m = many.embed(b, normalize=True)
+    for i in range(len(lens)):
+        assert np.abs(a[i].values - m[i].values).max() <= 4e-3
+    # the phases of a call one by one
+    many.stage(b, normalize=True)
+    many.run_staged()
+    many.sync()
+    pooled, raw, _ = many.fetch(n_pooled=6, raw_rows=1 + 300 + 2 + 64 + 511)
+    for row, i in enumerate([9, 0, 2, 3, 6, 8]):
+        assert np.array_equal(pooled[row], m[i].values)
+    assert np.array_equal(raw[0], m[10].values[0]) and np.array_equal(raw[1:301], m[1].values)
+    one.close()
+    many.close()
+
+
+def test_split_predict_over_replicas_of_one_gpu(lib, model_dirs):
+    import tei_b200
+    one = tei_b200.B200Backend(model_dirs["xlmr"], "float16", "classifier", devices=[0])
+    three = tei_b200.B200Backend(model_dirs["xlmr"], "float16", "classifier", devices=[0, 0, 0])
+    b = G.random_batch(17, [12, 200, 31, 77, 5, 300, 64], 5, 1000, position_offset=2)
+    a, m = one.predict(b), three.predict(b)
+    for i in range(7):
+        assert abs(a[i][0] - m[i][0]) <= 2e-3
+    one.close()
+    three.close()

@@ -632,7 +632,7 @@ int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on) {
 int tei_b200_set_fused_rope(tei_b200_t* h, int on) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
   AllReplicas all(h);
-  for (auto& r : h->replicas) r->set_fused_rope(on != 0);
+  for (auto& r : h->replicas) r->set_fused_rope(on < 0 ? -1 : (on != 0 ? 1 : 0));
   return TEI_B200_OK;
 }
 

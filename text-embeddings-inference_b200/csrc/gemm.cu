@@ -341,13 +341,10 @@ __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
 }
 
-// 32 accumulator columns of one row plus bias, rounded to T and widened again: the values the
-// plain projection would have stored and the standalone RoPE kernel would have read back.
+// 32 accumulator columns of one row plus bias, rounded to T: the values the plain projection
+// would have stored and the standalone RoPE kernel would have read back, two per word.
 template <class T>
-__device__ __forceinline__ void rounded_chunk(uint32_t taddr, const T* bias, int col, int N, float (&x)[32]) {
-  uint32_t r[32];
-  ptx::tmem_ld32(taddr, r);
-  ptx::tmem_ld_wait();
+__device__ __forceinline__ void round32(const uint32_t (&r)[32], const T* bias, int col, int N, uint32_t (&x)[16]) {
 #pragma unroll
   for (int j = 0; j < 32; j += 2) {
     float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
@@ -358,22 +355,29 @@ __device__ __forceinline__ void rounded_chunk(uint32_t taddr, const T* bias, int
                                                        col + j + 1 < N ? to_f32<T>(bias[col + j + 1]) : 0.f)),
                         v0, v1);
     }
-    const float2 f = unpack2<T>(pack2<T>(v0, v1));
-    x[j] = f.x;
-    x[j + 1] = f.y;
+    x[j / 2] = pack2<T>(v0, v1);
   }
 }
-
-// Writes 32 values of row `lane` into 16-byte chunks chunk0 .. chunk0 + 3 of a 32 x 64 staging
-// tile (128-byte rows, chunk index XORed with row & 7: the tensor map's 128-byte swizzle).
+// Two chunks with both TMEM loads in flight before the one wait.
 template <class T>
-__device__ __forceinline__ void stage32(uint8_t* buf, int lane, int chunk0, const float (&v)[32]) {
+__device__ __forceinline__ void rounded_pair(uint32_t ta, uint32_t tb, const T* bias, int col_a, int col_b, int N,
+                                             uint32_t (&a)[16], uint32_t (&b)[16]) {
+  uint32_t ra[32], rb[32];
+  ptx::tmem_ld32(ta, ra);
+  ptx::tmem_ld32(tb, rb);
+  ptx::tmem_ld_wait();
+  round32<T>(ra, bias, col_a, N, a);
+  round32<T>(rb, bias, col_b, N, b);
+}
+
+// Writes 32 values (16 words) of row `lane` into 16-byte chunks chunk0 .. chunk0 + 3 of a 32 x 64
+// staging tile (128-byte rows, chunk index XORed with row & 7: the tensor map's 128-byte swizzle).
+__device__ __forceinline__ void stage16(uint8_t* buf, int lane, int chunk0, const uint32_t (&w)[16]) {
   uint8_t* rowp = buf + lane * 128;
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     *reinterpret_cast<uint4*>(rowp + (((chunk0 + q) ^ (lane & 7)) * 16)) =
-        make_uint4(pack2<T>(v[q * 8 + 0], v[q * 8 + 1]), pack2<T>(v[q * 8 + 2], v[q * 8 + 3]),
-                   pack2<T>(v[q * 8 + 4], v[q * 8 + 5]), pack2<T>(v[q * 8 + 6], v[q * 8 + 7]));
+        make_uint4(w[q * 4 + 0], w[q * 4 + 1], w[q * 4 + 2], w[q * 4 + 3]);
   }
 }
 
@@ -384,26 +388,83 @@ __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
+// 8 consecutive elements held as 4 words -> fp32.
+template <class T>
+__device__ __forceinline__ void widen8(const uint32_t* w, float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack2<T>(w[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+// 8 consecutive norm weights (16-byte aligned) as fp32.
+template <class T>
+__device__ __forceinline__ void load_gamma8(const T* p, float (&v)[8]) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  widen8<T>(w, v);
+}
 
-// NP pairs (a[i], b[i]) = (x[j0 + i], x[j0 + i + D/2]) of one head: optional RMSNorm scale r with
-// the gammas of both halves, then the rotation with the table entries j0 .. j0 + NP - 1.
+// ropemath::ss8 on 8 + 8 elements held as words, the products taken two at a time (the same IEEE
+// operations in the same order: only the additions into ss are sequential).
+template <class T>
+__device__ __forceinline__ float ss8_words(const uint32_t* aw, const uint32_t* bw) {
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = unpack2<T>(aw[i]), fb = unpack2<T>(bw[i]);
+    const uint64_t a2 = ptx::pack_f32x2(fa.x, fa.y), b2 = ptx::pack_f32x2(fb.x, fb.y);
+    float t0, t1;
+    ptx::unpack_f32x2(ptx::fma_f32x2(a2, a2, ptx::mul_f32x2(b2, b2)), t0, t1);
+    ss = __fadd_rn(ss, t0);
+    ss = __fadd_rn(ss, t1);
+  }
+  return ss;
+}
+
+// NP pairs (a[i], b[i]) = (x[j0 + i], x[j0 + i + D/2]) of one head, held as NP/2 words each:
+// optional RMSNorm scale r with the gammas of both halves, then the rotation with the table
+// entries j0 .. j0 + NP - 1, rounded back to T in place.  Two pairs per instruction; operation
+// for operation ropemath::normed / rot_lo / rot_hi (-(b s) and b (-s) are the same number).
 template <class T, int NP>
-__device__ __forceinline__ void norm_rotate(float* a, float* b, bool norm, float r, const T* gamma, int j0,
+__device__ __forceinline__ void norm_rotate(uint32_t* aw, uint32_t* bw, bool norm, float r, const T* gamma, int j0,
                                             int half, const float* cos_row, const float* sin_row) {
+  const uint64_t r2 = ptx::pack_f32x2(r, r);
+  // Every table load of the call is issued before the first use: the rows come from L2 (the L1
+  // left beside 227 KB of shared memory holds next to nothing), and two warps per scheduler
+  // cannot hide one round trip per 8 pairs.
+  float c[NP], sn[NP];
 #pragma unroll
   for (int s = 0; s < NP / 8; ++s) {
-    float c[8], sn[8];
-    load8(cos_row + j0 + s * 8, c);
-    load8(sin_row + j0 + s * 8, sn);
+    load8(cos_row + j0 + s * 8, *reinterpret_cast<float(*)[8]>(c + s * 8));
+    load8(sin_row + j0 + s * 8, *reinterpret_cast<float(*)[8]>(sn + s * 8));
+  }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float x = a[s * 8 + i], y = b[s * 8 + i];
+  for (int s = 0; s < NP / 8; ++s) {
+    float ga[8], gb[8];
+    if (norm) {
+      load_gamma8<T>(gamma + j0 + s * 8, ga);
+      load_gamma8<T>(gamma + half + j0 + s * 8, gb);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const int w = s * 4 + i / 2;
+      const float2 fa = unpack2<T>(aw[w]), fb = unpack2<T>(bw[w]);
+      uint64_t x = ptx::pack_f32x2(fa.x, fa.y);
+      uint64_t y = ptx::pack_f32x2(fb.x, fb.y);
       if (norm) {
-        x = ropemath::normed(x, r, to_f32<T>(gamma[j0 + s * 8 + i]));
-        y = ropemath::normed(y, r, to_f32<T>(gamma[half + j0 + s * 8 + i]));
+        x = ptx::mul_f32x2(ptx::mul_f32x2(x, r2), ptx::pack_f32x2(ga[i], ga[i + 1]));
+        y = ptx::mul_f32x2(ptx::mul_f32x2(y, r2), ptx::pack_f32x2(gb[i], gb[i + 1]));
       }
-      a[s * 8 + i] = ropemath::rot_lo(x, y, c[i], sn[i]);
-      b[s * 8 + i] = ropemath::rot_hi(x, y, c[i], sn[i]);
+      const uint64_t c2 = ptx::pack_f32x2(c[s * 8 + i], c[s * 8 + i + 1]);
+      const uint64_t s2 = ptx::pack_f32x2(sn[s * 8 + i], sn[s * 8 + i + 1]);
+      const uint64_t ns2 = ptx::pack_f32x2(-sn[s * 8 + i], -sn[s * 8 + i + 1]);
+      float lo0, lo1, hi0, hi1;
+      ptx::unpack_f32x2(ptx::fma_f32x2(x, c2, ptx::mul_f32x2(y, ns2)), lo0, lo1);
+      ptx::unpack_f32x2(ptx::fma_f32x2(y, c2, ptx::mul_f32x2(x, s2)), hi0, hi1);
+      aw[w] = pack2<T>(lo0, lo1);
+      bw[w] = pack2<T>(hi0, hi1);
     }
   }
 }
@@ -413,7 +474,8 @@ __device__ __forceinline__ void norm_rotate(float* a, float* b, bool norm, float
 // thread owns one row; a head of D columns never straddles a 256-column tile, and in the CTA-pair
 // kernel each warp's half of the tile (128 columns) holds whole heads.  The arithmetic is that of
 // qk_norm_rope_vec_kernel on the rounded projection, operation for operation, so both paths give
-// the same bits.  Outputs leave through the same staging tiles and TMA stores as the plain path.
+// the same bits.  The rounded values stay packed two to a register between the passes; outputs
+// leave through the same staging tiles and TMA stores as the plain path.
 template <class T, int D>
 __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
                                                    int m0, int n0, int quad, int lane, const T* bias,
@@ -449,33 +511,33 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
       const bool rotate = col0 < rope_end;
       const T* gamma = reinterpret_cast<const T*>(col0 < rp.q_cols ? rp.q_gamma : rp.k_gamma);
       const bool norm = rotate && gamma != nullptr;
+      // the whole head in registers (64 words): one pass over TMEM
+      uint32_t a0[16], b0[16], a1[16], b1[16];
+      rounded_pair<T>(t_row + c * 64, t_row + c * 64 + 64, bias, col0, col0 + 64, p.N, a0, b0);
+      rounded_pair<T>(t_row + c * 64 + 32, t_row + c * 64 + 96, bias, col0 + 32, col0 + 96, p.N, a1, b1);
       float r = 1.f;
       if (norm) {
         float part_ss[8];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          float a[32], b[32];
-          rounded_chunk<T>(t_row + c * 64 + u * 32, bias, col0 + u * 32, p.N, a);
-          rounded_chunk<T>(t_row + c * 64 + 64 + u * 32, bias, col0 + 64 + u * 32, p.N, b);
-#pragma unroll
-          for (int t = 0; t < 4; ++t) part_ss[u * 4 + t] = ropemath::ss8(a + t * 8, b + t * 8);
+        for (int t = 0; t < 4; ++t) {
+          part_ss[t] = ss8_words<T>(a0 + t * 4, b0 + t * 4);
+          part_ss[4 + t] = ss8_words<T>(a1 + t * 4, b1 + t * 4);
         }
         r = ropemath::rms_scale(ropemath::combine<8>(part_ss), D, rp.eps);
+      }
+      if (rotate) {
+        norm_rotate<T, 32>(a0, b0, norm, r, gamma, 0, HALF, cos_row, sin_row);
+        norm_rotate<T, 32>(a1, b1, norm, r, gamma, 32, HALF, cos_row, sin_row);
       }
       // both staging tiles must have been read out by their TMA stores
       if (lane == 0) ptx::tma_store_wait_read<0>();
       __syncwarp();
       uint8_t* buf0 = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
       uint8_t* buf1 = stage_buf + ((store_count + 1) & 1) * EPI_BUF_BYTES;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        float a[32], b[32];
-        rounded_chunk<T>(t_row + c * 64 + u * 32, bias, col0 + u * 32, p.N, a);
-        rounded_chunk<T>(t_row + c * 64 + 64 + u * 32, bias, col0 + 64 + u * 32, p.N, b);
-        if (rotate) norm_rotate<T, 32>(a, b, norm, r, gamma, u * 32, HALF, cos_row, sin_row);
-        stage32<T>(buf0, lane, u * 4, a);
-        stage32<T>(buf1, lane, u * 4, b);
-      }
+      stage16(buf0, lane, 0, a0);
+      stage16(buf0, lane, 4, a1);
+      stage16(buf1, lane, 0, b0);
+      stage16(buf1, lane, 4, b1);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       store(buf0, col0);
@@ -486,9 +548,8 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
     for (int c = c_begin; c < c_end; ++c) {
       const int col0 = n0 + c * 64;
       if (col0 >= p.N) break;  // uniform across the CTA
-      float x0[32], x1[32];
-      rounded_chunk<T>(t_row + c * 64, bias, col0, p.N, x0);
-      rounded_chunk<T>(t_row + c * 64 + 32, bias, col0 + 32, p.N, x1);
+      uint32_t x0[16], x1[16];
+      rounded_pair<T>(t_row + c * 64, t_row + c * 64 + 32, bias, col0, col0 + 32, p.N, x0, x1);
       if constexpr (D == 64) {
         // the step is one head: x0 its first half, x1 the second
         if (col0 < rope_end) {
@@ -497,7 +558,7 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
           if (gamma) {
             float part_ss[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) part_ss[t] = ropemath::ss8(x0 + t * 8, x1 + t * 8);
+            for (int t = 0; t < 4; ++t) part_ss[t] = ss8_words<T>(x0 + t * 4, x1 + t * 4);
             r = ropemath::rms_scale(ropemath::combine<4>(part_ss), D, rp.eps);
           }
           norm_rotate<T, 32>(x0, x1, gamma != nullptr, r, gamma, 0, HALF, cos_row, sin_row);
@@ -506,7 +567,7 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
         // D == 32: each 32-column chunk is one head, elements [0, 16) pair with [16, 32)
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
-          float* x = hlf ? x1 : x0;
+          uint32_t* x = hlf ? x1 : x0;
           const int hcol = col0 + hlf * 32;
           if (hcol < rope_end) {
             const T* gamma = reinterpret_cast<const T*>(hcol < rp.q_cols ? rp.q_gamma : rp.k_gamma);
@@ -514,10 +575,10 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
             if (gamma) {
               float part_ss[2];
 #pragma unroll
-              for (int t = 0; t < 2; ++t) part_ss[t] = ropemath::ss8(x + t * 8, x + 16 + t * 8);
+              for (int t = 0; t < 2; ++t) part_ss[t] = ss8_words<T>(x + t * 4, x + 8 + t * 4);
               r = ropemath::rms_scale(ropemath::combine<2>(part_ss), D, rp.eps);
             }
-            norm_rotate<T, 16>(x, x + 16, gamma != nullptr, r, gamma, 0, HALF, cos_row, sin_row);
+            norm_rotate<T, 16>(x, x + 8, gamma != nullptr, r, gamma, 0, HALF, cos_row, sin_row);
           }
         }
       }
@@ -525,8 +586,8 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
       uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
       if (lane == 0) ptx::tma_store_wait_read<1>();
       __syncwarp();
-      stage32<T>(buf, lane, 0, x0);
-      stage32<T>(buf, lane, 4, x1);
+      stage16(buf, lane, 0, x0);
+      stage16(buf, lane, 4, x1);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       store(buf, col0);
@@ -961,7 +1022,9 @@ int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
     const RopeFusion& r = *g.rope;
     if (g.act != ACT_NONE || g.residual || !r.pos_ids || !r.cos_tab || !r.sin_tab || r.q_cols < 0 || r.k_cols < 0 ||
         r.q_cols + r.k_cols > g.N || (r.head_dim != 32 && r.head_dim != 64 && r.head_dim != 128) ||
-        r.q_cols % r.head_dim || r.k_cols % r.head_dim || g.N % r.head_dim || (g.bias && g.N % 2)) {
+        r.q_cols % r.head_dim || r.k_cols % r.head_dim || g.N % r.head_dim || (g.bias && g.N % 2) ||
+        (reinterpret_cast<uintptr_t>(r.q_gamma) & 15) || (reinterpret_cast<uintptr_t>(r.k_gamma) & 15) ||
+        (reinterpret_cast<uintptr_t>(r.cos_tab) & 15) || (reinterpret_cast<uintptr_t>(r.sin_tab) & 15)) {
       return static_cast<int>(cudaErrorInvalidValue);
     }
     switch (r.head_dim) {

@@ -168,9 +168,10 @@ class Replica {
   // computed, as the reference does.  Takes effect with the next stage().
   void set_last_layer_shortcut(bool on) { last_layer_shortcut_ = on; }
 
-  // RoPE (and the q/k RMSNorm) in the epilogue of the q/k/v projection (on by default) or as a
-  // kernel of its own behind it.  Same results bit for bit; takes effect with the next run().
-  void set_fused_rope(bool on) { fused_rope_ = on; }
+  // RoPE (and the q/k RMSNorm) in the epilogue of the q/k/v projection (1), as a kernel of its own
+  // behind it (0), or whichever is faster for the model (-1, the default: fused unless the model
+  // has a q/k RMSNorm).  Same results bit for bit; takes effect with the next run().
+  void set_fused_rope(int mode) { fused_rope_ = mode; }
 
   // Self-test hook: the next run() ends with a kernel that writes `code` to the status word,
   // exactly what a kernel whose bounded wait ran out leaves behind.  One shot.
@@ -301,7 +302,7 @@ class Replica {
   size_t n_work_first_ = 0;
   bool first_rows_only_ = false;
   bool last_layer_shortcut_ = true;
-  bool fused_rope_ = true;
+  int fused_rope_ = -1;
   int inject_status_ = 0;
   size_t out_floats_ = 0;
 };

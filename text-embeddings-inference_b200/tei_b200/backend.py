@@ -243,9 +243,10 @@ class B200Backend:
         """Off: every call computes every row of the last layer, as the reference does."""
         self._lib.tei_b200_set_last_layer_shortcut(self._h, int(on))
 
-    def set_fused_rope(self, on: bool) -> None:
-        """Off: RoPE / q-k RMSNorm run as a kernel of their own behind the q/k/v projection."""
-        self._lib.tei_b200_set_fused_rope(self._h, int(on))
+    def set_fused_rope(self, on) -> None:
+        """True: RoPE / q-k RMSNorm in the epilogue of the q/k/v projection; False: a kernel of
+        their own behind it; None: whichever is faster for the model (the default)."""
+        self._lib.tei_b200_set_fused_rope(self._h, -1 if on is None else int(bool(on)))
 
     def selftest_report_timeout(self, replica: int = 0, device_code: int = 104) -> None:
         """The next forward on `replica` reports `device_code` through the status word, like a

@@ -68,19 +68,23 @@ def linear(a, w, bias=None, residual=None, act="none", out=None, status=None):
     return out
 
 
-def linear_rope(a, w, bias, pos_ids, cos, sin, q_gamma, k_gamma, head_dim, q_cols, k_cols, eps=0.0, out=None):
+def linear_rope(a, w, bias, pos_ids, cos, sin, q_gamma, k_gamma, head_dim, q_cols, k_cols, eps=0.0, out=None,
+                status=None):
     """The fused q/k/v projection with per-head RMSNorm (optional) + RoPE on its q and k heads."""
     lib = _lib.load()
     M, K = a.shape
     N = w.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=a.dtype, device=a.device)
-    status = new_status(a.device)
+    own = status is None
+    if own:
+        status = new_status(a.device)
     rc = lib.tei_b200_op_linear_rope(
         _p(a), _p(w), _p(bias), _p(out), M, N, K, a.stride(0), out.stride(0), _p(pos_ids), _p(cos), _p(sin),
         _p(q_gamma), _p(k_gamma), int(head_dim), int(q_cols), int(k_cols), float(eps), _dt(a), _p(status), _stream())
     _check(rc, "tei_b200_op_linear_rope")
-    check_status(status, "linear_rope")
+    if own:
+        check_status(status, "linear_rope")
     return out
 
 
