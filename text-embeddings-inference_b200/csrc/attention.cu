@@ -278,6 +278,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (ptx::smem_u32(smem) & 1023u) {  // swizzled operand tiles need 1024-byte alignment
+    ptx::grid_dependency_sync();
     if (threadIdx.x == 0) atomicExch(p.status, DEV_SMEM_ALIGN);
     return;
   }
@@ -333,6 +334,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  // Barriers and TMEM are set up; from here on the kernel touches what its predecessor wrote.
+  ptx::grid_dependency_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   // Score tiles: S_BUFS x 64 columns from column 0; output tiles behind them.  With two output
   // tiles (D = 64) units alternate, so that a finished unit's rows can be read out while the
@@ -826,8 +829,8 @@ int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
   if (total > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
   const long long resident = static_cast<long long>(num_sms()) * AttnCfg<D>::CTAS_PER_SM;
   const long long grid = total < resident ? total : resident;
-  kern<<<static_cast<unsigned>(grid), ATTN_THREADS, L::TOTAL, stream>>>(tm_q, tm_k, tm_v, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(kern, dim3(static_cast<unsigned>(grid)), dim3(ATTN_THREADS), L::TOTAL, stream,
+                                           tm_q, tm_k, tm_v, p));
 }
 
 template <class T, int D>

@@ -614,11 +614,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int tiles_m = (effective_rows(p) + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
-
   if (threadIdx.x == 0) {
     ptx::prefetch_tmap(&tm_a);
     ptx::prefetch_tmap(&tm_b);
@@ -640,7 +635,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  // Set-up done; what follows reads what the previous kernel wrote (the row count included).
+  ptx::grid_dependency_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const int tiles_m = (effective_rows(p) + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -796,11 +797,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
-  const int tiles_m = (effective_rows(p) + 2 * BM - 1) / (2 * BM);
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
-
   if (threadIdx.x == 0) {
     ptx::prefetch_tmap(&tm_a);
     ptx::prefetch_tmap(&tm_b);
@@ -823,7 +819,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   __syncthreads();
   ptx::cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   ptx::tc_fence_after();
+  // Set-up done; what follows reads what the previous kernel wrote (the row count included).
+  ptx::grid_dependency_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const int tiles_m = (effective_rows(p) + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -1000,8 +1002,8 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     const int tiles2 = ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + BN - 1) / BN);
     const int max_pairs = num_sms() / 2;
     const int pairs = tiles2 < max_pairs ? tiles2 : max_pairs;
-    kern2<<<2 * pairs, P_THREADS, P_SMEM_BYTES, stream>>>(tm_a, tm_b2, tm_c, p);
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_dependent(kern2, dim3(2 * pairs), dim3(P_THREADS), P_SMEM_BYTES, stream, tm_a, tm_b2,
+                                             tm_c, p));
   }
   auto kern = gemm_tcgen05_kernel<T, ACT, ROPE_D>;
   if (!attr_set[dev].load(std::memory_order_acquire)) {
@@ -1012,8 +1014,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a, tm_b, tm_c, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tm_a, tm_b, tm_c, p));
 }
 
 template <class T>

@@ -33,6 +33,21 @@ __device__ __forceinline__ uint32_t elect_one() {
   return pred;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the forward is launched with programmatic stream serialisation: its CTAs may
+// become resident, set up their barriers and allocate their TMEM while the kernel before it in
+// the stream is still draining.  launch_dependents lets the NEXT kernel do the same with respect
+// to this one (it takes effect once every CTA of this grid has issued it or exited); wait blocks
+// until the previous kernel has completed and its writes are visible.  Nothing that an earlier
+// kernel wrote may be read, and nothing it reads may be overwritten, before the wait.  Without
+// the launch attribute both instructions do nothing.
+__device__ __forceinline__ void grid_dependency_sync() {
+#ifndef TEI_NO_PDL
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

@@ -5,6 +5,7 @@
 // All of them move each byte once with 16-byte accesses, keep the row in registers between the
 // statistics pass and the normalisation pass, and do their arithmetic in fp32.
 #include "kernels.h"
+#include "ptx.cuh"
 #include "rope_math.cuh"
 #include "tmap.h"
 
@@ -137,6 +138,7 @@ embed_ln_kernel(const int* __restrict__ ids, const int* __restrict__ type_ids,
                 const T* __restrict__ type_tab, const T* __restrict__ pos_tab,
                 const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ out, int T_,
                 int H, float eps) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T_) return;
@@ -183,7 +185,8 @@ template <class T, int MAXC, bool RMS, bool F32RES>
 __global__ void __launch_bounds__(256, (MAXC <= 3 ? 6 : (MAXC == 4 ? 4 : 1)))
 add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restrict__ gamma,
                 const T* __restrict__ beta, T* __restrict__ out, float* sum_out, int T_, int H,
-                float eps) {  // residual and sum_out may be the same buffer: no __restrict__
+                float eps) {
+  ptx::grid_dependency_sync();  // residual and sum_out may be the same buffer: no __restrict__
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= T_) return;
@@ -231,6 +234,7 @@ add_norm_kernel(const T* __restrict__ x, const void* residual, const T* __restri
 template <class T>
 __global__ void __launch_bounds__(256) layernorm_rows_f32_kernel(float* __restrict__ x, const T* __restrict__ gamma,
                                                                  int rows, int H, float eps) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -252,6 +256,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 layernorm_qk_kernel(T* q, T* k, int ld, const T* __restrict__ gq, const T* __restrict__ bq,
                     const T* __restrict__ gk, const T* __restrict__ bk, int T_, int H, float eps) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (idx >= 2 * T_) return;
@@ -285,6 +290,7 @@ qk_norm_rope_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restrict_
                     const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                     const T* __restrict__ q_gamma, const T* __restrict__ k_gamma, int T_, int nh,
                     int nkv, int dh, int ld_q, int ld_k, float eps) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int heads = nh + nkv;
@@ -342,6 +348,7 @@ qk_norm_rope_vec_kernel(T* __restrict__ q, T* __restrict__ k, const int* __restr
                         const float* __restrict__ cos_tab, const float* __restrict__ sin_tab,
                         const T* __restrict__ q_gamma, const T* __restrict__ k_gamma, int T_, int nh,
                         int nkv, int ld_q, int ld_k, float eps) {
+  ptx::grid_dependency_sync();
   constexpr int G = DH / 16;     // lanes per (token, head)
   constexpr int HALF = DH / 2;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -400,6 +407,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 pool_kernel(const T* __restrict__ x, const int* __restrict__ cu, const int* __restrict__ seq_index,
             float* __restrict__ out, int H, int mode) {
+  ptx::grid_dependency_sync();
   const int o = blockIdx.x;
   const int s = seq_index[o];
   const int start = cu[s], end = cu[s + 1];
@@ -451,6 +459,7 @@ pool_kernel(const T* __restrict__ x, const int* __restrict__ cu, const int* __re
 
 // In-place L2 normalisation of fp32 rows (core/src/infer.rs:288-303 does this on the host).
 __global__ void __launch_bounds__(256) l2_normalise_kernel(float* __restrict__ x, int rows, int H) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -466,6 +475,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_index,
                    float* __restrict__ out, int n_rows, int H) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
@@ -486,6 +496,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const float* __restrict__ in, const T* __restrict__ w, const T* __restrict__ b,
                    float* __restrict__ out, int rows, int N, int K, int act) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(rows) * N) return;
@@ -515,6 +526,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ logits, int ld, int T_, int E, int k, int* __restrict__ topk_e,
                  float* __restrict__ topk_w, int* __restrict__ pos, int* __restrict__ counts) {
+  ptx::grid_dependency_sync();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T_) return;
   float pr[kMoeMaxExperts];
@@ -549,6 +561,7 @@ template <class T>
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ topk_e, const int* __restrict__ pos,
                   T* __restrict__ xg, int n_picks, int k, int H, long long cap) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= n_picks) return;
@@ -564,6 +577,7 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const T* __restrict__ yg, const int* __restrict__ topk_e, const float* __restrict__ topk_w,
                    const int* __restrict__ pos, const T* __restrict__ bias, T* __restrict__ out, int T_,
                    int k, int H, long long cap) {
+  ptx::grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (t >= T_) return;
@@ -589,6 +603,7 @@ moe_combine_kernel(const T* __restrict__ yg, const int* __restrict__ topk_e, con
 
 template <class S, class D>
 __global__ void __launch_bounds__(256) convert_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+  ptx::grid_dependency_sync();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
     float v;
@@ -606,9 +621,9 @@ int convert_from(const void* src, void* dst, int dst_kind, size_t n, cudaStream_
   const size_t want = (n + 255) / 256;
   const unsigned grid = static_cast<unsigned>(want < 4096 ? (want ? want : 1) : 4096);
   const S* s = reinterpret_cast<const S*>(src);
-  if (dst_kind == DT_F16) convert_kernel<S, __half><<<grid, 256, 0, st>>>(s, reinterpret_cast<__half*>(dst), n);
-  else if (dst_kind == DT_BF16) convert_kernel<S, __nv_bfloat16><<<grid, 256, 0, st>>>(s, reinterpret_cast<__nv_bfloat16*>(dst), n);
-  else if (dst_kind == 2) convert_kernel<S, float><<<grid, 256, 0, st>>>(s, reinterpret_cast<float*>(dst), n);
+  if (dst_kind == DT_F16) launch_dependent(convert_kernel<S, __half>, dim3(grid), dim3(256), 0, st, s, reinterpret_cast<__half*>(dst), n);
+  else if (dst_kind == DT_BF16) launch_dependent(convert_kernel<S, __nv_bfloat16>, dim3(grid), dim3(256), 0, st, s, reinterpret_cast<__nv_bfloat16*>(dst), n);
+  else if (dst_kind == 2) launch_dependent(convert_kernel<S, float>, dim3(grid), dim3(256), 0, st, s, reinterpret_cast<float*>(dst), n);
   else return static_cast<int>(cudaErrorInvalidValue);
   return last_error();
 }
@@ -619,7 +634,7 @@ int embed_typed(const EmbedArgs& e, cudaStream_t st) {
   const int grid = (e.T + warps - 1) / warps;
   const int n_chunks = e.H / 8;
 #define TEI_EMBED(MAXC)                                                                          \
-  embed_ln_kernel<T, MAXC><<<grid, warps * 32, 0, st>>>(                                         \
+  launch_dependent(embed_ln_kernel<T, MAXC>, dim3(grid), dim3(warps * 32), 0, st,                                          \
       e.ids, e.type_ids, e.pos_ids, reinterpret_cast<const T*>(e.word),                          \
       reinterpret_cast<const T*>(e.type_tab), reinterpret_cast<const T*>(e.pos_tab),             \
       reinterpret_cast<const T*>(e.gamma), reinterpret_cast<const T*>(e.beta),                   \
@@ -638,7 +653,7 @@ int norm_typed(const NormArgs& n, cudaStream_t st) {
   const int grid = (n.T + warps - 1) / warps;
   const int n_chunks = n.H / 8;
 #define TEI_NORM(MAXC)                                                                           \
-  add_norm_kernel<T, MAXC, RMS, F32RES><<<grid, warps * 32, 0, st>>>(                                    \
+  launch_dependent(add_norm_kernel<T, MAXC, RMS, F32RES>, dim3(grid), dim3(warps * 32), 0, st,                                     \
       reinterpret_cast<const T*>(n.x), n.residual, reinterpret_cast<const T*>(n.gamma),          \
       reinterpret_cast<const T*>(n.beta), reinterpret_cast<T*>(n.out),                           \
       reinterpret_cast<float*>(n.sum_out), n.T, n.H, n.eps)
@@ -677,9 +692,9 @@ int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, floa
   const int warps = 8;
   const int grid = (rows + warps - 1) / warps;
   if (dtype == DT_F16) {
-    layernorm_rows_f32_kernel<__half><<<grid, warps * 32, 0, st>>>(x, reinterpret_cast<const __half*>(gamma), rows, H, eps);
+    launch_dependent(layernorm_rows_f32_kernel<__half>, dim3(grid), dim3(warps * 32), 0, st, x, reinterpret_cast<const __half*>(gamma), rows, H, eps);
   } else {
-    layernorm_rows_f32_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(layernorm_rows_f32_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, st, 
         x, reinterpret_cast<const __nv_bfloat16*>(gamma), rows, H, eps);
   }
   return last_error();
@@ -690,6 +705,7 @@ int launch_layernorm_rows_f32(float* x, const void* gamma, int rows, int H, floa
 __global__ void __launch_bounds__(256) first_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst,
                                                          const int* __restrict__ cu, int B, int vec_per_row,
                                                          int scatter, int last) {
+  ptx::grid_dependency_sync();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<long long>(B) * vec_per_row) return;
   const int b = static_cast<int>(i / vec_per_row), v = static_cast<int>(i % vec_per_row);
@@ -704,7 +720,7 @@ int launch_first_rows(const void* src, void* dst, const int* cu_seqlens, int B, 
   if (B <= 0) return 0;
   if (row_bytes % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const long long n = static_cast<long long>(B) * (row_bytes / 16);
-  first_rows_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(
+  launch_dependent(first_rows_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, st, 
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), cu_seqlens, B, row_bytes / 16, scatter, last);
   return last_error();
 }
@@ -716,12 +732,12 @@ int launch_layernorm_qk(void* q, void* k, int ld, const void* gq, const void* bq
   const int grid = (2 * T + warps - 1) / warps;
   if (dtype == DT_F16) {
     using X = __half;
-    layernorm_qk_kernel<X><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(layernorm_qk_kernel<X>, dim3(grid), dim3(warps * 32), 0, st, 
         static_cast<X*>(q), static_cast<X*>(k), ld, static_cast<const X*>(gq), static_cast<const X*>(bq),
         static_cast<const X*>(gk), static_cast<const X*>(bk), T, H, eps);
   } else {
     using X = __nv_bfloat16;
-    layernorm_qk_kernel<X><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(layernorm_qk_kernel<X>, dim3(grid), dim3(warps * 32), 0, st, 
         static_cast<X*>(q), static_cast<X*>(k), ld, static_cast<const X*>(gq), static_cast<const X*>(bq),
         static_cast<const X*>(gk), static_cast<const X*>(bk), T, H, eps);
   }
@@ -739,7 +755,7 @@ int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
     const long long threads = warps_total * (r.head_dim / 16);
     const unsigned grid_v = static_cast<unsigned>((threads + 255) / 256);
 #define TEI_ROPE_VEC(TYPE, DH)                                                                     \
-  qk_norm_rope_vec_kernel<TYPE, DH><<<grid_v, 256, 0, st>>>(                                       \
+  launch_dependent(qk_norm_rope_vec_kernel<TYPE, DH>, dim3(grid_v), dim3(256), 0, st,                                        \
       reinterpret_cast<TYPE*>(r.q), reinterpret_cast<TYPE*>(r.k), r.pos_ids, r.cos_tab, r.sin_tab, \
       reinterpret_cast<const TYPE*>(r.q_gamma), reinterpret_cast<const TYPE*>(r.k_gamma), r.T,     \
       r.n_heads, r.n_kv_heads, r.ld_q, r.ld_k, r.eps)
@@ -758,13 +774,13 @@ int launch_qk_norm_rope(const RopeArgs& r, cudaStream_t st) {
   const int warps = 8;
   const long long grid = (warps_total + warps - 1) / warps;
   if (r.dtype == DT_F16) {
-    qk_norm_rope_kernel<__half><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+    launch_dependent(qk_norm_rope_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, 
         reinterpret_cast<__half*>(r.q), reinterpret_cast<__half*>(r.k), r.pos_ids, r.cos_tab,
         r.sin_tab, reinterpret_cast<const __half*>(r.q_gamma),
         reinterpret_cast<const __half*>(r.k_gamma), r.T, r.n_heads, r.n_kv_heads, r.head_dim,
         r.ld_q, r.ld_k, r.eps);
   } else {
-    qk_norm_rope_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+    launch_dependent(qk_norm_rope_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, 
         reinterpret_cast<__nv_bfloat16*>(r.q), reinterpret_cast<__nv_bfloat16*>(r.k), r.pos_ids,
         r.cos_tab, r.sin_tab, reinterpret_cast<const __nv_bfloat16*>(r.q_gamma),
         reinterpret_cast<const __nv_bfloat16*>(r.k_gamma), r.T, r.n_heads, r.n_kv_heads,
@@ -778,10 +794,10 @@ int launch_pool(const PoolArgs& p, cudaStream_t st) {
   if (p.H % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   dim3 grid(p.n_out, (p.H + 255) / 256);
   if (p.dtype == DT_F16) {
-    pool_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(p.x), p.cu_seqlens,
+    launch_dependent(pool_kernel<__half>, dim3(grid), dim3(256), 0, st, reinterpret_cast<const __half*>(p.x), p.cu_seqlens,
                                               p.seq_index, p.out, p.H, p.mode);
   } else {
-    pool_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(p.x),
+    launch_dependent(pool_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(p.x),
                                                      p.cu_seqlens, p.seq_index, p.out, p.H,
                                                      p.mode);
   }
@@ -789,7 +805,7 @@ int launch_pool(const PoolArgs& p, cudaStream_t st) {
   if (rc) return rc;
   if (p.normalize) {
     const int warps = 8;
-    l2_normalise_kernel<<<(p.n_out + warps - 1) / warps, warps * 32, 0, st>>>(p.out, p.n_out, p.H);
+    launch_dependent(l2_normalise_kernel, dim3((p.n_out + warps - 1) / warps), dim3(warps * 32), 0, st, p.out, p.n_out, p.H);
     rc = last_error();
   }
   return rc;
@@ -798,7 +814,7 @@ int launch_pool(const PoolArgs& p, cudaStream_t st) {
 int launch_l2_normalise(float* x, int rows, int H, cudaStream_t st) {
   if (rows <= 0) return 0;
   const int warps = 8;
-  l2_normalise_kernel<<<(rows + warps - 1) / warps, warps * 32, 0, st>>>(x, rows, H);
+  launch_dependent(l2_normalise_kernel, dim3((rows + warps - 1) / warps), dim3(warps * 32), 0, st, x, rows, H);
   return last_error();
 }
 
@@ -809,10 +825,10 @@ int launch_gather_rows_f32(const void* x, const int* row_index, float* out, int 
   const int warps = 8;
   const int grid = (n_rows + warps - 1) / warps;
   if (dtype == DT_F16) {
-    gather_rows_kernel<__half><<<grid, warps * 32, 0, st>>>(reinterpret_cast<const __half*>(x),
+    launch_dependent(gather_rows_kernel<__half>, dim3(grid), dim3(warps * 32), 0, st, reinterpret_cast<const __half*>(x),
                                                             row_index, out, n_rows, H);
   } else {
-    gather_rows_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(gather_rows_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, st, 
         reinterpret_cast<const __nv_bfloat16*>(x), row_index, out, n_rows, H);
   }
   return last_error();
@@ -824,10 +840,10 @@ int launch_moe_route(const void* logits, int ld_logits, int T, int E, int k, int
   if (E <= 0 || E > kMoeMaxExperts || k <= 0 || k > kMoeMaxTopK || k > E) return static_cast<int>(cudaErrorInvalidValue);
   const int grid = (T + 255) / 256;
   if (dtype == DT_F16) {
-    moe_route_kernel<__half><<<grid, 256, 0, st>>>(reinterpret_cast<const __half*>(logits), ld_logits, T, E, k,
+    launch_dependent(moe_route_kernel<__half>, dim3(grid), dim3(256), 0, st, reinterpret_cast<const __half*>(logits), ld_logits, T, E, k,
                                                   topk_e, topk_w, pos, counts);
   } else {
-    moe_route_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(logits),
+    launch_dependent(moe_route_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16*>(logits),
                                                          ld_logits, T, E, k, topk_e, topk_w, pos, counts);
   }
   return last_error();
@@ -840,10 +856,10 @@ int launch_moe_gather(const void* x, const int* topk_e, const int* pos, void* xg
   const int n = T * k, warps = 8;
   const int grid = (n + warps - 1) / warps;
   if (dtype == DT_F16) {
-    moe_gather_kernel<__half><<<grid, warps * 32, 0, st>>>(reinterpret_cast<const __half*>(x), topk_e, pos,
+    launch_dependent(moe_gather_kernel<__half>, dim3(grid), dim3(warps * 32), 0, st, reinterpret_cast<const __half*>(x), topk_e, pos,
                                                            reinterpret_cast<__half*>(xg), n, k, H, cap);
   } else {
-    moe_gather_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(moe_gather_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, st, 
         reinterpret_cast<const __nv_bfloat16*>(x), topk_e, pos, reinterpret_cast<__nv_bfloat16*>(xg), n, k, H, cap);
   }
   return last_error();
@@ -857,11 +873,11 @@ int launch_moe_combine(const void* yg, const int* topk_e, const float* topk_w, c
   const int warps = 8;
   const int grid = (T + warps - 1) / warps;
   if (dtype == DT_F16) {
-    moe_combine_kernel<__half><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(moe_combine_kernel<__half>, dim3(grid), dim3(warps * 32), 0, st, 
         reinterpret_cast<const __half*>(yg), topk_e, topk_w, pos, reinterpret_cast<const __half*>(bias),
         reinterpret_cast<__half*>(out), T, k, H, cap);
   } else {
-    moe_combine_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+    launch_dependent(moe_combine_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, st, 
         reinterpret_cast<const __nv_bfloat16*>(yg), topk_e, topk_w, pos,
         reinterpret_cast<const __nv_bfloat16*>(bias), reinterpret_cast<__nv_bfloat16*>(out), T, k, H, cap);
   }
@@ -884,11 +900,11 @@ int launch_head_linear(const float* in, const void* w, const void* b, float* out
   const int warps = 8;
   const long long grid = (total + warps - 1) / warps;
   if (dtype == DT_F16) {
-    head_linear_kernel<__half><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+    launch_dependent(head_linear_kernel<__half>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, 
         in, reinterpret_cast<const __half*>(w), reinterpret_cast<const __half*>(b), out, rows, N, K,
         act);
   } else {
-    head_linear_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), warps * 32, 0, st>>>(
+    launch_dependent(head_linear_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(grid)), dim3(warps * 32), 0, st, 
         in, reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<const __nv_bfloat16*>(b),
         out, rows, N, K, act);
   }
