@@ -4,7 +4,9 @@
  * default stream).  Every function enqueues work and returns immediately: 0 on success, a
  * cudaError_t / CUresult value otherwise.  `status_dev` is a device int the caller zeroes; a
  * kernel whose bounded wait ran out stores a non-zero code there (101 producer, 102 MMA issuer,
- * 103 epilogue, 104 attention, 105 shared-memory alignment) instead of hanging.
+ * 103 epilogue, 104 attention, 105 shared-memory alignment) instead of hanging.  Where a
+ * function takes `status_dev` it is mandatory: NULL is refused with cudaErrorInvalidValue before
+ * anything is launched.
  *
  * dtype: 0 = float16, 1 = bfloat16.  Nothing here allocates device memory.
  */
