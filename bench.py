@@ -357,11 +357,14 @@ def run_kernel(args):
         fn = lambda: ops.attention(q, k, v, cu, work=work, out=out, status=st)  # noqa: E731
         flops = 4.0 * H * float(sum(n * n for n in lens))
         bytes_ = 2.0 * 4 * T * H
-    elif name in ("attention_long", "attention_causal128", "rope_qwen3"):
+    elif name in ("attention_long", "attention_causal128", "attention_d32", "rope_qwen3"):
         # 16 x 2048 tokens, 12 heads x 64, bidirectional / 4 x 4096 tokens, 16 query and 8 key-value
-        # heads x 128, causal, bf16 (the Qwen3 shape) / RoPE + q/k RMSNorm on the latter
+        # heads x 128, causal, bf16 (the Qwen3 shape) / RoPE + q/k RMSNorm on the latter / the ragged
+        # batch with 12 heads x 32 (the all-MiniLM-L6-v2 shape)
         if name == "attention_long":
             lens, nh, nkv, D, causal = [2048] * 16, 12, 12, 64, False
+        elif name == "attention_d32":
+            nh, nkv, D, causal = 12, 12, 32, False
         else:
             lens, nh, nkv, D, causal, dt = [4096] * 4, 16, 8, 128, True, torch.bfloat16
         T = int(sum(lens))
@@ -652,7 +655,7 @@ def main():
                     help="skip the flash_attn + cuBLASLt proxy forward that follows the main arm at N = 1")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone: gemm_qkv | gemm_out | gemm_ffn1 | gemm_ffn2 | attention | "
-                         "attention_long | attention_causal128 | rope_qwen3 | qkv_rope_nomic | qkv_rope_qwen3 | add_layernorm | "
+                         "attention_long | attention_causal128 | attention_d32 | rope_qwen3 | qkv_rope_nomic | qkv_rope_qwen3 | add_layernorm | "
                          "add_layernorm_h1024 | pool_mean")
     ap.add_argument("--config", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg2 is the headline workload (default, any --gpus); the others run on one GPU")
