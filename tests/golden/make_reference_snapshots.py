@@ -7,7 +7,7 @@ Keys are the snapshot file names without `.snap` (`test_flash_bert__mini_batch`,
 `test_flash_*` files are the reference's fp16 CUDA outputs, the others its fp32 CPU outputs.
 tests/reference_cases.py says which model, pooling and sentences each belongs to.
 
-Usage: python tests/golden/make_reference_snapshots.py [path to the reference checkout]
+Usage: python tests/golden/make_reference_snapshots.py <path to a text-embeddings-inference checkout>
 """
 import os
 import sys
@@ -43,7 +43,9 @@ def parse_snap(path):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    ref = sys.argv[1]
     snap_dir = os.path.join(ref, "backends", "candle", "tests", "snapshots")
     out = {}
     for key in reference_cases.all_snapshot_keys():
