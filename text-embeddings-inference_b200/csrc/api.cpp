@@ -624,25 +624,28 @@ int tei_b200_stats(const tei_b200_t* h, double* out, int n) {
 
 int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
-  AllReplicas all(h);
-  for (auto& r : h->replicas) r->set_last_layer_shortcut(on != 0);
-  return TEI_B200_OK;
+  return guarded(nullptr, nullptr, 0, [&]() {
+    AllReplicas all(h);
+    for (auto& r : h->replicas) r->set_last_layer_shortcut(on != 0);
+  });
 }
 
 int tei_b200_set_fused_rope(tei_b200_t* h, int on) {
   if (!h) return TEI_B200_ERR_UNHEALTHY;
-  AllReplicas all(h);
-  for (auto& r : h->replicas) r->set_fused_rope(on < 0 ? -1 : (on != 0 ? 1 : 0));
-  return TEI_B200_OK;
+  return guarded(nullptr, nullptr, 0, [&]() {
+    AllReplicas all(h);
+    for (auto& r : h->replicas) r->set_fused_rope(on < 0 ? -1 : (on != 0 ? 1 : 0));
+  });
 }
 
 int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code) {
   if (!h || replica < 0 || replica >= static_cast<int>(h->replicas.size()) || device_code <= 0) {
     return TEI_B200_ERR_INFERENCE;
   }
-  std::lock_guard<std::mutex> lock(*h->replica_locks[replica]);
-  h->replicas[replica]->report_status_once(device_code);
-  return TEI_B200_OK;
+  return guarded(nullptr, nullptr, 0, [&]() {
+    std::lock_guard<std::mutex> lock(*h->replica_locks[replica]);
+    h->replicas[replica]->report_status_once(device_code);
+  });
 }
 
 int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_ids, const uint32_t* position_ids,
