@@ -189,23 +189,22 @@ __device__ __forceinline__ void finish_and_store(float (&v)[32], const GemmParam
 // residual, then either swizzled staging + TMA store (64 columns per step) or plain per-thread
 // stores.  t_row: TMEM address of the warp's lane quadrant in the accumulator; m0 / n0: first
 // row / column of the tile in the output.
-template <class T, int ACT>
+template <class T, int ACT, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
                                               int m0, int n0, int quad, int lane, const T* bias,
                                               bool bias_vec, bool vec_ok, uint8_t* stage_buf,
-                                              uint32_t& store_count, int n_out, int part = 0,
+                                              uint32_t& store_count, int n_out, Release&& release, int part = 0,
                                               int n_parts = 1) {  // part: this warp's share of the columns
   const int row = m0 + quad * 32 + lane;
   const int m_rows = effective_rows(p);
   if (p.tma_store) {
-    // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.
+    // 64 output columns per step: TMEM -> registers -> swizzled staging tile -> TMA store.  The
+    // steps go two at a time: both are read from the accumulator (and converted) before the first
+    // is staged, and after the warp's last read the accumulator goes back to the MMA thread, so
+    // the staging writes and the stores of a tile no longer hold up the tile after next.
     constexpr int STEPS = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? 2 : 4;
     const int o0 = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? n0 / 2 : n0;
-#pragma unroll 1
-    for (int c = part * (STEPS / n_parts); c < (part + 1) * (STEPS / n_parts); ++c) {
-      const int ocol = o0 + c * 64;
-      if (ocol >= n_out) break;  // uniform across the CTA
-      uint32_t packed[32];
+    auto load_step = [&](int c, uint32_t (&packed)[32]) {
       if constexpr (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) {
         // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
 #pragma unroll
@@ -229,11 +228,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
           }
         }
       } else {
+        // both halves of the step in flight before the one wait
+        uint32_t rr[2][32];
+        ptx::tmem_ld32(t_row + c * 64, rr[0]);
+        ptx::tmem_ld32(t_row + c * 64 + 32, rr[1]);
+        ptx::tmem_ld_wait();
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
-          uint32_t r[32];
-          ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
-          ptx::tmem_ld_wait();
+          const uint32_t (&r)[32] = rr[hlf];
           const int col = n0 + c * 64 + hlf * 32;
           if (bias == nullptr) {
 #pragma unroll
@@ -263,6 +265,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
           }
         }
       }
+    };
+    auto store_step = [&](int c, const uint32_t (&packed)[32]) {
       // The staging buffer used two stores ago must have been read out by its TMA store.
       uint8_t* buf = stage_buf + (store_count & 1) * EPI_BUF_BYTES;
       if (lane == 0) ptx::tma_store_wait_read<1>();
@@ -280,11 +284,29 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
       if (lane == 0) {
         // A box that starts beyond the last row has nothing to write (the tensor map would clip
         // it anyway); the empty group keeps the wait_group accounting uniform.
-        if (m0 + quad * 32 < m_rows) ptx::tma_store_2d(tm_c, buf, ocol, m0 + quad * 32);
+        if (m0 + quad * 32 < m_rows) ptx::tma_store_2d(tm_c, buf, o0 + c * 64, m0 + quad * 32);
         ptx::tma_store_commit();
       }
       ++store_count;
+    };
+    const int c_end = (part + 1) * (STEPS / n_parts);
+    bool released = false;
+#pragma unroll 1
+    for (int c = part * (STEPS / n_parts); c < c_end; c += 2) {
+      if (o0 + c * 64 >= n_out) break;  // uniform across the CTA
+      const bool second = c + 1 < c_end && o0 + (c + 1) * 64 < n_out;
+      uint32_t pk0[32], pk1[32];
+      load_step(c, pk0);
+      if (second) load_step(c + 1, pk1);
+      if (c + 2 >= c_end || o0 + (c + 2) * 64 >= n_out) {  // the warp's last read of this accumulator
+        release();
+        released = true;
+      }
+      store_step(c, pk0);
+      if (second) store_step(c + 1, pk1);
     }
+    if (!released) release();
+    return;
   } else if constexpr (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) {
     // Columns [0,128) of the tile are gate rows, [128,256) the matching up rows.
 #pragma unroll 1
@@ -328,6 +350,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
       if (row < m_rows) finish_and_store<T, ACT>(v, p, row, col, n_valid, vec_ok);
     }
   }
+  release();
 }
 
 template <class T>
@@ -476,11 +499,11 @@ __device__ __forceinline__ void norm_rotate(uint32_t* aw, uint32_t* bw, bool nor
 // qk_norm_rope_vec_kernel on the rounded projection, operation for operation, so both paths give
 // the same bits.  The rounded values stay packed two to a register between the passes; outputs
 // leave through the same staging tiles and TMA stores as the plain path.
-template <class T, int D>
+template <class T, int D, class Release>
 __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
                                                    int m0, int n0, int quad, int lane, const T* bias,
-                                                   uint8_t* stage_buf, uint32_t& store_count, int part,
-                                                   int n_parts) {
+                                                   uint8_t* stage_buf, uint32_t& store_count, Release&& release,
+                                                   int part, int n_parts) {
   constexpr int HALF = D / 2;
   const int row = m0 + quad * 32 + lane;
   const int m_rows = effective_rows(p);
@@ -501,6 +524,9 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
   };
   constexpr int STEPS = 4;  // 64 output columns each
   const int c_begin = part * (STEPS / n_parts), c_end = (part + 1) * (STEPS / n_parts);
+  // The accumulator goes back to the MMA thread after the warp's last read of it: the table
+  // loads, the arithmetic and the stores of a tile then run beside the next tiles' main loops.
+  bool released = false;
   if constexpr (D == 128) {
     // One head = two steps: the first half of the head in one staging tile, the second half in
     // the other.
@@ -515,6 +541,10 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
       uint32_t a0[16], b0[16], a1[16], b1[16];
       rounded_pair<T>(t_row + c * 64, t_row + c * 64 + 64, bias, col0, col0 + 64, p.N, a0, b0);
       rounded_pair<T>(t_row + c * 64 + 32, t_row + c * 64 + 96, bias, col0 + 32, col0 + 96, p.N, a1, b1);
+      if (c + 2 >= c_end || n0 + (c + 2) * 64 >= p.N) {
+        release();
+        released = true;
+      }
       float r = 1.f;
       if (norm) {
         float part_ss[8];
@@ -550,6 +580,10 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
       if (col0 >= p.N) break;  // uniform across the CTA
       uint32_t x0[16], x1[16];
       rounded_pair<T>(t_row + c * 64, t_row + c * 64 + 32, bias, col0, col0 + 32, p.N, x0, x1);
+      if (c + 1 >= c_end || n0 + (c + 1) * 64 >= p.N) {
+        release();
+        released = true;
+      }
       if constexpr (D == 64) {
         // the step is one head: x0 its first half, x1 the second
         if (col0 < rope_end) {
@@ -593,6 +627,7 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
       store(buf, col0);
     }
   }
+  if (!released) release();
 }
 
 template <class T, int ACT, int ROPE_D>
@@ -734,16 +769,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      // Hands the accumulator back to the MMA warp (once per tile and warp, after its last read).
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
+      };
       if constexpr (ROPE_D != 0) {
-        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, 0, 1);
+        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, release, 0, 1);
       } else {
         epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
-                              n_out);
+                              n_out, release);
       }
-      // Hand the accumulator back to the MMA warp.
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
     }
     // Global writes of the TMA stores must have completed before the CTA exits.
     if (p.tma_store && lane == 0) ptx::tma_store_wait<0>();
@@ -921,16 +958,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       }
       ptx::tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      // Hands the accumulator back to the MMA thread of the even CTA (once per tile and warp,
+      // after its last read).
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::smem_u32(&acc_empty[acc]) & ptx::kPeerBitMask);
+      };
       if constexpr (ROPE_D != 0) {
-        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, part, 2);
+        epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, release, part,
+                                      2);
       } else {
         epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
-                              n_out, part, 2);
+                              n_out, release, part, 2);
       }
-      // Hand the accumulator back to the MMA thread of the even CTA.
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive_cluster(ptx::smem_u32(&acc_empty[acc]) & ptx::kPeerBitMask);
     }
     if (p.tma_store && lane == 0) ptx::tma_store_wait<0>();
   }
