@@ -343,15 +343,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t tmem_o0 = tmem_base + S_BUFS * BKV;
   const int group = p.n_heads / p.n_kv_heads;
 
+  // A work item {seq_start, seq_len, q0, first key} is read from global memory once per unit, as
+  // one 16-byte load, and the NEXT unit's item is already on its way while the current one runs:
+  // the issuing threads are the busiest of the CTA and should not wait for a load per step.
+  auto item_at = [&](int w) { return __ldg(reinterpret_cast<const int4*>(p.work) + w / p.n_heads); };
   // One past the last key any row of the query tile can see (causal = win_right 0).
-  auto unit_kv_end = [&](const int* it) {
-    return p.win_right >= 0 ? min(it[1], it[2] + BQ + p.win_right) : it[1];
+  auto unit_kv_end = [&](const int4& it) {
+    return p.win_right >= 0 ? min(it.y, it.z + BQ + p.win_right) : it.y;
   };
-  // Steps of one unit: 64-key tiles from the unit's first key (it[3]; 0 unless a left window
-  // cuts the early keys off) up to the last key any row can see.
-  auto unit_steps = [&](const int* it) { return (unit_kv_end(it) - it[3] + BKV - 1) / BKV; };
-  // Number of keys of step j of a unit that any row can see (CTA-uniform).
-  auto keys_in_tile = [&](const int* it, int j) { return min(BKV, unit_kv_end(it) - it[3] - j * BKV); };
   // The CTA's n-th work unit.  Units are sorted by cost; handing them out in alternating
   // direction (0..G-1, then G-1..0, ...) keeps the sums per CTA close when the costs fall
   // steadily, as they do for causal batches.
@@ -365,20 +364,38 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   struct Cursor {
     int w, j, n_kv;
     uint32_t n;
-    const int* it;
+    int kv_end;   // one past the last key any row of the unit can see
+    int4 it;      // the unit's work item
+    int4 next;    // the item of the CTA's next unit, loaded a unit ahead
+    // Steps of the unit: 64-key tiles from its first key (it.w; 0 unless a left window cuts the
+    // early keys off) up to kv_end.  Keys of step j that any row can see (CTA-uniform):
+    __device__ __forceinline__ int keys_in_tile(int step) const { return min(BKV, kv_end - it.w - step * BKV); }
   };
-  auto load_unit = [&](Cursor& c) {
+  auto enter_unit = [&](Cursor& c) {  // c.it holds the item of unit c.w
     if (c.w < total) {
-      c.it = p.work + (c.w / p.n_heads) * 4;
-      c.n_kv = unit_steps(c.it);
+      c.kv_end = unit_kv_end(c.it);
+      c.n_kv = (c.kv_end - c.it.w + BKV - 1) / BKV;
+      const int w_next = unit_at(c.n + 1);
+      if (w_next < total) c.next = item_at(w_next);
     }
+  };
+  auto start_cursor = [&](Cursor& c) {
+    c.w = static_cast<int>(blockIdx.x);
+    c.j = 0;
+    c.n_kv = 0;
+    c.n = 0u;
+    c.kv_end = 0;
+    c.it = c.next = make_int4(0, 0, 0, 0);
+    if (c.w < total) c.it = item_at(c.w);
+    enter_unit(c);
   };
   auto advance = [&](Cursor& c) {
     if (++c.j == c.n_kv) {
       ++c.n;
       c.w = unit_at(c.n);
       c.j = 0;
-      load_unit(c);
+      c.it = c.next;
+      enter_unit(c);
     }
   };
 
@@ -394,9 +411,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       // K runs one step ahead of V: K of step t (and Q, at the first step of a unit), then V of
       // step t - 1.  K(t) only waits for the S MMA of step t - K_STAGES, V(t) for the P V of
       // step t - V_STAGES, which finishes a whole softmax later.
-      Cursor ck{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cv = ck;
-      load_unit(ck);
-      load_unit(cv);
+      Cursor ck, cv;
+      start_cursor(ck);
+      cv = ck;
       uint32_t gk = 0, gv = 0;
       int k_col = 0, v_col = 0;  // first column of the unit's K / V head (divisions once per unit)
       bool ok = true;
@@ -419,7 +436,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int a = 0; a < D_ATOMS; ++a) {
               ptx::tma_load_2d(smem + L::OFF_Q + qb * L::Q_BYTES + a * (BQ * ROW_BYTES), &tm_q, &bar_q[qb],
-                               head * D + a * ATOM, ck.it[0] + ck.it[2]);
+                               head * D + a * ATOM, ck.it.x + ck.it.z);
             }
           }
           const int st = gk % K_STAGES;
@@ -435,7 +452,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
             ptx::tma_load_2d(smem + L::OFF_K + st * L::KV_BYTES + a * (BKV * ROW_BYTES), &tm_k, &bar_k[st],
-                             k_col + a * ATOM, ck.it[0] + ck.it[3] + ck.j * BKV);
+                             k_col + a * ATOM, ck.it.x + ck.it.w + ck.j * BKV);
           }
           ++gk;
         }
@@ -453,7 +470,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
           for (int a = 0; a < D_ATOMS; ++a) {
             ptx::tma_load_2d(smem + L::OFF_V + st * L::KV_BYTES + a * (BKV * ROW_BYTES), &tm_v, landed,
-                             v_col + a * ATOM, cv.it[0] + cv.it[3] + cv.j * BKV);
+                             v_col + a * ATOM, cv.it.x + cv.it.w + cv.j * BKV);
           }
           ++gv;
         }
@@ -476,9 +493,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint64_t dq = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_Q), 16, 8 * ROW_BYTES, SWZ);
       const uint64_t dk = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_K), 16, 8 * ROW_BYTES, SWZ);
       const uint64_t dv = ptx::make_smem_desc(ptx::smem_u32(smem + L::OFF_V), BKV * ROW_BYTES, 8 * ROW_BYTES, SWZ);
-      Cursor cs{static_cast<int>(blockIdx.x), 0, 0, 0u, nullptr}, cp = cs;
-      load_unit(cs);
-      load_unit(cp);
+      Cursor cs, cp;
+      start_cursor(cs);
+      cp = cs;
       uint32_t gs = 0, g = 0;  // steps whose S / P V has been issued
       uint32_t gvr = 0;        // steps whose V tile is known to have landed (own barrier only)
       uint32_t idle = 0;
@@ -493,7 +510,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                              ptx::mbar_test_wait(&bar_k[gs % K_STAGES], (gs / K_STAGES) & 1);
           if (ready) {
             ptx::tc_fence_after();
-            const int keys = keys_in_tile(cs.it, cs.j);
+            const int keys = cs.keys_in_tile(cs.j);
             // only ceil(keys / 16) * 16 columns are computed
             const uint32_t idesc_s = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BQ, ((keys + 15) / 16) * 16, 0, 0);
             const uint64_t dqs = dq + static_cast<uint64_t>((qb * L::Q_BYTES) >> 4);
@@ -521,7 +538,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (g < gs && (!C::K_EARLY || g < gvr) &&
             ptx::mbar_test_wait(&bar_p[g % S_BUFS], (g / S_BUFS) & 1)) {
           ptx::tc_fence_after();
-          const int k_steps = (keys_in_tile(cp.it, cp.j) + 15) / 16;
+          const int k_steps = (cp.keys_in_tile(cp.j) + 15) / 16;
           const uint32_t tmem_o = tmem_o0 + (cp.n % O_BUFS) * D;
           const uint32_t t_p = tmem_base + (g % S_BUFS) * BKV;  // P lies over the scores of the step
           const uint64_t dvs = dv + static_cast<uint64_t>(((g % V_STAGES) * L::KV_BYTES) >> 4);
@@ -633,11 +650,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       return true;
     };
     for (int w = unit_at(n); w < total && ok; w = unit_at(++n)) {
-      const int* it = p.work + (w / p.n_heads) * 4;
+      const int4 it = item_at(w);
       const int head = w % p.n_heads;
       const uint32_t tmem_o = tmem_o0 + (n % O_BUFS) * D;
-      const int seq_start = it[0], seq_len = it[1], q0 = it[2];
-      const int kv_begin = it[3];
+      const int seq_start = it.x, seq_len = it.y, q0 = it.z;
+      const int kv_begin = it.w;
       const int kv_end = unit_kv_end(it);
       const int n_kv = (kv_end - kv_begin + BKV - 1) / BKV;
       const int qi = q0 + r;                  // position inside the sequence
