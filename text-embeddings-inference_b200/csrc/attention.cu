@@ -61,8 +61,8 @@ struct AttnCfg {
   // K and V tiles live in two rings of their own: a K tile is free again as soon as the S MMA
   // that read it is done, long before the P V of the same step releases the V tile, so with
   // separate rings two stages each already let the next K arrive a whole step early.
-  static constexpr int K_STAGES = (D <= 64) ? 3 : 2;
-  static constexpr int V_STAGES = (D <= 64) ? 3 : 2;
+  static constexpr int K_STAGES = (D <= 64) ? 4 : 2;
+  static constexpr int V_STAGES = (D <= 64) ? 4 : 2;
   // With more stages than score tiles (D = 64) the early release buys nothing: there a K tile is
   // released together with the V tile of its step and both are loaded in the same turn.
   static constexpr bool K_EARLY = K_STAGES <= S_BUFS;
@@ -118,17 +118,6 @@ template <>
 __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
-}
-
-template <class T>
-__device__ __forceinline__ float2 unpack2(uint32_t v);
-template <>
-__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&v));
-}
-template <>
-__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
 }
 
 __device__ __forceinline__ float ex2_fast(float x) {
@@ -214,55 +203,13 @@ __device__ __forceinline__ float write_probs(const uint32_t (&sc)[BKV / 32][32],
   return (s0 + s1) + (s2 + s3);
 }
 
-// Pass 2 without pass 1: probabilities relative to the maximum the row already has, and the
-// largest exponent met on the way (amax, relative to m_use).  As long as amax stays below the
-// rescale threshold the result is final; otherwise the caller raises the maximum and runs the
-// two passes again from the scores it still holds in registers.
-template <class T, bool MASKED, bool ALIBI>
-__device__ __forceinline__ float write_probs_tracking(const uint32_t (&sc)[BKV / 32][32], uint32_t t_p, int lo, int lim,
-                                                      int n_chunks, float sl2, float slope, int rel, float m_use,
-                                                      float& amax) {
-  const unsigned span = static_cast<unsigned>(max(0, lim - lo));
-  const uint64_t sl2_2 = ptx::pack_f32x2(sl2, sl2), neg_m2 = ptx::pack_f32x2(-m_use, -m_use);
-  uint64_t acc[2] = {0ull, 0ull};
-  float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-  for (int c = 0; c < BKV / 32; ++c) {
-    if (c >= n_chunks) break;
-    const uint32_t (&s)[32] = sc[c];
-    uint32_t pk[16];
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const int kk = c * 32 + i;
-      float a0, a1;
-      if (ALIBI) {
-        a0 = __uint_as_float(s[i]) * sl2 - slope * fabsf(static_cast<float>(rel - kk)) - m_use;
-        a1 = __uint_as_float(s[i + 1]) * sl2 - slope * fabsf(static_cast<float>(rel - kk - 1)) - m_use;
-      } else {
-        ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sl2_2, neg_m2), a0, a1);
-      }
-      if (MASKED) {  // 2^-inf = 0: a masked key adds nothing and cannot raise the maximum
-        a0 = static_cast<unsigned>(kk - lo) < span ? a0 : -INFINITY;
-        a1 = static_cast<unsigned>(kk + 1 - lo) < span ? a1 : -INFINITY;
-      }
-      mx[(i >> 1) & 1] = ptx::max3(mx[(i >> 1) & 1], a0, a1);
-      const float e0 = ex2_fast(a0), e1 = ex2_fast(a1);
-      acc[(i >> 1) & 1] = ptx::add_f32x2(acc[(i >> 1) & 1], ptx::pack_f32x2(e0, e1));
-      pk[i / 2] = pack2<T>(e0, e1);
-    }
-    ptx::tmem_st16(t_p + c * 16, pk);
-  }
-  amax = fmaxf(mx[0], mx[1]);
-  float s0, s1, s2, s3;
-  ptx::unpack_f32x2(acc[0], s0, s1);
-  ptx::unpack_f32x2(acc[1], s2, s3);
-  return (s0 + s1) + (s2 + s3);
-}
-
-// The running maximum is only raised when it grows by more than this many powers of two; until
-// then probabilities are taken relative to the stale maximum (they stay below 2^8, far inside
-// fp16 / bf16 range) and the accumulator in TMEM needs no rescaling.
-constexpr float kRescaleThreshold = 8.0f;
+// After a unit's first step the probabilities of a step are first taken relative to the maximum
+// the row already has (one pass, no dependency on a maximum of this step).  The result stands
+// as long as the step's sum stays below this bound: then no probability exceeded it either (far
+// inside fp16 / bf16 range), and the accumulator in TMEM needs no rescaling.  A larger sum (inf
+// and NaN included) means some exponent was above log2(bound / 64) = 2: the row takes the true
+// maximum of the step and its warp redoes the step with the two passes.
+constexpr float kLazySumBound = 256.0f;
 
 
 // ALIBI is a compile-time switch: the softmax code of the models without a positional bias
@@ -717,13 +664,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         } else {
           // Later steps first try the maximum the row already has: one pass, no dependency of
           // the exponentials on a maximum of this step.
-          const float m_old = (m == -INFINITY) ? 0.f : m;
-          float amax;
-          if constexpr (ALIBI) sum = write_probs_tracking<T, true, true>(sc, t_s, lo, lim, n_chunks, p.scale_log2, slope, rel, m_old, amax);
-          else if (tile_full) sum = write_probs_tracking<T, false, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
-          else sum = write_probs_tracking<T, true, false>(sc, t_s, lo, lim, n_chunks, p.scale_log2, 0.f, 0, m_old, amax);
-          const float mx = amax + m_old;  // this step's maximum in the scaled log2 domain
-          const bool grow = mx > m + kRescaleThreshold;
+          sum = probs(m == -INFINITY ? 0.f : m);
+          const bool grow = !(sum <= kLazySumBound);  // also true for inf and NaN
           if (__any_sync(0xffffffffu, grow)) {
             // Raise the maximum of the rows that need it and rescale their partial outputs in
             // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
@@ -734,6 +676,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
               break;
             }
             ptx::tc_fence_after();
+            const float mx = true_max();  // from the scores still in registers; above m + 2 where grow is set
             const float alpha = grow ? ex2_fast(m - mx) : 1.0f;
             if (grow) {
               l *= alpha;
