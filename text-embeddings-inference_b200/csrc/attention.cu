@@ -22,15 +22,14 @@
 //                      and V from shared memory (MN-major operand).
 //   warps 0-3          one query row per thread: the 64 scores of the step are read from TMEM
 //                      into registers once; exp2 against the row's running maximum in one pass
-//                      that also tracks the largest exponent (a row maximum pass first only at
-//                      a unit's first step and when a maximum has to be raised), P written
-//                      back as fp16/bf16
+//                      (a row maximum pass first only at a unit's first step and when a
+//                      maximum has to be raised), P written back as fp16/bf16
 //                      over the row's own scores in TMEM, so P never touches shared memory (the
 //                      kernel is bound by shared-memory bandwidth otherwise: every MMA operand
 //                      read and every TMA write goes through it).  O stays in TMEM across the
-//                      key steps; the running maximum is raised lazily (only when it grows by
-//                      more than 2^8), in which case the rows rescale their partial output in
-//                      TMEM.  A finished unit's rows are read, normalised, transposed through
+//                      key steps; the running maximum is raised lazily (only when a step's sum
+//                      of probabilities against the old maximum exceeds 2^8), in which case
+//                      the rows rescale their partial output in TMEM.  A finished unit's rows are read, normalised, transposed through
 //                      a staging tile in shared memory and stored as whole 128-byte lines.
 // Every mbarrier wait is bounded and reports through *status instead of spinning forever.
 #include "kernels.h"
@@ -50,8 +49,9 @@ constexpr int ATTN_THREADS = 192;
 // of a step (512 of them on the exp2 unit alone), the tensor pipe 320 (D = 64) to 640 (D = 128):
 // what bounds the kernel is how many softmax warps an SM keeps busy, so both head sizes run two
 // CTAs per SM (eight softmax warps, two per scheduler), each with half of the TMEM columns and
-// of the shared memory.  D = 64 (and 32): two score tiles, two output tiles, two Q buffers, three
-// K/V stages.  D = 128: two score tiles, one output tile, one Q buffer and only two K and two V
+// of the shared memory.  D = 64 (and 32): two score tiles, two output tiles, two Q buffers, four
+// K/V stages (a K/V tile takes about 1,750 cycles from the load's issue to the barrier, more
+// than a step: with three stages the ring, not the softmax, set the pace).  D = 128: two score tiles, one output tile, one Q buffer and only two K and two V
 // stages (112 KB per CTA), which is enough because the K ring is released early (see K_EARLY).
 template <int D>
 struct AttnCfg {
@@ -240,8 +240,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   // and, with the early K release, the producer that the K stage is free (K_STAGES == S_BUFS, so
   // stage and score tile share their index); bar_done (P V of a step done) serves the output
   // read-out, the rescale, the V stage and, without the early release, the K stage.  bar_done
-  // is a ring of DONE_RING barriers indexed by the step: nobody waits for a step more than three
-  // steps after its P V can have finished, so a phase is always looked at before it comes round.
+  // is a ring of DONE_RING barriers indexed by the step: the producer, which waits for the step
+  // K_STAGES back before it loads the tiles of the next one, is the last to look at a step, and
+  // no P V can run more than one step beyond what the producer has loaded, so a phase is
+  // always looked at before its barrier comes round (DONE_RING > K_STAGES + 1).
   uint64_t* bar_q = bars;             // [Q_BUFS] Q buffer landed
   uint64_t* bar_qfree = bars + 2;     // [Q_BUFS] last S of the unit that used the Q buffer is done
   uint64_t* bar_k = bars + 4;         // [K_STAGES] K tile landed
@@ -250,6 +252,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* bar_p = bars + 16;        // [S_BUFS] P written over the scores of the step (one arrival per warp)
   uint64_t* bar_done = bars + 20;     // [DONE_RING] the P V of step g is done: slot g % DONE_RING
   constexpr uint32_t DONE_RING = 6;
+  static_assert(DONE_RING > K_STAGES + 1 && DONE_RING > V_STAGES + 1, "done ring");
   static_assert(!C::K_EARLY || K_STAGES == S_BUFS, "the early K release shares bar_s with the score tile");
   auto done_bar = [&](uint32_t step) { return &bar_done[step % DONE_RING]; };
   auto done_parity = [](uint32_t step) { return (step / DONE_RING) & 1u; };
@@ -560,9 +563,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
         __syncwarp();
-        ptx::tc_fence_before();
-        return true;
-      }
+      } else {
 #pragma unroll
       for (int c2 = 0; c2 < D / 64; ++c2) {
 #pragma unroll
@@ -592,6 +593,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
         }
         __syncwarp();
+      }
       }
       ptx::tc_fence_before();
       return true;
