@@ -667,7 +667,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           // Later steps first try the maximum the row already has: one pass, no dependency of
           // the exponentials on a maximum of this step.
           sum = probs(m == -INFINITY ? 0.f : m);
-          const bool grow = !(sum <= kLazySumBound);  // also true for inf and NaN
+          // Also true for inf and NaN.  A row that has not seen a key yet (left window: its keys
+          // start in a later tile) has nothing to be lazy about: it takes the true maximum of
+          // the first tile in which it sees one.
+          const bool grow = !(sum <= kLazySumBound) || (m == -INFINITY && lim > lo);
           if (__any_sync(0xffffffffu, grow)) {
             // Raise the maximum of the rows that need it and rescale their partial outputs in
             // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
