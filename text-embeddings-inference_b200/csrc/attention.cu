@@ -214,7 +214,9 @@ constexpr float kLazySumBound = 256.0f;
 
 // ALIBI is a compile-time switch: the softmax code of the models without a positional bias
 // (all but JinaBERT with ALiBi) then holds two variants of each pass instead of three.
-template <class T, int D, bool ALIBI>
+// LWIN (a left window is set) is one too: only then can a row pass a key tile without seeing a
+// key, and the softmax loop of every other model is spared the test for it.
+template <class T, int D, bool ALIBI, bool LWIN>
 __global__ void __launch_bounds__(ATTN_THREADS, AttnCfg<D>::CTAS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_k,
@@ -666,12 +668,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         } else {
           // Later steps first try the maximum the row already has: one pass, no dependency of
           // the exponentials on a maximum of this step.
-          sum = probs(m == -INFINITY ? 0.f : m);
-          // Also true for inf and NaN.  A row that has not seen a key yet (left window: its keys
-          // start in a later tile) has nothing to be lazy about: it takes the true maximum of
-          // the first tile in which it sees one.
-          const bool grow = !(sum <= kLazySumBound) || (m == -INFINITY && lim > lo);
-          if (__any_sync(0xffffffffu, grow)) {
+          // A row that has not seen a key yet (left window: its keys start in a later tile) has
+          // no maximum to be lazy about: its warp goes straight to the true maxima.  Without a
+          // left window every row sees a key in the unit's first tile.
+          bool unseen = false;
+          if constexpr (LWIN) unseen = __any_sync(0xffffffffu, m == -INFINITY);
+          bool grow = false;
+          if (!unseen) {
+            sum = probs(m);
+            grow = !(sum <= kLazySumBound);  // also true for inf and NaN
+          }
+          if (unseen || __any_sync(0xffffffffu, grow)) {
             // Raise the maximum of the rows that need it and rescale their partial outputs in
             // TMEM (warp-wide tcgen05.ld / st; rows that keep their maximum scale by 1).  Every
             // P V issued so far must be complete; the next one is only issued after this
@@ -682,6 +689,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             ptx::tc_fence_after();
             const float mx = true_max();  // from the scores still in registers; above m + 2 where grow is set
+            // without the lazy pass: raise where the maximum grew by more than 2^8 (always, for a
+            // row that sees its first key)
+            if (unseen) grow = mx > m + 8.0f;
             const float alpha = grow ? ex2_fast(m - mx) : 1.0f;
             if (grow) {
               l *= alpha;
@@ -751,8 +761,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
   }
 }
 
-template <class T, int D, bool ALIBI>
-int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
+template <class T, int D, bool ALIBI, bool LWIN>
+int launch_variant(const AttnArgs& a, cudaStream_t stream) {
   using L = AttnSmem<D>;
   const CUtensorMapDataType dt =
       a.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -769,7 +779,7 @@ int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
   // The opt-in shared-memory size is a per-device function attribute; setting it twice is
   // harmless, so replicas on several threads may race to set it, but not on the flag itself.
   static std::atomic<bool> attr_set[64];
-  auto kern = attention_tcgen05_kernel<T, D, ALIBI>;
+  auto kern = attention_tcgen05_kernel<T, D, ALIBI, LWIN>;
   const int dev = current_device() & 63;
   if (!attr_set[dev].load(std::memory_order_acquire)) {
     cudaError_t e =
@@ -800,7 +810,10 @@ int launch_alibi(const AttnArgs& a, cudaStream_t stream) {
 
 template <class T, int D>
 int launch_typed(const AttnArgs& a, cudaStream_t stream) {
-  return a.alibi_slopes ? launch_alibi<T, D, true>(a, stream) : launch_alibi<T, D, false>(a, stream);
+  if (a.window_left >= 0) {
+    return a.alibi_slopes ? launch_variant<T, D, true, true>(a, stream) : launch_variant<T, D, false, true>(a, stream);
+  }
+  return a.alibi_slopes ? launch_variant<T, D, true, false>(a, stream) : launch_variant<T, D, false, false>(a, stream);
 }
 
 }  // namespace

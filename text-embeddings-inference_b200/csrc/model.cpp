@@ -1283,12 +1283,17 @@ void Replica::stage(const HostBatch& b, bool predict, bool normalize) {
   const uint32_t pos_limit = s.alibi ? 0xffffffffu : static_cast<uint32_t>(s.arch == ARCH_BERT ? s.max_pos : s.rope_table_len);
   const bool use_types = s.arch != ARCH_QWEN3 && s.type_vocab > 0;  // DistilBERT and the decoders have no token types
   if (use_types && !b.token_type_ids) throw TeiError(ERR_INFERENCE, "null token_type_ids");
-  for (size_t t = 0; t < b.n_tokens; ++t) {
-    if (b.input_ids[t] >= static_cast<uint32_t>(s.vocab)) throw TeiError(ERR_INFERENCE, "input id out of the vocabulary");
-    if (b.position_ids[t] >= pos_limit) throw TeiError(ERR_INFERENCE, "position id beyond the position table");
-    if (use_types && b.token_type_ids[t] >= static_cast<uint32_t>(s.type_vocab)) {
-      throw TeiError(ERR_INFERENCE, "token type id out of range");
-    }
+  // Branch-free passes (they vectorise): the largest value of each array is compared once.
+  uint32_t max_id = 0, max_pos = 0, max_type = 0;
+  for (size_t t = 0; t < b.n_tokens; ++t) max_id = std::max(max_id, b.input_ids[t]);
+  for (size_t t = 0; t < b.n_tokens; ++t) max_pos = std::max(max_pos, b.position_ids[t]);
+  if (use_types) {
+    for (size_t t = 0; t < b.n_tokens; ++t) max_type = std::max(max_type, b.token_type_ids[t]);
+  }
+  if (max_id >= static_cast<uint32_t>(s.vocab)) throw TeiError(ERR_INFERENCE, "input id out of the vocabulary");
+  if (max_pos >= pos_limit) throw TeiError(ERR_INFERENCE, "position id beyond the position table");
+  if (use_types && max_type >= static_cast<uint32_t>(s.type_vocab)) {
+    throw TeiError(ERR_INFERENCE, "token type id out of range");
   }
   size_t n_pooled = predict ? 0 : b.n_pooled;
   size_t n_raw = predict ? 0 : b.n_raw;
