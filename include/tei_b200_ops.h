@@ -38,6 +38,13 @@ int tei_b200_op_linear(const void* a_dev, const void* w_dev, const void* bias_de
                        const void* residual_dev, void* out_dev, int M, int N, int K, int lda,
                        int ldo, int ldr, int act, int dtype, int* status_dev, void* stream);
 
+/* Host helper (no GPU needed): the tiling tei_b200_op_linear uses for an M x N problem on a GPU
+ * of `sms` SMs: 0 = pairs of CTAs on 256 x 256 tiles (cta_group::2), 256 / 128 / 64 = one CTA per
+ * 128 x that-many-columns tile.  The narrow tiles (narrow_ok != 0: no gated activation, no
+ * rotary epilogue) are taken when wider ones would leave SMs idle or end in a mostly empty
+ * wave: a 512-token batch, or a shard of a batch split over several GPUs.  -1 on bad arguments. */
+int tei_b200_gemm_tiling(int M, int N, int sms, int narrow_ok);
+
 /* Host helper: lists the (sequence, 128-row query tile) work items of a packed batch as
  * {seq_start, seq_len, q0, 0} int quadruples, most expensive first.  Returns the item count;
  * writes nothing when the count exceeds capacity_items or work_out is NULL.  cu_seqlens is a

@@ -43,6 +43,11 @@ def _close(got, ref, tol):
     (300, 512, 1000, "gelu", True, False, "f16"),     # K tail behind 15 full k-blocks (a Dense module of 1000 inputs)
     (100, 256, 1000, "none", False, False, "bf16"),   # the same on the single-CTA kernel
     (64, 384, 8, "none", True, False, "f16"),         # K smaller than one MMA step
+    (512, 768, 3072, "none", True, False, "f16"),     # 64-column tiles, 48 k-blocks through their 6 stages
+    (512, 3072, 768, "gelu", True, False, "f16"),     # 128-column tiles
+    (8572, 768, 768, "none", True, False, "bf16"),    # 128-column tiles picked for the waves (a shard of a split batch)
+    (512, 200, 768, "none", True, True, "f16"),       # narrow tiles, N tail inside a tile, fused residual (plain stores)
+    (300, 1000, 256, "tanh", False, False, "bf16"),   # narrow tiles, N tail, TMA stores clipped by the tensor map
 ])
 def test_linear(lib, M, N, K, act, bias, res, dtype):
     from tei_b200 import ops

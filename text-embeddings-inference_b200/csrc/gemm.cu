@@ -42,6 +42,18 @@ constexpr int TMEM_COLS = 512;
 constexpr int EPI_BUF_BYTES = 32 * 128;
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// The single-CTA kernel also comes with 128- and 64-column tiles, for problems whose 256-column
+// tiles would leave most SMs idle (a 512-token batch is 4 x 3 tiles on the N = 768 layers) or
+// whose last wave would be mostly empty.  Narrow tiles take more stages: a stage is smaller.
+template <int TN>
+struct SingleCfg {
+  static_assert(TN == 256 || TN == 128 || TN == 64, "tile widths");
+  static constexpr int N_STAGES = TN == 256 ? STAGES : 6;
+  static constexpr int B_TILE_BYTES = TN * BK * 2;
+  static constexpr int STAGE = A_BYTES + B_TILE_BYTES;
+  static constexpr int TMEM = 2 * TN;  // two accumulators; a power of two >= 32
+  static constexpr int SMEM = N_STAGES * STAGE + EPI_BYTES + 1024 + 256;
+};
 
 struct GemmParams {
   const void* bias;
@@ -189,7 +201,7 @@ __device__ __forceinline__ void finish_and_store(float (&v)[32], const GemmParam
 // residual, then either swizzled staging + TMA store (64 columns per step) or plain per-thread
 // stores.  t_row: TMEM address of the warp's lane quadrant in the accumulator; m0 / n0: first
 // row / column of the tile in the output.
-template <class T, int ACT, class Release>
+template <class T, int ACT, int TN = BN, class Release>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtensorMap* tm_c, uint32_t t_row,
                                               int m0, int n0, int quad, int lane, const T* bias,
                                               bool bias_vec, bool vec_ok, uint8_t* stage_buf,
@@ -202,7 +214,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     // steps go two at a time: both are read from the accumulator (and converted) before the first
     // is staged, and after the warp's last read the accumulator goes back to the MMA thread, so
     // the staging writes and the stores of a tile no longer hold up the tile after next.
-    constexpr int STEPS = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? 2 : 4;
+    static_assert(TN == BN || !(ACT == ACT_SWIGLU || ACT == ACT_GEGLU), "gated tiles are 256 wide");
+    constexpr int STEPS = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? 2 : TN / 64;
     const int o0 = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? n0 / 2 : n0;
     auto load_step = [&](int c, uint32_t (&packed)[32]) {
       if constexpr (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) {
@@ -333,7 +346,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     }
   } else {
 #pragma unroll 1
-    for (int c = part * (BN / 32 / n_parts); c < (part + 1) * (BN / 32 / n_parts); ++c) {
+    for (int c = part * (TN / 32 / n_parts); c < (part + 1) * (TN / 32 / n_parts); ++c) {
       const int col = n0 + c * 32;
       if (col >= p.N) break;  // uniform across the CTA
       uint32_t r[32];
@@ -630,10 +643,13 @@ __device__ __forceinline__ void epilogue_tile_rope(const GemmParams& p, const CU
   if (!released) release();
 }
 
-template <class T, int ACT, int ROPE_D>
+template <class T, int ACT, int ROPE_D, int TN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  using Cfg = SingleCfg<TN>;
+  static_assert(TN == BN || ROPE_D == 0, "the rotary epilogue works on 256-column tiles");
+  constexpr int STAGES = Cfg::N_STAGES, STAGE_BYTES = Cfg::STAGE, TMEM_COLS = Cfg::TMEM;  // shadow the 256-column values
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled operand tiles need 1024-byte alignment.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -674,7 +690,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   ptx::grid_dependency_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const int tiles_m = (effective_rows(p) + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_n = (p.N + TN - 1) / TN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + BK - 1) / BK;
 
@@ -686,7 +702,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / tiles_n) * BM;
-        const int n0 = (tile % tiles_n) * BN;
+        const int n0 = (tile % tiles_n) * TN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1)) {
             atomicExch(p.status, DEV_TIMEOUT_PRODUCER);
@@ -708,7 +724,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BM, BN, 0, 0);
+      constexpr uint32_t idesc = ptx::make_idesc_f16(ptx::DTypeFmt<T>::value, BM, TN, 0, 0);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -721,7 +737,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * TN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(&full_bar[stage], phase)) {
             atomicExch(p.status, DEV_TIMEOUT_MMA);
@@ -762,13 +778,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       const int m0 = (tile / tiles_n) * BM;
-      const int n0 = (tile % tiles_n) * BN;
+      const int n0 = (tile % tiles_n) * TN;
       if (!ptx::mbar_wait(&acc_full[acc], acc_phase)) {
         if (lane == 0) atomicExch(p.status, DEV_TIMEOUT_EPILOGUE);
         break;
       }
       ptx::tc_fence_after();
-      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t t_row = tmem_base + acc * TN + (static_cast<uint32_t>(quad * 32) << 16);
       // Hands the accumulator back to the MMA warp (once per tile and warp, after its last read).
       auto release = [&]() {
         ptx::tc_fence_before();
@@ -778,8 +794,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (ROPE_D != 0) {
         epilogue_tile_rope<T, ROPE_D>(p, &tm_c, t_row, m0, n0, quad, lane, bias, stage_buf, store_count, release, 0, 1);
       } else {
-        epilogue_tile<T, ACT>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf, store_count,
-                              n_out, release);
+        epilogue_tile<T, ACT, TN>(p, &tm_c, t_row, m0, n0, quad, lane, bias, bias_vec, vec_ok, stage_buf,
+                                  store_count, n_out, release);
       }
     }
     // Global writes of the TMA stores must have completed before the CTA exits.
@@ -987,14 +1003,58 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   }
 }
 
+// One CTA per 128 x TN tile.
+template <class T, int ACT, int ROPE_D, int TN>
+int launch_single(const GemmArgs& g, const GemmParams& p, const CUtensorMap& tm_a, const CUtensorMap& tm_c,
+                  CUtensorMapDataType dt, cudaStream_t stream) {
+  using Cfg = SingleCfg<TN>;
+  CUtensorMap tm_b;
+  const int rc = make_tmap_2d(&tm_b, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, TN);
+  if (rc) return rc;
+  // The opt-in shared-memory size is a per-device function attribute; setting it twice is
+  // harmless, so replicas on several threads may race to set it, but not on the flag itself.
+  static std::atomic<bool> attr_set[64];
+  const int dev = current_device() & 63;
+  auto kern = gemm_tcgen05_kernel<T, ACT, ROPE_D, TN>;
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev].store(true, std::memory_order_release);
+  }
+  const long long tiles = static_cast<long long>((g.M + BM - 1) / BM) * ((g.N + TN - 1) / TN);
+  const int grid = tiles < num_sms() ? static_cast<int>(tiles) : num_sms();
+  return static_cast<int>(launch_dependent(kern, dim3(grid), dim3(NUM_THREADS), Cfg::SMEM, stream, tm_a, tm_b, tm_c, p));
+}
+
+// Which tiling finishes first, counted in waves of the CTA-pair kernel (one 256 x 256 tile per
+// pair of SMs = one 128 x 256 tile per SM): a wave of 128-column tiles takes half as long, a
+// wave of 64-column tiles a quarter times 1.5 (an MMA of 64 columns runs at two thirds of the
+// rate).  The narrow tiles re-read A more often and get a small handicap, so that large problems,
+// where the wave counts tie, stay with the pairs.  0: CTA pairs, else the single-CTA tile width.
+inline int pick_tiling(int M, int N, int sms, bool narrow_ok) {
+  auto waves = [](long long tiles, int slots) { return static_cast<double>((tiles + slots - 1) / slots); };
+  const long long tm = (M + BM - 1) / BM, tm2 = (M + 2 * BM - 1) / (2 * BM);
+  int best = 256;
+  double best_cost = 1.10 * waves(tm * ((N + 255) / 256), sms);
+  if (M > BM && sms >= 2) {
+    const double c = waves(tm2 * ((N + 255) / 256), sms / 2);
+    if (c <= best_cost) best_cost = c, best = 0;
+  }
+  if (narrow_ok) {
+    const double c128 = 0.5 * 1.05 * waves(tm * ((N + 127) / 128), sms);
+    if (c128 < best_cost) best_cost = c128, best = 128;
+    const double c64 = 0.25 * 1.5 * 1.05 * waves(tm * ((N + 63) / 64), sms);
+    if (c64 < best_cost) best_cost = c64, best = 64;
+  }
+  return best;
+}
+
 template <class T, int ACT, int ROPE_D = 0>
 int launch_typed(const GemmArgs& g, cudaStream_t stream) {
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a;
   const CUtensorMapDataType dt =
       g.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   int rc = make_tmap_2d(&tm_a, g.a, dt, 2, g.K, g.M, static_cast<uint64_t>(g.lda) * 2, BK, BM);
-  if (rc) return rc;
-  rc = make_tmap_2d(&tm_b, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, BN);
   if (rc) return rc;
   // Outputs leave through TMA stores when the output rows are 16-byte aligned and no residual
   // is fused; otherwise the epilogue falls back to per-thread stores.
@@ -1007,10 +1067,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     if (rc) return rc;
   }
 
-  // The opt-in shared-memory size is a per-device function attribute; setting it twice is
-  // harmless, so replicas on several threads may race to set it, but not on the flag itself.
-  static std::atomic<bool> attr_set[64];
-  static std::atomic<bool> attr_set_pair[64];
+  static std::atomic<bool> attr_set_pair[64];  // see launch_single
   const int dev = current_device() & 63;
   GemmParams p;
   p.bias = g.bias;
@@ -1029,7 +1086,11 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     if (!tma_store || g.rope == nullptr) return static_cast<int>(cudaErrorInvalidValue);
     p.rope = *g.rope;
   }
-  if (g.M > BM) {
+  // Narrow tiles exist for the plain epilogues only; a row count known only on the device (the
+  // experts of a mixture) says nothing about the waves.
+  constexpr bool kNarrow = ROPE_D == 0 && !(ACT == ACT_SWIGLU || ACT == ACT_GEGLU);
+  const int tiling = pick_tiling(g.M, g.N, num_sms(), kNarrow && g.m_dev == nullptr);
+  if (tiling == 0) {
     // CTA pairs: 256 x 256 tiles, W loaded in halves of 128 rows.
     CUtensorMap tm_b2;
     rc = make_tmap_2d(&tm_b2, g.w, dt, 2, g.K, g.N, static_cast<uint64_t>(g.K) * 2, BK, 128);
@@ -1046,16 +1107,11 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
     return static_cast<int>(launch_dependent(kern2, dim3(2 * pairs), dim3(P_THREADS), P_SMEM_BYTES, stream, tm_a, tm_b2,
                                              tm_c, p));
   }
-  auto kern = gemm_tcgen05_kernel<T, ACT, ROPE_D>;
-  if (!attr_set[dev].load(std::memory_order_acquire)) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set[dev].store(true, std::memory_order_release);
+  if constexpr (kNarrow) {
+    if (tiling == 128) return launch_single<T, ACT, ROPE_D, 128>(g, p, tm_a, tm_c, dt, stream);
+    if (tiling == 64) return launch_single<T, ACT, ROPE_D, 64>(g, p, tm_a, tm_c, dt, stream);
   }
-  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
-  const int grid = tiles < num_sms() ? tiles : num_sms();
-  return static_cast<int>(launch_dependent(kern, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, stream, tm_a, tm_b, tm_c, p));
+  return launch_single<T, ACT, ROPE_D, 256>(g, p, tm_a, tm_c, dt, stream);
 }
 
 template <class T>
@@ -1090,6 +1146,8 @@ int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
 }  // namespace
 
 int gemm_smem_bytes() { return SMEM_BYTES; }
+
+int gemm_tiling(int M, int N, int sms, bool narrow_ok) { return pick_tiling(M, N, sms, narrow_ok); }
 
 int launch_gemm(const GemmArgs& g, cudaStream_t stream) {
   // The kernels report a wait that ran out through *status: without it there is nowhere to write.

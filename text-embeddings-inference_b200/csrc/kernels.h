@@ -72,6 +72,10 @@ struct GemmArgs {
 int launch_gemm(const GemmArgs& g, cudaStream_t stream);
 // Bytes of dynamic shared memory the GEMM kernel needs (for reporting).
 int gemm_smem_bytes();
+// The tiling launch_gemm picks for an M x N problem on `sms` SMs: 0 = CTA pairs (256 x 256 per
+// pair), else the tile width of the single-CTA kernel (256, 128 or 64 columns; the narrow ones
+// only where `narrow_ok`: plain epilogue, row count known on the host).  Host arithmetic only.
+int gemm_tiling(int M, int N, int sms, bool narrow_ok);
 
 struct AttnArgs {
   const void* q;  // token-major rows; head h of token t at q + t*ld_q + h*head_dim

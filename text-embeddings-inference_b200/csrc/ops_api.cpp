@@ -7,6 +7,11 @@ using namespace tei;
 
 extern "C" {
 
+int tei_b200_gemm_tiling(int M, int N, int sms, int narrow_ok) {
+  if (M <= 0 || N <= 0 || sms <= 0) return -1;
+  return tei::gemm_tiling(M, N, sms, narrow_ok != 0);
+}
+
 int tei_b200_op_linear(const void* a_dev, const void* w_dev, const void* bias_dev,
                        const void* residual_dev, void* out_dev, int M, int N, int K, int lda,
                        int ldo, int ldr, int act, int dtype, int* status_dev, void* stream) {

@@ -41,6 +41,7 @@ _OPS_PROTOTYPES = {
     "tei_b200_op_moe_route_noalloc": (
         c_int, [c_void_p, c_int, c_int, c_int, c_int] + [c_void_p] * 4 + [c_int, c_void_p, c_char_p, c_size_t]),
     "tei_b200_op_bounded_wait_probe": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
+    "tei_b200_gemm_tiling": (c_int, [c_int, c_int, c_int, c_int]),
     "tei_b200_op_moe_gather": (c_int, [c_void_p] * 4 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
     "tei_b200_op_moe_combine": (c_int, [c_void_p] * 6 + [c_int] * 3 + [c_longlong, c_int, c_void_p]),
 }
