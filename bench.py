@@ -498,6 +498,8 @@ def run_config(args):
         G.write_model_dir(model_dir, cfg, seed=seed, store_dtype="float16", **kw)
         (model_dir / ".complete").write_text("ok")
     be = tei_b200.B200Backend(model_dir, dtype, mtype, pool, devices=[0])
+    if args.fused_residual:
+        be.set_fused_residual(True)
     predict = mtype == "classifier"
     tokens = int(batch.cumulative_seq_lengths[-1])
     flops = G.algorithmic_flops(cfg, batch.lengths())
@@ -651,6 +653,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-residual", action="store_true",
+                    help="add the feed-forward residual in the output projection's epilogue instead of the "
+                         "LayerNorm kernel behind it (the default, the reference's form)")
     ap.add_argument("--no-gpu-proxy", action="store_true",
                     help="skip the flash_attn + cuBLASLt proxy forward that follows the main arm at N = 1")
     ap.add_argument("--kernel", default=None,
@@ -705,6 +710,8 @@ def main():
 
     model_dir = ensure_model_dir(local_rank)
     be = tei_b200.B200Backend(model_dir, "float16", "embedding", "mean", devices=[local_rank])
+    if args.fused_residual:
+        be.set_fused_residual(True)
     batch = G.batch_cfg2()
     tokens = int(batch.cumulative_seq_lengths[-1])
     lens = batch.lengths()

@@ -216,6 +216,15 @@ int tei_b200_set_last_layer_shortcut(tei_b200_t* h, int on);
  * with it.  The results are the same bit for bit in every mode. */
 int tei_b200_set_fused_rope(tei_b200_t* h, int on);
 
+/* Post-LN models (BERT family, NomicBERT): the residual of the feed-forward block is added by the
+ * LayerNorm kernel behind the block (on == 0, the default: the form the reference has, bert.rs /
+ * flash_bert.rs: `layer_norm.forward(&hidden_states, Some(&residual))`), or (on != 0) in the
+ * epilogue of the block's output projection, where that projection's reduction is at least 2048
+ * long so that the tile's main loop hides the extra reads; the LayerNorm then reads one tensor.
+ * The sum is rounded to the activation dtype once either way; results agree within that
+ * rounding, not bit for bit.  On the benchmark batch the two forms are equally fast. */
+int tei_b200_set_fused_residual(tei_b200_t* h, int on);
+
 #ifdef __cplusplus
 }
 #endif

@@ -431,3 +431,33 @@ def test_rope_in_the_projection_epilogue_equals_the_separate_kernel(lib, model_d
     assert n_split > n_fused
     assert n_auto == (n_split if key.startswith("qwen3") else n_fused)
     be.close()
+
+
+@pytest.mark.parametrize("family,dtype", [("bert", "float16"), ("bert", "bfloat16"), ("nomic", "float16")])
+def test_residual_in_the_projection_epilogue_matches_the_layernorm_form(lib, tmp_path, family, dtype):
+    """With a feed-forward width of 2048 and more, the post-LN models can add the block's residual
+    in the epilogue of the output projection (bert.rs: `layer_norm.forward(&hidden, Some(&residual))`
+    does it in the LayerNorm, and so does the default here).  Both forms against the oracle; mean and CLS pooling, so that the
+    last layer's first-rows path runs the same form; and the switch really changes the path (the
+    two results differ in the last bits, not more)."""
+    import tei_b200
+    cfg = (G.bert_config(hidden=128, layers=2, heads=2, inter=2048, vocab=1000, max_pos=512) if family == "bert"
+           else G.nomic_config(hidden=128, layers=2, heads=2, inter=2048, vocab=1000, n_positions=512))
+    d = G.write_model_dir(tmp_path / "m", cfg, seed=5)
+    lens = [7, 33, 150, 2, 64, 129, 300]
+    tv = 2
+    for pool in ("mean", "cls"):
+        b = G.random_batch(61, lens, 0, 1000, type_vocab=tv)
+        o = M.build_oracle(d, "embedding", pool)
+        ref, _ = o.embed(b)
+        be = tei_b200.B200Backend(d, dtype, "embedding", pool)
+        got_off = np.stack([be.embed(b)[i].values for i in range(len(lens))])  # the default
+        be.set_fused_residual(True)
+        got_on = np.stack([be.embed(b)[i].values for i in range(len(lens))])
+        again = np.stack([be.embed(b)[i].values for i in range(len(lens))])
+        be.close()
+        floor = COS_MIN if dtype == "float16" else 0.9995
+        assert _cos(got_on, ref.numpy()).min() >= floor and _cos(got_off, ref.numpy()).min() >= floor
+        assert np.array_equal(got_on, again)
+        assert not np.array_equal(got_on, got_off)
+        assert _cos(got_on, got_off).min() >= (0.99999 if dtype == "float16" else 0.9999)

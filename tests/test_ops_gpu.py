@@ -48,6 +48,9 @@ def _close(got, ref, tol):
     (8572, 768, 768, "none", True, False, "bf16"),    # 128-column tiles picked for the waves (a shard of a split batch)
     (512, 200, 768, "none", True, True, "f16"),       # narrow tiles, N tail inside a tile, fused residual (plain stores)
     (300, 1000, 256, "tanh", False, False, "bf16"),   # narrow tiles, N tail, TMA stores clipped by the tensor map
+    (1000, 768, 3072, "none", True, True, "f16"),     # residual added on the TMA-store path (CTA pairs)
+    (515, 768, 2048, "none", False, True, "bf16"),    # the same on 64-column tiles, no bias, M tail
+    (70000, 768, 3072, "none", True, True, "f16"),    # many waves of it
 ])
 def test_linear(lib, M, N, K, act, bias, res, dtype):
     from tei_b200 import ops

@@ -638,6 +638,14 @@ int tei_b200_set_fused_rope(tei_b200_t* h, int on) {
   });
 }
 
+int tei_b200_set_fused_residual(tei_b200_t* h, int on) {
+  if (!h) return TEI_B200_ERR_UNHEALTHY;
+  return guarded(nullptr, nullptr, 0, [&]() {
+    AllReplicas all(h);
+    for (auto& r : h->replicas) r->set_fused_residual(on != 0);
+  });
+}
+
 int tei_b200_selftest_report_timeout(tei_b200_t* h, int replica, int device_code) {
   if (!h || replica < 0 || replica >= static_cast<int>(h->replicas.size()) || device_code <= 0) {
     return TEI_B200_ERR_INFERENCE;

@@ -118,6 +118,24 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Internal epilogue variant, not part of the public activation list: no activation, and the
+// residual rows are added on the TMA-store path (GemmArgs::act == ACT_NONE with a residual whose
+// rows are 16-byte aligned and N a multiple of 64).  Meant for projections with a long K loop,
+// where the tile's main loop hides the epilogue's wait for the residual rows: the post-LN
+// models' feed-forward output, whose LayerNorm then reads one tensor instead of two.
+constexpr int ACT_ADD_RES = 64;
+
+template <class T>
+__device__ __forceinline__ float2 widen2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 widen2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+template <>
+__device__ __forceinline__ float2 widen2<__nv_bfloat16>(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+
 // Gate activation of the gated feed-forwards.
 template <int ACT>
 __device__ __forceinline__ float glu_gate(float x) {
@@ -240,6 +258,35 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
             packed[hlf * 16 + j / 2] = pack2<T>(glu_gate<ACT>(gv0) * uv0, glu_gate<ACT>(gv1) * uv1);
           }
         }
+      } else if constexpr (ACT == ACT_ADD_RES) {
+        // The thread's 64 residual values (one 128-byte line) are requested first and arrive
+        // while the accumulator is read.  Same arithmetic as the plain-store path: accumulator
+        // + bias, + residual, one rounding.
+        uint32_t rq[32];
+        {
+          const T* rp = reinterpret_cast<const T*>(p.residual) + static_cast<size_t>(row) * p.ldr + n0 + c * 64;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint4 v = row < m_rows ? *reinterpret_cast<const uint4*>(rp + q * 8) : make_uint4(0u, 0u, 0u, 0u);
+            rq[q * 4 + 0] = v.x; rq[q * 4 + 1] = v.y; rq[q * 4 + 2] = v.z; rq[q * 4 + 3] = v.w;
+          }
+        }
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t r[32];
+          ptx::tmem_ld32(t_row + c * 64 + hlf * 32, r);
+          ptx::tmem_ld_wait();
+          const int col = n0 + c * 64 + hlf * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            uint64_t x = ptx::pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            if (bias != nullptr) x = ptx::add_f32x2(x, ptx::pack_f32x2(to_f32<T>(bias[col + j]), to_f32<T>(bias[col + j + 1])));
+            const float2 rf = widen2<T>(rq[hlf * 16 + j / 2]);
+            float x0, x1;
+            ptx::unpack_f32x2(ptx::add_f32x2(x, ptx::pack_f32x2(rf.x, rf.y)), x0, x1);
+            packed[hlf * 16 + j / 2] = pack2<T>(x0, x1);
+          }
+        }
       } else {
         // both halves of the step in flight before the one wait
         uint32_t rr[2][32];
@@ -305,13 +352,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, const CUtenso
     const int c_end = (part + 1) * (STEPS / n_parts);
     bool released = false;
 #pragma unroll 1
-    for (int c = part * (STEPS / n_parts); c < c_end; c += 2) {
+    for (int c = part * (STEPS / n_parts); c < c_end; c += (ACT == ACT_ADD_RES ? 1 : 2)) {
       if (o0 + c * 64 >= n_out) break;  // uniform across the CTA
-      const bool second = c + 1 < c_end && o0 + (c + 1) * 64 < n_out;
+      // (the residual variant goes one step at a time: its main loop is long, registers are not)
+      const bool second = ACT != ACT_ADD_RES && c + 1 < c_end && o0 + (c + 1) * 64 < n_out;
       uint32_t pk0[32], pk1[32];
       load_step(c, pk0);
       if (second) load_step(c + 1, pk1);
-      if (c + 2 >= c_end || o0 + (c + 2) * 64 >= n_out) {  // the warp's last read of this accumulator
+      constexpr int kStride = ACT == ACT_ADD_RES ? 1 : 2;
+      if (c + kStride >= c_end || o0 + (c + kStride) * 64 >= n_out) {  // the warp's last read of this accumulator
         release();
         released = true;
       }
@@ -1059,7 +1108,7 @@ int launch_typed(const GemmArgs& g, cudaStream_t stream) {
   // Outputs leave through TMA stores when the output rows are 16-byte aligned and no residual
   // is fused; otherwise the epilogue falls back to per-thread stores.
   const int n_out = (ACT == ACT_SWIGLU || ACT == ACT_GEGLU) ? g.N / 2 : g.N;
-  const bool tma_store = g.residual == nullptr && g.ldo % 8 == 0 &&
+  const bool tma_store = (g.residual == nullptr || ACT == ACT_ADD_RES) && g.ldo % 8 == 0 &&
                          (reinterpret_cast<uintptr_t>(g.out) & 15) == 0;
   CUtensorMap tm_c = tm_a;  // placeholder when unused (never dereferenced by the kernel)
   if (tma_store) {
@@ -1130,6 +1179,10 @@ int launch_by_act(const GemmArgs& g, cudaStream_t stream) {
       case 64: return launch_typed<T, ACT_NONE, 64>(g, stream);
       default: return launch_typed<T, ACT_NONE, 128>(g, stream);
     }
+  }
+  if (g.act == ACT_NONE && g.residual != nullptr && g.N % 64 == 0 && g.ldr % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 && (g.bias == nullptr || g.N % 2 == 0)) {
+    return launch_typed<T, ACT_ADD_RES>(g, stream);
   }
   switch (g.act) {
     case ACT_NONE: return launch_typed<T, ACT_NONE>(g, stream);

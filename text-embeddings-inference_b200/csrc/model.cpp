@@ -1453,6 +1453,11 @@ GemmArgs gemm_args(const void* a, const void* w, const void* bias, void* out, in
   g.act = act; g.dtype = dtype; g.status = status;
   return g;
 }
+// The feed-forward output projection of the post-LN models: with a long K loop (the tile's main
+// loop then hides the epilogue's wait for the residual rows) the residual is added in the GEMM
+// and the LayerNorm behind it reads one tensor instead of two.  The model runs the same form on
+// every path (all rows or the last layer's first rows), so both keep giving the same bits.
+bool residual_fits_epilogue(int N, int K) { return K >= 2048 && N % 64 == 0; }
 }  // namespace
 
 // The fused q/k/v projection of the rotary models.  q/k RMSNorm and RoPE run in the epilogue of
@@ -1521,9 +1526,12 @@ void Replica::forward_bert() {
       } else {
         LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
       }
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
+      GemmArgs g2 = gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status);
+      const bool res_in_gemm = fused_residual_ && residual_fits_epilogue(H, I);
+      if (res_in_gemm) g2.residual = x1_c, g2.ldr = H;
+      LAUNCH(KC_GEMM, launch_gemm(g2, stream_), "output projection");
       NormArgs n2 = n1;
-      n2.x = tmp_c; n2.residual = x1_c; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = out_c;
+      n2.x = tmp_c; n2.residual = res_in_gemm ? nullptr : x1_c; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = out_c;
       LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "output LayerNorm");
       LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H * 2, 1, 0, stream_), "first rows back in place");
       break;
@@ -1564,9 +1572,12 @@ void Replica::forward_bert() {
     } else {
       LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "intermediate projection");
     }
-    LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "output projection");
+    GemmArgs g2 = gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status);
+    const bool res_in_gemm = fused_residual_ && residual_fits_epilogue(H, I);
+    if (res_in_gemm) g2.residual = x1_, g2.ldr = H;
+    LAUNCH(KC_GEMM, launch_gemm(g2, stream_), "output projection");
     NormArgs n2 = n1;
-    n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
+    n2.x = tmp_; n2.residual = res_in_gemm ? nullptr : x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
     LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "output LayerNorm");
   }
 }
@@ -1621,9 +1632,12 @@ void Replica::forward_nomic() {
       } else {
         LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_c, L.w1, L.b1, ffn_, B, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
       }
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
+      GemmArgs g2 = gemm_args(ffn_, L.w2, L.b2, tmp_c, B, H, I, I, H, ACT_NONE, s.dtype, status);
+      const bool res_in_gemm = fused_residual_ && residual_fits_epilogue(H, I);
+      if (res_in_gemm) g2.residual = x1_c, g2.ldr = H;
+      LAUNCH(KC_GEMM, launch_gemm(g2, stream_), "fc2");
       NormArgs m2 = m1;
-      m2.x = tmp_c; m2.residual = x1_c; m2.gamma = L.ln2_g; m2.beta = L.ln2_b; m2.out = out_c;
+      m2.x = tmp_c; m2.residual = res_in_gemm ? nullptr : x1_c; m2.gamma = L.ln2_g; m2.beta = L.ln2_b; m2.out = out_c;
       LAUNCH(KC_NORM, launch_add_norm(m2, stream_), "norm2");
       LAUNCH(KC_POOL, launch_first_rows(out_c, x_, d_cu_, B, H * 2, 1, 0, stream_), "first rows back in place");
       break;
@@ -1634,6 +1648,7 @@ void Replica::forward_nomic() {
     n1.x = tmp_; n1.residual = x_; n1.gamma = L.ln1_g; n1.beta = L.ln1_b; n1.out = x1_; n1.sum_out = nullptr;
     n1.T = T; n1.H = H; n1.eps = s.eps; n1.rms = 0; n1.dtype = s.dtype;
     LAUNCH(KC_NORM, launch_add_norm(n1, stream_), "norm1");
+    bool res_in_gemm = false;  // the experts' outputs are combined first: their residual stays with the LayerNorm
     if (L.moe_router) {
       // NomicMoELayer::forward (nomic.rs:384-393): router logits -> fp32 softmax -> top-k; every
       // expert runs act(x w1_e^T) w2_e on the tokens routed to it; the outputs are summed with
@@ -1665,10 +1680,13 @@ void Replica::forward_nomic() {
       } else {
         LAUNCH(KC_GEMM, launch_gemm(gemm_args(x1_, L.w1, L.b1, ffn_, T, I, H, H, I, s.act, s.dtype, status), stream_), "fc1");
       }
-      LAUNCH(KC_GEMM, launch_gemm(gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status), stream_), "fc2");
+      GemmArgs g2 = gemm_args(ffn_, L.w2, L.b2, tmp_, T, H, I, I, H, ACT_NONE, s.dtype, status);
+      res_in_gemm = fused_residual_ && residual_fits_epilogue(H, I);
+      if (res_in_gemm) g2.residual = x1_, g2.ldr = H;
+      LAUNCH(KC_GEMM, launch_gemm(g2, stream_), "fc2");
     }
     NormArgs n2 = n1;
-    n2.x = tmp_; n2.residual = x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
+    n2.x = tmp_; n2.residual = res_in_gemm ? nullptr : x1_; n2.gamma = L.ln2_g; n2.beta = L.ln2_b; n2.out = x_;
     LAUNCH(KC_NORM, launch_add_norm(n2, stream_), "norm2");
   }
 }

@@ -93,6 +93,7 @@ _BACKEND_PROTOTYPES = {
     "tei_b200_stats": (c_int, [c_void_p, POINTER(c_double), c_int]),
     "tei_b200_set_last_layer_shortcut": (c_int, [c_void_p, c_int]),
     "tei_b200_set_fused_rope": (c_int, [c_void_p, c_int]),
+    "tei_b200_set_fused_residual": (c_int, [c_void_p, c_int]),
     "tei_b200_selftest_report_timeout": (c_int, [c_void_p, c_int, c_int]),
     "tei_b200_split_echo": (
         c_int,

@@ -248,6 +248,11 @@ class B200Backend:
         their own behind it; None: whichever is faster for the model (the default)."""
         self._lib.tei_b200_set_fused_rope(self._h, -1 if on is None else int(bool(on)))
 
+    def set_fused_residual(self, on: bool) -> None:
+        """On: the feed-forward residual of the post-LN models is added in the output projection's
+        epilogue; off (the default): by the LayerNorm kernel behind it, as in the reference."""
+        self._lib.tei_b200_set_fused_residual(self._h, int(bool(on)))
+
     def selftest_report_timeout(self, replica: int = 0, device_code: int = 104) -> None:
         """The next forward on `replica` reports `device_code` through the status word, like a
         kernel whose bounded wait ran out (self-test of the TIMEOUT path; nothing hangs)."""
