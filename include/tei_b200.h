@@ -171,6 +171,15 @@ int tei_b200_kernel_times(const tei_b200_t* h, double* ms_out, double* launches_
  * number of values written (at most n). */
 int tei_b200_stats(const tei_b200_t* h, double* out, int n);
 
+/* Host-only helpers, no GPU needed.  The compute capability the library is built for, in the
+ * reference's notation (major * 10 + minor: 100), and the reference's rule for which device a
+ * build may run on (backends/candle/src/compute_cap.rs:8-12,27-40).  `create` applies the rule
+ * to every device it is given and refuses with a `Start` error worded like
+ * backends/candle/src/lib.rs:240-248 ("Runtime compute cap .. is not compatible with compile time
+ * compute cap ..") where the reference's CUDA build refuses too. */
+int tei_b200_compile_compute_cap(void);
+int tei_b200_compute_cap_matching(int runtime_cap, int compile_cap);
+
 /* Host-only helper, no GPU needed: the replica a sequence of a packed batch is sent to when a
  * handle has n_shards devices.  Cost of a sequence of length L: linear_cost * L +
  * quadratic_cost * L * L, balanced longest-first.  shard_of_seq has n_seqs entries. */

@@ -709,6 +709,12 @@ int tei_b200_split_echo(const uint32_t* input_ids, const uint32_t* token_type_id
   }
 }
 
+int tei_b200_compile_compute_cap(void) { return tei::kCompileComputeCap; }
+
+int tei_b200_compute_cap_matching(int runtime_cap, int compile_cap) {
+  return tei::compute_cap_matching(runtime_cap, compile_cap) ? 1 : 0;
+}
+
 int tei_b200_plan_shards(const uint32_t* cumulative_seq_lengths, size_t n_seqs, int n_shards,
                          double linear_cost, double quadratic_cost, int* shard_of_seq) {
   if (!cumulative_seq_lengths || !shard_of_seq || n_shards <= 0) return TEI_B200_ERR_INFERENCE;

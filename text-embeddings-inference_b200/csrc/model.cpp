@@ -344,14 +344,36 @@ ModelSpec parse_model_spec(const Json& c, int model_type_flag, int pool, int dty
   return s;
 }
 
+// A build runs on its own architecture and on the later ones of its family:
+// Turing 75 on 75; Ampere 80 on 80..89; 86 on 86..89; Ada 89 on 89; Hopper 90 on 90; Blackwell
+// 100 on 100; 120 on 120..121; 121 on 121 (compute_cap.rs:27-40).
+bool compute_cap_matching(int runtime_cap, int compile_cap) {
+  struct Range { int compile, lo, hi; };
+  static const Range kRanges[] = {{75, 75, 75}, {80, 80, 89}, {86, 86, 89}, {89, 89, 89},
+                                  {90, 90, 90}, {100, 100, 100}, {120, 120, 121}, {121, 121, 121}};
+  // builds between two listed Ampere targets (81..85) run where the 86 build would, as the
+  // reference's second arm says: runtime 86..89 with compile 80..=86
+  if (compile_cap > 80 && compile_cap < 86) return runtime_cap >= 86 && runtime_cap <= 89;
+  for (const Range& r : kRanges) {
+    if (r.compile == compile_cap) return runtime_cap >= r.lo && runtime_cap <= r.hi;
+  }
+  return false;
+}
+
 // ------------------------------------------------------------------------------ Replica
 Replica::Replica(int device, const ModelSpec& spec, const SafeTensors& st)
     : device_(device), spec_(spec) {
   cudaError_t e = cudaSetDevice(device_);
   if (e != cudaSuccess) throw TeiError(ERR_START, std::string("cudaSetDevice: ") + cudaGetErrorString(e));
-  int major = 0;
+  int major = 0, minor = 0;
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device_);
-  if (major != 10) throw TeiError(ERR_START, "this backend needs an sm_100 (B200) device");
+  cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device_);
+  const int runtime_cap = major * 10 + minor;
+  if (!compute_cap_matching(runtime_cap, kCompileComputeCap)) {  // the refusal of lib.rs:240-248
+    throw TeiError(ERR_START, "Runtime compute cap " + std::to_string(runtime_cap) +
+                                  " is not compatible with compile time compute cap " +
+                                  std::to_string(kCompileComputeCap) + " (this backend needs an sm_100 device)");
+  }
   TEI_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
   TEI_CUDA(cudaEventCreate(&ev_start_));
   TEI_CUDA(cudaEventCreate(&ev_stop_));

@@ -19,6 +19,14 @@
 
 namespace tei {
 
+// The compute capability this library is built for (sm_100a), in the reference's notation
+// (major * 10 + minor; backends/candle/src/compute_cap.rs:8-12).
+constexpr int kCompileComputeCap = 100;
+// Whether a binary built for `compile_cap` may run on a device of `runtime_cap`: the rule of
+// backends/candle/src/compute_cap.rs:27-40, which `create` applies like lib.rs:240-248 does.
+bool compute_cap_matching(int runtime_cap, int compile_cap);
+
+
 struct RopeArgs;
 
 // Error kinds that map onto the reference's BackendError (backends/core/src/lib.rs:84-95).

@@ -101,6 +101,8 @@ _BACKEND_PROTOTYPES = {
          POINTER(c_uint32), c_size_t, POINTER(c_uint32), c_size_t, c_int, c_int, c_double, c_double, c_int,
          POINTER(c_float), POINTER(c_float), POINTER(c_float), POINTER(c_int)],
     ),
+    "tei_b200_compile_compute_cap": (c_int, []),
+    "tei_b200_compute_cap_matching": (c_int, [c_int, c_int]),
     "tei_b200_plan_shards": (
         c_int,
         [POINTER(c_uint32), c_size_t, c_int, c_double, c_double, POINTER(c_int)],
