@@ -76,23 +76,22 @@ def test_plan_shards_balances_and_is_deterministic(lib):
 
 
 def test_gemm_tiling_follows_the_waves(lib):
-    """Host arithmetic of the GEMM launch: CTA pairs for large problems, narrow single-CTA tiles
-    where wide ones would leave SMs idle or end in a mostly empty wave."""
+    """Host arithmetic of the GEMM launch: CTA pairs wherever they fill the GPU, narrow
+    single-CTA tiles only where the wide ones would leave most SMs without a tile (a wave of
+    narrow tiles is hardly shorter than a wave of pairs: the main loop waits for its loads)."""
     t = lib.tei_b200_gemm_tiling
     sms = 148
-    # the headline batch (68,576 tokens, BERT-base): pairs on all four shapes
-    for n in (2304, 768, 3072):
-        assert t(68576, n, sms, 1) == 0
+    # the benchmark batches and their shards: pairs on every shape
+    for m in (68576, 34288, 16384, 8572, 4096):
+        for n in (2304, 768, 3072):
+            assert t(m, n, sms, 1) == 0, (m, n)
     # one 512-token sequence: 2 x 3 pair tiles would use 12 of 148 SMs
     assert t(512, 768, sms, 1) == 64
     assert t(512, 2304, sms, 1) == 64
     assert t(512, 3072, sms, 1) == 128      # 192 tiles of 64 columns would need a second wave
-    # a shard of the headline batch split over eight GPUs: 102 pair tiles = 1.4 waves of 74 pairs
-    assert t(8572, 768, sms, 1) == 128
-    assert t(8572, 2304, sms, 1) == 128     # 306 pair tiles = 4.1 waves: the fifth would be almost empty
-    # 32 x 512 tokens: the waves of the pairs are full enough
-    for n in (2304, 768, 3072):
-        assert t(16384, n, sms, 1) == 0
+    # 2,048 tokens: the pairs already fill one wave on the wide layers, not on the 768-column ones
+    assert t(2048, 2304, sms, 1) == 0 and t(2048, 3072, sms, 1) == 0
+    assert t(2048, 768, sms, 1) == 128
     # gated / rotary epilogues and device-side row counts have the 256-column tiles only
     assert t(512, 768, sms, 0) == 0
     assert t(100, 768, sms, 0) == 256       # at most 128 rows: no pair

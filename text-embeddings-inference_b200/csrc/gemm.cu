@@ -48,7 +48,8 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment s
 template <int TN>
 struct SingleCfg {
   static_assert(TN == 256 || TN == 128 || TN == 64, "tile widths");
-  static constexpr int N_STAGES = TN == 256 ? STAGES : 6;
+  // (a stage is in flight for about 1,750 cycles; the MMAs of a 64-column k-block take 200)
+  static constexpr int N_STAGES = TN == 256 ? STAGES : (TN == 128 ? 6 : 8);
   static constexpr int B_TILE_BYTES = TN * BK * 2;
   static constexpr int STAGE = A_BYTES + B_TILE_BYTES;
   static constexpr int TMEM = 2 * TN;  // two accumulators; a power of two >= 32
@@ -1076,23 +1077,26 @@ int launch_single(const GemmArgs& g, const GemmParams& p, const CUtensorMap& tm_
 }
 
 // Which tiling finishes first, counted in waves of the CTA-pair kernel (one 256 x 256 tile per
-// pair of SMs = one 128 x 256 tile per SM): a wave of 128-column tiles takes half as long, a
-// wave of 64-column tiles a quarter times 1.5 (an MMA of 64 columns runs at two thirds of the
-// rate).  The narrow tiles re-read A more often and get a small handicap, so that large problems,
-// where the wave counts tie, stay with the pairs.  0: CTA pairs, else the single-CTA tile width.
+// pair of SMs = one 128 x 256 tile per SM).  A narrow tile does a half or a quarter of the
+// arithmetic but its wave is hardly shorter: every k-block still waits for a 16 KB A tile and a
+// W tile from L2, and the main loop of these kernels is bound by those loads, not by the MMAs
+// (measured at 8,572 and 34,288 rows: a wave of 128-column tiles takes 0.8 to 0.9 of a wave of
+// pairs, a wave of 64-column tiles about 0.8).  So the narrow tiles only pay where the wide ones
+// would leave most SMs without a tile: batches of up to about two thousand tokens.
+// 0: CTA pairs, else the single-CTA tile width.
 inline int pick_tiling(int M, int N, int sms, bool narrow_ok) {
   auto waves = [](long long tiles, int slots) { return static_cast<double>((tiles + slots - 1) / slots); };
   const long long tm = (M + BM - 1) / BM, tm2 = (M + 2 * BM - 1) / (2 * BM);
   int best = 256;
-  double best_cost = 1.10 * waves(tm * ((N + 255) / 256), sms);
+  double best_cost = 1.25 * waves(tm * ((N + 255) / 256), sms);
   if (M > BM && sms >= 2) {
     const double c = waves(tm2 * ((N + 255) / 256), sms / 2);
     if (c <= best_cost) best_cost = c, best = 0;
   }
   if (narrow_ok) {
-    const double c128 = 0.5 * 1.05 * waves(tm * ((N + 127) / 128), sms);
+    const double c128 = 0.88 * waves(tm * ((N + 127) / 128), sms);
     if (c128 < best_cost) best_cost = c128, best = 128;
-    const double c64 = 0.25 * 1.5 * 1.05 * waves(tm * ((N + 63) / 64), sms);
+    const double c64 = 0.80 * waves(tm * ((N + 63) / 64), sms);
     if (c64 < best_cost) best_cost = c64, best = 64;
   }
   return best;
