@@ -790,6 +790,16 @@ def main():
     if ag_ms > 0:
         ag = (gemm_flops_per_step + attn_flops_per_step) / (ag_ms / 1e3) / 1e12
         roofline["attention_plus_gemm"] = {"tflops": ag, "frac": ag / peak_tf, "frac_burst": ag / peak_burst}
+    # Attention at head_dim 64 is bounded by the exp2 unit before the tensor pipe: one ex2 per
+    # score, 16 per clock and SM (4 per scheduler), against 4 x head_dim FLOP per score.
+    if attn_ms_per_step > 0 and clocks.get("sm_mhz"):
+        n_sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
+        head_dim = H // cfg["num_attention_heads"]
+        exp_peak = 16.0 * n_sms * clocks["sm_mhz"] * 1e6 * 4.0 * head_dim / 1e12
+        roofline["attention_exp2_bound"] = {
+            "tflops": roofline["attention_tflops"], "peak_tflops_at_sampled_clock": exp_peak,
+            "frac": roofline["attention_tflops"] / exp_peak,
+            "what": "16 ex2 per clock and SM x 4*head_dim FLOP per score, at the sampled median SM clock"}
     # The step runs under the power cap at whatever clock the box settles at; time x clock compares
     # runs at different clocks (time at the maximum clock = time x sampled median / maximum).
     if clocks.get("sm_mhz") and clocks.get("sm_max_mhz"):
