@@ -41,8 +41,9 @@ int tei_b200_op_linear(const void* a_dev, const void* w_dev, const void* bias_de
 /* Host helper (no GPU needed): the tiling tei_b200_op_linear uses for an M x N problem on a GPU
  * of `sms` SMs: 0 = pairs of CTAs on 256 x 256 tiles (cta_group::2), 256 / 128 / 64 = one CTA per
  * 128 x that-many-columns tile.  The narrow tiles (narrow_ok != 0: no gated activation, no
- * rotary epilogue) are taken when wider ones would leave SMs idle or end in a mostly empty
- * wave: a 512-token batch, or a shard of a batch split over several GPUs.  -1 on bad arguments. */
+ * rotary epilogue) are taken where the wide ones would leave most SMs without a tile: batches
+ * of up to about two thousand tokens (a wave of narrow tiles is hardly shorter than a wave of
+ * pairs, so larger batches stay with the pairs).  -1 on bad arguments. */
 int tei_b200_gemm_tiling(int M, int N, int sms, int narrow_ok);
 
 /* Host helper: lists the (sequence, 128-row query tile) work items of a packed batch as

@@ -43,8 +43,8 @@ constexpr int EPI_BUF_BYTES = 32 * 128;
 constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 // The single-CTA kernel also comes with 128- and 64-column tiles, for problems whose 256-column
-// tiles would leave most SMs idle (a 512-token batch is 4 x 3 tiles on the N = 768 layers) or
-// whose last wave would be mostly empty.  Narrow tiles take more stages: a stage is smaller.
+// tiles would leave most SMs idle (a 512-token batch is 4 x 3 tiles on the N = 768 layers).
+// Narrow tiles take more stages: a stage is smaller.
 template <int TN>
 struct SingleCfg {
   static_assert(TN == 256 || TN == 128 || TN == 64, "tile widths");
