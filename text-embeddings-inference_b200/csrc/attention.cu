@@ -29,8 +29,11 @@
 //                      read and every TMA write goes through it).  O stays in TMEM across the
 //                      key steps; the running maximum is raised lazily (only when a step's sum
 //                      of probabilities against the old maximum exceeds 2^8), in which case
-//                      the rows rescale their partial output in TMEM.  A finished unit's rows are read, normalised, transposed through
-//                      a staging tile in shared memory and stored as whole 128-byte lines.
+//                      the rows rescale their partial output in TMEM.  A finished unit's rows
+//                      are read, normalised and staged in shared memory (128-byte swizzle,
+//                      conflict-free both ways); a warp whose 32 rows all belong to
+//                      the sequence hands them to one TMA store, a ragged one writes them back
+//                      itself as whole 128-byte lines.
 // Every mbarrier wait is bounded and reports through *status instead of spinning forever.
 #include "kernels.h"
 #include "ptx.cuh"
@@ -220,7 +223,8 @@ template <class T, int D, bool ALIBI, bool LWIN>
 __global__ void __launch_bounds__(ATTN_THREADS, AttnCfg<D>::CTAS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_k,
-                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                         const AttnParams p) {
   using L = AttnSmem<D>;
   constexpr int D_ATOMS = L::D_ATOMS;  // swizzle atoms per head
   constexpr int ATOM = L::ATOM, ROW_BYTES = L::ROW_BYTES;
@@ -533,7 +537,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
     // them.  g_last: the unit's last step (its P V must be complete).  Each thread holds one
     // row, but a store instruction should cover whole 128-byte lines: the rows are transposed
     // through this warp's own 4 KB slice of the staging tile, 64 columns at a time, and
-    // written back with 8 lanes per row.  warp_dst: row 0 of the warp; rows_valid: how many of
+    // written back with 8 lanes per row, or, when all 32 rows belong to the sequence, by one TMA
+    // store of the slice (the tensor map knows nothing of sequence ends, so a ragged warp cannot
+    // use it).  warp_dst: row 0 of the warp; rows_valid: how many of
     // the 32 rows belong to the sequence.
     auto flush = [&](uint32_t g_last, uint32_t t_o, float inv, T* warp_dst, int rows_valid) -> bool {
       if (!ptx::mbar_wait(done_bar(g_last), done_parity(g_last))) return false;
@@ -566,8 +572,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         __syncwarp();
       } else {
+      // A warp whose 32 rows all belong to the sequence hands its staged rows to one TMA store.
+      const bool use_tma = rows_valid == 32;
+      const size_t off = static_cast<size_t>(warp_dst - reinterpret_cast<T*>(p.out));
+      const int row0 = static_cast<int>(off / p.ld_o), col0 = static_cast<int>(off % p.ld_o);
 #pragma unroll
       for (int c2 = 0; c2 < D / 64; ++c2) {
+        // the staging slice may still be read by the store of the piece (or unit) before
+        if (lane == 0) ptx::tma_store_wait_read<0>();
+        __syncwarp();
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t t[32];
@@ -584,6 +597,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
             *reinterpret_cast<uint4*>(stage + lane * 128 + (((h * 4 + q8) ^ (lane & 7)) * 16)) = v;
           }
         }
+        if (use_tma) {
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d(&tm_o, stage, col0 + c2 * 64, row0);
+            ptx::tma_store_commit();
+          }
+        } else {
         __syncwarp();
         const int sub = lane >> 3, ch = lane & 7;
 #pragma unroll
@@ -593,6 +614,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (row < rows_valid) {
             *reinterpret_cast<uint4*>(warp_dst + static_cast<size_t>(row) * p.ld_o + c2 * 64 + ch * 8) = v;
           }
+        }
         }
         __syncwarp();
       }
@@ -750,6 +772,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
     }
     if (ok && pend) ok = flush(pend_g, pend_o, pend_inv, pend_dst, pend_rows);
+    if (lane == 0) ptx::tma_store_wait<0>();  // the stores' global writes before the CTA exits
     if (!ok && lane == 0) atomicExch(p.status, DEV_TIMEOUT_ATTN);
   }
 
@@ -766,7 +789,7 @@ int launch_variant(const AttnArgs& a, cudaStream_t stream) {
   using L = AttnSmem<D>;
   const CUtensorMapDataType dt =
       a.dtype == DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = make_tmap_2d(&tm_q, a.q, dt, 2, static_cast<uint64_t>(a.n_heads) * D, a.total_tokens,
                         static_cast<uint64_t>(a.ld_q) * 2, L::ATOM, BQ);
   if (rc) return rc;
@@ -775,6 +798,10 @@ int launch_variant(const AttnArgs& a, cudaStream_t stream) {
   if (rc) return rc;
   rc = make_tmap_2d(&tm_v, a.v, dt, 2, static_cast<uint64_t>(a.n_kv_heads) * D, a.total_tokens,
                     static_cast<uint64_t>(a.ld_v) * 2, L::ATOM, BKV);
+  if (rc) return rc;
+  // output rows: boxes of 32 rows x 64 columns (the D = 32 variant stores by hand and never uses it)
+  rc = make_tmap_2d(&tm_o, a.out, dt, 2, static_cast<uint64_t>(a.n_heads) * D, a.total_tokens,
+                    static_cast<uint64_t>(a.ld_o) * 2, 64 <= D ? 64 : D, 32);
   if (rc) return rc;
   // The opt-in shared-memory size is a per-device function attribute; setting it twice is
   // harmless, so replicas on several threads may race to set it, but not on the flag itself.
@@ -805,7 +832,7 @@ int launch_variant(const AttnArgs& a, cudaStream_t stream) {
   const long long resident = static_cast<long long>(num_sms()) * AttnCfg<D>::CTAS_PER_SM;
   const long long grid = total < resident ? total : resident;
   return static_cast<int>(launch_dependent(kern, dim3(static_cast<unsigned>(grid)), dim3(ATTN_THREADS), L::TOTAL, stream,
-                                           tm_q, tm_k, tm_v, p));
+                                           tm_q, tm_k, tm_v, tm_o, p));
 }
 
 template <class T, int D>
