@@ -572,52 +572,52 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         __syncwarp();
       } else {
-      // A warp whose 32 rows all belong to the sequence hands its staged rows to one TMA store.
-      const bool use_tma = rows_valid == 32;
-      const size_t off = static_cast<size_t>(warp_dst - reinterpret_cast<T*>(p.out));
-      const int row0 = static_cast<int>(off / p.ld_o), col0 = static_cast<int>(off % p.ld_o);
+        // A warp whose 32 rows all belong to the sequence hands its staged rows to one TMA store.
+        const bool use_tma = rows_valid == 32;
+        const size_t off = static_cast<size_t>(warp_dst - reinterpret_cast<T*>(p.out));
+        const int row0 = static_cast<int>(off / p.ld_o), col0 = static_cast<int>(off % p.ld_o);
 #pragma unroll
-      for (int c2 = 0; c2 < D / 64; ++c2) {
-        // the staging slice may still be read by the store of the piece (or unit) before
-        if (lane == 0) ptx::tma_store_wait_read<0>();
-        __syncwarp();
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t t[32];
-          ptx::tmem_ld32(t_o + c2 * 64 + h * 32, t);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int q8 = 0; q8 < 4; ++q8) {
-            uint4 v;
-            v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
-            v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
-            v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
-            v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
-            // 16-byte chunk index XORed with (row & 7): conflict-free both ways
-            *reinterpret_cast<uint4*>(stage + lane * 128 + (((h * 4 + q8) ^ (lane & 7)) * 16)) = v;
-          }
-        }
-        if (use_tma) {
-          ptx::fence_proxy_async_smem();
+        for (int c2 = 0; c2 < D / 64; ++c2) {
+          // the staging slice may still be read by the store of the piece (or unit) before
+          if (lane == 0) ptx::tma_store_wait_read<0>();
           __syncwarp();
-          if (lane == 0) {
-            ptx::tma_store_2d(&tm_o, stage, col0 + c2 * 64, row0);
-            ptx::tma_store_commit();
-          }
-        } else {
-        __syncwarp();
-        const int sub = lane >> 3, ch = lane & 7;
 #pragma unroll
-        for (int i4 = 0; i4 < 8; ++i4) {
-          const int row = i4 * 4 + sub;
-          const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((ch ^ (row & 7)) * 16));
-          if (row < rows_valid) {
-            *reinterpret_cast<uint4*>(warp_dst + static_cast<size_t>(row) * p.ld_o + c2 * 64 + ch * 8) = v;
+          for (int h = 0; h < 2; ++h) {
+            uint32_t t[32];
+            ptx::tmem_ld32(t_o + c2 * 64 + h * 32, t);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {
+              uint4 v;
+              v.x = pack2<T>(__uint_as_float(t[q8 * 8 + 0]) * inv, __uint_as_float(t[q8 * 8 + 1]) * inv);
+              v.y = pack2<T>(__uint_as_float(t[q8 * 8 + 2]) * inv, __uint_as_float(t[q8 * 8 + 3]) * inv);
+              v.z = pack2<T>(__uint_as_float(t[q8 * 8 + 4]) * inv, __uint_as_float(t[q8 * 8 + 5]) * inv);
+              v.w = pack2<T>(__uint_as_float(t[q8 * 8 + 6]) * inv, __uint_as_float(t[q8 * 8 + 7]) * inv);
+              // 16-byte chunk index XORed with (row & 7): conflict-free both ways
+              *reinterpret_cast<uint4*>(stage + lane * 128 + (((h * 4 + q8) ^ (lane & 7)) * 16)) = v;
+            }
           }
+          if (use_tma) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_2d(&tm_o, stage, col0 + c2 * 64, row0);
+              ptx::tma_store_commit();
+            }
+          } else {
+            __syncwarp();
+            const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              const int row = i4 * 4 + sub;
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 128 + ((ch ^ (row & 7)) * 16));
+              if (row < rows_valid) {
+                *reinterpret_cast<uint4*>(warp_dst + static_cast<size_t>(row) * p.ld_o + c2 * 64 + ch * 8) = v;
+              }
+            }
+          }
+          __syncwarp();
         }
-        }
-        __syncwarp();
-      }
       }
       ptx::tc_fence_before();
       return true;
